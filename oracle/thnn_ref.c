@@ -1,0 +1,620 @@
+/*
+ * TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+ *
+ * CPU restatement of the math of the THCUNN convolutional hot path: depthwise
+ * convolution, im2col+GEMM convolution, batch normalisation, max pooling and
+ * the four small ops a MobileNetV1 training step needs around them.  It exists
+ * only so that tests, the smoke check and the CPU-baseline leg of the
+ * benchmark have something to compare the CUDA kernels with.  Nothing in the
+ * shipped library links, loads or calls it.
+ *
+ * The file is compiled twice (see the Makefile next to it):
+ *   -DREF_ACC=double -DREF_PREFIX=ref64_   the oracle proper: fp32 tensors,
+ *                                          every sum carried in fp64;
+ *   -DREF_ACC=float  -DREF_PREFIX=ref32_   the timed CPU baseline: the same
+ *                                          loops with fp32 accumulators, which
+ *                                          is the arithmetic torch/nn's CPU
+ *                                          THNN uses for float tensors.
+ *
+ * PARITY STATUS: the reference ships no golden vectors and its CPU comparison
+ * library (torch/nn THNN) is absent from the reference tree, so this
+ * restatement is pinned against (a) the reference's in-tree self-consistency
+ * tests (depthwise == per-channel SpatialConvolution, average-pool known
+ * answers) and (b) fixtures produced by PyTorch's CPU operators, a descendant
+ * of the same THNN code.  Against the reference's own CPU library: parity
+ * unpinned.
+ *
+ * Each function cites the reference file:line whose arithmetic it follows
+ * (paths relative to the reference project root).
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <float.h>
+#include <string.h>
+
+#ifndef REF_ACC
+#define REF_ACC double
+#endif
+#ifndef REF_PREFIX
+#define REF_PREFIX ref64_
+#endif
+#define CAT2(a, b) a##b
+#define CAT(a, b) CAT2(a, b)
+#define FN(name) CAT(REF_PREFIX, name)
+
+typedef REF_ACC acc_t;
+
+/* Index base of stored pooling indices and class targets.  libTH defines
+ * TH_INDEX_BASE as 1 for the Lua build the reference's tests run under
+ * (lib/THCUNN/SpatialDilatedMaxPooling.cu:40 adds it to every stored index). */
+#ifndef REF_INDEX_BASE
+#define REF_INDEX_BASE 1
+#endif
+
+int FN(index_base)(void) { return REF_INDEX_BASE; }
+
+/* ------------------------------------------------------------------------ */
+/* Depthwise convolution.                                                   */
+/* Layouts: x [N,C,H,W]; weight [M,C,kH,kW]; bias [M,C]; y [N,C*M,oH,oW]     */
+/* with output channel c*M+j  (lib/THCUNN/generic/SpatialDepthWiseConvolution.cu:76-121,244). */
+/* ------------------------------------------------------------------------ */
+
+/* Forward: per (image, channel) a [M x k*k]*[k*k x oHW] product on the unfolded
+ * plane plus a bias broadcast
+ * (lib/THCUNN/generic/SpatialDepthWiseConvolution.cu:150-226; unfold with zero
+ * padding: lib/THCUNN/im2col.h:18-37). */
+void FN(dwconv_forward)(const float *x, const float *w, const float *bias, float *y,
+                        int N, int C, int H, int W, int M, int kH, int kW,
+                        int dH, int dW, int padH, int padW)
+{
+    const int oH = (H + 2 * padH - kH) / dH + 1;
+    const int oW = (W + 2 * padW - kW) / dW + 1;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int n = 0; n < N; ++n)
+        for (int c = 0; c < C; ++c) {
+            const float *xp = x + ((size_t)n * C + c) * H * W;
+            for (int j = 0; j < M; ++j) {
+                const float *wp = w + ((size_t)j * C + c) * kH * kW;
+                float *yp = y + (((size_t)n * C + c) * M + j) * oH * oW;
+                const acc_t b = bias ? (acc_t)bias[(size_t)j * C + c] : (acc_t)0;
+                for (int oh = 0; oh < oH; ++oh)
+                    for (int ow = 0; ow < oW; ++ow) {
+                        acc_t s = b;
+                        for (int kh = 0; kh < kH; ++kh) {
+                            const int ih = oh * dH - padH + kh;
+                            if (ih < 0 || ih >= H) continue;
+                            for (int kw = 0; kw < kW; ++kw) {
+                                const int iw = ow * dW - padW + kw;
+                                if (iw < 0 || iw >= W) continue;
+                                s += (acc_t)wp[kh * kW + kw] * (acc_t)xp[ih * W + iw];
+                            }
+                        }
+                        yp[oh * oW + ow] = (float)s;
+                    }
+            }
+        }
+}
+
+/* Input gradient: W^T * gy per (image, channel), folded back with col2im
+ * (lib/THCUNN/generic/SpatialDepthWiseConvolution.cu:346-400; fold:
+ * lib/THCUNN/im2col.h:72-101).  gy is read as contiguous [N,C,M,oH,oW]. */
+void FN(dwconv_grad_input)(const float *gy, const float *w, float *gx,
+                           int N, int C, int H, int W, int M, int kH, int kW,
+                           int dH, int dW, int padH, int padW)
+{
+    const int oH = (H + 2 * padH - kH) / dH + 1;
+    const int oW = (W + 2 * padW - kW) / dW + 1;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int n = 0; n < N; ++n)
+        for (int c = 0; c < C; ++c) {
+            float *gxp = gx + ((size_t)n * C + c) * H * W;
+            for (int h = 0; h < H; ++h)
+                for (int wi = 0; wi < W; ++wi) {
+                    acc_t s = 0;
+                    for (int j = 0; j < M; ++j) {
+                        const float *wp = w + ((size_t)j * C + c) * kH * kW;
+                        const float *gyp = gy + (((size_t)n * C + c) * M + j) * oH * oW;
+                        for (int kh = 0; kh < kH; ++kh) {
+                            const int t = h + padH - kh;
+                            if (t < 0 || t % dH) continue;
+                            const int oh = t / dH;
+                            if (oh >= oH) continue;
+                            for (int kw = 0; kw < kW; ++kw) {
+                                const int u = wi + padW - kw;
+                                if (u < 0 || u % dW) continue;
+                                const int ow = u / dW;
+                                if (ow >= oW) continue;
+                                s += (acc_t)wp[kh * kW + kw] * (acc_t)gyp[oh * oW + ow];
+                            }
+                        }
+                    }
+                    gxp[h * W + wi] = (float)s;
+                }
+        }
+}
+
+/* Parameter gradients, ACCUMULATED into gw / gb (GEMM and GEMV with beta = 1:
+ * lib/THCUNN/generic/SpatialDepthWiseConvolution.cu:546-613). gb may be NULL. */
+void FN(dwconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
+                         int N, int C, int H, int W, int M, int kH, int kW,
+                         int dH, int dW, int padH, int padW, float scale)
+{
+    const int oH = (H + 2 * padH - kH) / dH + 1;
+    const int oW = (W + 2 * padW - kW) / dW + 1;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int c = 0; c < C; ++c)
+        for (int j = 0; j < M; ++j) {
+            acc_t sb = 0;
+            acc_t sw[64];
+            const int kk = kH * kW;
+            for (int i = 0; i < kk && i < 64; ++i) sw[i] = 0;
+            for (int n = 0; n < N; ++n) {
+                const float *xp = x + ((size_t)n * C + c) * H * W;
+                const float *gyp = gy + (((size_t)n * C + c) * M + j) * oH * oW;
+                for (int oh = 0; oh < oH; ++oh)
+                    for (int ow = 0; ow < oW; ++ow) {
+                        const acc_t g = gyp[oh * oW + ow];
+                        sb += g;
+                        for (int kh = 0; kh < kH; ++kh) {
+                            const int ih = oh * dH - padH + kh;
+                            if (ih < 0 || ih >= H) continue;
+                            for (int kw = 0; kw < kW; ++kw) {
+                                const int iw = ow * dW - padW + kw;
+                                if (iw < 0 || iw >= W) continue;
+                                sw[kh * kW + kw] += g * (acc_t)xp[ih * W + iw];
+                            }
+                        }
+                    }
+            }
+            float *gwp = gw + ((size_t)j * C + c) * kk;
+            for (int i = 0; i < kk; ++i) gwp[i] = (float)((acc_t)gwp[i] + (acc_t)scale * sw[i]);
+            if (gb) gb[(size_t)j * C + c] = (float)((acc_t)gb[(size_t)j * C + c] + (acc_t)scale * sb);
+        }
+}
+
+/* ------------------------------------------------------------------------ */
+/* SpatialConvolutionMM.  x [N,C,H,W]; weight [K, C*kH*kW]; bias [K];        */
+/* y [N,K,oH,oW].                                                            */
+/* ------------------------------------------------------------------------ */
+
+/* Forward: y_n = bias*ones + W * im2col(x_n)
+ * (lib/THCUNN/generic/SpatialConvolutionMM.cu:129-194). */
+void FN(convmm_forward)(const float *x, const float *w, const float *bias, float *y,
+                        int N, int C, int H, int W, int K, int kH, int kW,
+                        int dH, int dW, int padH, int padW)
+{
+    const int oH = (H + 2 * padH - kH) / dH + 1;
+    const int oW = (W + 2 * padW - kW) / dW + 1;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int n = 0; n < N; ++n)
+        for (int k = 0; k < K; ++k) {
+            float *yp = y + ((size_t)n * K + k) * oH * oW;
+            const acc_t b = bias ? (acc_t)bias[k] : (acc_t)0;
+            for (int oh = 0; oh < oH; ++oh)
+                for (int ow = 0; ow < oW; ++ow) {
+                    acc_t s = b;
+                    for (int c = 0; c < C; ++c) {
+                        const float *xp = x + ((size_t)n * C + c) * H * W;
+                        const float *wp = w + ((size_t)k * C + c) * kH * kW;
+                        for (int kh = 0; kh < kH; ++kh) {
+                            const int ih = oh * dH - padH + kh;
+                            if (ih < 0 || ih >= H) continue;
+                            for (int kw = 0; kw < kW; ++kw) {
+                                const int iw = ow * dW - padW + kw;
+                                if (iw < 0 || iw >= W) continue;
+                                s += (acc_t)wp[kh * kW + kw] * (acc_t)xp[ih * W + iw];
+                            }
+                        }
+                    }
+                    yp[oh * oW + ow] = (float)s;
+                }
+        }
+}
+
+/* Input gradient: gx_n = col2im(W^T * gy_n)
+ * (lib/THCUNN/generic/SpatialConvolutionMM.cu:272-308). */
+void FN(convmm_grad_input)(const float *gy, const float *w, float *gx,
+                           int N, int C, int H, int W, int K, int kH, int kW,
+                           int dH, int dW, int padH, int padW)
+{
+    const int oH = (H + 2 * padH - kH) / dH + 1;
+    const int oW = (W + 2 * padW - kW) / dW + 1;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int n = 0; n < N; ++n)
+        for (int c = 0; c < C; ++c) {
+            float *gxp = gx + ((size_t)n * C + c) * H * W;
+            for (int h = 0; h < H; ++h)
+                for (int wi = 0; wi < W; ++wi) {
+                    acc_t s = 0;
+                    for (int kh = 0; kh < kH; ++kh) {
+                        const int t = h + padH - kh;
+                        if (t < 0 || t % dH) continue;
+                        const int oh = t / dH;
+                        if (oh >= oH) continue;
+                        for (int kw = 0; kw < kW; ++kw) {
+                            const int u = wi + padW - kw;
+                            if (u < 0 || u % dW) continue;
+                            const int ow = u / dW;
+                            if (ow >= oW) continue;
+                            for (int k = 0; k < K; ++k)
+                                s += (acc_t)w[((size_t)k * C + c) * kH * kW + kh * kW + kw] *
+                                     (acc_t)gy[((size_t)n * K + k) * oH * oW + oh * oW + ow];
+                        }
+                    }
+                    gxp[h * W + wi] = (float)s;
+                }
+        }
+}
+
+/* Parameter gradients, accumulated: gW += scale * sum_n gy_n * im2col(x_n)^T,
+ * gb += scale * sum gy  (lib/THCUNN/generic/SpatialConvolutionMM.cu:396-470). */
+void FN(convmm_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
+                         int N, int C, int H, int W, int K, int kH, int kW,
+                         int dH, int dW, int padH, int padW, float scale)
+{
+    const int oH = (H + 2 * padH - kH) / dH + 1;
+    const int oW = (W + 2 * padW - kW) / dW + 1;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int k = 0; k < K; ++k)
+        for (int c = 0; c < C; ++c) {
+            for (int kh = 0; kh < kH; ++kh)
+                for (int kw = 0; kw < kW; ++kw) {
+                    acc_t s = 0;
+                    for (int n = 0; n < N; ++n) {
+                        const float *xp = x + ((size_t)n * C + c) * H * W;
+                        const float *gyp = gy + ((size_t)n * K + k) * oH * oW;
+                        for (int oh = 0; oh < oH; ++oh) {
+                            const int ih = oh * dH - padH + kh;
+                            if (ih < 0 || ih >= H) continue;
+                            for (int ow = 0; ow < oW; ++ow) {
+                                const int iw = ow * dW - padW + kw;
+                                if (iw < 0 || iw >= W) continue;
+                                s += (acc_t)gyp[oh * oW + ow] * (acc_t)xp[ih * W + iw];
+                            }
+                        }
+                    }
+                    float *p = gw + ((size_t)k * C + c) * kH * kW + kh * kW + kw;
+                    *p = (float)((acc_t)*p + (acc_t)scale * s);
+                }
+        }
+    if (gb) {
+#pragma omp parallel for schedule(static)
+        for (int k = 0; k < K; ++k) {
+            acc_t s = 0;
+            for (int n = 0; n < N; ++n) {
+                const float *gyp = gy + ((size_t)n * K + k) * oH * oW;
+                for (int i = 0; i < oH * oW; ++i) s += (acc_t)gyp[i];
+            }
+            gb[k] = (float)((acc_t)gb[k] + (acc_t)scale * s);
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------ */
+/* Batch normalisation over [N,C,S] (S = H*W).                               */
+/* ------------------------------------------------------------------------ */
+
+/* Forward.  Train: batch mean, biased variance, save_std = 1/sqrt(var+eps)
+ * (0 when var == 0 and eps == 0), running stats updated with the UNBIASED
+ * variance (lib/THCUNN/BatchNormalization.cu:167-212).  Eval: running stats
+ * (lib/THCUNN/BatchNormalization.cu:141-164).  weight/bias may be NULL. */
+void FN(bn_forward)(const float *x, float *y, const float *weight, const float *bias,
+                    float *running_mean, float *running_var, float *save_mean, float *save_std,
+                    int N, int C, int S, int train, double momentum, double eps)
+{
+#pragma omp parallel for schedule(static)
+    for (int c = 0; c < C; ++c) {
+        acc_t mean, invstd;
+        if (train) {
+            const acc_t cnt = (acc_t)N * S;
+            acc_t s = 0;
+            for (int n = 0; n < N; ++n) {
+                const float *xp = x + ((size_t)n * C + c) * S;
+                for (int i = 0; i < S; ++i) s += (acc_t)xp[i];
+            }
+            mean = s / cnt;
+            acc_t v = 0;
+            for (int n = 0; n < N; ++n) {
+                const float *xp = x + ((size_t)n * C + c) * S;
+                for (int i = 0; i < S; ++i) {
+                    const acc_t d = (acc_t)xp[i] - mean;
+                    v += d * d;
+                }
+            }
+            invstd = 0;
+            if (v != 0 || eps != 0) invstd = (acc_t)1 / (acc_t)sqrt((double)(v / cnt + (acc_t)eps));
+            const acc_t unbiased = v / (cnt - 1);
+            save_mean[c] = (float)mean;
+            save_std[c] = (float)invstd;
+            running_mean[c] = (float)((1 - momentum) * running_mean[c] + momentum * mean);
+            running_var[c] = (float)((1 - momentum) * running_var[c] + momentum * unbiased);
+        } else {
+            mean = running_mean[c];
+            invstd = (acc_t)1 / (acc_t)sqrt((double)((acc_t)running_var[c] + (acc_t)eps));
+        }
+        const acc_t g = weight ? (acc_t)weight[c] : (acc_t)1;
+        const acc_t b = bias ? (acc_t)bias[c] : (acc_t)0;
+        for (int n = 0; n < N; ++n) {
+            const float *xp = x + ((size_t)n * C + c) * S;
+            float *yp = y + ((size_t)n * C + c) * S;
+            for (int i = 0; i < S; ++i) yp[i] = (float)(g * ((acc_t)xp[i] - mean) * invstd + b);
+        }
+    }
+}
+
+/* Backward (lib/THCUNN/BatchNormalization.cu:215-283).  gx, gw, gb may each be
+ * NULL; gw and gb are accumulated with `scale`. */
+void FN(bn_backward)(const float *x, const float *gy, float *gx, float *gw, float *gb,
+                     const float *weight, const float *running_mean, const float *running_var,
+                     const float *save_mean, const float *save_std,
+                     int N, int C, int S, int train, double scale, double eps)
+{
+#pragma omp parallel for schedule(static)
+    for (int c = 0; c < C; ++c) {
+        acc_t mean, stdv;
+        if (train) {
+            mean = save_mean[c];
+            stdv = save_std[c];
+        } else {
+            mean = running_mean[c];
+            stdv = (acc_t)1 / (acc_t)sqrt((double)((acc_t)running_var[c] + (acc_t)eps));
+        }
+        const acc_t wv = weight ? (acc_t)weight[c] : (acc_t)1;
+        const acc_t norm = (acc_t)1 / ((acc_t)N * S);
+        acc_t sum = 0, dot = 0;
+        for (int n = 0; n < N; ++n) {
+            const float *xp = x + ((size_t)n * C + c) * S;
+            const float *gp = gy + ((size_t)n * C + c) * S;
+            for (int i = 0; i < S; ++i) {
+                sum += (acc_t)gp[i];
+                dot += (acc_t)gp[i] * ((acc_t)xp[i] - mean);
+            }
+        }
+        const acc_t grad_mean = sum * norm;
+        const acc_t proj_scale = dot * norm * stdv * stdv;
+        const acc_t grad_scale = stdv * wv;
+        if (gx) {
+            for (int n = 0; n < N; ++n) {
+                const float *xp = x + ((size_t)n * C + c) * S;
+                const float *gp = gy + ((size_t)n * C + c) * S;
+                float *op = gx + ((size_t)n * C + c) * S;
+                for (int i = 0; i < S; ++i) {
+                    if (train)
+                        op[i] = (float)(((acc_t)gp[i] - ((acc_t)xp[i] - mean) * proj_scale - grad_mean) * grad_scale);
+                    else
+                        op[i] = (float)((acc_t)gp[i] * grad_scale);
+                }
+            }
+        }
+        if (gw) gw[c] = (float)((acc_t)gw[c] + (acc_t)scale * dot * stdv);
+        if (gb) gb[c] = (float)((acc_t)gb[c] + (acc_t)scale * sum);
+    }
+}
+
+/* ------------------------------------------------------------------------ */
+/* Max pooling with argmax.                                                  */
+/* ------------------------------------------------------------------------ */
+
+/* Output extent along one axis, floor or ceil mode, with the "last window must
+ * start inside input + pad" fix-up
+ * (lib/THCUNN/generic/SpatialDilatedMaxPooling.cu:118-135), in integers. */
+int FN(pool_out_size)(int in, int k, int d, int pad, int dil, int ceil_mode)
+{
+    const int num = in - (dil * (k - 1) + 1) + 2 * pad;
+    int o;
+    if (ceil_mode) o = (num >= 0 ? (num + d - 1) / d : -((-num) / d)) + 1;
+    else           o = (num >= 0 ? num / d : -((-num + d - 1) / d)) + 1;
+    if (pad && (o - 1) * d >= in + pad) --o;
+    return o;
+}
+
+/* Forward: first strict maximum in row-major window order starting from
+ * -FLT_MAX with index -1; stored index = per-plane flat h*W+w + index base
+ * (lib/THCUNN/SpatialDilatedMaxPooling.cu:8-42).  NaN never wins. */
+void FN(maxpool_forward)(const float *x, float *y, int64_t *ind,
+                         int N, int C, int H, int W, int oH, int oW,
+                         int kH, int kW, int dH, int dW, int padH, int padW,
+                         int dilH, int dilW)
+{
+#pragma omp parallel for schedule(static)
+    for (long p = 0; p < (long)N * C; ++p) {
+        const float *xp = x + (size_t)p * H * W;
+        for (int ph = 0; ph < oH; ++ph)
+            for (int pw = 0; pw < oW; ++pw) {
+                int hs = ph * dH - padH, ws = pw * dW - padW;
+                int he = hs + (kH - 1) * dilH + 1; if (he > H) he = H;
+                int we = ws + (kW - 1) * dilW + 1; if (we > W) we = W;
+                while (hs < 0) hs += dilH;
+                while (ws < 0) ws += dilW;
+                float best = -FLT_MAX;
+                int bi = -1;
+                for (int h = hs; h < he; h += dilH)
+                    for (int w = ws; w < we; w += dilW)
+                        if (xp[h * W + w] > best) { bi = h * W + w; best = xp[bi]; }
+                y[(size_t)p * oH * oW + ph * oW + pw] = best;
+                ind[(size_t)p * oH * oW + ph * oW + pw] = (int64_t)bi + REF_INDEX_BASE;
+            }
+    }
+}
+
+/* Backward, gather form: every input pixel sums gy over the outputs whose
+ * stored index names it (lib/THCUNN/SpatialDilatedMaxPooling.cu:46-80). */
+void FN(maxpool_backward)(const float *gy, const int64_t *ind, float *gx,
+                          int N, int C, int H, int W, int oH, int oW,
+                          int kH, int kW, int dH, int dW, int padH, int padW,
+                          int dilH, int dilW)
+{
+#pragma omp parallel for schedule(static)
+    for (long p = 0; p < (long)N * C; ++p) {
+        const float *gp = gy + (size_t)p * oH * oW;
+        const int64_t *ip = ind + (size_t)p * oH * oW;
+        for (int h = 0; h < H; ++h)
+            for (int w = 0; w < W; ++w) {
+                const int eh = (kH - 1) * dilH + 1, ew = (kW - 1) * dilW + 1;
+                const int phs = (h + padH < eh) ? 0 : (h + padH - eh) / dH + 1;
+                int phe = (h + padH) / dH + 1; if (phe > oH) phe = oH;
+                const int pws = (w + padW < ew) ? 0 : (w + padW - ew) / dW + 1;
+                int pwe = (w + padW) / dW + 1; if (pwe > oW) pwe = oW;
+                acc_t g = 0;
+                for (int ph = phs; ph < phe; ++ph)
+                    for (int pw = pws; pw < pwe; ++pw)
+                        if (ip[ph * oW + pw] - REF_INDEX_BASE == h * W + w) g += (acc_t)gp[ph * oW + pw];
+                gx[(size_t)p * H * W + h * W + w] = (float)g;
+            }
+    }
+}
+
+/* ------------------------------------------------------------------------ */
+/* Support ops of the MobileNetV1 step.                                      */
+/* ------------------------------------------------------------------------ */
+
+/* Threshold forward: y = x > th ? x : val (lib/THCUNN/Threshold.cu:6-38). */
+void FN(threshold_forward)(const float *x, float *y, size_t n, float th, float val)
+{
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < (long)n; ++i) y[i] = x[i] > th ? x[i] : val;
+}
+
+/* Threshold backward: gx = x > th ? gy : 0 (lib/THCUNN/Threshold.cu:40-72). */
+void FN(threshold_backward)(const float *x, const float *gy, float *gx, size_t n, float th)
+{
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < (long)n; ++i) gx[i] = x[i] > th ? gy[i] : 0.0f;
+}
+
+/* Average pooling forward (lib/THCUNN/SpatialAveragePooling.cu:7-39): window
+ * clipped to input + pad for the divisor when count_include_pad, else to the
+ * input. */
+void FN(avgpool_forward)(const float *x, float *y, int N, int C, int H, int W, int oH, int oW,
+                         int kH, int kW, int dH, int dW, int padH, int padW, int count_include_pad)
+{
+#pragma omp parallel for schedule(static)
+    for (long p = 0; p < (long)N * C; ++p)
+        for (int ph = 0; ph < oH; ++ph)
+            for (int pw = 0; pw < oW; ++pw) {
+                int hs = ph * dH - padH, ws = pw * dW - padW;
+                int he = hs + kH; if (he > H + padH) he = H + padH;
+                int we = ws + kW; if (we > W + padW) we = W + padW;
+                const int pool = (he - hs) * (we - ws);
+                if (hs < 0) hs = 0;
+                if (ws < 0) ws = 0;
+                if (he > H) he = H;
+                if (we > W) we = W;
+                acc_t s = 0;
+                for (int h = hs; h < he; ++h)
+                    for (int w = ws; w < we; ++w) s += (acc_t)x[(size_t)p * H * W + h * W + w];
+                const int div = count_include_pad ? pool : (he - hs) * (we - ws);
+                y[(size_t)p * oH * oW + ph * oW + pw] = (float)(s / div);
+            }
+}
+
+/* Average pooling backward (lib/THCUNN/SpatialAveragePooling.cu:42-82). */
+void FN(avgpool_backward)(const float *gy, float *gx, int N, int C, int H, int W, int oH, int oW,
+                          int kH, int kW, int dH, int dW, int padH, int padW, int count_include_pad)
+{
+#pragma omp parallel for schedule(static)
+    for (long p = 0; p < (long)N * C; ++p)
+        for (int h0 = 0; h0 < H; ++h0)
+            for (int w0 = 0; w0 < W; ++w0) {
+                const int h = h0 + padH, w = w0 + padW;
+                const int phs = (h < kH) ? 0 : (h - kH) / dH + 1;
+                int phe = h / dH + 1; if (phe > oH) phe = oH;
+                const int pws = (w < kW) ? 0 : (w - kW) / dW + 1;
+                int pwe = w / dW + 1; if (pwe > oW) pwe = oW;
+                acc_t g = 0;
+                for (int ph = phs; ph < phe; ++ph)
+                    for (int pw = pws; pw < pwe; ++pw) {
+                        int hs = ph * dH - padH, ws = pw * dW - padW;
+                        int he = hs + kH; if (he > H + padH) he = H + padH;
+                        int we = ws + kW; if (we > W + padW) we = W + padW;
+                        const int pool = (he - hs) * (we - ws);
+                        if (hs < 0) hs = 0;
+                        if (ws < 0) ws = 0;
+                        if (he > H) he = H;
+                        if (we > W) we = W;
+                        const int div = count_include_pad ? pool : (he - hs) * (we - ws);
+                        g += (acc_t)gy[(size_t)p * oH * oW + ph * oW + pw] / div;
+                    }
+                gx[(size_t)p * H * W + h0 * W + w0] = (float)g;
+            }
+}
+
+/* LogSoftMax over the last dimension of [B, D]
+ * (lib/THCUNN/LogSoftMax.cu:246-296): x - max - log(sum exp(x - max)). */
+void FN(logsoftmax_forward)(const float *x, float *y, int B, int D)
+{
+#pragma omp parallel for schedule(static)
+    for (int b = 0; b < B; ++b) {
+        const float *xp = x + (size_t)b * D;
+        float m = -FLT_MAX;
+        for (int i = 0; i < D; ++i) if (xp[i] > m) m = xp[i];
+        acc_t s = 0;
+        for (int i = 0; i < D; ++i) s += (acc_t)exp((double)xp[i] - (double)m);
+        const acc_t l = (acc_t)m + (acc_t)log((double)s);
+        for (int i = 0; i < D; ++i) y[(size_t)b * D + i] = (float)((acc_t)xp[i] - l);
+    }
+}
+
+/* LogSoftMax backward (lib/THCUNN/LogSoftMax.cu:298-344):
+ * gx = gy - exp(y) * sum(gy). */
+void FN(logsoftmax_backward)(const float *y, const float *gy, float *gx, int B, int D)
+{
+#pragma omp parallel for schedule(static)
+    for (int b = 0; b < B; ++b) {
+        acc_t s = 0;
+        for (int i = 0; i < D; ++i) s += (acc_t)gy[(size_t)b * D + i];
+        for (int i = 0; i < D; ++i)
+            gx[(size_t)b * D + i] = (float)((acc_t)gy[(size_t)b * D + i] - (acc_t)exp((double)y[(size_t)b * D + i]) * s);
+    }
+}
+
+/* ClassNLL forward over log-probabilities [B, D] with targets carrying the
+ * index base (lib/THCUNN/ClassNLLCriterion.cu:38-84): loss = -sum w_t lp[t],
+ * divided by sum w_t when size_average.  weights may be NULL. */
+void FN(classnll_forward)(const float *lp, const int64_t *target, const float *weights,
+                          float *loss, float *total_weight, int B, int D,
+                          int size_average, int64_t ignore_index)
+{
+    acc_t s = 0, tw = 0;
+    for (int b = 0; b < B; ++b) {
+        const int64_t t = target[b] - REF_INDEX_BASE;
+        if (t == ignore_index - REF_INDEX_BASE) continue;
+        const acc_t w = weights ? (acc_t)weights[t] : (acc_t)1;
+        s -= w * (acc_t)lp[(size_t)b * D + t];
+        tw += w;
+    }
+    if (size_average && tw > 0) s /= tw;
+    *loss = (float)s;
+    *total_weight = (float)tw;
+}
+
+/* ClassNLL backward (lib/THCUNN/ClassNLLCriterion.cu:108-132): writes only the
+ * target entries of gx; the caller zeroes gx first, as nn.ClassNLLCriterion
+ * does. */
+void FN(classnll_backward)(const int64_t *target, const float *weights, float total_weight,
+                           float *gx, int B, int D, int size_average, int64_t ignore_index)
+{
+    if (total_weight <= 0) return;
+    const acc_t norm = size_average ? (acc_t)1 / (acc_t)total_weight : (acc_t)1;
+    for (int b = 0; b < B; ++b) {
+        const int64_t t = target[b] - REF_INDEX_BASE;
+        if (t == ignore_index - REF_INDEX_BASE) continue;
+        const acc_t w = weights ? (acc_t)weights[t] : (acc_t)1;
+        gx[(size_t)b * D + t] = (float)(-w * norm);
+    }
+}
+
+/* ------------------------------------------------------------------------ */
+/* DataParallelTable shard rule.                                             */
+/* ------------------------------------------------------------------------ */
+
+/* Rows [start, start+count) of a batch of `n` rows that replica `i` (0-based)
+ * of `g` receives: the first n mod g replicas get one extra row
+ * (DataParallelTable.lua:469-479).  Zero-based start. */
+void FN(slice_range)(long n, int g, int i, long *start, long *count)
+{
+    const long base = n / g, extra = n % g;
+    *count = base + (i < extra ? 1 : 0);
+    *start = (long)i * base + (i < extra ? i : extra);
+}

@@ -1,0 +1,226 @@
+"""ctypes front end of the CPU oracle (test infrastructure, not product code).
+
+Loads ``libthnn_ref.so`` built from ``thnn_ref.c`` by the Makefile in this
+folder and exposes each routine on numpy arrays.  ``Ref("ref64_")`` is the
+fp64-accumulating oracle, ``Ref("ref32_")`` the fp32 port that the benchmark
+times as its CPU baseline.  Only tests, the smoke check and the benchmark's
+CPU legs may import this module.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libthnn_ref.so")
+
+
+def build(force=False):
+    """Compile the oracle library if it is missing or older than its source."""
+    src = os.path.join(_HERE, "thnn_ref.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-s", "-C", _HERE])
+    return _SO
+
+
+def _f(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _p(a):
+    if a is None:
+        return None
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def conv_out(size, k, d, pad):
+    return (size + 2 * pad - k) // d + 1
+
+
+class Ref:
+    def __init__(self, prefix="ref64_"):
+        build()
+        self.lib = ctypes.CDLL(_SO)
+        self.prefix = prefix
+        self.index_base = self._fn("index_base", ctypes.c_int)()
+
+    def _fn(self, name, restype=None):
+        f = getattr(self.lib, self.prefix + name)
+        f.restype = restype
+        return f
+
+    # -- depthwise ---------------------------------------------------------
+    def dwconv_forward(self, x, w, b, dH, dW, padH, padW):
+        x, w = _f(x), _f(w)
+        b = None if b is None else _f(b)
+        N, C, H, W = x.shape
+        M, _, kH, kW = w.shape
+        y = np.empty((N, C * M, conv_out(H, kH, dH, padH), conv_out(W, kW, dW, padW)), np.float32)
+        self._fn("dwconv_forward")(_p(x), _p(w), _p(b), _p(y), N, C, H, W, M, kH, kW, dH, dW, padH, padW)
+        return y
+
+    def dwconv_grad_input(self, gy, w, H, W, dH, dW, padH, padW):
+        gy, w = _f(gy), _f(w)
+        M, C, kH, kW = w.shape
+        N = gy.shape[0]
+        gx = np.empty((N, C, H, W), np.float32)
+        self._fn("dwconv_grad_input")(_p(gy), _p(w), _p(gx), N, C, H, W, M, kH, kW, dH, dW, padH, padW)
+        return gx
+
+    def dwconv_acc_grad(self, x, gy, gw, gb, dH, dW, padH, padW, scale):
+        """Returns updated copies of gw [M,C,kH,kW] and gb [M,C] (or None)."""
+        x, gy = _f(x), _f(gy)
+        gw = _f(gw).copy()
+        gb = None if gb is None else _f(gb).copy()
+        N, C, H, W = x.shape
+        M, _, kH, kW = gw.shape
+        self._fn("dwconv_acc_grad")(_p(x), _p(gy), _p(gw), _p(gb), N, C, H, W, M, kH, kW, dH, dW, padH, padW,
+                                    ctypes.c_float(scale))
+        return gw, gb
+
+    # -- im2col + GEMM convolution ----------------------------------------------
+    def convmm_forward(self, x, w, b, dH, dW, padH, padW):
+        x, w = _f(x), _f(w)
+        b = None if b is None else _f(b)
+        N, C, H, W = x.shape
+        K, _, kH, kW = w.shape
+        y = np.empty((N, K, conv_out(H, kH, dH, padH), conv_out(W, kW, dW, padW)), np.float32)
+        self._fn("convmm_forward")(_p(x), _p(w), _p(b), _p(y), N, C, H, W, K, kH, kW, dH, dW, padH, padW)
+        return y
+
+    def convmm_grad_input(self, gy, w, H, W, dH, dW, padH, padW):
+        gy, w = _f(gy), _f(w)
+        K, C, kH, kW = w.shape
+        N = gy.shape[0]
+        gx = np.empty((N, C, H, W), np.float32)
+        self._fn("convmm_grad_input")(_p(gy), _p(w), _p(gx), N, C, H, W, K, kH, kW, dH, dW, padH, padW)
+        return gx
+
+    def convmm_acc_grad(self, x, gy, gw, gb, dH, dW, padH, padW, scale):
+        x, gy = _f(x), _f(gy)
+        gw = _f(gw).copy()
+        gb = None if gb is None else _f(gb).copy()
+        N, C, H, W = x.shape
+        K, _, kH, kW = gw.shape
+        self._fn("convmm_acc_grad")(_p(x), _p(gy), _p(gw), _p(gb), N, C, H, W, K, kH, kW, dH, dW, padH, padW,
+                                    ctypes.c_float(scale))
+        return gw, gb
+
+    # -- batch norm --------------------------------------------------------------
+    def bn_forward(self, x, weight, bias, running_mean, running_var, train, momentum, eps):
+        """Returns y, running_mean', running_var', save_mean, save_std."""
+        x = _f(x)
+        N, C = x.shape[:2]
+        S = int(np.prod(x.shape[2:])) if x.ndim > 2 else 1
+        y = np.empty_like(x)
+        rm, rv = _f(running_mean).copy(), _f(running_var).copy()
+        sm, ss = np.zeros(C, np.float32), np.zeros(C, np.float32)
+        weight = None if weight is None else _f(weight)
+        bias = None if bias is None else _f(bias)
+        self._fn("bn_forward")(_p(x), _p(y), _p(weight), _p(bias), _p(rm), _p(rv), _p(sm), _p(ss),
+                               N, C, S, int(train), ctypes.c_double(momentum), ctypes.c_double(eps))
+        return y, rm, rv, sm, ss
+
+    def bn_backward(self, x, gy, weight, running_mean, running_var, save_mean, save_std, train, scale, eps,
+                    gw=None, gb=None, want_gx=True):
+        x, gy = _f(x), _f(gy)
+        N, C = x.shape[:2]
+        S = int(np.prod(x.shape[2:])) if x.ndim > 2 else 1
+        gx = np.empty_like(x) if want_gx else None
+        gw = None if gw is None else _f(gw).copy()
+        gb = None if gb is None else _f(gb).copy()
+        weight = None if weight is None else _f(weight)
+        self._fn("bn_backward")(_p(x), _p(gy), _p(gx), _p(gw), _p(gb), _p(weight),
+                                _p(_f(running_mean)), _p(_f(running_var)), _p(_f(save_mean)), _p(_f(save_std)),
+                                N, C, S, int(train), ctypes.c_double(scale), ctypes.c_double(eps))
+        return gx, gw, gb
+
+    # -- max pooling ---------------------------------------------------------------
+    def pool_out_size(self, size, k, d, pad, dil, ceil_mode):
+        return self._fn("pool_out_size", ctypes.c_int)(size, k, d, pad, dil, int(ceil_mode))
+
+    def maxpool_forward(self, x, kH, kW, dH, dW, padH, padW, ceil_mode, dilH=1, dilW=1):
+        x = _f(x)
+        N, C, H, W = x.shape
+        oH = self.pool_out_size(H, kH, dH, padH, dilH, ceil_mode)
+        oW = self.pool_out_size(W, kW, dW, padW, dilW, ceil_mode)
+        y = np.empty((N, C, oH, oW), np.float32)
+        ind = np.empty((N, C, oH, oW), np.int64)
+        self._fn("maxpool_forward")(_p(x), _p(y), _p(ind), N, C, H, W, oH, oW, kH, kW, dH, dW, padH, padW,
+                                    dilH, dilW)
+        return y, ind
+
+    def maxpool_backward(self, gy, ind, H, W, kH, kW, dH, dW, padH, padW, dilH=1, dilW=1):
+        gy = _f(gy)
+        ind = np.ascontiguousarray(ind, dtype=np.int64)
+        N, C, oH, oW = gy.shape
+        gx = np.empty((N, C, H, W), np.float32)
+        self._fn("maxpool_backward")(_p(gy), _p(ind), _p(gx), N, C, H, W, oH, oW, kH, kW, dH, dW, padH, padW,
+                                     dilH, dilW)
+        return gx
+
+    # -- support ops --------------------------------------------------------------
+    def threshold_forward(self, x, th=0.0, val=0.0):
+        x = _f(x)
+        y = np.empty_like(x)
+        self._fn("threshold_forward")(_p(x), _p(y), ctypes.c_size_t(x.size), ctypes.c_float(th), ctypes.c_float(val))
+        return y
+
+    def threshold_backward(self, x, gy, th=0.0):
+        x, gy = _f(x), _f(gy)
+        gx = np.empty_like(x)
+        self._fn("threshold_backward")(_p(x), _p(gy), _p(gx), ctypes.c_size_t(x.size), ctypes.c_float(th))
+        return gx
+
+    def avgpool_forward(self, x, kH, kW, dH, dW, padH, padW, ceil_mode=False, count_include_pad=True):
+        x = _f(x)
+        N, C, H, W = x.shape
+        oH = self.pool_out_size(H, kH, dH, padH, 1, ceil_mode)
+        oW = self.pool_out_size(W, kW, dW, padW, 1, ceil_mode)
+        y = np.empty((N, C, oH, oW), np.float32)
+        self._fn("avgpool_forward")(_p(x), _p(y), N, C, H, W, oH, oW, kH, kW, dH, dW, padH, padW,
+                                    int(count_include_pad))
+        return y
+
+    def avgpool_backward(self, gy, H, W, kH, kW, dH, dW, padH, padW, count_include_pad=True):
+        gy = _f(gy)
+        N, C, oH, oW = gy.shape
+        gx = np.empty((N, C, H, W), np.float32)
+        self._fn("avgpool_backward")(_p(gy), _p(gx), N, C, H, W, oH, oW, kH, kW, dH, dW, padH, padW,
+                                     int(count_include_pad))
+        return gx
+
+    def logsoftmax_forward(self, x):
+        x = _f(x)
+        y = np.empty_like(x)
+        self._fn("logsoftmax_forward")(_p(x), _p(y), x.shape[0], x.shape[1])
+        return y
+
+    def logsoftmax_backward(self, y, gy):
+        y, gy = _f(y), _f(gy)
+        gx = np.empty_like(y)
+        self._fn("logsoftmax_backward")(_p(y), _p(gy), _p(gx), y.shape[0], y.shape[1])
+        return gx
+
+    def classnll_forward(self, lp, target, weights=None, size_average=True, ignore_index=-100):
+        lp = _f(lp)
+        target = np.ascontiguousarray(target, dtype=np.int64)
+        weights = None if weights is None else _f(weights)
+        loss, tw = ctypes.c_float(), ctypes.c_float()
+        self._fn("classnll_forward")(_p(lp), _p(target), _p(weights), ctypes.byref(loss), ctypes.byref(tw),
+                                     lp.shape[0], lp.shape[1], int(size_average), ctypes.c_int64(ignore_index))
+        return loss.value, tw.value
+
+    def classnll_backward(self, target, total_weight, B, D, weights=None, size_average=True, ignore_index=-100):
+        target = np.ascontiguousarray(target, dtype=np.int64)
+        weights = None if weights is None else _f(weights)
+        gx = np.zeros((B, D), np.float32)
+        self._fn("classnll_backward")(_p(target), _p(weights), ctypes.c_float(total_weight), _p(gx), B, D,
+                                      int(size_average), ctypes.c_int64(ignore_index))
+        return gx
+
+    def slice_range(self, n, g, i):
+        s, c = ctypes.c_long(), ctypes.c_long()
+        self._fn("slice_range")(ctypes.c_long(n), g, i, ctypes.byref(s), ctypes.byref(c))
+        return s.value, c.value
