@@ -1,0 +1,62 @@
+"""Loads libTHCUNN.so and declares the flat C ABI (include/cunn_b200.h) for ctypes.
+
+There is no fallback: if the library has not been built, importing raises.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+SO_PATH = os.path.join(_HERE, "lib", "libTHCUNN.so")
+
+if not os.path.exists(SO_PATH):
+    raise ImportError(
+        "cunn_b200: %s is missing; build it with `python -m cunn_b200.build` "
+        "(there is no CPU or PyTorch fallback)" % SO_PATH)
+
+lib = ctypes.CDLL(SO_PATH)
+
+c_int, c_float, c_double, c_void_p, c_size_t = ctypes.c_int, ctypes.c_float, ctypes.c_double, ctypes.c_void_p, ctypes.c_size_t
+
+
+def _decl(name, restype, argtypes):
+    f = getattr(lib, name)
+    f.restype = restype
+    f.argtypes = argtypes
+    return f
+
+
+_decl("cunn_b200_last_error", ctypes.c_char_p, [])
+_decl("cunn_b200_device_status", c_int, [])
+
+_CONV = [c_int] * 11  # N C H W M|K kH kW dH dW padH padW
+_decl("cunn_b200_dwconv_forward", c_int, [c_void_p] * 4 + _CONV + [c_void_p])
+_decl("cunn_b200_dwconv_grad_input", c_int, [c_void_p] * 3 + _CONV + [c_void_p])
+_decl("cunn_b200_dwconv_acc_grad_workspace", c_size_t, _CONV)
+_decl("cunn_b200_dwconv_acc_grad", c_int, [c_void_p] * 4 + _CONV + [c_float, c_void_p, c_size_t, c_void_p])
+_decl("cunn_b200_dwconv_tuning", None, [ctypes.POINTER(c_int), c_int])
+_decl("cunn_b200_dwconv_describe_plan", c_int, [c_int] * 6 + [ctypes.c_char_p, c_int])
+
+
+class CunnError(RuntimeError):
+    """Raised when an entry point rejects its arguments or a launch fails."""
+
+
+def check(rc):
+    if rc != 0:
+        raise CunnError(lib.cunn_b200_last_error().decode())
+
+
+def device_status():
+    return lib.cunn_b200_device_status()
+
+
+def dwconv_tuning(*values):
+    """Overrides the depthwise fast-path tile plan (see cunn_b200_dwconv_tuning); no arguments resets it."""
+    arr = (c_int * max(len(values), 1))(*values)
+    lib.cunn_b200_dwconv_tuning(arr, len(values))
+
+
+def dwconv_describe_plan(mode, N, C, H, W, stride):
+    buf = ctypes.create_string_buffer(512)
+    lib.cunn_b200_dwconv_describe_plan(mode, N, C, H, W, stride, buf, 512)
+    return buf.value.decode()
