@@ -1,0 +1,422 @@
+#!/usr/bin/env python
+"""Benchmark of the depthwise-convolution hot path (BASELINE config 2: the 13 depthwise 3x3 layers of
+MobileNetV1, fp32 NCHW, batch 64 per GPU, forward + input gradient + parameter gradient per layer).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = 39 kernel launches: all 13 forwards, then all 13 input gradients, then all 13 parameter
+gradients.  The tensors of one step total 2.5 GB, so every kernel finds its inputs in HBM, not in L2.
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank runs the same stack on its
+own batch of 64 images (weak scaling) and the ranks all-reduce the flat depthwise weight-gradient buffer
+over NCCL at the end of each step, as the batch-sharded DataParallelTable does.
+
+Prints ONE JSON line (rank 0).  `value` is whole-job algorithmic GB/s with inputs resident in HBM;
+`e2e` is the same metric through the C ABI with pinned host buffers, host<->device copies timed;
+`roofline` describes the kernel launch that takes the most time; `cpu_baseline` is the fp32 CPU port of
+the oracle timed on this box's host cores on a bounded sample.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# (C, H=W, stride) of MobileNetV1's depthwise layers; the 512x14x14 stride-1 layer occurs five times.
+LAYERS = [(32, 112, 1), (64, 112, 2), (128, 56, 1), (128, 56, 2), (256, 28, 1), (256, 28, 2),
+          (512, 14, 1), (512, 14, 1), (512, 14, 1), (512, 14, 1), (512, 14, 1), (512, 14, 2), (1024, 7, 1)]
+BATCH = 64
+SEED = 1234
+METRIC = "dwconv_fwd_bwd_hbm_gbs"
+
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum, MB) of one launch of the kernel that
+# `roofline` reports, from the ncu capture summarised in profiles/; None until captured.
+NCU_TRAFFIC_MB = {}
+
+
+def out_size(hw, stride):
+    return (hw + 2 - 3) // stride + 1
+
+
+def layer_bytes(C, HW, stride, n):
+    """Algorithmic bytes of one pass (forward, input gradient or parameter gradient) of one layer:
+    4 bytes per element of the layer's input-side and output-side tensors."""
+    o = out_size(HW, stride)
+    return 4 * n * C * (HW * HW + o * o)
+
+
+def step_bytes(n):
+    return 3 * sum(layer_bytes(C, HW, s, n) for C, HW, s in LAYERS)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, uuid=None):
+        self.proc = None
+        self.file = None
+        self.uuid = uuid
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            cmd = ["nvidia-smi", "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100"]
+            if self.uuid:
+                cmd += ["-i", self.uuid]
+            self.proc = subprocess.Popen(cmd, stdout=self.file, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.proc:
+            return out
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        clocks, maxes, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                maxes.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.unlink(self.file.name)
+        except OSError:
+            pass
+        if clocks:
+            clocks.sort()
+            out.update(sm_mhz=clocks[len(clocks) // 2], sm_max_mhz=max(maxes), reasons=sorted(reasons),
+                       samples=len(clocks))
+        return out
+
+
+def make_host_inputs(n):
+    """Seeded synthetic inputs of the workload: x ~ U(-1,1), weights and bias ~ U(-1/3, 1/3)
+    (kaiming-uniform bound 1/sqrt(fan_in), fan_in = 9), gy ~ N(0,1)."""
+    import numpy as np
+    rng = np.random.default_rng(SEED)
+    data = []
+    for C, HW, s in LAYERS:
+        o = out_size(HW, s)
+        data.append(dict(
+            x=rng.uniform(-1, 1, (n, C, HW, HW)).astype(np.float32),
+            gy=rng.standard_normal((n, C, o, o), dtype=np.float32),
+            w=rng.uniform(-1 / 3, 1 / 3, (1, C, 3, 3)).astype(np.float32),
+            b=rng.uniform(-1 / 3, 1 / 3, (1, C)).astype(np.float32)))
+    return data
+
+
+def run_reference(args):
+    """--impl reference: the CPU arm.  torch/nn's CPU THNN (what the reference's tests compare with) is not
+    part of the reference tree and nothing of the reference compiles here, so this times the fp32 OpenMP
+    port of the oracle on all host cores, on a bounded sample (a few images per layer) of the workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    res = cpu_baseline(target_seconds=8.0, steps=args.steps, warmup=min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": res["value"], "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(res["sample_images"], 1),
+        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": res["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def cpu_baseline(target_seconds=12.0, steps=1, warmup=0):
+    """Times the fp32 CPU port (oracle/thnn_ref.c, ref32_*) of the same 13-layer fwd+dgrad+wgrad stack on
+    `n` images per layer, with n chosen so one step takes about target_seconds / (steps + warmup)."""
+    import numpy as np
+    from oracle.thnn_ref import Ref
+    ref = Ref("ref32_")
+    cores = os.cpu_count() or 1
+
+    def one_step(data):
+        for (C, HW, s), d in zip(LAYERS, data):
+            ref.dwconv_forward(d["x"], d["w"], d["b"], s, s, 1, 1)
+        for (C, HW, s), d in zip(LAYERS, data):
+            ref.dwconv_grad_input(d["gy"], d["w"], HW, HW, s, s, 1, 1)
+        for (C, HW, s), d in zip(LAYERS, data):
+            ref.dwconv_acc_grad(d["x"], d["gy"], np.zeros_like(d["w"]), np.zeros_like(d["b"]), s, s, 1, 1, 1.0)
+
+    probe = make_host_inputs(1)
+    one_step(probe)
+    t0 = time.perf_counter()
+    one_step(probe)
+    t1 = time.perf_counter() - t0
+    per_step_budget = target_seconds / max(1, steps + warmup)
+    n = int(max(1, min(BATCH, per_step_budget / max(t1, 1e-4))))
+    data = make_host_inputs(n) if n > 1 else probe
+    for _ in range(warmup):
+        one_step(data)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_step(data)
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": step_bytes(n) / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": "13-layer depthwise stack fwd+dgrad+wgrad on %d image(s) per layer (of %d), fp32 OpenMP "
+                      "port of the oracle, %d step(s)" % (n, BATCH, steps),
+            "ms_per_step": dt * 1e3, "sample_images": n}
+
+
+def workload_config(n, world):
+    return {"workload": "MobileNetV1 depthwise stack: 13 SpatialDepthWiseConvolution 3x3 pad 1 layers, "
+                        "fwd + updateGradInput + accGradParameters each (BASELINE config 2)",
+            "batch_per_gpu": n, "global_batch": n * world, "layers": len(LAYERS),
+            "layout": "NCHW fp32", "l2": "inputs larger than L2: one step touches 2.5 GB of tensors per GPU and a "
+                                         "tensor is re-read only after >= 1.2 GB of other traffic",
+            "parallelism": "dp%d (batch-sharded, NCCL all-reduce of depthwise weight gradients)" % world
+                           if world > 1 else "single GPU",
+            "launch": "39 kernels per step replayed from one CUDA graph"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import cunn_b200.functional as F
+    from cunn_b200 import device_status
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    warmup = max(args.warmup, 3)
+    steps = max(args.steps, 1)
+
+    # ---- device-resident tensors -------------------------------------------------------------------
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(SEED + rank)
+    nparams = sum(C * 10 for C, _, _ in LAYERS)
+    flat_grad = torch.zeros(nparams, device=dev)       # [gw | gb] per layer, the DataParallelTable flat layout
+    T, off = [], 0
+    for C, HW, s in LAYERS:
+        o = out_size(HW, s)
+        t = dict(C=C, HW=HW, s=s, o=o,
+                 x=torch.rand((BATCH, C, HW, HW), device=dev, generator=gen) * 2 - 1,
+                 gy=torch.randn((BATCH, C, o, o), device=dev, generator=gen),
+                 w=(torch.rand((1, C, 3, 3), device=dev, generator=gen) * 2 - 1) / 3,
+                 b=(torch.rand((1, C), device=dev, generator=gen) * 2 - 1) / 3,
+                 y=torch.empty((BATCH, C, o, o), device=dev),
+                 gx=torch.empty((BATCH, C, HW, HW), device=dev),
+                 gw=flat_grad[off:off + 9 * C].view(1, C, 3, 3),
+                 gb=flat_grad[off + 9 * C:off + 10 * C].view(1, C))
+        off += 10 * C
+        T.append(t)
+
+    def fwd(t):
+        F.dwconv_forward(t["x"], t["w"], t["b"], t["s"], t["s"], 1, 1, out=t["y"])
+
+    def dgrad(t):
+        F.dwconv_grad_input(t["gy"], t["w"], t["HW"], t["HW"], t["s"], t["s"], 1, 1, out=t["gx"])
+
+    def wgrad(t):
+        F.dwconv_acc_grad(t["x"], t["gy"], t["gw"], t["gb"], t["s"], t["s"], 1, 1, 1.0)
+
+    OPS = [("fwd", fwd), ("dgrad", dgrad), ("wgrad", wgrad)]
+
+    def kernels():
+        for _, op in OPS:
+            for t in T:
+                op(t)
+
+    launches_per_step = len(OPS) * len(T)
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    kernels()                       # first call: workspace allocation, function attributes
+    torch.cuda.synchronize()
+    graph = None
+    if not args.no_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            kernels()
+
+    def step():
+        if graph is not None:
+            graph.replay()
+        else:
+            kernels()
+        if world > 1:
+            dist.all_reduce(flat_grad)
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(str(torch.cuda.get_device_properties(dev).uuid)) if rank == 0 else None
+    if sampler:
+        sampler.uuid = "GPU-" + sampler.uuid if not sampler.uuid.startswith("GPU-") else sampler.uuid
+        sampler.start()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        dist.barrier()
+        tt = torch.tensor([ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+    ms_per_step = ms / steps
+    value = step_bytes(BATCH) * world / (ms_per_step * 1e-3) / 1e9
+
+    # ---- per-kernel durations (CUDA events around every launch, same stream) ------------------------
+    ksteps = min(steps, 10)
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(launches_per_step + 1)] for _ in range(ksteps)]
+    for it in range(ksteps):
+        evs[it][0].record()
+        i = 1
+        for _, op in OPS:
+            for t in T:
+                op(t)
+                evs[it][i].record()
+                i += 1
+    torch.cuda.synchronize()
+    per = []
+    i = 0
+    for name, _ in OPS:
+        for li, t in enumerate(T):
+            d = sorted(evs[it][i].elapsed_time(evs[it][i + 1]) for it in range(ksteps))[ksteps // 2]
+            per.append(dict(op=name, layer=li + 1, C=t["C"], HW=t["HW"], stride=t["s"], ms=d,
+                            bytes=layer_bytes(t["C"], t["HW"], t["s"], BATCH)))
+            i += 1
+    peak, peak_kind = measured_peaks()
+    top = max(per, key=lambda k: k["ms"])
+    achieved = top["bytes"] / (top["ms"] * 1e-3) / 1e9
+    key = "%s_%d" % (top["op"], top["layer"])
+    traffic = NCU_TRAFFIC_MB.get(key)
+    roofline = {"bound": "hbm", "kernel": "dwconv %s, layer %d (C=%d, %dx%d, stride %d)" %
+                (top["op"], top["layer"], top["C"], top["HW"], top["HW"], top["stride"]),
+                "achieved": round(achieved, 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                "frac": round(achieved / peak, 4),
+                "traffic": None if traffic is None else traffic * 1e6,
+                "algorithmic_bytes": top["bytes"], "launch_ms": round(top["ms"], 5),
+                "step": {"achieved": round(step_bytes(BATCH) / (ms_per_step * 1e-3) / 1e9 if world == 1 else
+                                           value / world, 1),
+                         "frac": round((value / world) / peak, 4),
+                         "note": "all 39 launches: algorithmic bytes / graph-replay time per step"},
+                "per_kernel": [dict(op=k["op"], layer=k["layer"], us=round(k["ms"] * 1e3, 2),
+                                    gbs=round(k["bytes"] / (k["ms"] * 1e-3) / 1e9, 0)) for k in per]}
+
+    # ---- end to end through the C ABI with host buffers ----------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        import numpy as np
+        esteps = max(1, min(steps, 3))
+        H = []
+        for t in T:
+            H.append(dict(x=t["x"].cpu().pin_memory(), gy=t["gy"].cpu().pin_memory(),
+                          y=torch.empty(t["y"].shape).pin_memory(), gx=torch.empty(t["gx"].shape).pin_memory()))
+        hgrad = torch.empty(nparams).pin_memory()
+        h2d = sum(h["x"].numel() + h["gy"].numel() for h in H) * 4
+        d2h = sum(h["y"].numel() + h["gx"].numel() for h in H) * 4 + nparams * 4
+
+        def e2e_step():
+            for t, h in zip(T, H):
+                t["x"].copy_(h["x"], non_blocking=True)
+                t["gy"].copy_(h["gy"], non_blocking=True)
+                fwd(t)
+                dgrad(t)
+                wgrad(t)
+                h["y"].copy_(t["y"], non_blocking=True)
+                h["gx"].copy_(t["gx"], non_blocking=True)
+            if world > 1:
+                dist.all_reduce(flat_grad)
+            hgrad.copy_(flat_grad, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        e2e_step()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(esteps):
+            e2e_step()
+        a1.record()
+        torch.cuda.synchronize()
+        ems = max(a0.elapsed_time(a1), (time.perf_counter() - t0) * 1e3)
+        if world > 1:
+            tt = torch.tensor([ems], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ems = float(tt.item())
+        e2e = {"value": round(step_bytes(BATCH) * world / (ems / esteps * 1e-3) / 1e9, 2), "unit": "GB/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": esteps,
+               "ms_per_step": round(ems / esteps, 3)}
+
+    status = device_status()
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        c = cpu_baseline(target_seconds=12.0, steps=1, warmup=0)
+        cpu = {k: (round(c[k], 3) if isinstance(c[k], float) else c[k]) for k in ("value", "unit", "cores", "kind", "sample")}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": steps,
+                "warmup": warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(BATCH, world),
+                "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * steps,
+                "roofline": roofline, "cpu_baseline": cpu, "device_status": status}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
