@@ -5,6 +5,15 @@ behind a C ABI).  This package is the Python host side used by the tests and
 the benchmark: ``functional`` calls the flat ABI on torch CUDA tensors (torch
 only provides device memory and streams), ``thnn`` drives the ``THNN_Cuda*``
 entry points the way the reference's LuaJIT FFI binding does.
+
+The library is loaded on first use (``cunn_b200._lib``); if it has not been
+built that import raises — there is no CPU or PyTorch fallback.  ``python -m
+cunn_b200.build`` builds it.
 """
-from . import _lib  # noqa: F401  (raises if the library is not built)
-from ._lib import CunnError, SO_PATH, device_status  # noqa: F401
+
+
+def __getattr__(name):
+    if name in ("CunnError", "SO_PATH", "device_status", "lib"):
+        from . import _lib
+        return getattr(_lib, name)
+    raise AttributeError(name)
