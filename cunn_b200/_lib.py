@@ -33,6 +33,8 @@ _decl("cunn_b200_dwconv_forward", c_int, [c_void_p] * 4 + _CONV + [c_void_p])
 _decl("cunn_b200_dwconv_grad_input", c_int, [c_void_p] * 3 + _CONV + [c_void_p])
 _decl("cunn_b200_dwconv_acc_grad_workspace", c_size_t, _CONV)
 _decl("cunn_b200_dwconv_acc_grad", c_int, [c_void_p] * 4 + _CONV + [c_float, c_void_p, c_size_t, c_void_p])
+_decl("cunn_b200_dwconv_acc_grad_static", c_int, [c_void_p] * 4 + _CONV + [c_float, c_void_p])
+_decl("cunn_b200_dwconv_acc_grad_static_capacity", c_size_t, [])
 _decl("cunn_b200_dwconv_tuning", None, [ctypes.POINTER(c_int), c_int])
 _decl("cunn_b200_dwconv_describe_plan", c_int, [c_int] * 6 + [ctypes.c_char_p, c_int])
 

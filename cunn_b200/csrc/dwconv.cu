@@ -1111,3 +1111,72 @@ extern "C" CUNN_API int cunn_b200_dwconv_describe_plan(int mode, int N, int C, i
              pl.out_floats * 4, pl.smem);
     return pl.ok ? 0 : 1;
 }
+
+// ---------------------------------------------------------------------------
+// Parameter gradient without caller-provided scratch
+// ---------------------------------------------------------------------------
+//
+// Some hosts cannot hand this library a workspace: a program that has given all device memory to an
+// arena of its own has nothing left to cudaMalloc from, and a binding that only passes tensors through
+// (the LuaJIT FFI signature of accGradParameters has no workspace argument) has no allocator to ask.
+// For them the scratch of the 3x3 parameter-gradient kernel lives in a fixed array inside this module.
+// Every GPU that loads the library holds these bytes until the process exits.
+static const size_t kStaticScratchBytes = (size_t)4 << 20;  // 4 MiB: 64 KiB of ticket counters + partial sums
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+// Device address of g_static_scratch per device.  In host code the array's name only stands for the
+// symbol; the address a kernel can use comes from cudaGetSymbolAddress with that device current.
+unsigned char *g_static_scratch_ptr[64];
+}
+
+extern "C" CUNN_API size_t cunn_b200_dwconv_acc_grad_static_capacity(void) { return kStaticScratchBytes; }
+
+extern "C" CUNN_API int cunn_b200_dwconv_acc_grad_static(const float *x, const float *gy, float *grad_weight,
+                                                         float *grad_bias, int N, int C, int H, int W, int M, int kH,
+                                                         int kW, int dH, int dW, int padH, int padW, float scale,
+                                                         cunn_stream_t stream_)
+{
+    clear_error();
+    cudaStream_t stream = (cudaStream_t)stream_;
+    int oH, oW;
+    if (check_common(N, C, H, W, M, kH, kW, dH, dW, padH, padW, &oH, &oW)) return 1;
+    if (N == 0) return 0;
+    CUNN_CHECK_ARG(x && gy && grad_weight, "null tensor pointer");
+    if (fast_shape(M, kH, kW, dH, dW, padH, padW) && aligned16(x) && aligned16(gy)) {
+        Plan pl = make_plan(MODE_WGRAD, N, C, H, W, oH, oW, dH);
+        if (pl.ok && finalize_plan(pl) == 0) {
+            const size_t need = wgrad_workspace_bytes(C, pl);
+            CUNN_CHECK_ARG(need <= kStaticScratchBytes,
+                           "dwconv acc_grad (static scratch): this shape needs %zu bytes of scratch, the built-in array "
+                           "holds %zu; use cunn_b200_dwconv_acc_grad with a caller-provided workspace",
+                           need, kStaticScratchBytes);
+            int dev = 0;
+            CUNN_CUDA(cudaGetDevice(&dev));
+            CUNN_CHECK_ARG(dev >= 0 && dev < 64, "device index %d out of range", dev);
+            if (!g_static_scratch_ptr[dev]) {
+                // one-time set-up for this device (it is the current one)
+                void *ptr = nullptr;
+                CUNN_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+                g_static_scratch_ptr[dev] = (unsigned char *)ptr;
+            }
+            unsigned char *scratch = g_static_scratch_ptr[dev];
+            // The array keeps whatever the previous call left.  The ticket counters must start at zero;
+            // the partial sums are fully written before they are read.
+            CUNN_CUDA(cudaMemsetAsync(scratch, 0, (size_t)(C / pl.P) * sizeof(unsigned int), stream));
+            FastParams fp{};
+            fill_params(fp, pl, N, C, H, W, oH, oW);
+            fp.in = x; fp.in2 = gy; fp.w = nullptr; fp.out = nullptr;
+            fp.gw = grad_weight; fp.gb = grad_bias; fp.scale = scale;
+            fp.counters = (unsigned int *)scratch;
+            fp.partials = (float *)(scratch + wgrad_counter_bytes(C, pl));
+            return launch_fast(fp, pl, stream, "dwconv acc grad (3x3, static scratch)");
+        }
+    }
+    // shapes outside the 3x3 fast path use the generic kernel, which needs no scratch at all
+    const int blocks = M * C * (kH * kW + 1);
+    wgrad_generic_kernel<<<blocks, 256, 0, stream>>>(x, gy, grad_weight, grad_bias, N, C, H, W, M, kH, kW, dH, dW, padH,
+                                                    padW, oH, oW, scale);
+    CUNN_LAUNCH_CHECK("dwconv acc grad (generic)");
+    return 0;
+}

@@ -74,6 +74,23 @@ CUNN_API int cunn_b200_dwconv_acc_grad(const float *x, const float *gy, float *g
                               int dH, int dW, int padH, int padW, float scale,
                               void *workspace, size_t workspace_bytes, cunn_stream_t stream);
 
+/* Parameter gradient for callers that cannot supply scratch memory.  It has no counterpart in the
+ * reference.  Same arguments and result as cunn_b200_dwconv_acc_grad minus the workspace: the scratch is
+ * a fixed 4 MiB array inside the library (resident on every GPU that loads it, until exit), so the call
+ * performs no cudaMalloc, cudaFree or other allocation.  It exists for hosts that have no allocator to
+ * offer: a program whose own arena already owns all device memory, or a pass-through binding whose
+ * signature carries tensors only.  Shapes whose scratch would exceed the array are rejected with an error
+ * naming both sizes (cunn_b200_dwconv_acc_grad_static_capacity() returns the limit); shapes outside the
+ * 3x3 fast path need no scratch and are accepted.  The first call on each device looks up the array's
+ * device address (cudaGetSymbolAddress); make that first call outside any stream capture.  All calls on
+ * a device share the one array: calls that may overlap on the GPU (different streams without an ordering
+ * between them) race on it and must be serialised by the caller. */
+CUNN_API int cunn_b200_dwconv_acc_grad_static(const float *x, const float *gy, float *grad_weight, float *grad_bias,
+                                              int N, int C, int H, int W, int M, int kH, int kW,
+                                              int dH, int dW, int padH, int padW, float scale,
+                                              cunn_stream_t stream);
+CUNN_API size_t cunn_b200_dwconv_acc_grad_static_capacity(void);
+
 /* Tuning hook for sweeps and tests: overrides the tile plan of the 3x3 fast path for the calling
  * thread.  values[0..count) = {planes_per_tile, rows_per_tile, rows_per_strip, stages, ctas_per_sm,
  * force_generic, stage_budget_kb, vec, staged_stores(-1 auto)}; 0 keeps the automatic choice, missing
