@@ -183,6 +183,8 @@ struct FastParams {
     int CG;             // column groups per row = oW / VEC
     int items;          // P * strips * CG  (<= blockDim.x)
     int maxseg;         // WGRAD: partial slots per CTA (channel groups one CTA's tile range can touch)
+    int tiles_base;     // every CTA takes tiles_base tiles of the sequence, the first tiles_rem CTAs one more
+    int tiles_rem;
     int stages;
     int stage_floats;   // floats per stage for `in`
     int stage2_floats;  // floats per stage for `in2`
@@ -195,53 +197,74 @@ struct Win {
     static constexpr int NV = (VEC - 1) * S + 3;  // input columns a thread needs per row
 };
 
-// Loads the NV input values of one row that a column group needs; r points at the group's first
-// interior column (column col0 of the row, or of the all-zero row for rows outside the plane).
+// Shared-memory loads on 32-bit shared-window addresses (cheaper address arithmetic than generic
+// pointers).  volatile + memory clobber keeps them ordered with the mbarrier waits and barriers.
+__device__ __forceinline__ float lds32(uint32_t a)
+{
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ float2 lds64(uint32_t a)
+{
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 lds128(uint32_t a)
+{
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a) : "memory");
+    return v;
+}
+
+// Loads the NV input values of one row that a column group needs; r is the shared address of the group's
+// first interior column (column col0 of the row, or of the all-zero row for rows outside the plane).
 // v[0] is column col0-1, v[NV-1] the last one; those two may lie outside the row and then read as zero.
 template <int S, int VEC>
-__device__ __forceinline__ void load_row(const float *r, bool has_left, bool has_right, float (&v)[Win<S, VEC>::NV])
+__device__ __forceinline__ void load_row(uint32_t r, bool has_left, bool has_right, float (&v)[Win<S, VEC>::NV])
 {
     constexpr int NV = Win<S, VEC>::NV;
     v[0] = 0.f;
-    if (has_left) v[0] = r[-1];
+    if (has_left) v[0] = lds32(r - 4);
     if (VEC == 4 && S == 1) {
-        const float4 q = *reinterpret_cast<const float4 *>(r);
+        const float4 q = lds128(r);
         v[1] = q.x; v[2] = q.y; v[3] = q.z; v[4] = q.w;
         v[NV - 1] = 0.f;
-        if (has_right) v[NV - 1] = r[4];
+        if (has_right) v[NV - 1] = lds32(r + 16);
     } else if (VEC == 4 && S == 2) {
-        const float4 q0 = *reinterpret_cast<const float4 *>(r);
-        const float4 q1 = *reinterpret_cast<const float4 *>(r + 4);
+        const float4 q0 = lds128(r);
+        const float4 q1 = lds128(r + 16);
         v[1] = q0.x; v[2] = q0.y; v[3] = q0.z; v[4] = q0.w;
         v[5] = q1.x; v[6] = q1.y; v[7] = q1.z; v[NV - 1] = q1.w;
     } else if (VEC == 2 && S == 1) {
-        const float2 q = *reinterpret_cast<const float2 *>(r);
+        const float2 q = lds64(r);
         v[1] = q.x; v[2] = q.y;
         v[NV - 1] = 0.f;
-        if (has_right) v[NV - 1] = r[2];
+        if (has_right) v[NV - 1] = lds32(r + 8);
     } else if (VEC == 2 && S == 2) {
-        const float4 q = *reinterpret_cast<const float4 *>(r);
+        const float4 q = lds128(r);
         v[1] = q.x; v[2] = q.y; v[3] = q.z; v[NV - 1] = q.w;
     } else {
 #pragma unroll
-        for (int i = 1; i < NV - 1; ++i) v[i] = r[i - 1];
+        for (int i = 1; i < NV - 1; ++i) v[i] = lds32(r + 4 * (i - 1));
         v[NV - 1] = 0.f;
-        if (has_right) v[NV - 1] = r[NV - 2];
+        if (has_right) v[NV - 1] = lds32(r + 4 * (NV - 2));
     }
 }
 
 template <int VEC>
-__device__ __forceinline__ void load_vec(const float *p, float (&g)[VEC])
+__device__ __forceinline__ void load_vec(uint32_t a, float (&g)[VEC])
 {
     if (VEC == 4) {
-        const float4 q = *reinterpret_cast<const float4 *>(p);
+        const float4 q = lds128(a);
         g[0] = q.x; g[1] = q.y; g[2] = q.z; g[3] = q.w;
     } else if (VEC == 2) {
-        const float2 q = *reinterpret_cast<const float2 *>(p);
+        const float2 q = lds64(a);
         g[0] = q.x; g[1] = q.y;
     } else {
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) g[i] = p[i];
+        for (int i = 0; i < VEC; ++i) g[i] = lds32(a + 4 * i);
     }
 }
 
@@ -263,28 +286,51 @@ struct Tile {
     int r0, r1;         // staged rows of `in` [r0, r1)
 };
 
-// Tiles are numbered group-major, then image, then band: t = (g * N + n) * bands + band.
+// Position in the tile sequence, which runs group-major, then image, then band:
+// t = (g * N + n) * bands + band.  Advanced incrementally; divisions happen once per CTA.
+struct Cursor {
+    int g, n, band;
+};
+
+__device__ __forceinline__ Cursor cursor_at(const FastParams &p, int t)
+{
+    Cursor c;
+    const int tpg = p.N * p.bands;
+    c.g = t / tpg;
+    const int r = t - c.g * tpg;
+    c.n = r / p.bands;
+    c.band = r - c.n * p.bands;
+    return c;
+}
+
+__device__ __forceinline__ void cursor_next(const FastParams &p, Cursor &c)
+{
+    if (++c.band == p.bands) {
+        c.band = 0;
+        if (++c.n == p.N) {
+            c.n = 0;
+            ++c.g;
+        }
+    }
+}
+
 template <int MODE, int S>
-__device__ __forceinline__ Tile tile_of(const FastParams &p, int t)
+__device__ __forceinline__ Tile tile_of(const FastParams &p, const Cursor &c)
 {
     Tile tl;
-    const int tpg = p.N * p.bands;
-    tl.g = t / tpg;
-    const int r = t - tl.g * tpg;
-    tl.n = r / p.bands;
-    const int band = r - tl.n * p.bands;
-    tl.d0 = band * p.R;
+    tl.g = c.g;
+    tl.n = c.n;
+    tl.d0 = c.band * p.R;
     tl.d1 = min(p.oH, tl.d0 + p.R);
-    if (MODE == MODE_DGRAD_S2) {
+    if (p.bands == 1) {  // whole planes
+        tl.r0 = 0;
+        tl.r1 = (MODE == MODE_DGRAD_S2) ? p.oH : p.H;
+    } else if (MODE == MODE_DGRAD_S2) {
         tl.r0 = tl.d0;
         tl.r1 = min(p.oH, tl.d1 + 1);
     } else {
         tl.r0 = max(0, tl.d0 * S - 1);
         tl.r1 = min(p.H, (tl.d1 - 1) * S + 2);
-    }
-    if (p.bands == 1) {  // whole planes
-        tl.r0 = 0;
-        tl.r1 = (MODE == MODE_DGRAD_S2) ? p.oH : p.H;
     }
     return tl;
 }
@@ -312,62 +358,98 @@ __device__ __forceinline__ void issue_tile(const FastParams &p, const Tile &tl, 
     if (MODE == MODE_WGRAD) bulk_g2s(smem_u32(stage_in2), src2, bytes2, bar);
 }
 
-// CTA range helpers shared by the kernel and the last-ticket reduction.
-__device__ __forceinline__ long long cta_begin(long long TT, int grid, int b) { return TT * b / grid; }
+// The tile sequence is split evenly: CTA b owns tiles [cta_begin(b), cta_begin(b + 1)).
+__device__ __forceinline__ int cta_begin(const FastParams &p, int b) { return b * p.tiles_base + min(b, p.tiles_rem); }
+__device__ __forceinline__ int cta_of_tile(const FastParams &p, int t)
+{
+    const int big = p.tiles_rem * (p.tiles_base + 1);  // tiles owned by the CTAs that hold one extra
+    return t < big ? t / (p.tiles_base + 1) : p.tiles_rem + (t - big) / p.tiles_base;
+}
 
 // Hands in the ten running sums of the channel group `g` this CTA just finished: per-plane reduction
 // in shared memory -> partial slot of (this CTA, g) -> ticket; the last ticket holder of the group
-// folds every CTA's partial into gw / gb.
+// folds every CTA's partial into gw / gb in CTA order.
 __device__ __forceinline__ void wgrad_flush(const FastParams &p, const float (&acc)[10], float *red, int *flag,
-                                            bool active, int per_plane, int g, int g_first, long long TT)
+                                            bool active, int per_plane, int g, int g_first)
 {
     const int tid = threadIdx.x;
-    const int grid = gridDim.x;
     __syncthreads();
     if (active) {
 #pragma unroll
         for (int k = 0; k < 10; ++k) red[tid * 10 + k] = acc[k];
     }
     __syncthreads();
-    const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
     float *slot = p.partials + ((size_t)blockIdx.x * p.maxseg + (g - g_first)) * p.P * 10;
-    for (int pair = warp; pair < p.P * 10; pair += nwarps) {
-        const int ppl = pair / 10, k = pair - ppl * 10;
-        float s = 0.f;
-        for (int i = lane; i < per_plane; i += 32) s += red[(ppl * per_plane + i) * 10 + k];
-        s = warp_sum(s);
-        if (lane == 0) __stcg(slot + pair, s);
+    if (per_plane <= 16) {
+        // few items per plane: one thread per (plane, sum) pair adds them serially
+        for (int pair = tid; pair < p.P * 10; pair += blockDim.x) {
+            const int ppl = pair / 10, k = pair - ppl * 10;
+            const float *r = red + ppl * per_plane * 10 + k;
+            float s = 0.f;
+            for (int i = 0; i < per_plane; ++i) s += r[i * 10];
+            __stcg(slot + pair, s);
+        }
+    } else {
+        const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
+        for (int pair = warp; pair < p.P * 10; pair += nwarps) {
+            const int ppl = pair / 10, k = pair - ppl * 10;
+            float s = 0.f;
+            for (int i = lane; i < per_plane; i += 32) s += red[(ppl * per_plane + i) * 10 + k];
+            s = warp_sum(s);
+            if (lane == 0) __stcg(slot + pair, s);
+        }
     }
     __threadfence();
     __syncthreads();
-    // CTAs whose tile range meets this group's tiles [lo, hi)
-    const int tpg = p.N * p.bands;
-    const long long lo = (long long)g * tpg, hi = lo + tpg;
-    int b_lo = (int)(lo * grid / TT);
-    while (b_lo > 0 && cta_begin(TT, grid, b_lo) > lo) --b_lo;
-    while (cta_begin(TT, grid, b_lo + 1) <= lo) ++b_lo;
-    int b_hi = (int)((hi - 1) * grid / TT);
-    while (b_hi + 1 < grid && cta_begin(TT, grid, b_hi + 1) < hi) ++b_hi;
-    while (cta_begin(TT, grid, b_hi) >= hi) --b_hi;
     if (tid == 0) {
+        // CTAs whose tile range meets this group's tiles [lo, lo + tpg)
+        const int tpg = p.N * p.bands;
+        const int lo = g * tpg;
+        const int b_lo = cta_of_tile(p, lo), b_hi = cta_of_tile(p, lo + tpg - 1);
         const unsigned int ticket = atomicAdd(p.counters + g, 1u);
-        *flag = (ticket == (unsigned int)(b_hi - b_lo)) ? 1 : 0;
+        flag[0] = (ticket == (unsigned int)(b_hi - b_lo)) ? 1 : 0;
+        flag[1] = b_lo;
+        flag[2] = b_hi;
+        flag[3] = g - cta_begin(p, b_lo) / tpg;  // slot of group g inside CTA b_lo; every later CTA starts in g
     }
     __syncthreads();
-    if (*flag) {
+    if (flag[0]) {
         __threadfence();
-        for (int idx = tid; idx < p.P * 10; idx += blockDim.x) {
-            const int ppl = idx / 10, k = idx - ppl * 10;
-            const int c = g * p.P + ppl;
-            double s = 0.0;
-            for (int b = b_lo; b <= b_hi; ++b) {
-                const long long tb = cta_begin(TT, grid, b);
-                if (cta_begin(TT, grid, b + 1) <= tb) continue;  // CTA without tiles
-                const int seg = g - (int)(tb / tpg);
-                s += (double)__ldcg(p.partials + ((size_t)b * p.maxseg + seg) * p.P * 10 + idx);
+        const int b_lo = flag[1], b_hi = flag[2], seg_lo = flag[3];
+        const size_t stride = (size_t)p.maxseg * p.P * 10;
+        const int n10 = p.P * 10;
+        const float *first = p.partials + b_lo * stride + (size_t)seg_lo * n10;   // CTA b_lo's slot of group g
+        const float *rest = p.partials + (size_t)(b_lo + 1) * stride;             // later CTAs start inside g
+        const int nrest = b_hi - b_lo;
+        if ((n10 & 3) == 0) {
+            // four sums per thread, 16-byte loads, several CTAs' partials in flight at once
+            for (int q = tid * 4; q < n10; q += blockDim.x * 4) {
+                const float4 f = __ldcg(reinterpret_cast<const float4 *>(first + q));
+                double s0 = f.x, s1 = f.y, s2 = f.z, s3 = f.w;
+#pragma unroll 8
+                for (int b = 0; b < nrest; ++b) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(rest + b * stride + q));
+                    s0 += (double)v.x; s1 += (double)v.y; s2 += (double)v.z; s3 += (double)v.w;
+                }
+                const double sv[4] = {s0, s1, s2, s3};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int idx = q + j, ppl = idx / 10, k = idx - ppl * 10;
+                    const int c = g * p.P + ppl;
+                    if (k < 9) p.gw[(size_t)c * 9 + k] = (float)((double)p.gw[(size_t)c * 9 + k] + (double)p.scale * sv[j]);
+                    else if (p.gb) p.gb[c] = (float)((double)p.gb[c] + (double)p.scale * sv[j]);
+                }
             }
-            if (k < 9) p.gw[(size_t)c * 9 + k] = (float)((double)p.gw[(size_t)c * 9 + k] + (double)p.scale * s);
-            else if (p.gb) p.gb[c] = (float)((double)p.gb[c] + (double)p.scale * s);
+        } else {
+            for (int idx = tid; idx < n10; idx += blockDim.x) {
+                const int ppl = idx / 10, k = idx - ppl * 10;
+                const int c = g * p.P + ppl;
+                double s = (double)__ldcg(first + idx);
+#pragma unroll 8
+                for (int b = 0; b < nrest; ++b) s += (double)__ldcg(rest + b * stride + idx);
+                if (k < 9) p.gw[(size_t)c * 9 + k] = (float)((double)p.gw[(size_t)c * 9 + k] + (double)p.scale * s);
+                else if (p.gb) p.gb[c] = (float)((double)p.gb[c] + (double)p.scale * s);
+            }
         }
         if (tid == 0) p.counters[g] = 0u;  // leave the control words zero for the next call
     }
@@ -400,12 +482,10 @@ fast_kernel(const FastParams p)
     float *red = reinterpret_cast<float *>(flag + 4);
 
     // Persistent CTA: a contiguous, balanced range of the global tile sequence.
-    const long long TT = (long long)(p.C / p.P) * p.N * p.bands;
-    const int t_begin = (int)cta_begin(TT, gridDim.x, blockIdx.x);
-    const int t_end = (int)cta_begin(TT, gridDim.x, blockIdx.x + 1);
-    const int T = t_end - t_begin;
-    const int tpg = p.N * p.bands;
-    const int g_first = T > 0 ? t_begin / tpg : 0;
+    const int t_begin = cta_begin(p, blockIdx.x);
+    const int T = p.tiles_base + ((int)blockIdx.x < p.tiles_rem ? 1 : 0);
+    Cursor cur = cursor_at(p, t_begin);
+    const int g_first = cur.g;
 
     const int tid = threadIdx.x;
     for (int i = tid; i < zlen; i += blockDim.x) zrow_base[i] = 0.f;
@@ -414,12 +494,14 @@ fast_kernel(const FastParams p)
         mbar_fence_init();
     }
     __syncthreads();
+    Cursor pre = cur;  // thread 0: cursor of the next tile to fetch
     if (tid == 0) {
-        const int pre = min(T, p.stages);
-        for (int i = 0; i < pre; ++i) {
-            const Tile tl = tile_of<MODE, S>(p, t_begin + i);
+        const int npre = min(T, p.stages);
+        for (int i = 0; i < npre; ++i) {
+            const Tile tl = tile_of<MODE, S>(p, pre);
             issue_tile<MODE, S>(p, tl, in_s + (size_t)i * p.stage_floats, in2_s + (size_t)i * p.stage2_floats,
                                 smem_u32(bars + i));
+            cursor_next(p, pre);
         }
     }
 
@@ -439,14 +521,15 @@ fast_kernel(const FastParams p)
     for (int i = 0; i < 10; ++i) acc[i] = 0.f;
     int cur_g = -1;
     int c = 0;
+    int st = 0;            // stage of the current tile and the parity of its barrier phase
+    uint32_t phase = 0;
 
     for (int t = 0; t < T; ++t) {
-        const int st = t % p.stages;
-        const Tile tl = tile_of<MODE, S>(p, t_begin + t);
+        const Tile tl = tile_of<MODE, S>(p, cur);
         if (tl.g != cur_g) {
             // entering a new channel group: fetch its weights, or (WGRAD) hand in the sums of the last one
             if (MODE == MODE_WGRAD && cur_g >= 0) {
-                wgrad_flush(p, acc, red, flag, active, per_plane, cur_g, g_first, TT);
+                wgrad_flush(p, acc, red, flag, active, per_plane, cur_g, g_first);
 #pragma unroll
                 for (int i = 0; i < 10; ++i) acc[i] = 0.f;
             }
@@ -459,7 +542,7 @@ fast_kernel(const FastParams p)
                 if (MODE == MODE_FWD && p.bias) bias = __ldg(p.bias + c);
             }
         }
-        if (!mbar_wait(smem_u32(bars + st), (uint32_t)((t / p.stages) & 1), p.status)) return;
+        if (!mbar_wait(smem_u32(bars + st), phase, p.status)) return;
         const int dbeg = tl.d0 + strip * p.RS;
         const int dend = min(tl.d1, dbeg + p.RS);
         float *os = out_s + (size_t)(t & 1) * p.out_floats;
@@ -470,22 +553,21 @@ fast_kernel(const FastParams p)
                 const int col0 = cg * VEC * S;
                 const bool has_left = col0 > 0;
                 const bool has_right = col0 + NV - 2 < W;
-                // row_base + row * W is column col0 of plane row `row` in the stage
-                const float *row_base = in_s + (size_t)st * p.stage_floats + (pl * H - tl.r0) * W + col0;
-                const float *zr = zrow + col0;
-                auto rowp = [&](int row) -> const float * {
-                    return ((unsigned)row < (unsigned)H) ? row_base + row * W : zr;
-                };
+                // shared address of column col0 of plane row `row` is row_base + row * 4W
+                const uint32_t row_base = smem_u32(in_s + (size_t)st * p.stage_floats) + (uint32_t)(((pl * H - tl.r0) * W + col0) * 4);
+                const uint32_t zr = smem_u32(zrow) + (uint32_t)(col0 * 4);
+                const uint32_t W4 = (uint32_t)W * 4u;
                 float *yp = nullptr;
                 float *osp = nullptr;
-                const float *gp = nullptr;
+                uint32_t gp = 0;
                 if (MODE == MODE_FWD) {
-                    if (STAGE_OUT) osp = os + (pl * p.oH - tl.d0) * oW + cg * VEC;
-                    else yp = p.out + (((size_t)tl.n * p.C + c) * p.oH) * oW + cg * VEC;
+                    if (STAGE_OUT) osp = os + (pl * p.oH - tl.d0 + dbeg) * oW + cg * VEC;
+                    else yp = p.out + (((size_t)tl.n * p.C + c) * p.oH + dbeg) * oW + cg * VEC;
                 } else {
-                    gp = in2_s + (size_t)st * p.stage2_floats + (pl * p.oH - tl.d0) * oW + cg * VEC;
+                    gp = smem_u32(in2_s + (size_t)st * p.stage2_floats) + (uint32_t)((((pl * p.oH - tl.d0 + dbeg) * oW) + cg * VEC) * 4);
                 }
-                auto compute = [&](int o, const float (&ra)[NV], const float (&rb)[NV], const float (&rc)[NV]) {
+                // one output row from the three window rows; advances the output / gy cursor by one row
+                auto compute = [&](const float (&ra)[NV], const float (&rb)[NV], const float (&rc)[NV]) {
                     if (MODE == MODE_FWD) {
                         float ov[VEC];
 #pragma unroll
@@ -501,13 +583,16 @@ fast_kernel(const FastParams p)
                         }
                         if (STAGE_OUT) {
 #pragma unroll
-                            for (int v = 0; v < VEC; ++v) osp[o * oW + v] = ov[v];
+                            for (int v = 0; v < VEC; ++v) osp[v] = ov[v];
+                            osp += oW;
                         } else {
-                            store_vec<VEC>(yp + (size_t)o * oW, ov);
+                            store_vec<VEC>(yp, ov);
+                            yp += oW;
                         }
                     } else {
                         float g[VEC];
-                        load_vec<VEC>(gp + o * oW, g);
+                        load_vec<VEC>(gp, g);
+                        gp += (uint32_t)oW * 4u;
 #pragma unroll
                         for (int v = 0; v < VEC; ++v) {
 #pragma unroll
@@ -521,31 +606,44 @@ fast_kernel(const FastParams p)
                     }
                 };
                 float r0[NV], r1[NV], r2[NV];
+                const int n_out = dend - dbeg;
                 if (S == 1) {
-                    // window rows (o-1, o, o+1); roles rotate so no register copies are needed
-                    load_row<S, VEC>(rowp(dbeg - 1), has_left, has_right, r0);
-                    load_row<S, VEC>(rowp(dbeg), has_left, has_right, r1);
-                    for (int o = dbeg; o < dend; o += 3) {
-                        load_row<S, VEC>(rowp(o + 1), has_left, has_right, r2);
-                        compute(o, r0, r1, r2);
-                        if (o + 1 >= dend) break;
-                        load_row<S, VEC>(rowp(o + 2), has_left, has_right, r0);
-                        compute(o + 1, r1, r2, r0);
-                        if (o + 2 >= dend) break;
-                        load_row<S, VEC>(rowp(o + 3), has_left, has_right, r1);
-                        compute(o + 2, r2, r0, r1);
+                    // window rows (o-1, o, o+1); roles rotate so no register copies are needed.  Only the
+                    // first row (above the plane) and the last one (below it) can be outside.
+                    uint32_t rp = row_base + (uint32_t)(dbeg - 1) * W4;
+                    load_row<S, VEC>(dbeg > 0 ? rp : zr, has_left, has_right, r0);
+                    rp += W4;
+                    load_row<S, VEC>(rp, has_left, has_right, r1);
+                    const bool bottom_out = dend >= H;   // row `dend` is below the plane
+                    for (int i = 0; i < n_out; i += 3) {
+                        rp += W4;
+                        load_row<S, VEC>((i + 1 == n_out && bottom_out) ? zr : rp, has_left, has_right, r2);
+                        compute(r0, r1, r2);
+                        if (i + 1 >= n_out) break;
+                        rp += W4;
+                        load_row<S, VEC>((i + 2 == n_out && bottom_out) ? zr : rp, has_left, has_right, r0);
+                        compute(r1, r2, r0);
+                        if (i + 2 >= n_out) break;
+                        rp += W4;
+                        load_row<S, VEC>((i + 3 == n_out && bottom_out) ? zr : rp, has_left, has_right, r1);
+                        compute(r2, r0, r1);
                     }
                 } else {
-                    // window rows (2o-1, 2o, 2o+1); the last row is the next window's first
-                    load_row<S, VEC>(rowp(dbeg * 2 - 1), has_left, has_right, r0);
-                    for (int o = dbeg; o < dend; o += 2) {
-                        load_row<S, VEC>(rowp(o * 2), has_left, has_right, r1);
-                        load_row<S, VEC>(rowp(o * 2 + 1), has_left, has_right, r2);
-                        compute(o, r0, r1, r2);
-                        if (o + 1 >= dend) break;
-                        load_row<S, VEC>(rowp(o * 2 + 2), has_left, has_right, r1);
-                        load_row<S, VEC>(rowp(o * 2 + 3), has_left, has_right, r0);
-                        compute(o + 1, r2, r1, r0);
+                    // window rows (2o-1, 2o, 2o+1); the last row is the next window's first.  Row 2o+1 of the
+                    // last output row is below the plane when H is odd.
+                    uint32_t rp = row_base + (uint32_t)(dbeg * 2 - 1) * W4;
+                    load_row<S, VEC>(dbeg > 0 ? rp : zr, has_left, has_right, r0);
+                    const bool bottom_out = 2 * dend - 1 >= H;
+                    for (int i = 0; i < n_out; i += 2) {
+                        load_row<S, VEC>(rp + W4, has_left, has_right, r1);
+                        rp += 2 * W4;
+                        load_row<S, VEC>((i + 1 == n_out && bottom_out) ? zr : rp, has_left, has_right, r2);
+                        compute(r0, r1, r2);
+                        if (i + 1 >= n_out) break;
+                        load_row<S, VEC>(rp + W4, has_left, has_right, r1);
+                        rp += 2 * W4;
+                        load_row<S, VEC>((i + 2 == n_out && bottom_out) ? zr : rp, has_left, has_right, r0);
+                        compute(r2, r1, r0);
                     }
                 }
             } else {
@@ -558,20 +656,20 @@ fast_kernel(const FastParams p)
                 const int oW = p.oW, oH = p.oH, W = p.W, H = p.H;
                 const int b0 = cg * VEC;
                 const bool has_right = b0 + VEC < oW;
-                const float *row_base = in_s + (size_t)st * p.stage_floats + (pl * oH - tl.r0) * oW + b0;
-                const float *zr = zrow + b0;
+                const uint32_t row_base = smem_u32(in_s + (size_t)st * p.stage_floats) + (uint32_t)(((pl * oH - tl.r0) * oW + b0) * 4);
+                const uint32_t zr = smem_u32(zrow) + (uint32_t)(b0 * 4);
                 float *xp = nullptr;
                 float *osp = nullptr;
                 if (STAGE_OUT) osp = os + pl * H * W + 2 * b0;
                 else xp = p.out + (((size_t)tl.n * p.C + c) * H) * W + 2 * b0;
                 auto load_g = [&](int a, float (&G)[VEC + 1]) {
-                    const float *r = (a < oH) ? row_base + a * oW : zr;
+                    const uint32_t r = (a < oH) ? row_base + (uint32_t)(a * oW * 4) : zr;
                     float tmp[VEC];
                     load_vec<VEC>(r, tmp);
 #pragma unroll
                     for (int v = 0; v < VEC; ++v) G[v] = tmp[v];
                     G[VEC] = 0.f;
-                    if (has_right) G[VEC] = r[VEC];
+                    if (has_right) G[VEC] = lds32(r + 4 * VEC);
                 };
                 auto emit = [&](int a, const float (&G0)[VEC + 1], const float (&G1)[VEC + 1]) {
                     float e[2 * VEC], o2[2 * VEC];
@@ -628,14 +726,20 @@ fast_kernel(const FastParams p)
                 bulk_s2g(dst, smem_u32(os), (uint32_t)(p.P * rows_o * cols_o * 4));
             }
             if (t + p.stages < T) {
-                const Tile nt = tile_of<MODE, S>(p, t_begin + t + p.stages);
+                const Tile nt = tile_of<MODE, S>(p, pre);
                 issue_tile<MODE, S>(p, nt, in_s + (size_t)st * p.stage_floats, in2_s + (size_t)st * p.stage2_floats,
                                     smem_u32(bars + st));
+                cursor_next(p, pre);
             }
+        }
+        cursor_next(p, cur);
+        if (++st == p.stages) {
+            st = 0;
+            phase ^= 1u;
         }
     }
     if (STAGE_OUT && tid == 0) bulk_wait_read0();  // shared memory must outlive the last store's reads
-    if (MODE == MODE_WGRAD && cur_g >= 0) wgrad_flush(p, acc, red, flag, active, per_plane, cur_g, g_first, TT);
+    if (MODE == MODE_WGRAD && cur_g >= 0) wgrad_flush(p, acc, red, flag, active, per_plane, cur_g, g_first);
 }
 
 // ---------------------------------------------------------------------------
@@ -825,8 +929,9 @@ static Plan make_plan(int mode, int N, int C, int H, int W, int oH, int oW, int 
     if (mode == MODE_WGRAD && C / pl.P > kMaxGroups) return pl;
     pl.mode = mode;
     pl.tiles = (long long)(C / pl.P) * N * pl.bands;
+    if (pl.tiles >= (1LL << 30)) return pl;
     pl.tiles_per_group = N * pl.bands;
-    pl.stages = g_tuning.stages > 0 ? g_tuning.stages : 3;
+    pl.stages = g_tuning.stages > 0 ? g_tuning.stages : 4;
     const size_t fixed = (size_t)2 * pl.out_floats * 4 + (size_t)round_up(in_cols + 8, 32) * 4 + 64 +
                          ((mode == MODE_WGRAD) ? (size_t)pl.items * 10 * 4 : 0);
     const size_t per_stage = (size_t)(pl.stage_floats + pl.stage2_floats) * 4 + 8;
@@ -912,6 +1017,8 @@ static int launch_fast(FastParams &fp, const Plan &pl, cudaStream_t stream, cons
     FastKernel kern = pick_kernel(pl);
     if (!kern) return fail("dwconv: no kernel for VEC=%d", pl.VEC);
     fp.maxseg = pl.maxseg;
+    fp.tiles_base = (int)(pl.tiles / pl.grid);
+    fp.tiles_rem = (int)(pl.tiles % pl.grid);
     void *args[] = {(void *)&fp};
     CUNN_CUDA(cudaLaunchKernel((const void *)kern, dim3(pl.grid), dim3(pl.threads), args, pl.smem, stream));
     (void)name;
