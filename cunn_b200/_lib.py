@@ -35,6 +35,12 @@ _decl("cunn_b200_dwconv_acc_grad_workspace", c_size_t, _CONV)
 _decl("cunn_b200_dwconv_acc_grad", c_int, [c_void_p] * 4 + _CONV + [c_float, c_void_p, c_size_t, c_void_p])
 _decl("cunn_b200_dwconv_acc_grad_static", c_int, [c_void_p] * 4 + _CONV + [c_float, c_void_p])
 _decl("cunn_b200_dwconv_acc_grad_static_capacity", c_size_t, [])
+_decl("cunn_b200_maxpool_out_size", c_int, [c_int] * 6)
+_decl("cunn_b200_maxpool_forward", c_int, [c_void_p] * 3 + [c_int] * 13 + [c_void_p])
+_decl("cunn_b200_maxpool_backward", c_int, [c_void_p] * 3 + [c_int] * 13 + [c_void_p])
+_decl("cunn_b200_batchnorm_workspace", c_size_t, [c_int, c_int])
+_decl("cunn_b200_batchnorm_forward", c_int, [c_void_p] * 8 + [c_int] * 4 + [c_double, c_double, c_void_p, c_size_t, c_void_p])
+_decl("cunn_b200_batchnorm_backward", c_int, [c_void_p] * 10 + [c_int] * 4 + [c_double, c_double, c_void_p, c_size_t, c_void_p])
 _decl("cunn_b200_dwconv_tuning", None, [ctypes.POINTER(c_int), c_int])
 _decl("cunn_b200_dwconv_describe_plan", c_int, [c_int] * 6 + [ctypes.c_char_p, c_int])
 

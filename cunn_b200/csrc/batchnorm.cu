@@ -1,0 +1,376 @@
+// Batch normalisation over [N, C, S] (S = H*W) for sm_100a: forward (training and inference) and backward.
+//
+// The reference runs one 512-thread CTA per channel, which leaves most of a 148-SM GPU idle when C is
+// small and reads the input three times.  Here every pass is spread over (channel x chunk) CTAs:
+//   * statistics: each CTA reduces a contiguous run of planes of one channel with 16-byte loads.  Sums
+//     are taken of (x - K) and (x - K)^2 with K the first element of the chunk, which keeps fp32
+//     accumulation accurate even when |mean| >> std; chunks are merged in fp64 (Chan's formula) by a
+//     small second kernel that also writes save_mean / save_std and updates the running statistics;
+//   * normalisation / gradient: one grid-stride pass with 16-byte loads and stores.
+// Formulas (lib/THCUNN/BatchNormalization.cu:141-283): save_std holds 1/sqrt(biased var + eps) (0 when
+// var == 0 and eps == 0), running_var is updated with the unbiased variance n/(n-1).
+#include "common.cuh"
+
+#include <algorithm>
+
+namespace cunn {
+namespace bn {
+
+struct ChunkStat {
+    float k;      // shift
+    float s1;     // sum (x - k)
+    float s2;     // sum (x - k)^2
+    float n;      // element count
+};
+
+__device__ __forceinline__ float block_sum(float v, float *sh)
+{
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    float r = 0.f;
+    if (warp == 0) {
+        r = (lane < (int)(blockDim.x >> 5)) ? sh[lane] : 0.f;
+        r = warp_sum(r);
+        if (lane == 0) sh[0] = r;
+    }
+    __syncthreads();
+    return sh[0];
+}
+
+// Planes of channel c: image n at x + (n*C + c)*S.  Chunk j of `chunks` covers images [n0, n1).
+__device__ __forceinline__ void chunk_range(int N, int chunks, int j, int *n0, int *n1)
+{
+    const int per = N / chunks, extra = N % chunks;
+    *n0 = j * per + min(j, extra);
+    *n1 = *n0 + per + (j < extra ? 1 : 0);
+}
+
+// grid = C * chunks.  One partial statistic per CTA.
+__global__ void __launch_bounds__(256)
+stats_kernel(const float *__restrict__ x, ChunkStat *__restrict__ part, int N, int C, int S, int chunks)
+{
+    __shared__ float sh[8];
+    const int c = blockIdx.x / chunks, j = blockIdx.x % chunks;
+    int n0, n1;
+    chunk_range(N, chunks, j, &n0, &n1);
+    if (n0 >= n1) {
+        if (threadIdx.x == 0) part[blockIdx.x] = ChunkStat{0.f, 0.f, 0.f, 0.f};
+        return;
+    }
+    const float k = __ldg(x + ((size_t)n0 * C + c) * S);
+    float s1 = 0.f, s2 = 0.f;
+    const bool vec = (S % 4 == 0) && (((uintptr_t)x & 15) == 0);
+    for (int n = n0; n < n1; ++n) {
+        const float *p = x + ((size_t)n * C + c) * S;
+        if (vec) {
+            const float4 *p4 = reinterpret_cast<const float4 *>(p);
+#pragma unroll 4
+            for (int i = threadIdx.x; i < S / 4; i += blockDim.x) {
+                const float4 v = __ldg(p4 + i);
+                const float a = v.x - k, b = v.y - k, d = v.z - k, e = v.w - k;
+                s1 += (a + b) + (d + e);
+                s2 = fmaf(a, a, s2); s2 = fmaf(b, b, s2); s2 = fmaf(d, d, s2); s2 = fmaf(e, e, s2);
+            }
+        } else {
+            for (int i = threadIdx.x; i < S; i += blockDim.x) {
+                const float a = __ldg(p + i) - k;
+                s1 += a;
+                s2 = fmaf(a, a, s2);
+            }
+        }
+    }
+    s1 = block_sum(s1, sh);
+    s2 = block_sum(s2, sh);
+    if (threadIdx.x == 0) part[blockIdx.x] = ChunkStat{k, s1, s2, (float)((long long)(n1 - n0) * S)};
+}
+
+// One thread per channel: merge the chunk statistics in fp64, publish mean / inverse std, update
+// the running statistics.
+__global__ void __launch_bounds__(128)
+stats_finish_kernel(const ChunkStat *__restrict__ part, int C, int chunks, float *__restrict__ running_mean,
+                    float *__restrict__ running_var, float *__restrict__ save_mean, float *__restrict__ save_std,
+                    double momentum, double eps)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    double n = 0.0, mean = 0.0, m2 = 0.0;
+    for (int j = 0; j < chunks; ++j) {
+        const ChunkStat p = part[c * chunks + j];
+        if (p.n <= 0.f) continue;
+        const double nb = p.n;
+        const double mb = (double)p.k + (double)p.s1 / nb;
+        const double m2b = (double)p.s2 - (double)p.s1 * (double)p.s1 / nb;
+        const double delta = mb - mean, nt = n + nb;
+        mean += delta * nb / nt;
+        m2 += m2b + delta * delta * n * nb / nt;
+        n = nt;
+    }
+    if (m2 < 0.0) m2 = 0.0;
+    // The reference computes in float for float tensors; follow its formulas on the float-rounded mean.
+    const float meanf = (float)mean;
+    const float varN = (float)m2;
+    float invstd = 0.f;
+    if (varN != 0.f || (float)eps != 0.f) invstd = 1.f / sqrtf((float)(m2 / n) + (float)eps);
+    const float unbiased = (float)(m2 / (n - 1.0));
+    save_mean[c] = meanf;
+    save_std[c] = invstd;
+    running_mean[c] = (float)((1.0 - momentum) * (double)running_mean[c] + momentum * (double)meanf);
+    running_var[c] = (float)((1.0 - momentum) * (double)running_var[c] + momentum * (double)unbiased);
+}
+
+// y = gamma * (x - mean) * invstd + beta, per plane.  Training reads mean / invstd from save_*, inference
+// derives them from the running statistics.
+__global__ void __launch_bounds__(256)
+apply_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__restrict__ weight,
+             const float *__restrict__ bias, const float *__restrict__ mean_v, const float *__restrict__ std_or_var,
+             int train, float eps, int C, int S, long long planes)
+{
+    const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)y) & 15) == 0);
+    // a CTA walks planes; threads walk the plane
+    for (long long pl = blockIdx.x; pl < planes; pl += gridDim.x) {
+        const int c = (int)(pl % C);
+        const float mean = __ldg(mean_v + c);
+        const float invstd = train ? __ldg(std_or_var + c) : 1.f / sqrtf(__ldg(std_or_var + c) + eps);
+        const float g = weight ? __ldg(weight + c) : 1.f;
+        const float b = bias ? __ldg(bias + c) : 0.f;
+        const float *xp = x + pl * S;
+        float *yp = y + pl * S;
+        if (vec) {
+            const float4 *x4 = reinterpret_cast<const float4 *>(xp);
+            float4 *y4 = reinterpret_cast<float4 *>(yp);
+#pragma unroll 4
+            for (int i = threadIdx.x; i < S / 4; i += blockDim.x) {
+                const float4 v = __ldg(x4 + i);
+                float4 o;
+                o.x = g * (v.x - mean) * invstd + b;
+                o.y = g * (v.y - mean) * invstd + b;
+                o.z = g * (v.z - mean) * invstd + b;
+                o.w = g * (v.w - mean) * invstd + b;
+                y4[i] = o;
+            }
+        } else {
+            for (int i = threadIdx.x; i < S; i += blockDim.x) yp[i] = g * (__ldg(xp + i) - mean) * invstd + b;
+        }
+    }
+}
+
+// Backward, pass 1: per (channel, chunk) sums of gy and gy * (x - mean).
+__global__ void __launch_bounds__(256)
+grad_stats_kernel(const float *__restrict__ x, const float *__restrict__ gy, float2 *__restrict__ part,
+                  const float *__restrict__ mean_v, int N, int C, int S, int chunks)
+{
+    __shared__ float sh[8];
+    const int c = blockIdx.x / chunks, j = blockIdx.x % chunks;
+    int n0, n1;
+    chunk_range(N, chunks, j, &n0, &n1);
+    const float mean = __ldg(mean_v + c);
+    float s = 0.f, d = 0.f;
+    const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)gy) & 15) == 0);
+    for (int n = n0; n < n1; ++n) {
+        const size_t off = ((size_t)n * C + c) * S;
+        if (vec) {
+            const float4 *x4 = reinterpret_cast<const float4 *>(x + off);
+            const float4 *g4 = reinterpret_cast<const float4 *>(gy + off);
+#pragma unroll 4
+            for (int i = threadIdx.x; i < S / 4; i += blockDim.x) {
+                const float4 v = __ldg(x4 + i), g = __ldg(g4 + i);
+                s += (g.x + g.y) + (g.z + g.w);
+                d = fmaf(g.x, v.x - mean, d); d = fmaf(g.y, v.y - mean, d);
+                d = fmaf(g.z, v.z - mean, d); d = fmaf(g.w, v.w - mean, d);
+            }
+        } else {
+            for (int i = threadIdx.x; i < S; i += blockDim.x) {
+                const float g = __ldg(gy + off + i);
+                s += g;
+                d = fmaf(g, __ldg(x + off + i) - mean, d);
+            }
+        }
+    }
+    s = block_sum(s, sh);
+    d = block_sum(d, sh);
+    if (threadIdx.x == 0) part[blockIdx.x] = make_float2(s, d);
+}
+
+// Backward, pass 2 (one thread per channel): total the chunk sums in fp64, accumulate gradWeight /
+// gradBias, and publish the three per-channel coefficients of the input gradient:
+//   gx = (gy - (x - mean) * proj - gmean) * gscale      (training)
+//   gx = gy * gscale                                     (inference)
+struct GradCoef {
+    float mean, proj, gmean, gscale;
+};
+
+__global__ void __launch_bounds__(128)
+grad_finish_kernel(const float2 *__restrict__ part, int C, int chunks, long long count,
+                   const float *__restrict__ weight, const float *__restrict__ mean_v,
+                   const float *__restrict__ std_or_var, int train, double eps, double scale,
+                   float *__restrict__ grad_weight, float *__restrict__ grad_bias, GradCoef *__restrict__ coef)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    double s = 0.0, d = 0.0;
+    for (int j = 0; j < chunks; ++j) {
+        const float2 p = part[c * chunks + j];
+        s += (double)p.x;
+        d += (double)p.y;
+    }
+    const float mean = mean_v[c];
+    const float stdv = train ? std_or_var[c] : (float)(1.0 / sqrt((double)std_or_var[c] + eps));
+    const float w = weight ? weight[c] : 1.f;
+    const double norm = 1.0 / (double)count;
+    GradCoef k;
+    k.mean = mean;
+    k.gmean = (float)(s * norm);
+    k.proj = (float)(d * norm * (double)stdv * (double)stdv);
+    k.gscale = stdv * w;
+    coef[c] = k;
+    if (grad_weight) grad_weight[c] = (float)((double)grad_weight[c] + scale * d * (double)stdv);
+    if (grad_bias) grad_bias[c] = (float)((double)grad_bias[c] + scale * s);
+}
+
+// Backward, pass 3: the input gradient.
+__global__ void __launch_bounds__(256)
+grad_apply_kernel(const float *__restrict__ x, const float *__restrict__ gy, float *__restrict__ gx,
+                  const GradCoef *__restrict__ coef, int train, int C, int S, long long planes)
+{
+    const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)gy | (uintptr_t)gx) & 15) == 0);
+    for (long long pl = blockIdx.x; pl < planes; pl += gridDim.x) {
+        const GradCoef k = coef[pl % C];
+        const float *xp = x + pl * S;
+        const float *gp = gy + pl * S;
+        float *op = gx + pl * S;
+        if (vec) {
+            const float4 *x4 = reinterpret_cast<const float4 *>(xp);
+            const float4 *g4 = reinterpret_cast<const float4 *>(gp);
+            float4 *o4 = reinterpret_cast<float4 *>(op);
+#pragma unroll 4
+            for (int i = threadIdx.x; i < S / 4; i += blockDim.x) {
+                const float4 g = __ldg(g4 + i);
+                float4 o;
+                if (train) {
+                    const float4 v = __ldg(x4 + i);
+                    o.x = (g.x - (v.x - k.mean) * k.proj - k.gmean) * k.gscale;
+                    o.y = (g.y - (v.y - k.mean) * k.proj - k.gmean) * k.gscale;
+                    o.z = (g.z - (v.z - k.mean) * k.proj - k.gmean) * k.gscale;
+                    o.w = (g.w - (v.w - k.mean) * k.proj - k.gmean) * k.gscale;
+                } else {
+                    o.x = g.x * k.gscale; o.y = g.y * k.gscale; o.z = g.z * k.gscale; o.w = g.w * k.gscale;
+                }
+                o4[i] = o;
+            }
+        } else {
+            for (int i = threadIdx.x; i < S; i += blockDim.x) {
+                const float g = __ldg(gp + i);
+                op[i] = train ? (g - (__ldg(xp + i) - k.mean) * k.proj - k.gmean) * k.gscale : g * k.gscale;
+            }
+        }
+    }
+}
+
+// Chunks per channel so that C * chunks CTAs fill the GPU a few times over, at most one chunk per image.
+static int pick_chunks(int N, int C)
+{
+    const int want = ceil_div(sm_count() * 8, C);
+    return std::max(1, std::min(N, want));
+}
+
+static int plane_grid(long long planes)
+{
+    const long long cap = (long long)sm_count() * 16;
+    return (int)std::max(1LL, std::min(planes, cap));
+}
+
+}  // namespace bn
+}  // namespace cunn
+
+using namespace cunn;
+using namespace cunn::bn;
+
+extern "C" CUNN_API size_t cunn_b200_batchnorm_workspace(int N, int C)
+{
+    if (N <= 0 || C <= 0) return 0;
+    const size_t chunks = (size_t)pick_chunks(N, C);
+    return (size_t)C * chunks * sizeof(ChunkStat) + (size_t)C * sizeof(GradCoef) + 256;
+}
+
+extern "C" CUNN_API int cunn_b200_batchnorm_forward(const float *x, float *y, const float *weight, const float *bias,
+                                                    float *running_mean, float *running_var, float *save_mean,
+                                                    float *save_std, int N, int C, int S, int train, double momentum,
+                                                    double eps, void *workspace, size_t workspace_bytes,
+                                                    cunn_stream_t stream_)
+{
+    clear_error();
+    cudaStream_t stream = (cudaStream_t)stream_;
+    CUNN_CHECK_ARG(N >= 0 && C > 0 && S > 0, "bad batch-norm sizes N=%d C=%d S=%d", N, C, S);
+    CUNN_CHECK_ARG((long long)N * C * (long long)S < (1LL << 31), "tensors of 2^31 or more elements are not supported");
+    if (N == 0) return 0;
+    CUNN_CHECK_ARG(x && y && running_mean && running_var, "null tensor pointer");
+    const long long planes = (long long)N * C;
+    if (train) {
+        CUNN_CHECK_ARG(save_mean && save_std, "training-mode batch norm needs save_mean and save_std");
+        const int chunks = pick_chunks(N, C);
+        const size_t need = (size_t)C * chunks * sizeof(ChunkStat);
+        CUNN_CHECK_ARG(workspace && workspace_bytes >= need && ((uintptr_t)workspace & 15) == 0,
+                       "batch norm needs %zu bytes of 16-byte aligned workspace, got %zu", need,
+                       workspace ? workspace_bytes : (size_t)0);
+        ChunkStat *part = (ChunkStat *)workspace;
+        stats_kernel<<<C * chunks, 256, 0, stream>>>(x, part, N, C, S, chunks);
+        CUNN_LAUNCH_CHECK("batch norm statistics");
+        stats_finish_kernel<<<ceil_div(C, 128), 128, 0, stream>>>(part, C, chunks, running_mean, running_var, save_mean,
+                                                                 save_std, momentum, eps);
+        CUNN_LAUNCH_CHECK("batch norm statistics finish");
+        apply_kernel<<<plane_grid(planes), 256, 0, stream>>>(x, y, weight, bias, save_mean, save_std, 1, (float)eps, C, S,
+                                                            planes);
+    } else {
+        apply_kernel<<<plane_grid(planes), 256, 0, stream>>>(x, y, weight, bias, running_mean, running_var, 0, (float)eps,
+                                                            C, S, planes);
+    }
+    CUNN_LAUNCH_CHECK("batch norm apply");
+    return 0;
+}
+
+extern "C" CUNN_API int cunn_b200_batchnorm_backward(const float *x, const float *gy, float *gx, float *grad_weight,
+                                                     float *grad_bias, const float *weight, const float *running_mean,
+                                                     const float *running_var, const float *save_mean,
+                                                     const float *save_std, int N, int C, int S, int train, double scale,
+                                                     double eps, void *workspace, size_t workspace_bytes,
+                                                     cunn_stream_t stream_)
+{
+    clear_error();
+    cudaStream_t stream = (cudaStream_t)stream_;
+    CUNN_CHECK_ARG(N >= 0 && C > 0 && S > 0, "bad batch-norm sizes N=%d C=%d S=%d", N, C, S);
+    CUNN_CHECK_ARG((long long)N * C * (long long)S < (1LL << 31), "tensors of 2^31 or more elements are not supported");
+    if (N == 0) return 0;
+    CUNN_CHECK_ARG(x && gy, "null tensor pointer");
+    CUNN_CHECK_ARG(train ? (save_mean && save_std) : (running_mean && running_var),
+                   "batch norm backward needs %s", train ? "save_mean and save_std" : "running_mean and running_var");
+    const int chunks = pick_chunks(N, C);
+    const size_t part_bytes = ((size_t)C * chunks * sizeof(ChunkStat) + 255) & ~(size_t)255;
+    const size_t need = part_bytes + (size_t)C * sizeof(GradCoef);
+    CUNN_CHECK_ARG(workspace && workspace_bytes >= need && ((uintptr_t)workspace & 15) == 0,
+                   "batch norm backward needs %zu bytes of 16-byte aligned workspace, got %zu", need,
+                   workspace ? workspace_bytes : (size_t)0);
+    float2 *part = (float2 *)workspace;
+    GradCoef *coef = (GradCoef *)((char *)workspace + part_bytes);
+    const float *mean_v = train ? save_mean : running_mean;
+    const float *sv = train ? save_std : running_var;
+    const long long planes = (long long)N * C;
+    // inference-mode input gradient needs no sums; they are still required for gradWeight / gradBias
+    const bool need_sums = train || grad_weight || grad_bias;
+    if (need_sums) {
+        grad_stats_kernel<<<C * chunks, 256, 0, stream>>>(x, gy, part, mean_v, N, C, S, chunks);
+        CUNN_LAUNCH_CHECK("batch norm gradient sums");
+    } else {
+        CUNN_CUDA(cudaMemsetAsync(part, 0, (size_t)C * chunks * sizeof(float2), stream));
+    }
+    grad_finish_kernel<<<ceil_div(C, 128), 128, 0, stream>>>(part, C, chunks, (long long)N * S, weight, mean_v, sv, train,
+                                                            eps, scale, grad_weight, grad_bias, coef);
+    CUNN_LAUNCH_CHECK("batch norm gradient finish");
+    if (gx) {
+        grad_apply_kernel<<<plane_grid(planes), 256, 0, stream>>>(x, gy, gx, coef, train, C, S, planes);
+        CUNN_LAUNCH_CHECK("batch norm input gradient");
+    }
+    return 0;
+}

@@ -76,3 +76,72 @@ def dwconv_acc_grad(x, gy, grad_weight, grad_bias, dH, dW, padH, padW, scale=1.0
                                         dH, dW, padH, padW, scale, _ptr(ws), ws.numel() if ws is not None else 0,
                                         _stream()))
     return grad_weight, grad_bias
+
+
+def maxpool_out_size(size, k, d, pad, ceil_mode, dil=1):
+    return lib.cunn_b200_maxpool_out_size(size, k, d, pad, dil, int(ceil_mode))
+
+
+def maxpool_forward(x, kH, kW, dH, dW, padH, padW, ceil_mode=False, out=None, indices=None):
+    _chk(x)
+    N, C, H, W = x.shape
+    oH = max(maxpool_out_size(H, kH, dH, padH, ceil_mode), 0) if dH > 0 and kH > 0 else 0
+    oW = max(maxpool_out_size(W, kW, dW, padW, ceil_mode), 0) if dW > 0 and kW > 0 else 0
+    if out is None:
+        out = torch.empty((N, C, oH, oW), dtype=torch.float32, device=x.device)
+    if indices is None:
+        indices = torch.empty((N, C, oH, oW), dtype=torch.int64, device=x.device)
+    check(lib.cunn_b200_maxpool_forward(_ptr(x), _ptr(out), _ptr(indices), N, C, H, W, kH, kW, dH, dW, padH, padW,
+                                        1, 1, int(ceil_mode), _stream()))
+    return out, indices
+
+
+def maxpool_backward(gy, indices, H, W, kH, kW, dH, dW, padH, padW, ceil_mode=False, out=None):
+    _chk(gy, indices)
+    N, C = gy.shape[:2]
+    if out is None:
+        out = torch.empty((N, C, H, W), dtype=torch.float32, device=gy.device)
+    check(lib.cunn_b200_maxpool_backward(_ptr(gy), _ptr(indices), _ptr(out), N, C, H, W, kH, kW, dH, dW, padH, padW,
+                                         1, 1, int(ceil_mode), _stream()))
+    return out
+
+
+def _bn_dims(x):
+    N, C = x.shape[0], x.shape[1]
+    S = 1
+    for d in x.shape[2:]:
+        S *= d
+    return N, C, S
+
+
+def batchnorm_forward(x, weight, bias, running_mean, running_var, train, momentum=0.1, eps=1e-5, out=None,
+                      save_mean=None, save_std=None):
+    """Updates running_mean / running_var in place when train; returns (y, save_mean, save_std)."""
+    _chk(x, weight, bias, running_mean, running_var)
+    N, C, S = _bn_dims(x)
+    if out is None:
+        out = torch.empty_like(x)
+    if save_mean is None:
+        save_mean = torch.empty(C, dtype=torch.float32, device=x.device)
+    if save_std is None:
+        save_std = torch.empty(C, dtype=torch.float32, device=x.device)
+    ws = workspace(lib.cunn_b200_batchnorm_workspace(N, C), x.device)
+    check(lib.cunn_b200_batchnorm_forward(_ptr(x), _ptr(out), _ptr(weight), _ptr(bias), _ptr(running_mean),
+                                          _ptr(running_var), _ptr(save_mean), _ptr(save_std), N, C, S, int(train),
+                                          momentum, eps, _ptr(ws), ws.numel(), _stream()))
+    return out, save_mean, save_std
+
+
+def batchnorm_backward(x, gy, weight, running_mean, running_var, save_mean, save_std, train, scale=1.0, eps=1e-5,
+                       grad_weight=None, grad_bias=None, want_gx=True, out=None):
+    """Accumulates into grad_weight / grad_bias in place (each may be None); returns gx or None."""
+    _chk(x, gy, weight, grad_weight, grad_bias)
+    N, C, S = _bn_dims(x)
+    if want_gx and out is None:
+        out = torch.empty_like(x)
+    ws = workspace(lib.cunn_b200_batchnorm_workspace(N, C), x.device)
+    check(lib.cunn_b200_batchnorm_backward(_ptr(x), _ptr(gy), _ptr(out) if want_gx else None, _ptr(grad_weight),
+                                           _ptr(grad_bias), _ptr(weight), _ptr(running_mean), _ptr(running_var),
+                                           _ptr(save_mean), _ptr(save_std), N, C, S, int(train), scale, eps,
+                                           _ptr(ws), ws.numel(), _stream()))
+    return out if want_gx else None

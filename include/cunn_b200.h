@@ -91,6 +91,52 @@ CUNN_API int cunn_b200_dwconv_acc_grad_static(const float *x, const float *gy, f
                                               cunn_stream_t stream);
 CUNN_API size_t cunn_b200_dwconv_acc_grad_static_capacity(void);
 
+/* ---- SpatialMaxPooling --------------------------------------------------------
+ * x [N,C,H,W] -> y [N,C,oH,oW] and int64 indices of the same shape holding the flat position h*W + w of
+ * the maximum inside its plane plus CUNN_B200_INDEX_BASE.  The window is scanned row-major with a strict
+ * "greater than" from -FLT_MAX / index -1, as in the reference, so indices are reproducible bit for bit.
+ * oH, oW = cunn_b200_maxpool_out_size(...) (floor or ceil mode with the reference's fix-up that the last
+ * window must start inside the padded input).  Requires pad <= k/2.
+ * Replaces THNN_(SpatialMaxPooling_updateOutput) -> THNN_(SpatialDilatedMaxPooling_updateOutput)
+ * (lib/THCUNN/generic/SpatialMaxPooling.cu:7-21, generic/SpatialDilatedMaxPooling.cu:84-158; kernel
+ * lib/THCUNN/SpatialDilatedMaxPooling.cu:8-42). */
+CUNN_API int cunn_b200_maxpool_out_size(int in, int k, int d, int pad, int dil, int ceil_mode);
+CUNN_API int cunn_b200_maxpool_forward(const float *x, float *y, int64_t *indices, int N, int C, int H, int W,
+                                       int kH, int kW, int dH, int dW, int padH, int padW, int dilH, int dilW,
+                                       int ceil_mode, cunn_stream_t stream);
+
+/* gx [N,C,H,W]: every input pixel receives the sum of gy over the outputs whose index names it (gather
+ * form, deterministic).  Replaces THNN_(SpatialMaxPooling_updateGradInput)
+ * (lib/THCUNN/generic/SpatialMaxPooling.cu:23-38, generic/SpatialDilatedMaxPooling.cu:160-235; kernel
+ * lib/THCUNN/SpatialDilatedMaxPooling.cu:46-80). */
+CUNN_API int cunn_b200_maxpool_backward(const float *gy, const int64_t *indices, float *gx, int N, int C, int H, int W,
+                                        int kH, int kW, int dH, int dW, int padH, int padW, int dilH, int dilW,
+                                        int ceil_mode, cunn_stream_t stream);
+
+/* ---- BatchNormalization over [N, C, S] (S = product of the trailing dimensions) ----------------
+ * Training (train != 0): per-channel batch mean and biased variance; y = gamma (x - mean) invstd + beta;
+ * save_mean = mean, save_std = invstd = 1/sqrt(var + eps); running_mean/var updated with `momentum`,
+ * running_var from the UNBIASED variance.  Inference: uses the running statistics and leaves them alone.
+ * weight / bias may be NULL (gamma = 1, beta = 0).  `workspace`: caller-owned scratch of at least
+ * cunn_b200_batchnorm_workspace(N, C) bytes, 16-byte aligned, contents irrelevant.
+ * Replaces THNN_(BatchNormalization_updateOutput) (lib/THCUNN/generic/BatchNormalization.cu:34-66,
+ * kernels lib/THCUNN/BatchNormalization.cu:141-212). */
+CUNN_API size_t cunn_b200_batchnorm_workspace(int N, int C);
+CUNN_API int cunn_b200_batchnorm_forward(const float *x, float *y, const float *weight, const float *bias,
+                                         float *running_mean, float *running_var, float *save_mean, float *save_std,
+                                         int N, int C, int S, int train, double momentum, double eps,
+                                         void *workspace, size_t workspace_bytes, cunn_stream_t stream);
+
+/* Backward: gx (may be NULL), grad_weight += scale * sum gy (x - mean) invstd, grad_bias += scale * sum gy
+ * (either may be NULL).  Training mode uses save_mean / save_std, inference mode the running statistics.
+ * Replaces THNN_(BatchNormalization_backward) (lib/THCUNN/generic/BatchNormalization.cu:68-94, kernel
+ * lib/THCUNN/BatchNormalization.cu:215-283). */
+CUNN_API int cunn_b200_batchnorm_backward(const float *x, const float *gy, float *gx, float *grad_weight,
+                                          float *grad_bias, const float *weight, const float *running_mean,
+                                          const float *running_var, const float *save_mean, const float *save_std,
+                                          int N, int C, int S, int train, double scale, double eps,
+                                          void *workspace, size_t workspace_bytes, cunn_stream_t stream);
+
 /* Tuning hook for sweeps and tests: overrides the tile plan of the 3x3 fast path for the calling
  * thread.  values[0..count) = {planes_per_tile, rows_per_tile, rows_per_strip, stages, ctas_per_sm,
  * force_generic, stage_budget_kb, vec, staged_stores(-1 auto)}; 0 keeps the automatic choice, missing
