@@ -35,6 +35,10 @@ _decl("cunn_b200_dwconv_acc_grad_workspace", c_size_t, _CONV)
 _decl("cunn_b200_dwconv_acc_grad", c_int, [c_void_p] * 4 + _CONV + [c_float, c_void_p, c_size_t, c_void_p])
 _decl("cunn_b200_dwconv_acc_grad_static", c_int, [c_void_p] * 4 + _CONV + [c_float, c_void_p])
 _decl("cunn_b200_dwconv_acc_grad_static_capacity", c_size_t, [])
+_decl("cunn_b200_convmm_forward", c_int, [c_void_p] * 4 + _CONV + [c_void_p])
+_decl("cunn_b200_convmm_grad_input", c_int, [c_void_p] * 3 + _CONV + [c_void_p])
+_decl("cunn_b200_convmm_acc_grad_workspace", c_size_t, _CONV)
+_decl("cunn_b200_convmm_acc_grad", c_int, [c_void_p] * 4 + _CONV + [c_float, c_void_p, c_size_t, c_void_p])
 _decl("cunn_b200_maxpool_out_size", c_int, [c_int] * 6)
 _decl("cunn_b200_maxpool_forward", c_int, [c_void_p] * 3 + [c_int] * 13 + [c_void_p])
 _decl("cunn_b200_maxpool_backward", c_int, [c_void_p] * 3 + [c_int] * 13 + [c_void_p])

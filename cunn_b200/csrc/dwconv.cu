@@ -268,6 +268,60 @@ __device__ __forceinline__ void load_vec(uint32_t a, float (&g)[VEC])
     }
 }
 
+// The same two loaders on global memory (read-only path), for the variant that skips shared memory.
+template <int S, int VEC>
+__device__ __forceinline__ void load_row_g(const float *r, bool valid, bool has_left, bool has_right,
+                                           float (&v)[Win<S, VEC>::NV])
+{
+    constexpr int NV = Win<S, VEC>::NV;
+    if (!valid) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) v[i] = 0.f;
+        return;
+    }
+    v[0] = 0.f;
+    if (has_left) v[0] = __ldg(r - 1);
+    if (VEC == 4 && S == 1) {
+        const float4 q = __ldg(reinterpret_cast<const float4 *>(r));
+        v[1] = q.x; v[2] = q.y; v[3] = q.z; v[4] = q.w;
+        v[NV - 1] = 0.f;
+        if (has_right) v[NV - 1] = __ldg(r + 4);
+    } else if (VEC == 4 && S == 2) {
+        const float4 q0 = __ldg(reinterpret_cast<const float4 *>(r));
+        const float4 q1 = __ldg(reinterpret_cast<const float4 *>(r + 4));
+        v[1] = q0.x; v[2] = q0.y; v[3] = q0.z; v[4] = q0.w;
+        v[5] = q1.x; v[6] = q1.y; v[7] = q1.z; v[NV - 1] = q1.w;
+    } else if (VEC == 2 && S == 1) {
+        const float2 q = __ldg(reinterpret_cast<const float2 *>(r));
+        v[1] = q.x; v[2] = q.y;
+        v[NV - 1] = 0.f;
+        if (has_right) v[NV - 1] = __ldg(r + 2);
+    } else if (VEC == 2 && S == 2) {
+        const float4 q = __ldg(reinterpret_cast<const float4 *>(r));
+        v[1] = q.x; v[2] = q.y; v[3] = q.z; v[NV - 1] = q.w;
+    } else {
+#pragma unroll
+        for (int i = 1; i < NV - 1; ++i) v[i] = __ldg(r + i - 1);
+        v[NV - 1] = 0.f;
+        if (has_right) v[NV - 1] = __ldg(r + NV - 2);
+    }
+}
+
+template <int VEC>
+__device__ __forceinline__ void load_vec_g(const float *p, float (&g)[VEC])
+{
+    if (VEC == 4) {
+        const float4 q = __ldg(reinterpret_cast<const float4 *>(p));
+        g[0] = q.x; g[1] = q.y; g[2] = q.z; g[3] = q.w;
+    } else if (VEC == 2) {
+        const float2 q = __ldg(reinterpret_cast<const float2 *>(p));
+        g[0] = q.x; g[1] = q.y;
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) g[i] = __ldg(p + i);
+    }
+}
+
 template <int VEC>
 __device__ __forceinline__ void store_vec(float *p, const float (&o)[VEC])
 {
@@ -464,7 +518,9 @@ __device__ __forceinline__ void bulk_s2g(void *dst, uint32_t src_smem, uint32_t 
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-template <int MODE, int S, int VEC, bool STAGE_OUT>
+// DIRECT = true skips the shared-memory ring: rows are read straight from global memory through the
+// read-only path (L1 absorbs the halo re-reads) and nothing in the tile loop synchronises the CTA.
+template <int MODE, int S, int VEC, bool STAGE_OUT, bool DIRECT>
 __global__ void __launch_bounds__(256)
 fast_kernel(const FastParams p)
 {
@@ -489,13 +545,13 @@ fast_kernel(const FastParams p)
 
     const int tid = threadIdx.x;
     for (int i = tid; i < zlen; i += blockDim.x) zrow_base[i] = 0.f;
-    if (tid == 0) {
+    if (!DIRECT && tid == 0) {
         for (int s = 0; s < p.stages; ++s) mbar_init(smem_u32(bars + s), 1);
         mbar_fence_init();
     }
     __syncthreads();
     Cursor pre = cur;  // thread 0: cursor of the next tile to fetch
-    if (tid == 0) {
+    if (!DIRECT && tid == 0) {
         const int npre = min(T, p.stages);
         for (int i = 0; i < npre; ++i) {
             const Tile tl = tile_of<MODE, S>(p, pre);
@@ -542,7 +598,9 @@ fast_kernel(const FastParams p)
                 if (MODE == MODE_FWD && p.bias) bias = __ldg(p.bias + c);
             }
         }
-        if (!mbar_wait(smem_u32(bars + st), phase, p.status)) return;
+        if (!DIRECT) {
+            if (!mbar_wait(smem_u32(bars + st), phase, p.status)) return;
+        }
         const int dbeg = tl.d0 + strip * p.RS;
         const int dend = min(tl.d1, dbeg + p.RS);
         float *os = out_s + (size_t)(t & 1) * p.out_floats;
@@ -557,6 +615,16 @@ fast_kernel(const FastParams p)
                 const uint32_t row_base = smem_u32(in_s + (size_t)st * p.stage_floats) + (uint32_t)(((pl * H - tl.r0) * W + col0) * 4);
                 const uint32_t zr = smem_u32(zrow) + (uint32_t)(col0 * 4);
                 const uint32_t W4 = (uint32_t)W * 4u;
+                const float *gbase = nullptr;   // DIRECT: column col0 of row 0 of this thread's plane
+                const float *gyg = nullptr;     // DIRECT, WGRAD: this thread's gy columns of row dbeg
+                if (DIRECT) {
+                    gbase = p.in + (((size_t)tl.n * p.C + c) * H) * W + col0;
+                    if (MODE == MODE_WGRAD) gyg = p.in2 + (((size_t)tl.n * p.C + c) * p.oH + dbeg) * oW + cg * VEC;
+                }
+                auto ldrow = [&](int row, uint32_t saddr, float (&r)[NV]) {
+                    if (DIRECT) load_row_g<S, VEC>(gbase + (ptrdiff_t)row * W, (unsigned)row < (unsigned)H, has_left, has_right, r);
+                    else load_row<S, VEC>(saddr, has_left, has_right, r);
+                };
                 float *yp = nullptr;
                 float *osp = nullptr;
                 uint32_t gp = 0;
@@ -591,8 +659,13 @@ fast_kernel(const FastParams p)
                         }
                     } else {
                         float g[VEC];
-                        load_vec<VEC>(gp, g);
-                        gp += (uint32_t)oW * 4u;
+                        if (DIRECT) {
+                            load_vec_g<VEC>(gyg, g);
+                            gyg += oW;
+                        } else {
+                            load_vec<VEC>(gp, g);
+                            gp += (uint32_t)oW * 4u;
+                        }
 #pragma unroll
                         for (int v = 0; v < VEC; ++v) {
 #pragma unroll
@@ -611,38 +684,38 @@ fast_kernel(const FastParams p)
                     // window rows (o-1, o, o+1); roles rotate so no register copies are needed.  Only the
                     // first row (above the plane) and the last one (below it) can be outside.
                     uint32_t rp = row_base + (uint32_t)(dbeg - 1) * W4;
-                    load_row<S, VEC>(dbeg > 0 ? rp : zr, has_left, has_right, r0);
+                    ldrow(dbeg - 1, dbeg > 0 ? rp : zr, r0);
                     rp += W4;
-                    load_row<S, VEC>(rp, has_left, has_right, r1);
+                    ldrow(dbeg, rp, r1);
                     const bool bottom_out = dend >= H;   // row `dend` is below the plane
                     for (int i = 0; i < n_out; i += 3) {
                         rp += W4;
-                        load_row<S, VEC>((i + 1 == n_out && bottom_out) ? zr : rp, has_left, has_right, r2);
+                        ldrow(dbeg + i + 1, (i + 1 == n_out && bottom_out) ? zr : rp, r2);
                         compute(r0, r1, r2);
                         if (i + 1 >= n_out) break;
                         rp += W4;
-                        load_row<S, VEC>((i + 2 == n_out && bottom_out) ? zr : rp, has_left, has_right, r0);
+                        ldrow(dbeg + i + 2, (i + 2 == n_out && bottom_out) ? zr : rp, r0);
                         compute(r1, r2, r0);
                         if (i + 2 >= n_out) break;
                         rp += W4;
-                        load_row<S, VEC>((i + 3 == n_out && bottom_out) ? zr : rp, has_left, has_right, r1);
+                        ldrow(dbeg + i + 3, (i + 3 == n_out && bottom_out) ? zr : rp, r1);
                         compute(r2, r0, r1);
                     }
                 } else {
                     // window rows (2o-1, 2o, 2o+1); the last row is the next window's first.  Row 2o+1 of the
                     // last output row is below the plane when H is odd.
                     uint32_t rp = row_base + (uint32_t)(dbeg * 2 - 1) * W4;
-                    load_row<S, VEC>(dbeg > 0 ? rp : zr, has_left, has_right, r0);
+                    ldrow(dbeg * 2 - 1, dbeg > 0 ? rp : zr, r0);
                     const bool bottom_out = 2 * dend - 1 >= H;
                     for (int i = 0; i < n_out; i += 2) {
-                        load_row<S, VEC>(rp + W4, has_left, has_right, r1);
+                        ldrow((dbeg + i) * 2, rp + W4, r1);
                         rp += 2 * W4;
-                        load_row<S, VEC>((i + 1 == n_out && bottom_out) ? zr : rp, has_left, has_right, r2);
+                        ldrow((dbeg + i) * 2 + 1, (i + 1 == n_out && bottom_out) ? zr : rp, r2);
                         compute(r0, r1, r2);
                         if (i + 1 >= n_out) break;
-                        load_row<S, VEC>(rp + W4, has_left, has_right, r1);
+                        ldrow((dbeg + i) * 2 + 2, rp + W4, r1);
                         rp += 2 * W4;
-                        load_row<S, VEC>((i + 2 == n_out && bottom_out) ? zr : rp, has_left, has_right, r0);
+                        ldrow((dbeg + i) * 2 + 3, (i + 2 == n_out && bottom_out) ? zr : rp, r0);
                         compute(r2, r1, r0);
                     }
                 }
@@ -662,14 +735,28 @@ fast_kernel(const FastParams p)
                 float *osp = nullptr;
                 if (STAGE_OUT) osp = os + pl * H * W + 2 * b0;
                 else xp = p.out + (((size_t)tl.n * p.C + c) * H) * W + 2 * b0;
+                const float *gbase = DIRECT ? p.in + (((size_t)tl.n * p.C + c) * oH) * oW + b0 : nullptr;
                 auto load_g = [&](int a, float (&G)[VEC + 1]) {
-                    const uint32_t r = (a < oH) ? row_base + (uint32_t)(a * oW * 4) : zr;
                     float tmp[VEC];
-                    load_vec<VEC>(r, tmp);
+                    if (DIRECT) {
+                        if (a < oH) {
+                            const float *r = gbase + (ptrdiff_t)a * oW;
+                            load_vec_g<VEC>(r, tmp);
+                            G[VEC] = 0.f;
+                            if (has_right) G[VEC] = __ldg(r + VEC);
+                        } else {
+#pragma unroll
+                            for (int v = 0; v < VEC; ++v) tmp[v] = 0.f;
+                            G[VEC] = 0.f;
+                        }
+                    } else {
+                        const uint32_t r = (a < oH) ? row_base + (uint32_t)(a * oW * 4) : zr;
+                        load_vec<VEC>(r, tmp);
+                        G[VEC] = 0.f;
+                        if (has_right) G[VEC] = lds32(r + 4 * VEC);
+                    }
 #pragma unroll
                     for (int v = 0; v < VEC; ++v) G[v] = tmp[v];
-                    G[VEC] = 0.f;
-                    if (has_right) G[VEC] = lds32(r + 4 * VEC);
                 };
                 auto emit = [&](int a, const float (&G0)[VEC + 1], const float (&G1)[VEC + 1]) {
                     float e[2 * VEC], o2[2 * VEC];
@@ -717,8 +804,8 @@ fast_kernel(const FastParams p)
             fence_async_smem();               // make this thread's staged outputs visible to the TMA unit
             if (tid == 0) bulk_wait_read0();  // the store issued one tile ago has left its buffer
         }
-        __syncthreads();  // every thread is done with stage st (and with the output buffer)
-        if (tid == 0) {
+        if (!DIRECT) __syncthreads();  // every thread is done with stage st (and with the output buffer)
+        if (!DIRECT && tid == 0) {
             if (STAGE_OUT) {
                 const int rows_o = (MODE == MODE_DGRAD_S2) ? p.H : p.oH;
                 const int cols_o = (MODE == MODE_DGRAD_S2) ? p.W : p.oW;
@@ -749,7 +836,7 @@ fast_kernel(const FastParams p)
 static const int kMaxGroups = 16384;  // ticket counters in the parameter-gradient workspace
 
 struct Tuning {
-    int P = 0, R = 0, RS = 0, stages = 0, ctas_per_sm = 0, force_generic = 0, budget_kb = 0, vec = 0, stage_out = -1;
+    int P = 0, R = 0, RS = 0, stages = 0, ctas_per_sm = 0, force_generic = 0, budget_kb = 0, vec = 0, stage_out = -1, direct = -1;
 };
 static thread_local Tuning g_tuning;
 
@@ -757,6 +844,7 @@ struct Plan {
     bool ok = false;
     int S = 1, VEC = 1;
     bool stage_out = false;
+    bool direct = false;      // read rows straight from global memory instead of through the TMA ring
     int P = 1, bands = 1, R = 0, RS = 0, strips = 0, CG = 0, items = 0, threads = 0, stages = 0, grid = 1, maxseg = 1;
     int stage_floats = 0, stage2_floats = 0, out_floats = 0;
     size_t smem = 0;
@@ -901,6 +989,7 @@ static Plan make_plan(int mode, int N, int C, int H, int W, int oH, int oW, int 
     }
     if (bestVEC <= 0 || bestP <= 0 || bestRS <= 0 || bestR <= 0) return pl;
     if (C % bestP) return pl;
+    const bool direct_ok = (mode == MODE_DGRAD_S2) ? bestVEC == 2 : bestVEC == 4;
     pl.VEC = bestVEC;
     pl.CG = oW / pl.VEC;
     pl.P = bestP;
@@ -932,6 +1021,11 @@ static Plan make_plan(int mode, int N, int C, int H, int W, int oH, int oW, int 
     if (pl.tiles >= (1LL << 30)) return pl;
     pl.tiles_per_group = N * pl.bands;
     pl.stages = g_tuning.stages > 0 ? g_tuning.stages : 4;
+    pl.direct = direct_ok && !pl.stage_out && (g_tuning.direct >= 0 ? g_tuning.direct != 0 : false);
+    if (pl.direct) {
+        pl.stages = 0;
+        pl.stage_floats = pl.stage2_floats = pl.out_floats = 0;
+    }
     const size_t fixed = (size_t)2 * pl.out_floats * 4 + (size_t)round_up(in_cols + 8, 32) * 4 + 64 +
                          ((mode == MODE_WGRAD) ? (size_t)pl.items * 10 * 4 : 0);
     const size_t per_stage = (size_t)(pl.stage_floats + pl.stage2_floats) * 4 + 8;
@@ -946,23 +1040,25 @@ static bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 typedef void (*FastKernel)(const FastParams);
 
 template <int MODE, int S>
-static FastKernel pick_kernel_s(int VEC, bool staged)
+static FastKernel pick_kernel_s(int VEC, bool staged, bool direct)
 {
     constexpr bool kCanStage = MODE != MODE_WGRAD;
+    constexpr int kDirectVec = (MODE == MODE_DGRAD_S2) ? 2 : 4;
+    if (direct) return VEC == kDirectVec ? (FastKernel)fast_kernel<MODE, S, kDirectVec, false, true> : nullptr;
     if (kCanStage && staged) {
         switch (VEC) {
-            case 7: return fast_kernel<MODE, S, 7, kCanStage>;
-            case 2: return fast_kernel<MODE, S, 2, kCanStage>;
-            case 1: return fast_kernel<MODE, S, 1, kCanStage>;
-            case 4: return MODE == MODE_DGRAD_S2 ? nullptr : (FastKernel)fast_kernel<MODE, S, (MODE == MODE_DGRAD_S2 ? 2 : 4), kCanStage>;
+            case 7: return fast_kernel<MODE, S, 7, kCanStage, false>;
+            case 2: return fast_kernel<MODE, S, 2, kCanStage, false>;
+            case 1: return fast_kernel<MODE, S, 1, kCanStage, false>;
+            case 4: return MODE == MODE_DGRAD_S2 ? nullptr : (FastKernel)fast_kernel<MODE, S, kDirectVec, kCanStage, false>;
             default: return nullptr;
         }
     }
     switch (VEC) {
-        case 7: return fast_kernel<MODE, S, 7, false>;
-        case 2: return fast_kernel<MODE, S, 2, false>;
-        case 1: return fast_kernel<MODE, S, 1, false>;
-        case 4: return MODE == MODE_DGRAD_S2 ? nullptr : (FastKernel)fast_kernel<MODE, S, (MODE == MODE_DGRAD_S2 ? 2 : 4), false>;
+        case 7: return fast_kernel<MODE, S, 7, false, false>;
+        case 2: return fast_kernel<MODE, S, 2, false, false>;
+        case 1: return fast_kernel<MODE, S, 1, false, false>;
+        case 4: return MODE == MODE_DGRAD_S2 ? nullptr : (FastKernel)fast_kernel<MODE, S, kDirectVec, false, false>;
         default: return nullptr;
     }
 }
@@ -970,9 +1066,9 @@ static FastKernel pick_kernel_s(int VEC, bool staged)
 static FastKernel pick_kernel(const Plan &pl)
 {
     switch (pl.mode) {
-        case MODE_FWD: return pl.S == 2 ? pick_kernel_s<MODE_FWD, 2>(pl.VEC, pl.stage_out) : pick_kernel_s<MODE_FWD, 1>(pl.VEC, pl.stage_out);
-        case MODE_DGRAD_S2: return pick_kernel_s<MODE_DGRAD_S2, 2>(pl.VEC, pl.stage_out);
-        default: return pl.S == 2 ? pick_kernel_s<MODE_WGRAD, 2>(pl.VEC, false) : pick_kernel_s<MODE_WGRAD, 1>(pl.VEC, false);
+        case MODE_FWD: return pl.S == 2 ? pick_kernel_s<MODE_FWD, 2>(pl.VEC, pl.stage_out, pl.direct) : pick_kernel_s<MODE_FWD, 1>(pl.VEC, pl.stage_out, pl.direct);
+        case MODE_DGRAD_S2: return pick_kernel_s<MODE_DGRAD_S2, 2>(pl.VEC, pl.stage_out, pl.direct);
+        default: return pl.S == 2 ? pick_kernel_s<MODE_WGRAD, 2>(pl.VEC, false, pl.direct) : pick_kernel_s<MODE_WGRAD, 1>(pl.VEC, false, pl.direct);
     }
 }
 
@@ -1083,8 +1179,8 @@ using namespace cunn::dw;
 
 extern "C" CUNN_API void cunn_b200_dwconv_tuning(const int *values, int count)
 {
-    int v[9] = {0, 0, 0, 0, 0, 0, 0, 0, -1};
-    for (int i = 0; i < count && i < 9; ++i) v[i] = values[i];
+    int v[10] = {0, 0, 0, 0, 0, 0, 0, 0, -1, -1};
+    for (int i = 0; i < count && i < 10; ++i) v[i] = values[i];
     g_tuning.P = v[0];
     g_tuning.R = v[1];
     g_tuning.RS = v[2];
@@ -1094,6 +1190,7 @@ extern "C" CUNN_API void cunn_b200_dwconv_tuning(const int *values, int count)
     g_tuning.budget_kb = v[6];
     g_tuning.vec = v[7];
     g_tuning.stage_out = v[8];
+    g_tuning.direct = v[9];
 }
 
 extern "C" int cunn_b200_dwconv_forward(const float *x, const float *weight, const float *bias, float *y, int N, int C,
@@ -1211,9 +1308,9 @@ extern "C" CUNN_API int cunn_b200_dwconv_describe_plan(int mode, int N, int C, i
     Plan pl = make_plan(mode, N, C, H, W, oH, oW, stride);
     if (pl.ok) finalize_plan(pl);
     snprintf(buf, buflen,
-             "ok=%d S=%d VEC=%d staged_out=%d P=%d bands=%d R=%d RS=%d strips=%d CG=%d items=%d threads=%d stages=%d "
+             "ok=%d S=%d VEC=%d staged_out=%d direct=%d P=%d bands=%d R=%d RS=%d strips=%d CG=%d items=%d threads=%d stages=%d "
              "maxseg=%d grid=%d stage_bytes=%d+%d out_bytes=2x%d smem=%zu",
-             (int)pl.ok, pl.S, pl.VEC, (int)pl.stage_out, pl.P, pl.bands, pl.R, pl.RS, pl.strips, pl.CG, pl.items,
+             (int)pl.ok, pl.S, pl.VEC, (int)pl.stage_out, (int)pl.direct, pl.P, pl.bands, pl.R, pl.RS, pl.strips, pl.CG, pl.items,
              pl.threads, pl.stages, pl.maxseg, pl.ok ? pl.grid : 0, pl.stage_floats * 4, pl.stage2_floats * 4,
              pl.out_floats * 4, pl.smem);
     return pl.ok ? 0 : 1;

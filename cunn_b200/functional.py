@@ -145,3 +145,39 @@ def batchnorm_backward(x, gy, weight, running_mean, running_var, save_mean, save
                                            _ptr(save_mean), _ptr(save_std), N, C, S, int(train), scale, eps,
                                            _ptr(ws), ws.numel(), _stream()))
     return out if want_gx else None
+
+
+def convmm_forward(x, weight, bias, dH, dW, padH, padW, out=None):
+    """weight: [K, C, kH, kW] contiguous (the reference's [K, C*kH*kW] view of the same memory)."""
+    _chk(x, weight, bias)
+    N, C, H, W = x.shape
+    K, _, kH, kW = weight.shape
+    oH, oW = conv_out(H, kH, dH, padH), conv_out(W, kW, dW, padW)
+    if out is None:
+        out = torch.empty((N, K, max(oH, 0), max(oW, 0)), dtype=torch.float32, device=x.device)
+    check(lib.cunn_b200_convmm_forward(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), N, C, H, W, K, kH, kW,
+                                       dH, dW, padH, padW, _stream()))
+    return out
+
+
+def convmm_grad_input(gy, weight, H, W, dH, dW, padH, padW, out=None):
+    _chk(gy, weight)
+    K, C, kH, kW = weight.shape
+    N = gy.shape[0]
+    if out is None:
+        out = torch.empty((N, C, H, W), dtype=torch.float32, device=gy.device)
+    check(lib.cunn_b200_convmm_grad_input(_ptr(gy), _ptr(weight), _ptr(out), N, C, H, W, K, kH, kW,
+                                          dH, dW, padH, padW, _stream()))
+    return out
+
+
+def convmm_acc_grad(x, gy, grad_weight, grad_bias, dH, dW, padH, padW, scale=1.0):
+    """Accumulates into grad_weight [K,C,kH,kW] and grad_bias [K] (may be None) in place."""
+    _chk(x, gy, grad_weight, grad_bias)
+    N, C, H, W = x.shape
+    K, _, kH, kW = grad_weight.shape
+    need = lib.cunn_b200_convmm_acc_grad_workspace(N, C, H, W, K, kH, kW, dH, dW, padH, padW)
+    ws = workspace(need, x.device)
+    check(lib.cunn_b200_convmm_acc_grad(_ptr(x), _ptr(gy), _ptr(grad_weight), _ptr(grad_bias), N, C, H, W, K, kH, kW,
+                                        dH, dW, padH, padW, scale, _ptr(ws), ws.numel(), _stream()))
+    return grad_weight, grad_bias

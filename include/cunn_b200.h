@@ -91,6 +91,32 @@ CUNN_API int cunn_b200_dwconv_acc_grad_static(const float *x, const float *gy, f
                                               cunn_stream_t stream);
 CUNN_API size_t cunn_b200_dwconv_acc_grad_static_capacity(void);
 
+/* ---- SpatialConvolutionMM -----------------------------------------------------
+ * x [N,C,H,W]; weight [K, C*kH*kW] (= contiguous [K,C,kH,kW]); bias [K] or NULL; y [N,K,oH,oW].
+ * Implicit GEMM on tcgen05 tensor cores with a 3xTF32 split (fp32-class accuracy); no column buffer.
+ * Replaces THNN_(SpatialConvolutionMM_updateOutput)
+ * (lib/THCUNN/generic/SpatialConvolutionMM.cu:58-209, unfold kernel lib/THCUNN/im2col.h:10-61). */
+CUNN_API int cunn_b200_convmm_forward(const float *x, const float *weight, const float *bias, float *y,
+                                      int N, int C, int H, int W, int K, int kH, int kW,
+                                      int dH, int dW, int padH, int padW, cunn_stream_t stream);
+
+/* gx [N,C,H,W] from gy [N,K,oH,oW].  Replaces ..._updateGradInput
+ * (lib/THCUNN/generic/SpatialConvolutionMM.cu:211-325, fold kernel lib/THCUNN/im2col.h:64-121). */
+CUNN_API int cunn_b200_convmm_grad_input(const float *gy, const float *weight, float *gx,
+                                         int N, int C, int H, int W, int K, int kH, int kW,
+                                         int dH, int dW, int padH, int padW, cunn_stream_t stream);
+
+/* grad_weight [K, C*kH*kW] += scale * dL/dW, grad_bias [K] += scale * sum gy (may be NULL).  `workspace`:
+ * caller-owned scratch of at least cunn_b200_convmm_acc_grad_workspace(...) bytes, 16-byte aligned,
+ * contents irrelevant.  Replaces ..._accGradParameters
+ * (lib/THCUNN/generic/SpatialConvolutionMM.cu:327-486). */
+CUNN_API size_t cunn_b200_convmm_acc_grad_workspace(int N, int C, int H, int W, int K, int kH, int kW,
+                                                    int dH, int dW, int padH, int padW);
+CUNN_API int cunn_b200_convmm_acc_grad(const float *x, const float *gy, float *grad_weight, float *grad_bias,
+                                       int N, int C, int H, int W, int K, int kH, int kW,
+                                       int dH, int dW, int padH, int padW, float scale,
+                                       void *workspace, size_t workspace_bytes, cunn_stream_t stream);
+
 /* ---- SpatialMaxPooling --------------------------------------------------------
  * x [N,C,H,W] -> y [N,C,oH,oW] and int64 indices of the same shape holding the flat position h*W + w of
  * the maximum inside its plane plus CUNN_B200_INDEX_BASE.  The window is scanned row-major with a strict
