@@ -45,6 +45,16 @@ _decl("cunn_b200_maxpool_backward", c_int, [c_void_p] * 3 + [c_int] * 13 + [c_vo
 _decl("cunn_b200_batchnorm_workspace", c_size_t, [c_int, c_int])
 _decl("cunn_b200_batchnorm_forward", c_int, [c_void_p] * 8 + [c_int] * 4 + [c_double, c_double, c_void_p, c_size_t, c_void_p])
 _decl("cunn_b200_batchnorm_backward", c_int, [c_void_p] * 10 + [c_int] * 4 + [c_double, c_double, c_void_p, c_size_t, c_void_p])
+c_longlong = ctypes.c_longlong
+_decl("cunn_b200_threshold_forward", c_int, [c_void_p, c_void_p, c_longlong, c_float, c_float, c_void_p])
+_decl("cunn_b200_threshold_backward", c_int, [c_void_p, c_void_p, c_void_p, c_longlong, c_float, c_void_p])
+_decl("cunn_b200_avgpool_forward", c_int, [c_void_p, c_void_p] + [c_int] * 13 + [c_void_p])
+_decl("cunn_b200_avgpool_backward", c_int, [c_void_p, c_void_p] + [c_int] * 13 + [c_void_p])
+_decl("cunn_b200_logsoftmax_forward", c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p])
+_decl("cunn_b200_logsoftmax_backward", c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+_decl("cunn_b200_classnll_forward", c_int, [c_void_p] * 4 + [c_int, c_int, c_int, c_longlong, c_void_p])
+_decl("cunn_b200_classnll_backward", c_int, [c_void_p] * 4 + [c_int, c_int, c_int, c_longlong, c_void_p])
+_decl("cunn_b200_sgd_update", c_int, [c_void_p, c_void_p, c_longlong, c_float, c_void_p])
 _decl("cunn_b200_dwconv_tuning", None, [ctypes.POINTER(c_int), c_int])
 _decl("cunn_b200_dwconv_describe_plan", c_int, [c_int] * 6 + [ctypes.c_char_p, c_int])
 

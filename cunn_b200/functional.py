@@ -181,3 +181,81 @@ def convmm_acc_grad(x, gy, grad_weight, grad_bias, dH, dW, padH, padW, scale=1.0
     check(lib.cunn_b200_convmm_acc_grad(_ptr(x), _ptr(gy), _ptr(grad_weight), _ptr(grad_bias), N, C, H, W, K, kH, kW,
                                         dH, dW, padH, padW, scale, _ptr(ws), ws.numel(), _stream()))
     return grad_weight, grad_bias
+
+
+def threshold_forward(x, threshold=0.0, value=0.0, out=None):
+    _chk(x, out)
+    if out is None:
+        out = torch.empty_like(x)
+    check(lib.cunn_b200_threshold_forward(_ptr(x), _ptr(out), x.numel(), threshold, value, _stream()))
+    return out
+
+
+def threshold_backward(x, gy, threshold=0.0, out=None):
+    _chk(x, gy, out)
+    if out is None:
+        out = torch.empty_like(x)
+    check(lib.cunn_b200_threshold_backward(_ptr(x), _ptr(gy), _ptr(out), x.numel(), threshold, _stream()))
+    return out
+
+
+def avgpool_forward(x, kH, kW, dH, dW, padH, padW, ceil_mode=False, count_include_pad=True, out=None):
+    _chk(x)
+    N, C, H, W = x.shape
+    oH, oW = maxpool_out_size(H, kH, dH, padH, ceil_mode), maxpool_out_size(W, kW, dW, padW, ceil_mode)
+    if out is None:
+        out = torch.empty((N, C, oH, oW), dtype=torch.float32, device=x.device)
+    check(lib.cunn_b200_avgpool_forward(_ptr(x), _ptr(out), N, C, H, W, oH, oW, kH, kW, dH, dW, padH, padW,
+                                        int(count_include_pad), _stream()))
+    return out
+
+
+def avgpool_backward(gy, H, W, kH, kW, dH, dW, padH, padW, count_include_pad=True, out=None):
+    _chk(gy)
+    N, C, oH, oW = gy.shape
+    if out is None:
+        out = torch.empty((N, C, H, W), dtype=torch.float32, device=gy.device)
+    check(lib.cunn_b200_avgpool_backward(_ptr(gy), _ptr(out), N, C, H, W, oH, oW, kH, kW, dH, dW, padH, padW,
+                                         int(count_include_pad), _stream()))
+    return out
+
+
+def logsoftmax_forward(x, out=None):
+    _chk(x)
+    if out is None:
+        out = torch.empty_like(x)
+    check(lib.cunn_b200_logsoftmax_forward(_ptr(x), _ptr(out), x.shape[0], x.shape[1], _stream()))
+    return out
+
+
+def logsoftmax_backward(y, gy, out=None):
+    _chk(y, gy)
+    if out is None:
+        out = torch.empty_like(y)
+    check(lib.cunn_b200_logsoftmax_backward(_ptr(y), _ptr(gy), _ptr(out), y.shape[0], y.shape[1], _stream()))
+    return out
+
+
+def classnll_forward(logprob, target, weights=None, size_average=True, ignore_index=-100, out=None):
+    """Returns a 2-element device tensor [loss, total_weight]."""
+    _chk(logprob, target, weights)
+    if out is None:
+        out = torch.zeros(2, dtype=torch.float32, device=logprob.device)
+    check(lib.cunn_b200_classnll_forward(_ptr(logprob), _ptr(target), _ptr(weights), _ptr(out), logprob.shape[0],
+                                         logprob.shape[1], int(size_average), ignore_index, _stream()))
+    return out
+
+
+def classnll_backward(target, loss_and_weight, B, D, weights=None, size_average=True, ignore_index=-100, out=None):
+    _chk(target, weights)
+    if out is None:
+        out = torch.zeros((B, D), dtype=torch.float32, device=target.device)
+    check(lib.cunn_b200_classnll_backward(_ptr(target), _ptr(weights), loss_and_weight[1:].data_ptr(), _ptr(out), B, D,
+                                          int(size_average), ignore_index, _stream()))
+    return out
+
+
+def sgd_update(params, grads, lr):
+    _chk(params, grads)
+    check(lib.cunn_b200_sgd_update(_ptr(params), _ptr(grads), params.numel(), lr, _stream()))
+    return params

@@ -163,6 +163,42 @@ CUNN_API int cunn_b200_batchnorm_backward(const float *x, const float *gy, float
                                           int N, int C, int S, int train, double scale, double eps,
                                           void *workspace, size_t workspace_bytes, cunn_stream_t stream);
 
+/* ---- Support operators of the MobileNetV1 step ---------------------------------------------
+ * Threshold (ReLU is threshold 0, value 0; y may alias x, gx may alias gy):
+ * THNN_(Threshold_updateOutput / _updateGradInput), lib/THCUNN/generic/Threshold.cu:7-67. */
+CUNN_API int cunn_b200_threshold_forward(const float *x, float *y, long long n, float threshold, float value,
+                                         cunn_stream_t stream);
+CUNN_API int cunn_b200_threshold_backward(const float *x, const float *gy, float *gx, long long n, float threshold,
+                                          cunn_stream_t stream);
+
+/* SpatialAveragePooling with caller-computed output size (cunn_b200_maxpool_out_size with dil = 1 gives it):
+ * THNN_(SpatialAveragePooling_updateOutput / _updateGradInput), lib/THCUNN/generic/SpatialAveragePooling.cu:72-235. */
+CUNN_API int cunn_b200_avgpool_forward(const float *x, float *y, int N, int C, int H, int W, int oH, int oW,
+                                       int kH, int kW, int dH, int dW, int padH, int padW, int count_include_pad,
+                                       cunn_stream_t stream);
+CUNN_API int cunn_b200_avgpool_backward(const float *gy, float *gx, int N, int C, int H, int W, int oH, int oW,
+                                        int kH, int kW, int dH, int dW, int padH, int padW, int count_include_pad,
+                                        cunn_stream_t stream);
+
+/* LogSoftMax over the last dimension of [B, D]:
+ * THNN_(LogSoftMax_updateOutput / _updateGradInput), lib/THCUNN/generic/LogSoftMax.cu:7-237. */
+CUNN_API int cunn_b200_logsoftmax_forward(const float *x, float *y, int B, int D, cunn_stream_t stream);
+CUNN_API int cunn_b200_logsoftmax_backward(const float *y, const float *gy, float *gx, int B, int D, cunn_stream_t stream);
+
+/* ClassNLLCriterion on log-probabilities [B, D]; targets are int64 and carry CUNN_B200_INDEX_BASE;
+ * loss_and_total_weight[0] = loss, [1] = total weight (device memory).  Backward writes only the target
+ * entries of gx: zero gx first, as nn.ClassNLLCriterion does.
+ * THNN_(ClassNLLCriterion_updateOutput / _updateGradInput), lib/THCUNN/generic/ClassNLLCriterion.cu:5-177. */
+CUNN_API int cunn_b200_classnll_forward(const float *logprob, const int64_t *target, const float *weights,
+                                        float *loss_and_total_weight, int B, int D, int size_average,
+                                        long long ignore_index, cunn_stream_t stream);
+CUNN_API int cunn_b200_classnll_backward(const int64_t *target, const float *weights, const float *total_weight,
+                                         float *gx, int B, int D, int size_average, long long ignore_index,
+                                         cunn_stream_t stream);
+
+/* params -= lr * grads: the update DataParallelTable:updateParameters applies (DataParallelTable.lua:315-321). */
+CUNN_API int cunn_b200_sgd_update(float *params, const float *grads, long long n, float lr, cunn_stream_t stream);
+
 /* Tuning hook for sweeps and tests: overrides the tile plan of the 3x3 fast path for the calling
  * thread.  values[0..count) = {planes_per_tile, rows_per_tile, rows_per_strip, stages, ctas_per_sm,
  * force_generic, stage_budget_kb, vec, staged_stores(-1 auto)}; 0 keeps the automatic choice, missing
