@@ -54,6 +54,7 @@ _decl("cunn_b200_logsoftmax_forward", c_int, [c_void_p, c_void_p, c_int, c_int, 
 _decl("cunn_b200_logsoftmax_backward", c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
 _decl("cunn_b200_classnll_forward", c_int, [c_void_p] * 4 + [c_int, c_int, c_int, c_longlong, c_void_p])
 _decl("cunn_b200_classnll_backward", c_int, [c_void_p] * 4 + [c_int, c_int, c_int, c_longlong, c_void_p])
+_decl("cunn_b200_fill", c_int, [c_void_p, c_longlong, c_float, c_void_p])
 _decl("cunn_b200_sgd_update", c_int, [c_void_p, c_void_p, c_longlong, c_float, c_void_p])
 _decl("cunn_b200_dwconv_tuning", None, [ctypes.POINTER(c_int), c_int])
 _decl("cunn_b200_dwconv_describe_plan", c_int, [c_int] * 6 + [ctypes.c_char_p, c_int])

@@ -319,3 +319,24 @@ extern "C" CUNN_API int cunn_b200_sgd_update(float *params, const float *grads, 
     CUNN_LAUNCH_CHECK("sgd update");
     return 0;
 }
+
+namespace cunn {
+namespace sup {
+__global__ void __launch_bounds__(256)
+fill_kernel(float *__restrict__ p, long long n, float v)
+{
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) p[i] = v;
+}
+}  // namespace sup
+}  // namespace cunn
+
+extern "C" CUNN_API int cunn_b200_fill(float *p, long long n, float value, cunn_stream_t stream)
+{
+    clear_error();
+    CUNN_CHECK_ARG(n >= 0, "negative element count");
+    if (n == 0) return 0;
+    CUNN_CHECK_ARG(p, "null tensor pointer");
+    cunn::sup::fill_kernel<<<cunn::sup::grid_for(n, 1), 256, 0, (cudaStream_t)stream>>>(p, n, value);
+    CUNN_LAUNCH_CHECK("fill");
+    return 0;
+}

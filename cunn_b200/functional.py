@@ -27,10 +27,11 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
-def workspace(nbytes, device):
-    """Grow-only, zero-initialised scratch buffer per (device, stream); the kernels that use it keep its
-    control words zero between calls."""
-    key = (device.index, torch.cuda.current_stream().cuda_stream)
+def workspace(nbytes, device, tag="scratch"):
+    """Grow-only, zero-initialised scratch buffer per (device, stream, tag).  The depthwise parameter
+    gradient keeps ticket counters in its buffer (tag "dwconv") that must stay zero between calls, so no
+    other operator may write there; everything else shares the "scratch" buffer."""
+    key = (device.index, torch.cuda.current_stream().cuda_stream, tag)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.zeros(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
@@ -71,7 +72,7 @@ def dwconv_acc_grad(x, gy, grad_weight, grad_bias, dH, dW, padH, padW, scale=1.0
     N, C, H, W = x.shape
     M, _, kH, kW = grad_weight.shape
     need = lib.cunn_b200_dwconv_acc_grad_workspace(N, C, H, W, M, kH, kW, dH, dW, padH, padW)
-    ws = workspace(need, x.device) if need else None
+    ws = workspace(need, x.device, "dwconv") if need else None
     check(lib.cunn_b200_dwconv_acc_grad(_ptr(x), _ptr(gy), _ptr(grad_weight), _ptr(grad_bias), N, C, H, W, M, kH, kW,
                                         dH, dW, padH, padW, scale, _ptr(ws), ws.numel() if ws is not None else 0,
                                         _stream()))

@@ -199,6 +199,33 @@ CUNN_API int cunn_b200_classnll_backward(const int64_t *target, const float *wei
 /* params -= lr * grads: the update DataParallelTable:updateParameters applies (DataParallelTable.lua:315-321). */
 CUNN_API int cunn_b200_sgd_update(float *params, const float *grads, long long n, float lr, cunn_stream_t stream);
 
+CUNN_API int cunn_b200_fill(float *p, long long n, float value, cunn_stream_t stream);
+
+/* ---- MobileNetV1 replica step (the module a batch-sharded DataParallelTable replicates) ----------
+ * image_hw: input resolution (224), width_div: channel divisor (1 = full width; 2, 4, 8 ... for tests),
+ * num_classes: classifier outputs.  Parameters and gradients are flat fp32 buffers of
+ * cunn_b200_mobilenet_param_count() floats in module order (DataParallelTable.lua:104-128 flattenParameters);
+ * cunn_b200_mobilenet_layer_info() gives every tensor's offset.  bn_running holds running mean | var per
+ * layer (cunn_b200_mobilenet_bn_stat_count() floats) and stays per replica.  One call runs forward, loss
+ * and backward on `batch` local images and ACCUMULATES parameter gradients of
+ * (1 / global batch) * sum of the local rows' NLL into `grads`; *loss (device) receives that scaled sum, so
+ * replica losses and gradients simply add up (the data-parallel step all-reduces `grads`).  The arena is
+ * caller-owned device memory of cunn_b200_mobilenet_arena_bytes() bytes, 256-byte aligned. */
+typedef struct cunn_b200_mobilenet_config {
+    int image_hw;
+    int width_div;
+    int num_classes;
+} cunn_b200_mobilenet_config;
+CUNN_API long long cunn_b200_mobilenet_param_count(const cunn_b200_mobilenet_config *cfg);
+CUNN_API long long cunn_b200_mobilenet_bn_stat_count(const cunn_b200_mobilenet_config *cfg);
+CUNN_API int cunn_b200_mobilenet_num_layers(const cunn_b200_mobilenet_config *cfg);
+CUNN_API int cunn_b200_mobilenet_layer_info(const cunn_b200_mobilenet_config *cfg, int layer, long long *info12);
+CUNN_API size_t cunn_b200_mobilenet_arena_bytes(const cunn_b200_mobilenet_config *cfg, int batch);
+CUNN_API int cunn_b200_mobilenet_step(const cunn_b200_mobilenet_config *cfg, const float *images, const int64_t *labels,
+                                      int batch, float inv_global_batch, const float *params, float *grads,
+                                      float *bn_running, void *arena, size_t arena_bytes, float *loss,
+                                      double momentum, double eps, cunn_stream_t stream);
+
 /* Tuning hook for sweeps and tests: overrides the tile plan of the 3x3 fast path for the calling
  * thread.  values[0..count) = {planes_per_tile, rows_per_tile, rows_per_strip, stages, ctas_per_sm,
  * force_generic, stage_budget_kb, vec, staged_stores(-1 auto)}; 0 keeps the automatic choice, missing
