@@ -204,6 +204,57 @@ def workload_config(n, world):
             "launch": "39 kernels per step replayed from one CUDA graph"}
 
 
+def mobilenet_bench(args, dev, world, rank, dist):
+    """Full MobileNetV1 (1.0, 224x224, 1000 classes) training step: forward, loss, backward, all-reduce of the
+    flat gradient buffer, SGD update; global batch sharded over the ranks with DataParallelTable's slice rule.
+    Returns images/s of the whole job (device-resident inputs) and the same with the shard's images copied
+    from pinned host memory and the loss read back every step."""
+    import torch
+    from cunn_b200 import mobilenet as mb
+    gb = args.mobilenet_batch
+    cfg = mb.Config(224, 1, 1000)
+    start, count = mb.slice_range(gb, world, rank)
+    torch.manual_seed(SEED + 17 * rank)
+    images = torch.randn((count, 3, 224, 224), device=dev)
+    labels = torch.randint(1, 1001, (count,), device=dev, dtype=torch.int64)
+    rep = mb.MobileNetV1(cfg, dev, mb.init_params(cfg, SEED), max_batch=max(count, 1))
+    step = mb.DataParallelStep(rep, dist)
+    warm, timed = 2, max(3, min(args.steps, 8))
+    for _ in range(warm):
+        step.train_step(images, labels, gb, 0.01)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(timed):
+        loss = step.train_step(images, labels, gb, 0.01)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / timed
+    # end to end: images from pinned host memory, loss back to the host, every step
+    himg = images.cpu().pin_memory()
+    hlab = labels.cpu().pin_memory()
+    hloss = torch.zeros(1).pin_memory()
+    t0 = time.perf_counter()
+    for _ in range(timed):
+        images.copy_(himg, non_blocking=True)
+        labels.copy_(hlab, non_blocking=True)
+        loss = step.train_step(images, labels, gb, 0.01)
+        hloss.copy_(loss, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    ems = (time.perf_counter() - t0) * 1e3 / timed
+    if dist is not None:
+        tt = torch.tensor([ms, ems], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, ems = float(tt[0]), float(tt[1])
+    return {"img_s": round(gb / (ms * 1e-3), 1), "e2e_img_s": round(gb / (ems * 1e-3), 1), "global_batch": gb,
+            "per_gpu_batch": count, "ms_per_step": round(ms, 3), "e2e_ms_per_step": round(ems, 3), "steps": timed,
+            "loss": float(hloss[0]), "params": rep.nparams, "allreduce_bytes_per_step": rep.nparams * 4 if world > 1 else 0,
+            "h2d_bytes_per_step": himg.numel() * 4 + hlab.numel() * 8,
+            "step": "fwd + NLL loss + bwd + gradient all-reduce + SGD, fp32, BN statistics per shard"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -213,6 +264,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-mobilenet", action="store_true")
+    ap.add_argument("--mobilenet-batch", type=int, default=1024, help="global batch of the MobileNetV1 step")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -401,6 +454,11 @@ def main():
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": esteps,
                "ms_per_step": round(ems / esteps, 3)}
 
+    # ---- MobileNetV1 training step, batch-sharded over the ranks (BASELINE config 5) ----------------
+    mbn = None
+    if not args.no_mobilenet:
+        mbn = mobilenet_bench(args, dev, world, rank, dist if world > 1 else None)
+
     status = device_status()
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -412,7 +470,7 @@ def main():
                 "warmup": warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(BATCH, world),
                 "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * steps,
-                "roofline": roofline, "cpu_baseline": cpu, "device_status": status}
+                "roofline": roofline, "cpu_baseline": cpu, "mobilenet_v1": mbn, "device_status": status}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
