@@ -1,0 +1,712 @@
+// THNN_Cuda* entry points: the reference's C ABI for the convolutional hot path, over a minimal
+// THC-compatible tensor struct.  Each wrapper does what the reference's host wrapper does around its
+// kernels — shape checks with the same messages, resizing outputs in place, contiguous copies of
+// strided inputs — and then calls the flat C ABI (cunn_b200.h) on the state's current stream.
+// Errors go through the state's error hook (TH's THError); if the hook returns, the entry point returns.
+#include "common.cuh"
+#include "../../include/THCUNN_b200.h"
+
+#include <stdlib.h>
+#include <string.h>
+#include <string>
+#include <vector>
+
+struct THCState {
+    cudaStream_t stream = nullptr;
+    THCUNN_b200_error_fn handler = nullptr;
+    void *handler_ctx = nullptr;
+    std::string last_error;
+    // grow-only scratch owned by the state: [0] general, [1] depthwise parameter gradient (zero-filled, its
+    // ticket counters must stay zero between calls)
+    void *scratch[2] = {nullptr, nullptr};
+    size_t scratch_bytes[2] = {0, 0};
+};
+
+namespace {
+
+const char kOwned = 1;     // storage flag: memory belongs to the storage (cudaMalloc'ed here)
+
+void raise(THCState *s, const char *fmt, ...)
+{
+    char buf[600];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    s->last_error = buf;
+    if (s->handler) s->handler(buf, s->handler_ctx);
+    else fprintf(stderr, "THCUNN error: %s\n", buf);
+}
+
+#define TH_CHECK(state, cond, ...)         \
+    do {                                   \
+        if (!(cond)) {                     \
+            raise(state, __VA_ARGS__);     \
+            return;                        \
+        }                                  \
+    } while (0)
+// a flat-ABI call failed: forward its message
+#define TH_CALL(state, call)                                  \
+    do {                                                      \
+        if ((call) != 0) {                                    \
+            raise(state, "%s", cunn_b200_last_error());      \
+            goto done;                                        \
+        }                                                     \
+    } while (0)
+
+ptrdiff_t nelem(const THCudaTensor *t)
+{
+    if (!t || t->nDimension == 0) return 0;
+    ptrdiff_t n = 1;
+    for (int i = 0; i < t->nDimension; ++i) n *= t->size[i];
+    return n;
+}
+
+bool is_contiguous(const THCudaTensor *t)
+{
+    long z = 1;
+    for (int d = t->nDimension - 1; d >= 0; --d) {
+        if (t->size[d] != 1) {
+            if (t->stride[d] != z) return false;
+            z *= t->size[d];
+        }
+    }
+    return true;
+}
+
+std::string size_desc(const THCudaTensor *t)
+{
+    std::string s = "[";
+    for (int i = 0; t && i < t->nDimension; ++i) {
+        s += std::to_string(t->size[i]);
+        if (i + 1 < t->nDimension) s += " x ";
+    }
+    return s + "]";
+}
+
+THCudaTensor *tensor_new()
+{
+    THCudaTensor *t = (THCudaTensor *)calloc(1, sizeof(THCudaTensor));
+    t->refcount = 1;
+    t->flag = 1;
+    return t;
+}
+
+void storage_release(THCudaStorage *st)
+{
+    if (!st) return;
+    if (--st->refcount > 0) return;
+    if ((st->flag & kOwned) && st->data) cudaFree(st->data);
+    free(st);
+}
+
+void tensor_free(THCudaTensor *t)
+{
+    if (!t) return;
+    if (--t->refcount > 0) return;
+    storage_release(t->storage);
+    free(t->size);
+    free(t->stride);
+    free(t);
+}
+
+// Gives t the contiguous shape `sizes`; grows its storage when needed.  elem = element size in bytes.
+bool tensor_resize(THCState *s, THCudaTensor *t, int nd, const long *sizes, int elem)
+{
+    ptrdiff_t n = nd ? 1 : 0;
+    for (int i = 0; i < nd; ++i) n *= sizes[i];
+    bool same = t->nDimension == nd;
+    for (int i = 0; same && i < nd; ++i) same = t->size[i] == sizes[i];
+    if (!(same && is_contiguous(t))) {
+        t->size = (long *)realloc(t->size, sizeof(long) * (nd ? nd : 1));
+        t->stride = (long *)realloc(t->stride, sizeof(long) * (nd ? nd : 1));
+        t->nDimension = nd;
+        long z = 1;
+        for (int d = nd - 1; d >= 0; --d) {
+            t->size[d] = sizes[d];
+            t->stride[d] = z;
+            z *= sizes[d];
+        }
+    }
+    const ptrdiff_t need = t->storageOffset + n;
+    if (!t->storage) {
+        t->storage = (THCudaStorage *)calloc(1, sizeof(THCudaStorage));
+        t->storage->refcount = 1;
+        t->storage->flag = kOwned;
+        cudaGetDevice(&t->storage->device);
+    }
+    if (need > t->storage->size) {
+        if (!(t->storage->flag & kOwned)) {
+            raise(s, "cannot resize a tensor over caller-owned memory from %td to %td elements", t->storage->size, need);
+            return false;
+        }
+        void *p = nullptr;
+        if (need > 0 && cudaMalloc(&p, (size_t)need * elem) != cudaSuccess) {
+            raise(s, "cudaMalloc of %zu bytes failed", (size_t)need * elem);
+            return false;
+        }
+        if (t->storage->data && t->storage->size > 0)
+            cudaMemcpyAsync(p, t->storage->data, (size_t)t->storage->size * elem, cudaMemcpyDeviceToDevice, s->stream);
+        if (t->storage->data) {
+            cudaStreamSynchronize(s->stream);
+            cudaFree(t->storage->data);
+        }
+        t->storage->data = p;
+        t->storage->size = need;
+    }
+    return true;
+}
+
+template <typename T>
+T *tdata(const THCudaTensor *t)
+{
+    if (!t || !t->storage || !t->storage->data) return nullptr;
+    return (T *)t->storage->data + t->storageOffset;
+}
+
+// dst (contiguous) = src (any strides), up to 5 dimensions, element size 4 or 8.
+template <typename T>
+__global__ void strided_copy_kernel(const T *__restrict__ src, T *__restrict__ dst, long long n, int nd, long s0, long s1,
+                                    long s2, long s3, long s4, long t0, long t1, long t2, long t3, long t4)
+{
+    const long size[5] = {s0, s1, s2, s3, s4};
+    const long stride[5] = {t0, t1, t2, t3, t4};
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        long long r = i, off = 0;
+        for (int d = nd - 1; d >= 0; --d) {
+            off += (r % size[d]) * stride[d];
+            r /= size[d];
+        }
+        dst[i] = src[off];
+    }
+}
+
+// A contiguous tensor with t's contents: t itself (retained) when already contiguous, else a copy.
+THCudaTensor *new_contiguous(THCState *s, THCudaTensor *t, int elem = 4)
+{
+    if (is_contiguous(t)) {
+        ++t->refcount;
+        return t;
+    }
+    if (t->nDimension > 5) {
+        raise(s, "non-contiguous tensors of more than 5 dimensions are not supported");
+        return nullptr;
+    }
+    THCudaTensor *c = tensor_new();
+    if (!tensor_resize(s, c, t->nDimension, t->size, elem)) {
+        tensor_free(c);
+        return nullptr;
+    }
+    long sz[5] = {1, 1, 1, 1, 1}, st[5] = {0, 0, 0, 0, 0};
+    for (int i = 0; i < t->nDimension; ++i) { sz[i] = t->size[i]; st[i] = t->stride[i]; }
+    const long long n = nelem(t);
+    if (n > 0) {
+        const int blocks = (int)std::min<long long>((n + 255) / 256, 65535);
+        if (elem == 4)
+            strided_copy_kernel<float><<<blocks, 256, 0, s->stream>>>(tdata<float>(t), tdata<float>(c), n, t->nDimension, sz[0], sz[1], sz[2], sz[3], sz[4], st[0], st[1], st[2], st[3], st[4]);
+        else
+            strided_copy_kernel<long long><<<blocks, 256, 0, s->stream>>>(tdata<long long>(t), tdata<long long>(c), n, t->nDimension, sz[0], sz[1], sz[2], sz[3], sz[4], st[0], st[1], st[2], st[3], st[4]);
+    }
+    return c;
+}
+
+void *state_scratch(THCState *s, int which, size_t bytes)
+{
+    if (bytes <= s->scratch_bytes[which]) return s->scratch[which];
+    const size_t want = std::max(bytes, (size_t)1 << 20);
+    void *p = nullptr;
+    if (cudaMalloc(&p, want) != cudaSuccess) {
+        raise(s, "cudaMalloc of %zu bytes of scratch failed", want);
+        return nullptr;
+    }
+    cudaMemsetAsync(p, 0, want, s->stream);
+    if (s->scratch[which]) {
+        cudaStreamSynchronize(s->stream);
+        cudaFree(s->scratch[which]);
+    }
+    s->scratch[which] = p;
+    s->scratch_bytes[which] = want;
+    return p;
+}
+
+bool check_dim_size(THCState *s, const THCudaTensor *t, const char *name, int dim, int dim_size, long size)
+{
+    if (t->nDimension != dim || t->size[dim_size] != size) {
+        raise(s, "Need %s of dimension %d and %s.size[%d] == %ld but got %s to be of shape: %s", name, dim, name, dim_size,
+              size, name, size_desc(t).c_str());
+        return false;
+    }
+    return true;
+}
+
+}  // namespace
+
+extern "C" void thcunn_b200_not_implemented(THCState *state, const char *name)
+{
+    if (state) raise(state, "%s is not implemented in this build (only the convolutional hot path is)", name);
+    else fprintf(stderr, "THCUNN error: %s is not implemented in this build\n", name);
+}
+
+// ---- harness helpers --------------------------------------------------------------------------------
+extern "C" CUNN_API THCState *THCState_b200_new(void) { return new THCState(); }
+extern "C" CUNN_API void THCState_b200_free(THCState *s)
+{
+    if (!s) return;
+    for (int i = 0; i < 2; ++i)
+        if (s->scratch[i]) cudaFree(s->scratch[i]);
+    delete s;
+}
+extern "C" CUNN_API void THCState_b200_setStream(THCState *s, cunn_stream_t stream) { s->stream = (cudaStream_t)stream; }
+extern "C" CUNN_API void THCState_b200_setErrorHandler(THCState *s, THCUNN_b200_error_fn fn, void *ctx)
+{
+    s->handler = fn;
+    s->handler_ctx = ctx;
+}
+extern "C" CUNN_API const char *THCState_b200_lastError(THCState *s) { return s->last_error.c_str(); }
+extern "C" CUNN_API THCudaTensor *THCudaTensor_b200_new(THCState *) { return tensor_new(); }
+extern "C" CUNN_API THCudaLongTensor *THCudaLongTensor_b200_new(THCState *) { return tensor_new(); }
+extern "C" CUNN_API THCudaTensor *THCudaTensor_b200_wrap(THCState *, void *data, ptrdiff_t capacity, int ndim,
+                                                         const long *sizes, const long *strides, int)
+{
+    THCudaTensor *t = tensor_new();
+    t->storage = (THCudaStorage *)calloc(1, sizeof(THCudaStorage));
+    t->storage->refcount = 1;
+    t->storage->flag = 0;   // caller-owned
+    t->storage->data = data;
+    t->storage->size = capacity;
+    cudaGetDevice(&t->storage->device);
+    t->nDimension = ndim;
+    t->size = (long *)malloc(sizeof(long) * (ndim ? ndim : 1));
+    t->stride = (long *)malloc(sizeof(long) * (ndim ? ndim : 1));
+    long z = 1;
+    for (int d = ndim - 1; d >= 0; --d) {
+        t->size[d] = sizes[d];
+        t->stride[d] = strides ? strides[d] : z;
+        z *= sizes[d];
+    }
+    return t;
+}
+extern "C" CUNN_API void THCudaTensor_b200_free(THCState *, THCudaTensor *t) { tensor_free(t); }
+extern "C" CUNN_API void *THCudaTensor_b200_data(THCState *, THCudaTensor *t) { return tdata<char>(t) ? (void *)((char *)t->storage->data) : nullptr; }
+
+// ---- SpatialDepthWiseConvolution -------------------------------------------------------------------
+// Shape rules of lib/THCUNN/generic/SpatialDepthWiseConvolution.cu:5-56.  A 2-D weight [M, C*kH*kW] is
+// given its 4-D shape in place, as the reference does (:76-80).
+static bool dw_prepare(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *weight, THCudaTensor *bias,
+                       int kH, int kW, int dH, int dW, int padH, int padW, long *N, long *C, long *M, long *H, long *W,
+                       long *oH, long *oW)
+{
+    if (!(kW > 0 && kH > 0)) { raise(s, "kernel size should be greater than zero, but got kH: %d kW: %d", kH, kW); return false; }
+    if (!(dW > 0 && dH > 0)) { raise(s, "stride should be greater than zero, but got dH: %d dW: %d", dH, dW); return false; }
+    if (weight->nDimension == 2) {
+        const long m = weight->size[0], c = weight->size[1] / (kH * kW);
+        const long sz[4] = {m, c, kH, kW};
+        if (!tensor_resize(s, weight, 4, sz, 4)) return false;
+    }
+    if (weight->nDimension != 4) { raise(s, "2D or 4D weight tensor expected, but got: %s", size_desc(weight).c_str()); return false; }
+    if (bias && !(check_dim_size(s, bias, "bias", 2, 0, weight->size[0]) && check_dim_size(s, bias, "bias", 2, 1, weight->size[1]))) return false;
+    const int nd = input->nDimension;
+    if (nd != 3 && nd != 4) { raise(s, "3D or 4D input tensor expected but got: %s", size_desc(input).c_str()); return false; }
+    const int b = nd == 4;
+    *M = weight->size[0]; *C = weight->size[1];
+    *N = b ? input->size[0] : 1; *H = input->size[b + 1]; *W = input->size[b + 2];
+    *oH = (*H + 2 * padH - kH) / dH + 1; *oW = (*W + 2 * padW - kW) / dW + 1;
+    if (*oW < 1 || *oH < 1) {
+        raise(s, "Given input size: (%ld x %ld x %ld). Calculated output size: (%ld x %ld x %ld). Output size is too small", *C, *H, *W, *M * *C, *oH, *oW);
+        return false;
+    }
+    if (!check_dim_size(s, input, "input", nd, b, *C)) return false;
+    if (gradOutput) {
+        // the reference views gradOutput as [N, C, M, oH, oW]; here the 4-D [N, C*M, oH, oW] form is checked
+        if (gradOutput->nDimension != nd || gradOutput->size[b] != *C * *M || gradOutput->size[b + 1] != *oH || gradOutput->size[b + 2] != *oW) {
+            raise(s, "Need gradOutput of shape [.. x %ld x %ld x %ld] but got gradOutput to be of shape: %s", *C * *M, *oH, *oW, size_desc(gradOutput).c_str());
+            return false;
+        }
+    }
+    return true;
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialDepthWiseConvolution_updateOutput(
+    THCState *s, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias, THCudaTensor *,
+    THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH)
+{
+    long N, C, M, H, W, oH, oW;
+    if (!dw_prepare(s, input, nullptr, weight, bias, kH, kW, dH, dW, padH, padW, &N, &C, &M, &H, &W, &oH, &oW)) return;
+    THCudaTensor *x = new_contiguous(s, input), *w = new_contiguous(s, weight), *b = bias ? new_contiguous(s, bias) : nullptr;
+    if (x && w && (!bias || b)) {
+        const long sz4[4] = {N, C * M, oH, oW};
+        if (tensor_resize(s, output, 4, sz4, 4)) {
+            TH_CALL(s, cunn_b200_dwconv_forward(tdata<float>(x), tdata<float>(w), tdata<float>(b), tdata<float>(output), (int)N,
+                                                (int)C, (int)H, (int)W, (int)M, kH, kW, dH, dW, padH, padW, s->stream));
+            if (input->nDimension == 3) tensor_resize(s, output, 3, sz4 + 1, 4);
+        }
+    }
+done:
+    tensor_free(x); tensor_free(w); tensor_free(b);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialDepthWiseConvolution_updateGradInput(
+    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight,
+    THCudaTensor *, THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH)
+{
+    long N, C, M, H, W, oH, oW;
+    if (!dw_prepare(s, input, gradOutput, weight, nullptr, kH, kW, dH, dW, padH, padW, &N, &C, &M, &H, &W, &oH, &oW)) return;
+    // unlike the reference (which views a strided gradOutput as if it were contiguous), gy is made contiguous
+    THCudaTensor *gy = new_contiguous(s, gradOutput), *w = new_contiguous(s, weight);
+    if (gy && w) {
+        const long sz4[4] = {N, C, H, W};
+        if (tensor_resize(s, gradInput, 4, sz4, 4)) {
+            TH_CALL(s, cunn_b200_dwconv_grad_input(tdata<float>(gy), tdata<float>(w), tdata<float>(gradInput), (int)N, (int)C,
+                                                   (int)H, (int)W, (int)M, kH, kW, dH, dW, padH, padW, s->stream));
+            if (input->nDimension == 3) tensor_resize(s, gradInput, 3, sz4 + 1, 4);
+        }
+    }
+done:
+    tensor_free(gy); tensor_free(w);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialDepthWiseConvolution_accGradParameters(
+    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias,
+    THCudaTensor *, THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH, float scale)
+{
+    long N, C, M, H, W, oH, oW;
+    if (!dw_prepare(s, input, gradOutput, gradWeight, gradBias, kH, kW, dH, dW, padH, padW, &N, &C, &M, &H, &W, &oH, &oW)) return;
+    TH_CHECK(s, is_contiguous(gradWeight) && (!gradBias || is_contiguous(gradBias)), "gradWeight and gradBias have to be contiguous");
+    THCudaTensor *x = new_contiguous(s, input), *gy = new_contiguous(s, gradOutput);
+    if (x && gy) {
+        const size_t need = cunn_b200_dwconv_acc_grad_workspace((int)N, (int)C, (int)H, (int)W, (int)M, kH, kW, dH, dW, padH, padW);
+        void *ws = need ? state_scratch(s, 1, need) : nullptr;
+        if (!need || ws)
+            TH_CALL(s, cunn_b200_dwconv_acc_grad(tdata<float>(x), tdata<float>(gy), tdata<float>(gradWeight), tdata<float>(gradBias),
+                                                 (int)N, (int)C, (int)H, (int)W, (int)M, kH, kW, dH, dW, padH, padW, scale, ws,
+                                                 s->scratch_bytes[1], s->stream));
+    }
+done:
+    tensor_free(x); tensor_free(gy);
+}
+
+// ---- SpatialConvolutionMM ----------------------------------------------------------------------------
+// Shape rules of lib/THCUNN/generic/SpatialConvolutionMM.cu:5-56; the weight must be contiguous (:74) and
+// may be 2-D [K, C*kH*kW] or 4-D.
+static bool mm_prepare(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *weight, THCudaTensor *bias,
+                       int kH, int kW, int dH, int dW, int padH, int padW, long *N, long *C, long *K, long *H, long *W,
+                       long *oH, long *oW)
+{
+    if (!(kW > 0 && kH > 0)) { raise(s, "kernel size should be greater than zero, but got kH: %d kW: %d", kH, kW); return false; }
+    if (!(dW > 0 && dH > 0)) { raise(s, "stride should be greater than zero, but got dH: %d dW: %d", dH, dW); return false; }
+    if (!is_contiguous(weight)) { raise(s, "weight tensor has to be contiguous"); return false; }
+    if (bias && !is_contiguous(bias)) { raise(s, "bias tensor has to be contiguous"); return false; }
+    if (weight->nDimension != 2 && weight->nDimension != 4) { raise(s, "2D or 4D weight tensor expected, but got: %s", size_desc(weight).c_str()); return false; }
+    *K = weight->size[0];
+    *C = weight->nDimension == 2 ? weight->size[1] / (kH * kW) : weight->size[1];
+    if (bias && !check_dim_size(s, bias, "bias", 1, 0, *K)) return false;
+    const int nd = input->nDimension;
+    if (nd != 3 && nd != 4) { raise(s, "3D or 4D input tensor expected but got: %s", size_desc(input).c_str()); return false; }
+    const int b = nd == 4;
+    *N = b ? input->size[0] : 1; *H = input->size[b + 1]; *W = input->size[b + 2];
+    *oH = (*H + 2 * padH - kH) / dH + 1; *oW = (*W + 2 * padW - kW) / dW + 1;
+    if (*oW < 1 || *oH < 1) {
+        raise(s, "Given input size: (%ld x %ld x %ld). Calculated output size: (%ld x %ld x %ld). Output size is too small", *C, *H, *W, *K, *oH, *oW);
+        return false;
+    }
+    if (!check_dim_size(s, input, "input", nd, b, *C)) return false;
+    if (gradOutput && !(check_dim_size(s, gradOutput, "gradOutput", nd, b, *K) && check_dim_size(s, gradOutput, "gradOutput", nd, b + 1, *oH) &&
+                        check_dim_size(s, gradOutput, "gradOutput", nd, b + 2, *oW))) return false;
+    return true;
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialConvolutionMM_updateOutput(
+    THCState *s, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias, THCudaTensor *,
+    THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH)
+{
+    long N, C, K, H, W, oH, oW;
+    if (!mm_prepare(s, input, nullptr, weight, bias, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW)) return;
+    THCudaTensor *x = new_contiguous(s, input);
+    if (x) {
+        const long sz4[4] = {N, K, oH, oW};
+        if (tensor_resize(s, output, 4, sz4, 4)) {
+            TH_CALL(s, cunn_b200_convmm_forward(tdata<float>(x), tdata<float>(weight), bias ? tdata<float>(bias) : nullptr, tdata<float>(output),
+                                                (int)N, (int)C, (int)H, (int)W, (int)K, kH, kW, dH, dW, padH, padW, s->stream));
+            if (input->nDimension == 3) tensor_resize(s, output, 3, sz4 + 1, 4);
+        }
+    }
+done:
+    tensor_free(x);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialConvolutionMM_updateGradInput(
+    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight,
+    THCudaTensor *, THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH)
+{
+    long N, C, K, H, W, oH, oW;
+    if (!mm_prepare(s, input, gradOutput, weight, nullptr, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW)) return;
+    THCudaTensor *gy = new_contiguous(s, gradOutput);
+    if (gy) {
+        const long sz4[4] = {N, C, H, W};
+        if (tensor_resize(s, gradInput, 4, sz4, 4)) {
+            TH_CALL(s, cunn_b200_convmm_grad_input(tdata<float>(gy), tdata<float>(weight), tdata<float>(gradInput), (int)N, (int)C, (int)H,
+                                                   (int)W, (int)K, kH, kW, dH, dW, padH, padW, s->stream));
+            if (input->nDimension == 3) tensor_resize(s, gradInput, 3, sz4 + 1, 4);
+        }
+    }
+done:
+    tensor_free(gy);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialConvolutionMM_accGradParameters(
+    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias,
+    THCudaTensor *, THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH, float scale)
+{
+    long N, C, K, H, W, oH, oW;
+    if (!mm_prepare(s, input, gradOutput, gradWeight, gradBias, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW)) return;
+    THCudaTensor *x = new_contiguous(s, input), *gy = new_contiguous(s, gradOutput);
+    if (x && gy) {
+        const size_t need = cunn_b200_convmm_acc_grad_workspace((int)N, (int)C, (int)H, (int)W, (int)K, kH, kW, dH, dW, padH, padW);
+        void *ws = state_scratch(s, 0, need);
+        if (ws)
+            TH_CALL(s, cunn_b200_convmm_acc_grad(tdata<float>(x), tdata<float>(gy), tdata<float>(gradWeight), gradBias ? tdata<float>(gradBias) : nullptr,
+                                                 (int)N, (int)C, (int)H, (int)W, (int)K, kH, kW, dH, dW, padH, padW, scale, ws,
+                                                 s->scratch_bytes[0], s->stream));
+    }
+done:
+    tensor_free(x); tensor_free(gy);
+}
+
+// ---- BatchNormalization --------------------------------------------------------------------------------
+// Any [N, C, ...] input is viewed as [N, C, S] (lib/THCUNN/generic/BatchNormalization.cu:8-32).
+static bool bn_dims(THCState *s, const THCudaTensor *t, long *N, long *C, long *S)
+{
+    if (t->nDimension < 2) { raise(s, "batch normalisation expects at least 2 dimensions, got: %s", size_desc(t).c_str()); return false; }
+    *N = t->size[0]; *C = t->size[1]; *S = 1;
+    for (int i = 2; i < t->nDimension; ++i) *S *= t->size[i];
+    return true;
+}
+
+extern "C" CUNN_API void THNN_CudaBatchNormalization_updateOutput(
+    THCState *s, THCudaTensor *input_, THCudaTensor *output_, THCudaTensor *weight_, THCudaTensor *bias_,
+    THCudaTensor *runningMean_, THCudaTensor *runningVar_, THCudaTensor *saveMean_, THCudaTensor *saveStd_, bool train,
+    double momentum, double eps)
+{
+    long N, C, S;
+    if (!bn_dims(s, input_, &N, &C, &S)) return;
+    THCudaTensor *x = new_contiguous(s, input_);
+    if (x && tensor_resize(s, output_, input_->nDimension, input_->size, 4)) {
+        const long c1[1] = {C};
+        if (!train || (tensor_resize(s, saveMean_, 1, c1, 4) && tensor_resize(s, saveStd_, 1, c1, 4))) {
+            void *ws = state_scratch(s, 0, cunn_b200_batchnorm_workspace((int)N, (int)C));
+            if (ws)
+                TH_CALL(s, cunn_b200_batchnorm_forward(tdata<float>(x), tdata<float>(output_), weight_ ? tdata<float>(weight_) : nullptr,
+                                                       bias_ ? tdata<float>(bias_) : nullptr, tdata<float>(runningMean_), tdata<float>(runningVar_),
+                                                       tdata<float>(saveMean_), tdata<float>(saveStd_), (int)N, (int)C, (int)S, train ? 1 : 0,
+                                                       momentum, eps, ws, s->scratch_bytes[0], s->stream));
+        }
+    }
+done:
+    tensor_free(x);
+}
+
+extern "C" CUNN_API void THNN_CudaBatchNormalization_backward(
+    THCState *s, THCudaTensor *input_, THCudaTensor *gradOutput_, THCudaTensor *gradInput_, THCudaTensor *gradWeight_,
+    THCudaTensor *gradBias_, THCudaTensor *weight_, THCudaTensor *runningMean_, THCudaTensor *runningVar_,
+    THCudaTensor *saveMean_, THCudaTensor *saveStd_, bool train, double scale, double eps)
+{
+    long N, C, S;
+    if (!bn_dims(s, input_, &N, &C, &S)) return;
+    TH_CHECK(s, nelem(gradOutput_) == nelem(input_), "input and gradOutput have different number of elements: input%s, gradOutput%s",
+             size_desc(input_).c_str(), size_desc(gradOutput_).c_str());
+    THCudaTensor *x = new_contiguous(s, input_), *gy = new_contiguous(s, gradOutput_);
+    if (x && gy && (!gradInput_ || tensor_resize(s, gradInput_, input_->nDimension, input_->size, 4))) {
+        void *ws = state_scratch(s, 0, cunn_b200_batchnorm_workspace((int)N, (int)C));
+        if (ws)
+            TH_CALL(s, cunn_b200_batchnorm_backward(tdata<float>(x), tdata<float>(gy), gradInput_ ? tdata<float>(gradInput_) : nullptr,
+                                                    gradWeight_ ? tdata<float>(gradWeight_) : nullptr, gradBias_ ? tdata<float>(gradBias_) : nullptr,
+                                                    weight_ ? tdata<float>(weight_) : nullptr, tdata<float>(runningMean_), tdata<float>(runningVar_),
+                                                    tdata<float>(saveMean_), tdata<float>(saveStd_), (int)N, (int)C, (int)S, train ? 1 : 0, scale, eps,
+                                                    ws, s->scratch_bytes[0], s->stream));
+    }
+done:
+    tensor_free(x); tensor_free(gy);
+}
+
+// ---- SpatialMaxPooling ------------------------------------------------------------------------------------
+extern "C" CUNN_API void THNN_CudaSpatialMaxPooling_updateOutput(THCState *s, THCudaTensor *input, THCudaTensor *output,
+                                                                 THCudaLongTensor *indices, int kW, int kH, int dW, int dH,
+                                                                 int padW, int padH, bool ceil_mode)
+{
+    const int nd = input->nDimension;
+    TH_CHECK(s, nd == 3 || nd == 4, "3D or 4D input tensor expected but got: %s", size_desc(input).c_str());
+    TH_CHECK(s, kW > 0 && kH > 0, "kernel size should be greater than zero, but got kH: %d kW: %d", kH, kW);
+    TH_CHECK(s, dW > 0 && dH > 0, "stride should be greater than zero, but got dH: %d dW: %d", dH, dW);
+    const int b = nd == 4;
+    const long N = b ? input->size[0] : 1, C = input->size[b], H = input->size[b + 1], W = input->size[b + 2];
+    const long oH = cunn_b200_maxpool_out_size((int)H, kH, dH, padH, 1, ceil_mode), oW = cunn_b200_maxpool_out_size((int)W, kW, dW, padW, 1, ceil_mode);
+    THCudaTensor *x = new_contiguous(s, input);
+    if (x) {
+        const long sz4[4] = {N, C, oH > 0 ? oH : 0, oW > 0 ? oW : 0};
+        if (oH < 1 || oW < 1 || (tensor_resize(s, output, 4, sz4, 4) && tensor_resize(s, indices, 4, sz4, 8))) {
+            TH_CALL(s, cunn_b200_maxpool_forward(tdata<float>(x), tdata<float>(output), tdata<int64_t>(indices), (int)N, (int)C, (int)H, (int)W, kH,
+                                                 kW, dH, dW, padH, padW, 1, 1, ceil_mode, s->stream));
+            if (nd == 3) tensor_resize(s, output, 3, sz4 + 1, 4);   // indices stay 4-D, as in the reference
+        }
+    }
+done:
+    tensor_free(x);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialMaxPooling_updateGradInput(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput,
+                                                                    THCudaTensor *gradInput, THCudaLongTensor *indices, int kW,
+                                                                    int kH, int dW, int dH, int padW, int padH, bool ceil_mode)
+{
+    const int nd = input->nDimension;
+    TH_CHECK(s, nd == 3 || nd == 4, "3D or 4D input tensor expected but got: %s", size_desc(input).c_str());
+    const int b = nd == 4;
+    const long N = b ? input->size[0] : 1, C = input->size[b], H = input->size[b + 1], W = input->size[b + 2];
+    const long oH = cunn_b200_maxpool_out_size((int)H, kH, dH, padH, 1, ceil_mode), oW = cunn_b200_maxpool_out_size((int)W, kW, dW, padW, 1, ceil_mode);
+    TH_CHECK(s, gradOutput->nDimension == nd && gradOutput->size[b] == C && gradOutput->size[b + 1] == oH && gradOutput->size[b + 2] == oW,
+             "Need gradOutput of dimension %d and shape [.. x %ld x %ld x %ld] but got gradOutput to be of shape: %s", nd, C, oH, oW,
+             size_desc(gradOutput).c_str());
+    TH_CHECK(s, nelem(indices) == nelem(gradOutput) && is_contiguous(indices), "indices and gradOutput shapes do not match");
+    THCudaTensor *gy = new_contiguous(s, gradOutput);
+    if (gy && tensor_resize(s, gradInput, nd, input->size, 4))
+        TH_CALL(s, cunn_b200_maxpool_backward(tdata<float>(gy), tdata<int64_t>(indices), tdata<float>(gradInput), (int)N, (int)C, (int)H, (int)W,
+                                              kH, kW, dH, dW, padH, padW, 1, 1, ceil_mode, s->stream));
+done:
+    tensor_free(gy);
+}
+
+// ---- support operators ---------------------------------------------------------------------------------------
+extern "C" CUNN_API void THNN_CudaThreshold_updateOutput(THCState *s, THCudaTensor *input, THCudaTensor *output, float threshold,
+                                                         float val, bool inplace)
+{
+    if (inplace) {
+        TH_CHECK(s, is_contiguous(input), "in-place Threshold needs a contiguous input");
+        if (cunn_b200_threshold_forward(tdata<float>(input), tdata<float>(input), nelem(input), threshold, val, s->stream)) raise(s, "%s", cunn_b200_last_error());
+        // the reference makes output share input's storage (THCTensor_set); callers keep using `input`
+        return;
+    }
+    THCudaTensor *x = new_contiguous(s, input);
+    if (x && tensor_resize(s, output, input->nDimension, input->size, 4))
+        TH_CALL(s, cunn_b200_threshold_forward(tdata<float>(x), tdata<float>(output), nelem(input), threshold, val, s->stream));
+done:
+    tensor_free(x);
+}
+
+extern "C" CUNN_API void THNN_CudaThreshold_updateGradInput(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput,
+                                                            THCudaTensor *gradInput, float threshold, float, bool inplace)
+{
+    TH_CHECK(s, nelem(input) == nelem(gradOutput), "input and gradOutput have different number of elements");
+    THCudaTensor *x = new_contiguous(s, input), *gy = new_contiguous(s, gradOutput);
+    if (x && gy) {
+        if (inplace) {
+            if (gy != gradOutput) raise(s, "in-place Threshold needs a contiguous gradOutput");
+            else TH_CALL(s, cunn_b200_threshold_backward(tdata<float>(x), tdata<float>(gy), tdata<float>(gy), nelem(input), threshold, s->stream));
+        } else if (tensor_resize(s, gradInput, input->nDimension, input->size, 4)) {
+            TH_CALL(s, cunn_b200_threshold_backward(tdata<float>(x), tdata<float>(gy), tdata<float>(gradInput), nelem(input), threshold, s->stream));
+        }
+    }
+done:
+    tensor_free(x); tensor_free(gy);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialAveragePooling_updateOutput(THCState *s, THCudaTensor *input, THCudaTensor *output, int kW,
+                                                                     int kH, int dW, int dH, int padW, int padH, bool ceil_mode,
+                                                                     bool count_include_pad)
+{
+    const int nd = input->nDimension;
+    TH_CHECK(s, nd == 3 || nd == 4, "3D or 4D input tensor expected but got: %s", size_desc(input).c_str());
+    TH_CHECK(s, kW > 0 && kH > 0 && dW > 0 && dH > 0, "kernel size and stride should be greater than zero");
+    const int b = nd == 4;
+    const long N = b ? input->size[0] : 1, C = input->size[b], H = input->size[b + 1], W = input->size[b + 2];
+    const long oH = cunn_b200_maxpool_out_size((int)H, kH, dH, padH, 1, ceil_mode), oW = cunn_b200_maxpool_out_size((int)W, kW, dW, padW, 1, ceil_mode);
+    TH_CHECK(s, oH >= 1 && oW >= 1, "Given input size: (%ldx%ldx%ld). Calculated output size: (%ldx%ldx%ld). Output size is too small", C, H, W, C, oH, oW);
+    THCudaTensor *x = new_contiguous(s, input);
+    const long sz4[4] = {N, C, oH, oW};
+    if (x && tensor_resize(s, output, 4, sz4, 4)) {
+        TH_CALL(s, cunn_b200_avgpool_forward(tdata<float>(x), tdata<float>(output), (int)N, (int)C, (int)H, (int)W, (int)oH, (int)oW, kH, kW, dH, dW,
+                                             padH, padW, count_include_pad, s->stream));
+        if (nd == 3) tensor_resize(s, output, 3, sz4 + 1, 4);
+    }
+done:
+    tensor_free(x);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialAveragePooling_updateGradInput(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput,
+                                                                        THCudaTensor *gradInput, int kW, int kH, int dW, int dH,
+                                                                        int padW, int padH, bool ceil_mode, bool count_include_pad)
+{
+    const int nd = input->nDimension;
+    TH_CHECK(s, nd == 3 || nd == 4, "3D or 4D input tensor expected but got: %s", size_desc(input).c_str());
+    const int b = nd == 4;
+    const long N = b ? input->size[0] : 1, C = input->size[b], H = input->size[b + 1], W = input->size[b + 2];
+    const long oH = cunn_b200_maxpool_out_size((int)H, kH, dH, padH, 1, ceil_mode), oW = cunn_b200_maxpool_out_size((int)W, kW, dW, padW, 1, ceil_mode);
+    TH_CHECK(s, gradOutput->nDimension == nd && gradOutput->size[b + 1] == oH && gradOutput->size[b + 2] == oW,
+             "gradOutput has the wrong shape: %s", size_desc(gradOutput).c_str());
+    THCudaTensor *gy = new_contiguous(s, gradOutput);
+    if (gy && tensor_resize(s, gradInput, nd, input->size, 4))
+        TH_CALL(s, cunn_b200_avgpool_backward(tdata<float>(gy), tdata<float>(gradInput), (int)N, (int)C, (int)H, (int)W, (int)oH, (int)oW, kH, kW, dH,
+                                              dW, padH, padW, count_include_pad, s->stream));
+done:
+    tensor_free(gy);
+}
+
+extern "C" CUNN_API void THNN_CudaLogSoftMax_updateOutput(THCState *s, THCudaTensor *input, THCudaTensor *output)
+{
+    TH_CHECK(s, input->nDimension == 1 || input->nDimension == 2, "vector or matrix expected");
+    const long B = input->nDimension == 2 ? input->size[0] : 1, D = input->size[input->nDimension - 1];
+    THCudaTensor *x = new_contiguous(s, input);
+    if (x && tensor_resize(s, output, input->nDimension, input->size, 4))
+        TH_CALL(s, cunn_b200_logsoftmax_forward(tdata<float>(x), tdata<float>(output), (int)B, (int)D, s->stream));
+done:
+    tensor_free(x);
+}
+
+extern "C" CUNN_API void THNN_CudaLogSoftMax_updateGradInput(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput,
+                                                             THCudaTensor *gradInput, THCudaTensor *output)
+{
+    TH_CHECK(s, output->nDimension == 1 || output->nDimension == 2, "vector or matrix expected");
+    TH_CHECK(s, nelem(output) == nelem(gradOutput), "output and gradOutput have different number of elements");
+    const long B = output->nDimension == 2 ? output->size[0] : 1, D = output->size[output->nDimension - 1];
+    THCudaTensor *y = new_contiguous(s, output), *gy = new_contiguous(s, gradOutput);
+    if (y && gy && tensor_resize(s, gradInput, output->nDimension, output->size, 4))
+        TH_CALL(s, cunn_b200_logsoftmax_backward(tdata<float>(y), tdata<float>(gy), tdata<float>(gradInput), (int)B, (int)D, s->stream));
+done:
+    (void)input;
+    tensor_free(y); tensor_free(gy);
+}
+
+extern "C" CUNN_API void THNN_CudaClassNLLCriterion_updateOutput(THCState *s, THCudaTensor *input, THCudaLongTensor *target,
+                                                                 THCudaTensor *output, bool sizeAverage, THCudaTensor *weights,
+                                                                 THCudaTensor *total_weight, long ignore_index)
+{
+    TH_CHECK(s, input->nDimension == 1 || input->nDimension == 2, "input tensor should be 1D or 2D");
+    const long B = input->nDimension == 2 ? input->size[0] : 1, D = input->size[input->nDimension - 1];
+    TH_CHECK(s, nelem(target) == B, "mismatch between the batch size of input (%ld) and that of target (%td)", B, nelem(target));
+    TH_CHECK(s, !weights || nelem(weights) == D, "weight tensor should be defined either for all %ld classes or no classes", D);
+    TH_CHECK(s, is_contiguous(input) && is_contiguous(target) && (!weights || is_contiguous(weights)), "input, target and weights have to be contiguous");
+    const long one[1] = {1};
+    if (!(tensor_resize(s, output, 1, one, 4) && tensor_resize(s, total_weight, 1, one, 4))) return;
+    // the flat ABI writes loss and total weight side by side; route them through the state's scratch
+    float *pair = (float *)state_scratch(s, 0, 16);
+    if (!pair) return;
+    if (cunn_b200_classnll_forward(tdata<float>(input), tdata<int64_t>(target), weights ? tdata<float>(weights) : nullptr, pair, (int)B, (int)D,
+                                   sizeAverage, ignore_index, s->stream)) {
+        raise(s, "%s", cunn_b200_last_error());
+        return;
+    }
+    cudaMemcpyAsync(tdata<float>(output), pair, 4, cudaMemcpyDeviceToDevice, s->stream);
+    cudaMemcpyAsync(tdata<float>(total_weight), pair + 1, 4, cudaMemcpyDeviceToDevice, s->stream);
+}
+
+extern "C" CUNN_API void THNN_CudaClassNLLCriterion_updateGradInput(THCState *s, THCudaTensor *input, THCudaLongTensor *target,
+                                                                    THCudaTensor *gradInput, bool sizeAverage, THCudaTensor *weights,
+                                                                    THCudaTensor *total_weight, long ignore_index)
+{
+    TH_CHECK(s, input->nDimension == 1 || input->nDimension == 2, "input tensor should be 1D or 2D");
+    const long B = input->nDimension == 2 ? input->size[0] : 1, D = input->size[input->nDimension - 1];
+    TH_CHECK(s, nelem(target) == B, "mismatch between the batch size of input (%ld) and that of target (%td)", B, nelem(target));
+    // gradInput is NOT zeroed here: nn.ClassNLLCriterion resizes and zeroes it before the call
+    TH_CHECK(s, nelem(gradInput) == nelem(input) && is_contiguous(gradInput), "gradInput must be contiguous and of input's size");
+    if (cunn_b200_classnll_backward(tdata<int64_t>(target), weights ? tdata<float>(weights) : nullptr, tdata<float>(total_weight), tdata<float>(gradInput),
+                                    (int)B, (int)D, sizeAverage, ignore_index, s->stream))
+        raise(s, "%s", cunn_b200_last_error());
+}

@@ -1,0 +1,140 @@
+/*
+ * THNN_Cuda* entry points of libTHCUNN.so — the symbols the reference's LuaJIT FFI binding looks up
+ * (THCUNN.lua:129-138) — for the convolutional hot path, with the reference's signatures
+ * (lib/THCUNN/generic/THCUNN.h).  `accreal` is `float` for the Cuda type (THCUNN.lua:48).
+ *
+ * The tensor and storage structs restate the public layout of cutorch 1.0's THCTensor.h / THCStorage.h.
+ * cutorch is not part of the reference tree and is absent from this image, so binary compatibility with
+ * a real Lua-Torch install could not be verified; inside a cutorch build compile the entry points against
+ * the real <THC/THC.h> instead (define CUNN_B200_USE_REAL_THC before including this header).
+ *
+ * The small THCudaTensor_* / THCState_* helper set below is what a C harness needs to drive the entry
+ * points without cutorch; it is not a reimplementation of libTHC.
+ */
+#ifndef THCUNN_B200_H
+#define THCUNN_B200_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "cunn_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef CUNN_B200_USE_REAL_THC
+typedef struct THCudaStorage {
+    void *data;                 /* float* (THCudaStorage) or long* (THCudaLongStorage) */
+    ptrdiff_t size;             /* elements */
+    int refcount;
+    char flag;
+    void *allocator;
+    void *allocatorContext;
+    struct THCudaStorage *view;
+    int device;
+} THCudaStorage;
+
+typedef struct THCudaTensor {
+    long *size;
+    long *stride;
+    int nDimension;
+    THCudaStorage *storage;
+    ptrdiff_t storageOffset;
+    int refcount;
+    char flag;
+} THCudaTensor;
+
+typedef THCudaTensor THCudaLongTensor;   /* same layout, 8-byte elements */
+typedef struct THCState THCState;        /* opaque here: current stream, error hook, scratch */
+#endif
+
+/* ---- harness helpers ---------------------------------------------------------------------------- */
+CUNN_API THCState *THCState_b200_new(void);
+CUNN_API void THCState_b200_free(THCState *state);
+CUNN_API void THCState_b200_setStream(THCState *state, cunn_stream_t stream);
+/* Error hook, the counterpart of TH's THError handler.  Argument and launch errors are reported through it
+ * (under Lua it raises a Lua error and does not return).  If it returns, the entry point returns at once.
+ * The default hook prints the message to stderr. */
+typedef void (*THCUNN_b200_error_fn)(const char *msg, void *ctx);
+CUNN_API void THCState_b200_setErrorHandler(THCState *state, THCUNN_b200_error_fn fn, void *ctx);
+CUNN_API const char *THCState_b200_lastError(THCState *state);
+
+CUNN_API THCudaTensor *THCudaTensor_b200_new(THCState *state);                    /* empty, 0 dimensions */
+CUNN_API THCudaLongTensor *THCudaLongTensor_b200_new(THCState *state);
+/* A tensor over caller-owned device memory (never freed or reallocated by the library; a resize that does
+ * not fit raises an error).  sizes/strides in elements; strides == NULL means contiguous. */
+CUNN_API THCudaTensor *THCudaTensor_b200_wrap(THCState *state, void *data, ptrdiff_t capacity_elems, int ndim,
+                                              const long *sizes, const long *strides, int elem_size);
+CUNN_API void THCudaTensor_b200_free(THCState *state, THCudaTensor *t);
+CUNN_API void *THCudaTensor_b200_data(THCState *state, THCudaTensor *t);
+
+/* ---- hot path (float) ---------------------------------------------------------------------------- */
+CUNN_API void THNN_CudaSpatialDepthWiseConvolution_updateOutput(
+    THCState *state, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias,
+    THCudaTensor *columns, THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH);
+CUNN_API void THNN_CudaSpatialDepthWiseConvolution_updateGradInput(
+    THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight,
+    THCudaTensor *gradColumns, THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH);
+CUNN_API void THNN_CudaSpatialDepthWiseConvolution_accGradParameters(
+    THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias,
+    THCudaTensor *columns, THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH, float scale);
+
+CUNN_API void THNN_CudaSpatialConvolutionMM_updateOutput(
+    THCState *state, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias,
+    THCudaTensor *columns, THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH);
+CUNN_API void THNN_CudaSpatialConvolutionMM_updateGradInput(
+    THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight,
+    THCudaTensor *gradColumns, THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH);
+CUNN_API void THNN_CudaSpatialConvolutionMM_accGradParameters(
+    THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias,
+    THCudaTensor *columns, THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH, float scale);
+
+CUNN_API void THNN_CudaBatchNormalization_updateOutput(
+    THCState *state, THCudaTensor *input_, THCudaTensor *output_, THCudaTensor *weight_, THCudaTensor *bias_,
+    THCudaTensor *runningMean_, THCudaTensor *runningVar_, THCudaTensor *saveMean_, THCudaTensor *saveStd_,
+    bool train, double momentum, double eps);
+CUNN_API void THNN_CudaBatchNormalization_backward(
+    THCState *state, THCudaTensor *input_, THCudaTensor *gradOutput_, THCudaTensor *gradInput_,
+    THCudaTensor *gradWeight_, THCudaTensor *gradBias_, THCudaTensor *weight_, THCudaTensor *runningMean_,
+    THCudaTensor *runningVar_, THCudaTensor *saveMean_, THCudaTensor *saveStd_, bool train, double scale, double eps);
+
+CUNN_API void THNN_CudaSpatialMaxPooling_updateOutput(
+    THCState *state, THCudaTensor *input, THCudaTensor *output, THCudaLongTensor *indices, int kW, int kH, int dW,
+    int dH, int padW, int padH, bool ceil_mode);
+CUNN_API void THNN_CudaSpatialMaxPooling_updateGradInput(
+    THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaLongTensor *indices,
+    int kW, int kH, int dW, int dH, int padW, int padH, bool ceil_mode);
+
+/* ---- support operators (float) --------------------------------------------------------------------- */
+CUNN_API void THNN_CudaThreshold_updateOutput(THCState *state, THCudaTensor *input, THCudaTensor *output,
+                                              float threshold, float val, bool inplace);
+CUNN_API void THNN_CudaThreshold_updateGradInput(THCState *state, THCudaTensor *input, THCudaTensor *gradOutput,
+                                                 THCudaTensor *gradInput, float threshold, float val, bool inplace);
+CUNN_API void THNN_CudaSpatialAveragePooling_updateOutput(THCState *state, THCudaTensor *input, THCudaTensor *output,
+                                                          int kW, int kH, int dW, int dH, int padW, int padH,
+                                                          bool ceil_mode, bool count_include_pad);
+CUNN_API void THNN_CudaSpatialAveragePooling_updateGradInput(THCState *state, THCudaTensor *input,
+                                                             THCudaTensor *gradOutput, THCudaTensor *gradInput, int kW,
+                                                             int kH, int dW, int dH, int padW, int padH, bool ceil_mode,
+                                                             bool count_include_pad);
+CUNN_API void THNN_CudaLogSoftMax_updateOutput(THCState *state, THCudaTensor *input, THCudaTensor *output);
+CUNN_API void THNN_CudaLogSoftMax_updateGradInput(THCState *state, THCudaTensor *input, THCudaTensor *gradOutput,
+                                                  THCudaTensor *gradInput, THCudaTensor *output);
+CUNN_API void THNN_CudaClassNLLCriterion_updateOutput(THCState *state, THCudaTensor *input, THCudaLongTensor *target,
+                                                      THCudaTensor *output, bool sizeAverage, THCudaTensor *weights,
+                                                      THCudaTensor *total_weight, long ignore_index);
+CUNN_API void THNN_CudaClassNLLCriterion_updateGradInput(THCState *state, THCudaTensor *input, THCudaLongTensor *target,
+                                                         THCudaTensor *gradInput, bool sizeAverage,
+                                                         THCudaTensor *weights, THCudaTensor *total_weight,
+                                                         long ignore_index);
+
+/* Every other THNN_Cuda<Op>_<method> and every THNN_CudaDouble<Op>_<method> name of the reference header is
+ * exported too, so the binding's symbol lookup cannot fail, but only reports "not implemented in this
+ * build" through the error hook of the state it is given. */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* THCUNN_B200_H */
