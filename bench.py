@@ -34,9 +34,10 @@ BATCH = 64
 SEED = 1234
 METRIC = "dwconv_fwd_bwd_hbm_gbs"
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum, MB) of one launch of the kernel that
-# `roofline` reports, from the ncu capture summarised in profiles/; None until captured.
-NCU_TRAFFIC_MB = {}
+# DRAM traffic (read + write, MB) of one launch of the kernels that can top the per-launch time, from the
+# ncu capture summarised in profiles/dwconv_stack_ncu_sections.md (key: "<op>_<layer>").
+NCU_TRAFFIC_MB = {"wgrad_2": 264.3, "wgrad_1": 210.2, "fwd_2": 238.0, "dgrad_2": 200.7, "fwd_1": 154.6,
+                  "wgrad_3": 211.1}
 
 
 def out_size(hw, stride):
