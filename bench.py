@@ -449,19 +449,35 @@ def main():
         h2d = sum(h["x"].numel() + h["gy"].numel() for h in H) * 4
         d2h = sum(h["y"].numel() + h["gx"].numel() for h in H) * 4 + nparams * 4
 
+        # Three streams: host->device copies, kernels, device->host copies.  PCIe is full duplex, so layer
+        # i's results travel back while layer i+1's inputs travel in; events order copy -> compute -> copy.
+        s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        s_cmp = torch.cuda.current_stream()
+
         def e2e_step():
+            s_in.wait_stream(s_cmp)
+            s_out.wait_stream(s_cmp)
             for t, h in zip(T, H):
-                t["x"].copy_(h["x"], non_blocking=True)
-                t["gy"].copy_(h["gy"], non_blocking=True)
+                with torch.cuda.stream(s_in):
+                    t["x"].copy_(h["x"], non_blocking=True)
+                    t["gy"].copy_(h["gy"], non_blocking=True)
+                    ev_in = torch.cuda.Event()
+                    ev_in.record(s_in)
+                s_cmp.wait_event(ev_in)
                 fwd(t)
                 dgrad(t)
                 wgrad(t)
-                h["y"].copy_(t["y"], non_blocking=True)
-                h["gx"].copy_(t["gx"], non_blocking=True)
+                ev_c = torch.cuda.Event()
+                ev_c.record(s_cmp)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_c)
+                    h["y"].copy_(t["y"], non_blocking=True)
+                    h["gx"].copy_(t["gx"], non_blocking=True)
             if world > 1:
                 dist.all_reduce(flat_grad)
             hgrad.copy_(flat_grad, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            s_cmp.wait_stream(s_out)
+            s_cmp.synchronize()
 
         e2e_step()
         if world > 1:

@@ -44,6 +44,8 @@ _decl("cunn_b200_maxpool_forward", c_int, [c_void_p] * 3 + [c_int] * 13 + [c_voi
 _decl("cunn_b200_maxpool_backward", c_int, [c_void_p] * 3 + [c_int] * 13 + [c_void_p])
 _decl("cunn_b200_batchnorm_workspace", c_size_t, [c_int, c_int])
 _decl("cunn_b200_batchnorm_forward", c_int, [c_void_p] * 8 + [c_int] * 4 + [c_double, c_double, c_void_p, c_size_t, c_void_p])
+_decl("cunn_b200_batchnorm_relu_forward", c_int, [c_void_p] * 8 + [c_int] * 4 + [c_double, c_double, c_void_p, c_size_t, c_void_p])
+_decl("cunn_b200_batchnorm_relu_backward", c_int, [c_void_p] * 11 + [c_int] * 4 + [c_double, c_double, c_void_p, c_size_t, c_void_p])
 _decl("cunn_b200_batchnorm_backward", c_int, [c_void_p] * 10 + [c_int] * 4 + [c_double, c_double, c_void_p, c_size_t, c_void_p])
 c_longlong = ctypes.c_longlong
 _decl("cunn_b200_threshold_forward", c_int, [c_void_p, c_void_p, c_longlong, c_float, c_float, c_void_p])
@@ -56,6 +58,8 @@ _decl("cunn_b200_classnll_forward", c_int, [c_void_p] * 4 + [c_int, c_int, c_int
 _decl("cunn_b200_classnll_backward", c_int, [c_void_p] * 4 + [c_int, c_int, c_int, c_longlong, c_void_p])
 _decl("cunn_b200_fill", c_int, [c_void_p, c_longlong, c_float, c_void_p])
 _decl("cunn_b200_sgd_update", c_int, [c_void_p, c_void_p, c_longlong, c_float, c_void_p])
+_decl("cunn_b200_set_deterministic", None, [c_int])
+_decl("cunn_b200_get_deterministic", c_int, [])
 _decl("cunn_b200_dwconv_tuning", None, [ctypes.POINTER(c_int), c_int])
 _decl("cunn_b200_dwconv_describe_plan", c_int, [c_int] * 6 + [ctypes.c_char_p, c_int])
 

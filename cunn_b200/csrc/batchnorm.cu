@@ -123,11 +123,13 @@ stats_finish_kernel(const ChunkStat *__restrict__ part, int C, int chunks, float
 
 // y = gamma * (x - mean) * invstd + beta, per plane.  Training reads mean / invstd from save_*, inference
 // derives them from the running statistics.
+template <bool RELU>
 __global__ void __launch_bounds__(256)
 apply_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__restrict__ weight,
              const float *__restrict__ bias, const float *__restrict__ mean_v, const float *__restrict__ std_or_var,
              int train, float eps, int C, int S, long long planes)
 {
+    auto act = [](float v) { return RELU ? (v > 0.f ? v : 0.f) : v; };
     const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)y) & 15) == 0);
     // a CTA walks planes; threads walk the plane
     for (long long pl = blockIdx.x; pl < planes; pl += gridDim.x) {
@@ -145,22 +147,23 @@ apply_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__
             for (int i = threadIdx.x; i < S / 4; i += blockDim.x) {
                 const float4 v = __ldg(x4 + i);
                 float4 o;
-                o.x = g * (v.x - mean) * invstd + b;
-                o.y = g * (v.y - mean) * invstd + b;
-                o.z = g * (v.z - mean) * invstd + b;
-                o.w = g * (v.w - mean) * invstd + b;
+                o.x = act(g * (v.x - mean) * invstd + b);
+                o.y = act(g * (v.y - mean) * invstd + b);
+                o.z = act(g * (v.z - mean) * invstd + b);
+                o.w = act(g * (v.w - mean) * invstd + b);
                 y4[i] = o;
             }
         } else {
-            for (int i = threadIdx.x; i < S; i += blockDim.x) yp[i] = g * (__ldg(xp + i) - mean) * invstd + b;
+            for (int i = threadIdx.x; i < S; i += blockDim.x) yp[i] = act(g * (__ldg(xp + i) - mean) * invstd + b);
         }
     }
 }
 
 // Backward, pass 1: per (channel, chunk) sums of gy and gy * (x - mean).
+template <bool RELU>
 __global__ void __launch_bounds__(256)
-grad_stats_kernel(const float *__restrict__ x, const float *__restrict__ gy, float2 *__restrict__ part,
-                  const float *__restrict__ mean_v, int N, int C, int S, int chunks)
+grad_stats_kernel(const float *__restrict__ x, const float *__restrict__ gy, const float *__restrict__ yact,
+                  float2 *__restrict__ part, const float *__restrict__ mean_v, int N, int C, int S, int chunks)
 {
     __shared__ float sh[8];
     const int c = blockIdx.x / chunks, j = blockIdx.x % chunks;
@@ -168,7 +171,7 @@ grad_stats_kernel(const float *__restrict__ x, const float *__restrict__ gy, flo
     chunk_range(N, chunks, j, &n0, &n1);
     const float mean = __ldg(mean_v + c);
     float s = 0.f, d = 0.f;
-    const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)gy) & 15) == 0);
+    const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)gy | (uintptr_t)yact) & 15) == 0);
     for (int n = n0; n < n1; ++n) {
         const size_t off = ((size_t)n * C + c) * S;
         if (vec) {
@@ -176,14 +179,20 @@ grad_stats_kernel(const float *__restrict__ x, const float *__restrict__ gy, flo
             const float4 *g4 = reinterpret_cast<const float4 *>(gy + off);
 #pragma unroll 4
             for (int i = threadIdx.x; i < S / 4; i += blockDim.x) {
-                const float4 v = __ldg(x4 + i), g = __ldg(g4 + i);
+                const float4 v = __ldg(x4 + i);
+                float4 g = __ldg(g4 + i);
+                if (RELU) {   // gradient of the fused ReLU: pass only where the activation was positive
+                    const float4 a = __ldg(reinterpret_cast<const float4 *>(yact + off) + i);
+                    g.x = a.x > 0.f ? g.x : 0.f; g.y = a.y > 0.f ? g.y : 0.f; g.z = a.z > 0.f ? g.z : 0.f; g.w = a.w > 0.f ? g.w : 0.f;
+                }
                 s += (g.x + g.y) + (g.z + g.w);
                 d = fmaf(g.x, v.x - mean, d); d = fmaf(g.y, v.y - mean, d);
                 d = fmaf(g.z, v.z - mean, d); d = fmaf(g.w, v.w - mean, d);
             }
         } else {
             for (int i = threadIdx.x; i < S; i += blockDim.x) {
-                const float g = __ldg(gy + off + i);
+                float g = __ldg(gy + off + i);
+                if (RELU) g = __ldg(yact + off + i) > 0.f ? g : 0.f;
                 s += g;
                 d = fmaf(g, __ldg(x + off + i) - mean, d);
             }
@@ -231,11 +240,12 @@ grad_finish_kernel(const float2 *__restrict__ part, int C, int chunks, long long
 }
 
 // Backward, pass 3: the input gradient.
+template <bool RELU>
 __global__ void __launch_bounds__(256)
-grad_apply_kernel(const float *__restrict__ x, const float *__restrict__ gy, float *__restrict__ gx,
-                  const GradCoef *__restrict__ coef, int train, int C, int S, long long planes)
+grad_apply_kernel(const float *__restrict__ x, const float *__restrict__ gy, const float *__restrict__ yact,
+                  float *__restrict__ gx, const GradCoef *__restrict__ coef, int train, int C, int S, long long planes)
 {
-    const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)gy | (uintptr_t)gx) & 15) == 0);
+    const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)gy | (uintptr_t)gx | (uintptr_t)yact) & 15) == 0);
     for (long long pl = blockIdx.x; pl < planes; pl += gridDim.x) {
         const GradCoef k = coef[pl % C];
         const float *xp = x + pl * S;
@@ -247,7 +257,11 @@ grad_apply_kernel(const float *__restrict__ x, const float *__restrict__ gy, flo
             float4 *o4 = reinterpret_cast<float4 *>(op);
 #pragma unroll 4
             for (int i = threadIdx.x; i < S / 4; i += blockDim.x) {
-                const float4 g = __ldg(g4 + i);
+                float4 g = __ldg(g4 + i);
+                if (RELU) {
+                    const float4 a = __ldg(reinterpret_cast<const float4 *>(yact + pl * S) + i);
+                    g.x = a.x > 0.f ? g.x : 0.f; g.y = a.y > 0.f ? g.y : 0.f; g.z = a.z > 0.f ? g.z : 0.f; g.w = a.w > 0.f ? g.w : 0.f;
+                }
                 float4 o;
                 if (train) {
                     const float4 v = __ldg(x4 + i);
@@ -262,7 +276,8 @@ grad_apply_kernel(const float *__restrict__ x, const float *__restrict__ gy, flo
             }
         } else {
             for (int i = threadIdx.x; i < S; i += blockDim.x) {
-                const float g = __ldg(gp + i);
+                float g = __ldg(gp + i);
+                if (RELU) g = __ldg(yact + pl * S + i) > 0.f ? g : 0.f;
                 op[i] = train ? (g - (__ldg(xp + i) - k.mean) * k.proj - k.gmean) * k.gscale : g * k.gscale;
             }
         }
@@ -295,11 +310,10 @@ extern "C" CUNN_API size_t cunn_b200_batchnorm_workspace(int N, int C)
     return (size_t)C * chunks * sizeof(ChunkStat) + (size_t)C * sizeof(GradCoef) + 256;
 }
 
-extern "C" CUNN_API int cunn_b200_batchnorm_forward(const float *x, float *y, const float *weight, const float *bias,
-                                                    float *running_mean, float *running_var, float *save_mean,
-                                                    float *save_std, int N, int C, int S, int train, double momentum,
-                                                    double eps, void *workspace, size_t workspace_bytes,
-                                                    cunn_stream_t stream_)
+static int bn_forward_impl(const float *x, float *y, const float *weight, const float *bias, float *running_mean,
+                           float *running_var, float *save_mean, float *save_std, int N, int C, int S, int train,
+                           double momentum, double eps, void *workspace, size_t workspace_bytes, cunn_stream_t stream_,
+                           bool relu)
 {
     clear_error();
     cudaStream_t stream = (cudaStream_t)stream_;
@@ -321,22 +335,40 @@ extern "C" CUNN_API int cunn_b200_batchnorm_forward(const float *x, float *y, co
         stats_finish_kernel<<<ceil_div(C, 128), 128, 0, stream>>>(part, C, chunks, running_mean, running_var, save_mean,
                                                                  save_std, momentum, eps);
         CUNN_LAUNCH_CHECK("batch norm statistics finish");
-        apply_kernel<<<plane_grid(planes), 256, 0, stream>>>(x, y, weight, bias, save_mean, save_std, 1, (float)eps, C, S,
-                                                            planes);
+        if (relu) apply_kernel<true><<<plane_grid(planes), 256, 0, stream>>>(x, y, weight, bias, save_mean, save_std, 1, (float)eps, C, S, planes);
+        else apply_kernel<false><<<plane_grid(planes), 256, 0, stream>>>(x, y, weight, bias, save_mean, save_std, 1, (float)eps, C, S, planes);
     } else {
-        apply_kernel<<<plane_grid(planes), 256, 0, stream>>>(x, y, weight, bias, running_mean, running_var, 0, (float)eps,
-                                                            C, S, planes);
+        if (relu) apply_kernel<true><<<plane_grid(planes), 256, 0, stream>>>(x, y, weight, bias, running_mean, running_var, 0, (float)eps, C, S, planes);
+        else apply_kernel<false><<<plane_grid(planes), 256, 0, stream>>>(x, y, weight, bias, running_mean, running_var, 0, (float)eps, C, S, planes);
     }
     CUNN_LAUNCH_CHECK("batch norm apply");
     return 0;
 }
 
-extern "C" CUNN_API int cunn_b200_batchnorm_backward(const float *x, const float *gy, float *gx, float *grad_weight,
-                                                     float *grad_bias, const float *weight, const float *running_mean,
-                                                     const float *running_var, const float *save_mean,
-                                                     const float *save_std, int N, int C, int S, int train, double scale,
-                                                     double eps, void *workspace, size_t workspace_bytes,
-                                                     cunn_stream_t stream_)
+extern "C" CUNN_API int cunn_b200_batchnorm_forward(const float *x, float *y, const float *weight, const float *bias,
+                                                    float *running_mean, float *running_var, float *save_mean,
+                                                    float *save_std, int N, int C, int S, int train, double momentum,
+                                                    double eps, void *workspace, size_t workspace_bytes,
+                                                    cunn_stream_t stream)
+{
+    return bn_forward_impl(x, y, weight, bias, running_mean, running_var, save_mean, save_std, N, C, S, train, momentum, eps,
+                           workspace, workspace_bytes, stream, false);
+}
+
+extern "C" CUNN_API int cunn_b200_batchnorm_relu_forward(const float *x, float *y, const float *weight, const float *bias,
+                                                         float *running_mean, float *running_var, float *save_mean,
+                                                         float *save_std, int N, int C, int S, int train, double momentum,
+                                                         double eps, void *workspace, size_t workspace_bytes,
+                                                         cunn_stream_t stream)
+{
+    return bn_forward_impl(x, y, weight, bias, running_mean, running_var, save_mean, save_std, N, C, S, train, momentum, eps,
+                           workspace, workspace_bytes, stream, true);
+}
+
+static int bn_backward_impl(const float *x, const float *gy, const float *yact, float *gx, float *grad_weight,
+                            float *grad_bias, const float *weight, const float *running_mean, const float *running_var,
+                            const float *save_mean, const float *save_std, int N, int C, int S, int train, double scale,
+                            double eps, void *workspace, size_t workspace_bytes, cunn_stream_t stream_)
 {
     clear_error();
     cudaStream_t stream = (cudaStream_t)stream_;
@@ -360,7 +392,8 @@ extern "C" CUNN_API int cunn_b200_batchnorm_backward(const float *x, const float
     // inference-mode input gradient needs no sums; they are still required for gradWeight / gradBias
     const bool need_sums = train || grad_weight || grad_bias;
     if (need_sums) {
-        grad_stats_kernel<<<C * chunks, 256, 0, stream>>>(x, gy, part, mean_v, N, C, S, chunks);
+        if (yact) grad_stats_kernel<true><<<C * chunks, 256, 0, stream>>>(x, gy, yact, part, mean_v, N, C, S, chunks);
+        else grad_stats_kernel<false><<<C * chunks, 256, 0, stream>>>(x, gy, nullptr, part, mean_v, N, C, S, chunks);
         CUNN_LAUNCH_CHECK("batch norm gradient sums");
     } else {
         CUNN_CUDA(cudaMemsetAsync(part, 0, (size_t)C * chunks * sizeof(float2), stream));
@@ -369,8 +402,33 @@ extern "C" CUNN_API int cunn_b200_batchnorm_backward(const float *x, const float
                                                             eps, scale, grad_weight, grad_bias, coef);
     CUNN_LAUNCH_CHECK("batch norm gradient finish");
     if (gx) {
-        grad_apply_kernel<<<plane_grid(planes), 256, 0, stream>>>(x, gy, gx, coef, train, C, S, planes);
+        if (yact) grad_apply_kernel<true><<<plane_grid(planes), 256, 0, stream>>>(x, gy, yact, gx, coef, train, C, S, planes);
+        else grad_apply_kernel<false><<<plane_grid(planes), 256, 0, stream>>>(x, gy, nullptr, gx, coef, train, C, S, planes);
         CUNN_LAUNCH_CHECK("batch norm input gradient");
     }
     return 0;
+}
+
+extern "C" CUNN_API int cunn_b200_batchnorm_backward(const float *x, const float *gy, float *gx, float *grad_weight,
+                                                     float *grad_bias, const float *weight, const float *running_mean,
+                                                     const float *running_var, const float *save_mean,
+                                                     const float *save_std, int N, int C, int S, int train, double scale,
+                                                     double eps, void *workspace, size_t workspace_bytes,
+                                                     cunn_stream_t stream)
+{
+    return bn_backward_impl(x, gy, nullptr, gx, grad_weight, grad_bias, weight, running_mean, running_var, save_mean, save_std,
+                            N, C, S, train, scale, eps, workspace, workspace_bytes, stream);
+}
+
+extern "C" CUNN_API int cunn_b200_batchnorm_relu_backward(const float *x, const float *y, const float *gy, float *gx,
+                                                          float *grad_weight, float *grad_bias, const float *weight,
+                                                          const float *running_mean, const float *running_var,
+                                                          const float *save_mean, const float *save_std, int N, int C,
+                                                          int S, int train, double scale, double eps, void *workspace,
+                                                          size_t workspace_bytes, cunn_stream_t stream)
+{
+    clear_error();
+    CUNN_CHECK_ARG(y || N == 0, "the fused BN+ReLU backward needs the forward output y");
+    return bn_backward_impl(x, gy, y, gx, grad_weight, grad_bias, weight, running_mean, running_var, save_mean, save_std, N, C,
+                            S, train, scale, eps, workspace, workspace_bytes, stream);
 }

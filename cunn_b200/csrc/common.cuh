@@ -108,6 +108,13 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uin
         : "memory");
 }
 
+// Programmatic dependent launch (PDL).  launch_dependents: the next kernel in the stream, if it was launched
+// as a programmatic dependent, may be scheduled once every CTA of this grid has passed this point or exited.
+// wait: blocks until the grids this one depends on have completed and their memory is visible; a no-op
+// when the kernel was launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -190,6 +190,8 @@ struct FastParams {
     int stage2_floats;  // floats per stage for `in2`
     int out_floats;     // floats per output staging buffer (two buffers), 0 when stores are direct
     int flip;           // FWD: use the 180-degree rotated kernel (stride-1 input gradient)
+    int atomic_flush;   // WGRAD: add each CTA's per-plane sums to gw / gb with fp32 atomics (fast, order-dependent
+                        // rounding) instead of the ticketed fixed-order reduction (bit-reproducible)
 };
 
 template <int S, int VEC>
@@ -433,6 +435,34 @@ __device__ __forceinline__ void wgrad_flush(const FastParams &p, const float (&a
         for (int k = 0; k < 10; ++k) red[tid * 10 + k] = acc[k];
     }
     __syncthreads();
+    if (p.atomic_flush) {
+        // fire-and-forget: scale * (sum over this CTA's items of the plane) straight into gw / gb
+        const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
+        if (per_plane <= 16) {
+            for (int pair = tid; pair < p.P * 10; pair += blockDim.x) {
+                const int ppl = pair / 10, k = pair - ppl * 10;
+                const float *r = red + ppl * per_plane * 10 + k;
+                float s = 0.f;
+                for (int i = 0; i < per_plane; ++i) s += r[i * 10];
+                const int c = g * p.P + ppl;
+                if (k < 9) atomicAdd(p.gw + (size_t)c * 9 + k, p.scale * s);
+                else if (p.gb) atomicAdd(p.gb + c, p.scale * s);
+            }
+        } else {
+            for (int pair = warp; pair < p.P * 10; pair += nwarps) {
+                const int ppl = pair / 10, k = pair - ppl * 10;
+                float s = 0.f;
+                for (int i = lane; i < per_plane; i += 32) s += red[(ppl * per_plane + i) * 10 + k];
+                s = warp_sum(s);
+                const int c = g * p.P + ppl;
+                if (lane == 0) {
+                    if (k < 9) atomicAdd(p.gw + (size_t)c * 9 + k, p.scale * s);
+                    else if (p.gb) atomicAdd(p.gb + c, p.scale * s);
+                }
+            }
+        }
+        return;
+    }
     float *slot = p.partials + ((size_t)blockIdx.x * p.maxseg + (g - g_first)) * p.P * 10;
     if (per_plane <= 16) {
         // few items per plane: one thread per (plane, sum) pair adds them serially
@@ -544,12 +574,17 @@ fast_kernel(const FastParams p)
     const int g_first = cur.g;
 
     const int tid = threadIdx.x;
+    // Programmatic dependent launch: let the next kernel in the stream start its prologue while this grid
+    // drains, and do this kernel's own shared-memory set-up before waiting for the previous grid.  Nothing
+    // before pdl_wait() touches global memory.
+    pdl_launch_dependents();
     for (int i = tid; i < zlen; i += blockDim.x) zrow_base[i] = 0.f;
     if (!DIRECT && tid == 0) {
         for (int s = 0; s < p.stages; ++s) mbar_init(smem_u32(bars + s), 1);
         mbar_fence_init();
     }
     __syncthreads();
+    pdl_wait();
     Cursor pre = cur;  // thread 0: cursor of the next tile to fetch
     if (!DIRECT && tid == 0) {
         const int npre = min(T, p.stages);
@@ -835,6 +870,10 @@ fast_kernel(const FastParams p)
 
 static const int kMaxGroups = 16384;  // ticket counters in the parameter-gradient workspace
 
+// Process-wide switch (cunn_b200_set_deterministic): 0 = parameter gradients are summed across CTAs with fp32
+// atomics (default), 1 = with the ticketed fixed-order reduction, whose results are bit-reproducible.
+static int g_deterministic = 0;
+
 struct Tuning {
     int P = 0, R = 0, RS = 0, stages = 0, ctas_per_sm = 0, force_generic = 0, budget_kb = 0, vec = 0, stage_out = -1, direct = -1;
 };
@@ -1116,7 +1155,19 @@ static int launch_fast(FastParams &fp, const Plan &pl, cudaStream_t stream, cons
     fp.tiles_base = (int)(pl.tiles / pl.grid);
     fp.tiles_rem = (int)(pl.tiles % pl.grid);
     void *args[] = {(void *)&fp};
-    CUNN_CUDA(cudaLaunchKernel((const void *)kern, dim3(pl.grid), dim3(pl.threads), args, pl.smem, stream));
+    // launched as a programmatic dependent of whatever precedes it in the stream: its prologue may overlap
+    // the tail of the previous kernel; the kernel itself waits (pdl_wait) before touching global memory
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(pl.grid);
+    cfg.blockDim = dim3(pl.threads);
+    cfg.dynamicSmemBytes = pl.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CUNN_CUDA(cudaLaunchKernelExC(&cfg, (const void *)kern, args));
     (void)name;
     return 0;
 }
@@ -1256,6 +1307,9 @@ extern "C" int cunn_b200_dwconv_grad_input(const float *gy, const float *weight,
     return 0;
 }
 
+extern "C" CUNN_API void cunn_b200_set_deterministic(int on) { g_deterministic = on ? 1 : 0; }
+extern "C" CUNN_API int cunn_b200_get_deterministic(void) { return g_deterministic; }
+
 extern "C" size_t cunn_b200_dwconv_acc_grad_workspace(int N, int C, int H, int W, int M, int kH, int kW, int dH, int dW,
                                                       int padH, int padW)
 {
@@ -1280,14 +1334,18 @@ extern "C" int cunn_b200_dwconv_acc_grad(const float *x, const float *gy, float 
     if (fast_shape(M, kH, kW, dH, dW, padH, padW) && aligned16(x) && aligned16(gy)) {
         Plan pl = make_plan(MODE_WGRAD, N, C, H, W, oH, oW, dH);
         if (pl.ok && finalize_plan(pl) == 0) {
-            const size_t need = wgrad_workspace_bytes(C, pl);
-            CUNN_CHECK_ARG(workspace && workspace_bytes >= need && aligned16(workspace),
-                           "dwconv acc_grad needs %zu bytes of 16-byte aligned workspace, got %zu", need,
-                           workspace ? workspace_bytes : (size_t)0);
             FastParams fp{};
             fill_params(fp, pl, N, C, H, W, oH, oW);
             fp.in = x; fp.in2 = gy; fp.w = nullptr; fp.out = nullptr;
             fp.gw = grad_weight; fp.gb = grad_bias; fp.scale = scale;
+            if (!g_deterministic) {
+                fp.atomic_flush = 1;   // no scratch needed: the workspace argument is ignored
+                return launch_fast(fp, pl, stream, "dwconv acc grad (3x3)");
+            }
+            const size_t need = wgrad_workspace_bytes(C, pl);
+            CUNN_CHECK_ARG(workspace && workspace_bytes >= need && aligned16(workspace),
+                           "dwconv acc_grad needs %zu bytes of 16-byte aligned workspace, got %zu", need,
+                           workspace ? workspace_bytes : (size_t)0);
             fp.counters = (unsigned int *)workspace;
             fp.partials = (float *)((char *)workspace + wgrad_counter_bytes(C, pl));
             return launch_fast(fp, pl, stream, "dwconv acc grad (3x3)");

@@ -213,10 +213,10 @@ extern "C" CUNN_API int cunn_b200_mobilenet_step(const cunn_b200_mobilenet_confi
             STEP(cunn_b200_convmm_forward(x, w, b, co, B, L.cin, L.hin, L.hin, L.cout, 1, 1, 1, 1, 0, 0, stream));
         else
             STEP(cunn_b200_convmm_forward(x, w, b, co, B, L.cin, L.hin, L.hin, L.cout, 3, 3, L.stride, L.stride, 1, 1, stream));
-        STEP(cunn_b200_batchnorm_forward(co, ac, params + L.g_off, params + L.beta_off, bn_running + L.bn_off,
-                                         bn_running + L.bn_off + L.cout, sv, sv + L.cout, B, L.cout, L.hout * L.hout, 1,
-                                         momentum, eps, work, wbytes, stream));
-        STEP(cunn_b200_threshold_forward(ac, ac, (long long)B * L.cout * L.hout * L.hout, 0.f, 0.f, stream));
+        // BN + ReLU in one pass (the caller-side fusion of nn.SpatialBatchNormalization + nn.ReLU)
+        STEP(cunn_b200_batchnorm_relu_forward(co, ac, params + L.g_off, params + L.beta_off, bn_running + L.bn_off,
+                                              bn_running + L.bn_off + L.cout, sv, sv + L.cout, B, L.cout, L.hout * L.hout,
+                                              1, momentum, eps, work, wbytes, stream));
         x = ac;
     }
     const int fh = m.final_hw;
@@ -245,11 +245,9 @@ extern "C" CUNN_API int cunn_b200_mobilenet_step(const cunn_b200_mobilenet_confi
         const Layer &L = m.layers[i];
         float *co = F(a.conv_out[i]), *ac = F(a.act[i]), *sv = F(a.save[i]);
         const float *xin = (i == 0) ? images : F(a.act[i - 1]);
-        const long long n = (long long)B * L.cout * L.hout * L.hout;
-        STEP(cunn_b200_threshold_backward(ac, g, g, n, 0.f, stream));
-        STEP(cunn_b200_batchnorm_backward(co, g, g2, grads + L.g_off, grads + L.beta_off, params + L.g_off,
-                                          bn_running + L.bn_off, bn_running + L.bn_off + L.cout, sv, sv + L.cout, B, L.cout,
-                                          L.hout * L.hout, 1, 1.0, eps, work, wbytes, stream));
+        STEP(cunn_b200_batchnorm_relu_backward(co, ac, g, g2, grads + L.g_off, grads + L.beta_off, params + L.g_off,
+                                               bn_running + L.bn_off, bn_running + L.bn_off + L.cout, sv, sv + L.cout, B,
+                                               L.cout, L.hout * L.hout, 1, 1.0, eps, work, wbytes, stream));
         // g2 = gradient w.r.t. the convolution output
         if (L.kind == KIND_DW) {
             STEP(cunn_b200_dwconv_acc_grad(xin, g2, grads + L.w_off, grads + L.b_off, B, L.cin, L.hin, L.hin, 1, 3, 3,

@@ -260,3 +260,32 @@ def sgd_update(params, grads, lr):
     _chk(params, grads)
     check(lib.cunn_b200_sgd_update(_ptr(params), _ptr(grads), params.numel(), lr, _stream()))
     return params
+
+
+def batchnorm_relu_forward(x, weight, bias, running_mean, running_var, train, momentum=0.1, eps=1e-5, out=None):
+    """y = max(0, BN(x)) in one pass; returns (y, save_mean, save_std)."""
+    _chk(x, weight, bias, running_mean, running_var)
+    N, C, S = _bn_dims(x)
+    if out is None:
+        out = torch.empty_like(x)
+    save_mean = torch.empty(C, dtype=torch.float32, device=x.device)
+    save_std = torch.empty(C, dtype=torch.float32, device=x.device)
+    ws = workspace(lib.cunn_b200_batchnorm_workspace(N, C), x.device)
+    check(lib.cunn_b200_batchnorm_relu_forward(_ptr(x), _ptr(out), _ptr(weight), _ptr(bias), _ptr(running_mean),
+                                               _ptr(running_var), _ptr(save_mean), _ptr(save_std), N, C, S, int(train),
+                                               momentum, eps, _ptr(ws), ws.numel(), _stream()))
+    return out, save_mean, save_std
+
+
+def batchnorm_relu_backward(x, y, gy, weight, running_mean, running_var, save_mean, save_std, train, scale=1.0, eps=1e-5,
+                            grad_weight=None, grad_bias=None):
+    """Backward of batchnorm_relu_forward given its output y; accumulates into grad_weight / grad_bias."""
+    _chk(x, y, gy, weight, grad_weight, grad_bias)
+    N, C, S = _bn_dims(x)
+    out = torch.empty_like(x)
+    ws = workspace(lib.cunn_b200_batchnorm_workspace(N, C), x.device)
+    check(lib.cunn_b200_batchnorm_relu_backward(_ptr(x), _ptr(y), _ptr(gy), _ptr(out), _ptr(grad_weight), _ptr(grad_bias),
+                                                _ptr(weight), _ptr(running_mean), _ptr(running_var), _ptr(save_mean),
+                                                _ptr(save_std), N, C, S, int(train), scale, eps, _ptr(ws), ws.numel(),
+                                                _stream()))
+    return out

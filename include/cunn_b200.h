@@ -58,13 +58,19 @@ CUNN_API int cunn_b200_dwconv_grad_input(const float *gy, const float *weight, f
                                 int N, int C, int H, int W, int M, int kH, int kW,
                                 int dH, int dW, int padH, int padW, cunn_stream_t stream);
 
-/* Scratch bytes cunn_b200_dwconv_acc_grad needs for these sizes (may be 0). */
+/* How parameter gradients are summed across thread blocks, process-wide.  0 (default): fp32 atomic adds — the
+ * fastest, but the rounding of the last bits depends on scheduling.  1: a fixed-order reduction through the
+ * caller's workspace — bit-reproducible from run to run, a few microseconds slower per call. */
+CUNN_API void cunn_b200_set_deterministic(int on);
+CUNN_API int cunn_b200_get_deterministic(void);
+
+/* Scratch bytes cunn_b200_dwconv_acc_grad needs for these sizes in deterministic mode (may be 0). */
 CUNN_API size_t cunn_b200_dwconv_acc_grad_workspace(int N, int C, int H, int W, int M, int kH, int kW,
                                            int dH, int dW, int padH, int padW);
 
 /* grad_weight [M,C,kH,kW] += scale * dL/dW, grad_bias [M,C] += scale * sum gy
- * (grad_bias may be NULL).  `workspace` is caller-owned device scratch of at
- * least the size the query above returns, 16-byte aligned.  Its first 64 KiB hold
+ * (grad_bias may be NULL).  `workspace` (used in deterministic mode only) is caller-owned device scratch
+ * of at least the size the query above returns, 16-byte aligned.  Its first 64 KiB hold
  * ticket counters: the buffer must be zero-filled once before its first use
  * (cudaMemset) and every call leaves the counters zero again, so one buffer can
  * serve all later calls that do not overlap on the GPU.  Replaces
@@ -162,6 +168,21 @@ CUNN_API int cunn_b200_batchnorm_backward(const float *x, const float *gy, float
                                           const float *running_var, const float *save_mean, const float *save_std,
                                           int N, int C, int S, int train, double scale, double eps,
                                           void *workspace, size_t workspace_bytes, cunn_stream_t stream);
+
+/* BatchNormalization followed by ReLU in one pass (y = max(0, BN(x))), and its backward given that y: the
+ * caller-side fusion of nn.SpatialBatchNormalization + nn.ReLU, which saves two full activation passes per
+ * layer in each direction.  No counterpart in the reference (it runs BatchNormalization.cu and Threshold.cu
+ * as separate kernels); results equal the two separate calls exactly. */
+CUNN_API int cunn_b200_batchnorm_relu_forward(const float *x, float *y, const float *weight, const float *bias,
+                                              float *running_mean, float *running_var, float *save_mean, float *save_std,
+                                              int N, int C, int S, int train, double momentum, double eps,
+                                              void *workspace, size_t workspace_bytes, cunn_stream_t stream);
+CUNN_API int cunn_b200_batchnorm_relu_backward(const float *x, const float *y, const float *gy, float *gx,
+                                               float *grad_weight, float *grad_bias, const float *weight,
+                                               const float *running_mean, const float *running_var,
+                                               const float *save_mean, const float *save_std, int N, int C, int S,
+                                               int train, double scale, double eps, void *workspace,
+                                               size_t workspace_bytes, cunn_stream_t stream);
 
 /* ---- Support operators of the MobileNetV1 step ---------------------------------------------
  * Threshold (ReLU is threshold 0, value 0; y may alias x, gx may alias gy):

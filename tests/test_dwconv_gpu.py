@@ -187,3 +187,29 @@ def test_dwconv_linearity_full_size(F):
         rhs = float((gy.double() * y1.double()).sum())
         assert abs(lhs - rhs) < 1e-6 * (abs(rhs) + 1e3)
         assert rel_err(host(gb).ravel(), host(gy.double().sum(dim=(0, 2, 3)).float())) < GRAD_TOL
+
+
+def test_dwconv_acc_grad_deterministic_mode(F, ref64):
+    # cunn_b200_set_deterministic(1): the ticketed fixed-order reduction; results are bit-identical from run
+    # to run and equal the default (atomic) mode within the gradient tolerance
+    from cunn_b200._lib import lib
+    x, w, b, gy, gw0, gb0 = make_case(31, 9, 64, 28, 28, 1, 3, 1, 1)
+    xd, gyd = dev(x), dev(gy)
+    rgw, rgb = ref64.dwconv_acc_grad(x, gy, gw0, gb0, 1, 1, 1, 1, 0.5)
+    assert lib.cunn_b200_get_deterministic() == 0
+    gw, gb = dev(gw0), dev(gb0)
+    F.dwconv_acc_grad(xd, gyd, gw, gb, 1, 1, 1, 1, 0.5)
+    assert rel_err(host(gw), rgw) < GRAD_TOL and rel_err(host(gb), rgb) < GRAD_TOL
+    lib.cunn_b200_set_deterministic(1)
+    try:
+        first = None
+        for _ in range(5):
+            gw, gb = dev(gw0), dev(gb0)
+            F.dwconv_acc_grad(xd, gyd, gw, gb, 1, 1, 1, 1, 0.5)
+            cur = (host(gw), host(gb))
+            assert rel_err(cur[0], rgw) < GRAD_TOL and rel_err(cur[1], rgb) < GRAD_TOL
+            if first is None:
+                first = cur
+            assert np.array_equal(first[0], cur[0]) and np.array_equal(first[1], cur[1])
+    finally:
+        lib.cunn_b200_set_deterministic(0)

@@ -215,3 +215,23 @@ def test_bn_single_element_and_zero_variance(F):
     y, sm, ss = F.batchnorm_forward(x, None, None, rm, rv, True, 0.1, 0.0)
     assert torch.all(ss == 0) and torch.all(y == 0) and torch.all(sm == 3.0)
     assert torch.all(torch.isnan(rv))
+
+
+@pytest.mark.parametrize("shape", [(4, 8, 14, 14), (3, 5, 7, 9)])
+def test_bn_relu_fused_equals_separate_calls(F, shape):
+    # the fused BN+ReLU pair must equal BatchNormalization followed by Threshold(0, 0), forward and backward
+    g = torch.Generator(device="cuda").manual_seed(9)
+    C = shape[1]
+    x = torch.randn(shape, device="cuda", generator=g) * 2 + 0.3
+    w, b = torch.rand(C, device="cuda", generator=g), torch.rand(C, device="cuda", generator=g) - 0.5
+    gy = torch.randn(shape, device="cuda", generator=g)
+    rm1, rv1, rm2, rv2 = (torch.zeros(C, device="cuda"), torch.ones(C, device="cuda"), torch.zeros(C, device="cuda"),
+                          torch.ones(C, device="cuda"))
+    z, sm, ss = F.batchnorm_forward(x, w, b, rm1, rv1, True)
+    y_ref = F.threshold_forward(z)
+    y, sm2, ss2 = F.batchnorm_relu_forward(x, w, b, rm2, rv2, True)
+    assert torch.equal(y, y_ref) and torch.equal(sm, sm2) and torch.equal(ss, ss2) and torch.equal(rm1, rm2)
+    gw1, gb1, gw2, gb2 = (torch.zeros(C, device="cuda") for _ in range(4))
+    gx_ref = F.batchnorm_backward(x, F.threshold_backward(z, gy), w, rm1, rv1, sm, ss, True, grad_weight=gw1, grad_bias=gb1)
+    gx = F.batchnorm_relu_backward(x, y, gy, w, rm2, rv2, sm2, ss2, True, grad_weight=gw2, grad_bias=gb2)
+    assert torch.equal(gx, gx_ref) and torch.equal(gw1, gw2) and torch.equal(gb1, gb2)
