@@ -435,15 +435,22 @@ __device__ __forceinline__ void wgrad_flush(const FastParams &p, const float (&a
         for (int k = 0; k < 10; ++k) red[tid * 10 + k] = acc[k];
     }
     __syncthreads();
+    // One thread per (plane, sum) pair adding the plane's items serially, or (long planes, few pairs) one
+    // warp per pair with a shuffle reduction.
+    const int npairs = p.P * 10;
+    const bool serial = per_plane <= 16 || ((npairs + (int)blockDim.x - 1) / (int)blockDim.x) * per_plane <= 96;
     if (p.atomic_flush) {
         // fire-and-forget: scale * (sum over this CTA's items of the plane) straight into gw / gb
         const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
-        if (per_plane <= 16) {
+        if (serial) {
             for (int pair = tid; pair < p.P * 10; pair += blockDim.x) {
                 const int ppl = pair / 10, k = pair - ppl * 10;
                 const float *r = red + ppl * per_plane * 10 + k;
-                float s = 0.f;
-                for (int i = 0; i < per_plane; ++i) s += r[i * 10];
+                float s0 = 0.f, s1 = 0.f;
+                int i = 0;
+                for (; i + 1 < per_plane; i += 2) { s0 += r[i * 10]; s1 += r[i * 10 + 10]; }
+                if (i < per_plane) s0 += r[i * 10];
+                const float s = s0 + s1;
                 const int c = g * p.P + ppl;
                 if (k < 9) atomicAdd(p.gw + (size_t)c * 9 + k, p.scale * s);
                 else if (p.gb) atomicAdd(p.gb + c, p.scale * s);
@@ -464,8 +471,7 @@ __device__ __forceinline__ void wgrad_flush(const FastParams &p, const float (&a
         return;
     }
     float *slot = p.partials + ((size_t)blockIdx.x * p.maxseg + (g - g_first)) * p.P * 10;
-    if (per_plane <= 16) {
-        // few items per plane: one thread per (plane, sum) pair adds them serially
+    if (serial) {
         for (int pair = tid; pair < p.P * 10; pair += blockDim.x) {
             const int ppl = pair / 10, k = pair - ppl * 10;
             const float *r = red + ppl * per_plane * 10 + k;
@@ -982,7 +988,8 @@ static Plan make_plan(int mode, int N, int C, int H, int W, int oH, int oW, int 
             // issue slots and shared-memory wavefronts per output element
             const double instr = (ld * rows_per_out + fma + st + 8.0) / outs;
             const double waves = wf * rows_per_out / (32.0 * outs);
-            double cost = instr + 40.0 * waves;
+            // scalar and 8-byte shared loads weigh more than the 16-byte ones (measured on 14x14 and 7x7 planes)
+            double cost = instr + (VEC == 4 ? 40.0 : 80.0) * waves;
             if (mode != MODE_WGRAD && !staged && VEC != 4 && !(mode == MODE_DGRAD_S2 && VEC == 2))
                 cost *= 2.0;  // narrow direct stores fill sectors piecemeal
             const double size = std::min(1.0, items / 128.0);
