@@ -206,6 +206,86 @@ def workload_config(n, world):
                       "overlaps the input-gradient kernels"}
 
 
+def other_configs_bench(dev):
+    """The other single-GPU configurations of the path, one kernel at a time (device-resident inputs, CUDA events on
+    the launching stream, median of the repeats): im2col-GEMM convolution (BASELINE config 3, 3xTF32 on the
+    tensor cores; TFLOP/s are fp32-equivalent: 2*N*K*C*kH*kW*oH*oW per pass) and batch normalisation +
+    3x3/2 max pooling at 256x64x112x112 (config 4; GB/s are algorithmic bytes: BN 2 tensors forward and 3
+    backward, pooling input + output + int64 indices).  Buffers rotate so that successive launches never
+    find their operands in L2."""
+    import torch
+    import cunn_b200.functional as F
+    peak, _ = measured_peaks()
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(SEED + 99)
+
+    def timed(fn, nbuf, reps=5):
+        for i in range(nbuf):
+            fn(i)
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for i in range(nbuf):
+                fn(i)
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) / nbuf)
+        return sorted(ts)[len(ts) // 2]
+
+    res = {}
+    # ---- config 3: SpatialConvolutionMM --------------------------------------------------------------
+    for name, (N, C, K, HW, k, pad) in (("convmm_3x3_256to256_14x14_n128", (128, 256, 256, 14, 3, 1)),
+                                         ("convmm_1x1_1024to256_14x14_n128", (128, 1024, 256, 14, 1, 0))):
+        nbuf = 6
+        xs = [torch.randn((N, C, HW, HW), device=dev, generator=gen) for _ in range(nbuf)]
+        gys = [torch.randn((N, K, HW, HW), device=dev, generator=gen) for _ in range(nbuf)]
+        ys = [torch.empty((N, K, HW, HW), device=dev) for _ in range(nbuf)]
+        gxs = [torch.empty((N, C, HW, HW), device=dev) for _ in range(nbuf)]
+        w = torch.randn((K, C, k, k), device=dev, generator=gen) * (2.0 / (C * k * k)) ** 0.5
+        b = torch.rand((K,), device=dev, generator=gen)
+        gw, gb = torch.zeros_like(w), torch.zeros_like(b)
+        flop = 2.0 * N * K * C * k * k * HW * HW
+        ops = {"fwd": lambda i: F.convmm_forward(xs[i], w, b, 1, 1, pad, pad, out=ys[i]),
+               "dgrad": lambda i: F.convmm_grad_input(gys[i], w, HW, HW, 1, 1, pad, pad, out=gxs[i]),
+               "wgrad": lambda i: F.convmm_acc_grad(xs[i], gys[i], gw, gb, 1, 1, pad, pad, 1.0)}
+        for op, fn in ops.items():
+            ms = timed(fn, nbuf)
+            res["%s_%s" % (name, op)] = {"us": round(ms * 1e3, 1), "value": round(flop / (ms * 1e-3) / 1e12, 1),
+                                         "unit": "TFLOP/s fp32-equivalent (3xTF32 tcgen05)"}
+        del xs, gys, ys, gxs
+    # ---- config 4: BatchNormalization and SpatialMaxPooling --------------------------------------------
+    N, C, HW = 256, 64, 112
+    x = torch.randn((N, C, HW, HW), device=dev, generator=gen) * 2 + 0.5
+    y = torch.empty_like(x)
+    gy = torch.randn((N, C, HW, HW), device=dev, generator=gen)
+    gx = torch.empty_like(x)
+    gamma = torch.rand((C,), device=dev, generator=gen)
+    beta = torch.zeros((C,), device=dev)
+    rm, rv = torch.zeros((C,), device=dev), torch.ones((C,), device=dev)
+    ggam, gbet = torch.zeros((C,), device=dev), torch.zeros((C,), device=dev)
+    S = x.numel() * 4
+    _, sm, ss = F.batchnorm_forward(x, gamma, beta, rm, rv, True, out=y)
+
+    def put(key, ms, nbytes):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        res[key] = {"us": round(ms * 1e3, 1), "value": round(gbs, 0), "unit": "GB/s algorithmic",
+                    "frac_of_measured_peak": round(gbs / peak, 3)}
+
+    put("batchnorm_train_fwd_256x64x112x112", timed(lambda i: F.batchnorm_forward(x, gamma, beta, rm, rv, True, out=y, save_mean=sm, save_std=ss), 1), 2 * S)
+    put("batchnorm_eval_fwd_256x64x112x112", timed(lambda i: F.batchnorm_forward(x, gamma, beta, rm, rv, False, out=y, save_mean=sm, save_std=ss), 1), 2 * S)
+    put("batchnorm_train_bwd_256x64x112x112", timed(lambda i: F.batchnorm_backward(x, gy, gamma, rm, rv, sm, ss, True, grad_weight=ggam, grad_bias=gbet, out=gx), 1), 3 * S)
+    oHW = F.maxpool_out_size(HW, 3, 2, 1, False)
+    py = torch.empty((N, C, oHW, oHW), device=dev)
+    pidx = torch.empty((N, C, oHW, oHW), device=dev, dtype=torch.int64)
+    pgy = torch.randn((N, C, oHW, oHW), device=dev, generator=gen)
+    pool_bytes = S + py.numel() * 4 + pidx.numel() * 8
+    put("maxpool_3x3s2p1_fwd_256x64x112x112", timed(lambda i: F.maxpool_forward(y, 3, 3, 2, 2, 1, 1, False, out=py, indices=pidx), 1), pool_bytes)
+    put("maxpool_3x3s2p1_bwd_256x64x112x112", timed(lambda i: F.maxpool_backward(pgy, pidx, HW, HW, 3, 3, 2, 2, 1, 1, False, out=gx), 1), pool_bytes)
+    return res
+
+
 def mobilenet_bench(args, dev, world, rank, dist):
     """Full MobileNetV1 (1.0, 224x224, 1000 classes) training step: forward, loss, backward, all-reduce of the
     flat gradient buffer, SGD update; global batch sharded over the ranks with DataParallelTable's slice rule.
@@ -267,6 +347,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-mobilenet", action="store_true")
+    ap.add_argument("--no-others", action="store_true", help="skip the config 3 / config 4 single-kernel timings")
     ap.add_argument("--mobilenet-batch", type=int, default=1024, help="global batch of the MobileNetV1 step")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -438,6 +519,7 @@ def main():
 
     # ---- end to end through the C ABI with host buffers ----------------------------------------------
     e2e = None
+    H = None
     if not args.no_e2e:
         import numpy as np
         esteps = max(1, min(steps, 3))
@@ -504,6 +586,12 @@ def main():
     if not args.no_mobilenet:
         mbn = mobilenet_bench(args, dev, world, rank, dist if world > 1 else None)
 
+    others = None
+    if world == 1 and not args.no_others:
+        del T, H
+        torch.cuda.empty_cache()
+        others = other_configs_bench(dev)
+
     status = device_status()
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -515,7 +603,7 @@ def main():
                 "warmup": warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(BATCH, world),
                 "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * steps,
-                "roofline": roofline, "cpu_baseline": cpu, "mobilenet_v1": mbn, "device_status": status}
+                "roofline": roofline, "cpu_baseline": cpu, "mobilenet_v1": mbn, "other_configs": others, "device_status": status}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
