@@ -100,6 +100,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
 // Shared-memory matrix descriptor: K-major, no swizzle, core matrices of 8 rows x 16 bytes.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr)
 {
@@ -526,6 +538,474 @@ dgrad_gather_kernel(const float *__restrict__ gy, const float *__restrict__ w, f
 }
 
 // ---------------------------------------------------------------------------
+// Pointwise convolutions (1x1, stride 1, no padding): persistent kernel
+// ---------------------------------------------------------------------------
+//
+// A 1x1 convolution is a plain matrix product per image and every operand is already laid out the way the
+// tensor core can take it, so nothing is gathered element by element:
+//
+//   forward      D[pixel, ko] = sum_c  x[img][c][pix]   * W[ko][c]      A: 4 pixels of one channel = 16 contiguous bytes (M-major)
+//                                                                        B: 4 channels of one filter = 16 contiguous bytes (K-major)
+//   input grad   D[pixel, c]  = sum_ko gy[img][ko][pix] * W[ko][c]      A: M-major as above;  B: 4 channels c of one ko (N-major)
+//   weight grad  D[ko, c]     = sum_{img,pix} gy[img][ko][pix] * x[img][c][pix]      A, B: 4 pixels of one row (K-major);
+//                                                                        k runs over (image, pixel) of this tile's image range
+//
+// tcgen05.mma takes M/N-major operands through the major bits of the instruction descriptor, so a 16-byte
+// global load becomes one 16-byte shared-memory store per tf32 half with no transposition.  One CTA per SM
+// walks a strided list of tiles; operand loads run two k-blocks ahead of the MMAs ACROSS tile boundaries, and
+// when the accumulators fit twice in TMEM the epilogue of a tile runs after the first MMAs of the next tile
+// have been issued, so the tensor core and the memory system keep working through it.
+namespace pw {
+
+constexpr int THREADS = 512;
+constexpr int PITCH = 144;               // K-major tile: bytes between neighbouring 16-byte k chunks: 128 + 16 of padding, so
+                                         // that eight neighbouring lanes storing 16 bytes each fall into 32 different banks
+constexpr int ROWGROUP = 8 * PITCH;      // K-major tile: bytes of one group of 8 rows (8 chunks of 4 k values)
+constexpr int TILE = 16 * ROWGROUP;      // 128 rows x 32 k values, K-major with padding; an M/N-major tile (16 KiB) fits too
+constexpr int MN_ATOM = 512;             // M/N-major tile: bytes of one swizzle atom (32 rows x 4 k values)
+constexpr int MN_KATOM = 4 * MN_ATOM;    // ... bytes from one group of 4 k values to the next (4 atoms cover 128 rows)
+constexpr int STAGE = 4 * TILE;          // A hi, A lo, B hi, B lo
+constexpr int STAGES = 3;
+constexpr size_t SMEM = (size_t)STAGES * STAGE + 1024;
+static_assert(8 * MN_KATOM <= TILE, "an M/N-major tile fits the stage slot");
+
+struct Params {
+    const float *a, *b, *bias;
+    float *out;        // FWD: y; DGRAD: gx; WGRAD: partial sums [splits][M_total][N_total]
+    float *bias_part;  // WGRAD: [M_total][splits] row sums of gy, or null
+    int *status;
+    int HW;            // pixels per image plane
+    int M_total, N_total, Kd;
+    int n_tiles, tiles_per_split, total_tiles;   // tile = (split * m_tiles + m_tile) * n_tiles + n_tile
+    int kblocks;       // k-blocks per tile
+    int n_img, imgs_per_split, splits;
+    int vec_a, vec_b;  // 16-byte global loads allowed for A / B
+    int nacc, sets;    // accumulators per tile (k-blocks are dealt round-robin), accumulator sets in TMEM (1 or 2)
+};
+
+// hi = v rounded to tf32 (round half away, done in integer arithmetic), lo = v - hi.
+__device__ __forceinline__ void split_rn(float v, float &hi, float &lo)
+{
+    hi = __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xffffe000u);
+    lo = v - hi;
+}
+__device__ __forceinline__ void store_split_at(unsigned char *hi_tile, unsigned char *lo_tile, uint32_t off, const float4 &v)
+{
+    float4 h, l;
+    split_rn(v.x, h.x, l.x);
+    split_rn(v.y, h.y, l.y);
+    split_rn(v.z, h.z, l.z);
+    split_rn(v.w, h.w, l.w);
+    *reinterpret_cast<float4 *>(hi_tile + off) = h;
+    *reinterpret_cast<float4 *>(lo_tile + off) = l;
+}
+__device__ __forceinline__ uint64_t desc_of(uint32_t addr, uint32_t lbo, uint32_t sbo)
+{
+    return (uint64_t)((addr >> 4) & 0x3fff) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
+}
+// M/N-major operand in the 128B-base-32B swizzle: leading offset = atom to atom along M/N, stride offset = along K.
+__device__ __forceinline__ uint64_t desc_mn(uint32_t addr)
+{
+    return desc_of(addr, MN_ATOM, MN_KATOM) | (1ull << 61);
+}
+__host__ __device__ constexpr uint32_t idesc_of(int n, bool a_mn, bool b_mn)
+{
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ float4 ldg4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
+__device__ __forceinline__ float4 zero4() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+
+// Where the operand loads of one thread stand: tile, k-block and the thread's element offsets inside that tile.
+// M/N-major pieces: lane = group of 4 rows, k = warp + 16 i.  K-major pieces: chunk kc = tid & 7, rows (tid >> 3) + 64 i.
+template <int OP, int BN>
+struct Loader {
+    int tile, kb;
+    int a_off[4];       // FWD/DGRAD: element offsets of the thread's 4 pixels (channel 0); WGRAD: [0..1] row offsets
+    int b_off[2];       // FWD: offsets of the thread's two filter rows (+ chunk); DGRAD: [0] first column; WGRAD: row offsets
+    unsigned a_mask, b_mask;
+    int img, pix, img_end;   // WGRAD: image and pixel of the thread's chunk in the current k-block
+
+    __device__ __forceinline__ void setup(const Params &p, int t)
+    {
+        const int tid = threadIdx.x, lane = tid & 31;
+        tile = t;
+        kb = 0;
+        a_mask = b_mask = 0;
+        if (OP != OP_WGRAD) {
+            const int m_tile = t / p.n_tiles, n_tile = t - m_tile * p.n_tiles;
+            const int m = m_tile * BM + lane * 4, n0 = n_tile * BN;
+            if (p.vec_a) {
+                if (m < p.M_total) {
+                    const int im = m / p.HW;
+                    a_off[0] = im * p.Kd * p.HW + (m - im * p.HW);
+                    a_mask = 15u;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    a_off[j] = 0;
+                    if (m + j < p.M_total) {
+                        const int im = (m + j) / p.HW;
+                        a_off[j] = im * p.Kd * p.HW + (m + j - im * p.HW);
+                        a_mask |= 1u << j;
+                    }
+                }
+            }
+            if (OP == OP_FWD) {
+                const int kc = tid & 7;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int row = (tid >> 3) + 64 * i, n = n0 + row;
+                    b_off[i] = n * p.Kd + kc * 4;
+                    if (row < BN && n < p.N_total) b_mask |= 1u << i;
+                }
+            } else {
+                const int col = n0 + lane * 4;
+                b_off[0] = col;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (lane * 4 < BN && col + j < p.N_total) b_mask |= 1u << j;
+            }
+        } else {
+            const int split = t / p.tiles_per_split, r = t - split * p.tiles_per_split;
+            const int m_tile = r / p.n_tiles, n_tile = r - m_tile * p.n_tiles;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int row = (tid >> 3) + 64 * i;
+                const int m = m_tile * BM + row, n = n_tile * BN + row;
+                a_off[i] = m * p.HW;
+                b_off[i] = n * p.HW;
+                if (m < p.M_total) a_mask |= 1u << i;
+                if (row < BN && n < p.N_total) b_mask |= 1u << i;
+            }
+            img = split * p.imgs_per_split;
+            img_end = min(p.n_img, img + p.imgs_per_split);
+            pix = (tid & 7) * 4;
+            while (pix >= p.HW) { pix -= p.HW; ++img; }
+        }
+    }
+
+    // Moves to the next k-block of this CTA's tile list.
+    __device__ __forceinline__ void advance(const Params &p)
+    {
+        if (++kb == p.kblocks) {
+            const int t = tile + (int)gridDim.x;
+            if (t < p.total_tiles) setup(p, t);
+            else tile = t;
+        } else if (OP == OP_WGRAD) {
+            pix += BK;
+            while (pix >= p.HW) { pix -= p.HW; ++img; }
+        }
+    }
+
+    // Four consecutive pixels of one row starting at (image i0, pixel p0); rows are HW long, images `stride` apart.
+    __device__ __forceinline__ float4 row_chunk(const Params &p, const float *base, int stride, bool vec) const
+    {
+        if (vec) return img < img_end ? ldg4(base + (size_t)img * stride + pix) : zero4();
+        float v[4];
+        int ij = img, pj = pix;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            while (pj >= p.HW) { pj -= p.HW; ++ij; }
+            v[j] = ij < img_end ? __ldg(base + (size_t)ij * stride + pj) : 0.f;
+            ++pj;
+        }
+        return make_float4(v[0], v[1], v[2], v[3]);
+    }
+
+    __device__ __forceinline__ void load(const Params &p, float4 (&ra)[2], float4 (&rb)[2]) const
+    {
+        const int tid = threadIdx.x, warp = tid >> 5;
+        if (tile >= p.total_tiles) return;
+        if (OP != OP_WGRAD) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int k = kb * BK + warp + 16 * i;
+                float4 v = zero4();
+                if (k < p.Kd && a_mask) {
+                    if (p.vec_a) {
+                        v = ldg4(p.a + a_off[0] + k * p.HW);
+                    } else {
+                        float t[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) t[j] = (a_mask >> j & 1u) ? __ldg(p.a + a_off[j] + k * p.HW) : 0.f;
+                        v = make_float4(t[0], t[1], t[2], t[3]);
+                    }
+                }
+                ra[i] = v;
+            }
+            if (OP == OP_FWD) {
+                const int k0 = kb * BK + (tid & 7) * 4;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    float4 v = zero4();
+                    if ((b_mask >> i & 1u) && k0 < p.Kd) {
+                        const float *src = p.b + b_off[i] + kb * BK;
+                        if (p.vec_b) {
+                            v = ldg4(src);
+                        } else {
+                            float t[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) t[j] = (k0 + j < p.Kd) ? __ldg(src + j) : 0.f;
+                            v = make_float4(t[0], t[1], t[2], t[3]);
+                        }
+                    }
+                    rb[i] = v;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int k = kb * BK + warp + 16 * i;
+                    float4 v = zero4();
+                    if (k < p.Kd && b_mask) {
+                        const float *src = p.b + (size_t)k * p.N_total + b_off[0];
+                        if (p.vec_b) {
+                            v = ldg4(src);
+                        } else {
+                            float t[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) t[j] = (b_mask >> j & 1u) ? __ldg(src + j) : 0.f;
+                            v = make_float4(t[0], t[1], t[2], t[3]);
+                        }
+                    }
+                    rb[i] = v;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                ra[i] = (a_mask >> i & 1u) ? row_chunk(p, p.a + a_off[i], p.M_total * p.HW, p.vec_a != 0) : zero4();
+                rb[i] = (b_mask >> i & 1u) ? row_chunk(p, p.b + b_off[i], p.N_total * p.HW, p.vec_b != 0) : zero4();
+            }
+        }
+    }
+};
+
+template <int OP, int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+pw_gemm_kernel(const Params p)
+{
+    constexpr bool A_MN = OP != OP_WGRAD;     // A is M-major (forward, input gradient)
+    constexpr bool B_MN = OP == OP_DGRAD;     // B is N-major (input gradient)
+    constexpr int ACC_COLS = BN < 32 ? 32 : BN;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t idesc = idesc_of(BN, A_MN, B_MN);
+
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ uint64_t bars[STAGES + 2];     // stage-free barriers, then one accumulators-ready barrier per set
+    __shared__ uint32_t tmem_base_s;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < STAGES + 2; ++s) mbar_init(smem_u32(bars + s), 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+
+    const int KB = p.kblocks;
+    const int my_tiles = ((int)blockIdx.x < p.total_tiles) ? (p.total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int total_it = my_tiles * KB;
+    const int nacc_used = KB < p.nacc ? KB : p.nacc;
+    const uint32_t set_cols = (uint32_t)(p.nacc * ACC_COLS);
+
+    // shared-memory offsets of this thread's pieces (same for every stage)
+    uint32_t a_so[2], b_so[2];
+    bool b_store[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int k = warp + 16 * i;                    // M/N-major: k inside the block
+        const int row = (tid >> 3) + 64 * i;            // K-major: tile row
+        // 128-byte rows of 32 consecutive M/N values, four k rows per 512-byte atom, the 32-byte chunk index
+        // XORed with the row index (the tensor core's 128B-base-32B swizzle, the only M/N-major form for tf32)
+        const uint32_t mn = (uint32_t)((lane >> 3) * MN_ATOM + (k >> 2) * MN_KATOM + (k & 3) * 128 +
+                                       ((((lane & 7) >> 1) ^ (k & 3)) << 5) + ((lane & 1) << 4));
+        const uint32_t km = (uint32_t)((row >> 3) * ROWGROUP + (tid & 7) * PITCH + (row & 7) * 16);
+        a_so[i] = A_MN ? mn : km;
+        b_so[i] = B_MN ? mn : km;
+        b_store[i] = B_MN ? (lane * 4 < BN) : (row < BN);
+    }
+
+    float bsum[2] = {0.f, 0.f};                         // WGRAD: running row sums of gy (bias gradient)
+    auto store_block = [&](int stage, const float4 (&ra)[2], const float4 (&rb)[2]) {
+        unsigned char *sa_hi = smem + (size_t)stage * STAGE;
+        unsigned char *sa_lo = sa_hi + TILE, *sb_hi = sa_lo + TILE, *sb_lo = sb_hi + TILE;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            store_split_at(sa_hi, sa_lo, a_so[i], ra[i]);
+            if (b_store[i]) store_split_at(sb_hi, sb_lo, b_so[i], rb[i]);
+            if (OP == OP_WGRAD) bsum[i] += (ra[i].x + ra[i].y) + (ra[i].z + ra[i].w);
+        }
+    };
+    auto issue_mmas = [&](int stage, uint32_t d_tmem, bool first) {
+        const uint32_t sa_hi = smem_u32(smem + (size_t)stage * STAGE);
+        const uint32_t sa_lo = sa_hi + TILE, sb_hi = sa_lo + TILE, sb_lo = sb_hi + TILE;
+#pragma unroll
+        for (int j = 0; j < BK / 8; ++j) {
+            const uint32_t ao = A_MN ? (uint32_t)(j * 2 * MN_KATOM) : (uint32_t)(j * 2 * PITCH);
+            const uint32_t bo = B_MN ? (uint32_t)(j * 2 * MN_KATOM) : (uint32_t)(j * 2 * PITCH);
+            const uint64_t ah = A_MN ? desc_mn(sa_hi + ao) : desc_of(sa_hi + ao, PITCH, ROWGROUP);
+            const uint64_t al = A_MN ? desc_mn(sa_lo + ao) : desc_of(sa_lo + ao, PITCH, ROWGROUP);
+            const uint64_t bh = B_MN ? desc_mn(sb_hi + bo) : desc_of(sb_hi + bo, PITCH, ROWGROUP);
+            const uint64_t bl = B_MN ? desc_mn(sb_lo + bo) : desc_of(sb_lo + bo, PITCH, ROWGROUP);
+            umma_tf32(d_tmem, al, bh, idesc, (first && j == 0) ? 0u : 1u);
+            umma_tf32(d_tmem, ah, bl, idesc, 1u);
+            umma_tf32(d_tmem, ah, bh, idesc, 1u);
+        }
+    };
+    // Reads the accumulators of tile `t` (the `count`-th tile of this CTA) and writes its part of the output.
+    auto epilogue = [&](int t, int count) -> bool {
+        const int set = (p.sets == 2) ? (count & 1) : 0;
+        const uint32_t parity = (uint32_t)(((p.sets == 2) ? (count >> 1) : count) & 1);
+        if (!mbar_wait(smem_u32(bars + STAGES + set), parity, p.status)) return false;
+        tc_fence_after();
+        const int quarter = warp & 3, cc = (warp >> 2) * 32;     // TMEM lanes of this warp, its 32 columns
+        if (cc < BN) {
+            const int row = quarter * 32 + lane;
+            int m, n_base;
+            size_t dst_off = 0;
+            if (OP != OP_WGRAD) {
+                const int m_tile = t / p.n_tiles, n_tile = t - m_tile * p.n_tiles;
+                m = m_tile * BM + row;
+                n_base = n_tile * BN + cc;
+                if (m < p.M_total) {
+                    const int im = m / p.HW;
+                    dst_off = (size_t)im * p.N_total * p.HW + (m - im * p.HW) + (size_t)n_base * p.HW;
+                }
+            } else {
+                const int split = t / p.tiles_per_split, r2 = t - split * p.tiles_per_split;
+                const int m_tile = r2 / p.n_tiles, n_tile = r2 - m_tile * p.n_tiles;
+                m = m_tile * BM + row;
+                n_base = n_tile * BN + cc;
+                dst_off = ((size_t)split * p.M_total + m) * p.N_total + n_base;
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {        // two passes of 16 columns keep the register count down
+                float acc[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+                for (int a = 0; a < nacc_used; ++a) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)set * set_cols + (uint32_t)(a * ACC_COLS + cc + 16 * h), r);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[j] += __uint_as_float(r[j]);
+                }
+                if (m < p.M_total) {
+                    const int n0 = n_base + 16 * h;
+                    if (OP != OP_WGRAD) {
+                        float *dst = p.out + dst_off + (size_t)(16 * h) * p.HW;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (n0 + j < p.N_total) {
+                                float v = acc[j];
+                                if (OP == OP_FWD && p.bias) v += __ldg(p.bias + n0 + j);
+                                dst[(size_t)j * p.HW] = v;
+                            }
+                        }
+                    } else {
+                        float *dst = p.out + dst_off + 16 * h;
+                        if ((p.N_total & 3) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 16; j += 4)
+                                if (n0 + j < p.N_total) *reinterpret_cast<float4 *>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (n0 + j < p.N_total) dst[j] = acc[j];
+                        }
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+        return true;
+    };
+
+    Loader<OP, BN> L;
+    L.tile = (int)blockIdx.x;
+    L.kb = 0;
+    if (my_tiles > 0) L.setup(p, L.tile);
+    float4 ra0[2], rb0[2], ra1[2], rb1[2];
+    if (total_it > 0) { L.load(p, ra0, rb0); L.advance(p); }
+    if (total_it > 1) { L.load(p, ra1, rb1); L.advance(p); }
+
+    int c_tile = (int)blockIdx.x, c_kb = 0, c_count = 0;   // tile, k-block and tile ordinal of the block being stored / issued
+    int pend_tile = -1, pend_count = 0;                    // tile whose epilogue is still to run (two accumulator sets)
+    bool ok = true;
+    for (int it = 0; it < total_it && ok; it += 2) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int i = it + half;
+            if (i >= total_it) break;
+            const int stage = i % STAGES;
+            if (i >= STAGES) {
+                if (!mbar_wait(smem_u32(bars + stage), (uint32_t)(((i / STAGES) - 1) & 1), p.status)) { ok = false; break; }
+            }
+            if (half == 0) store_block(stage, ra0, rb0);
+            else store_block(stage, ra1, rb1);
+            fence_async_smem();
+            __syncthreads();
+            if (tid == 0) {
+                tc_fence_after();
+                const int set = (p.sets == 2) ? (c_count & 1) : 0;
+                issue_mmas(stage, tmem_base + (uint32_t)set * set_cols + (uint32_t)((c_kb % p.nacc) * ACC_COLS), c_kb < p.nacc);
+                umma_commit(smem_u32(bars + stage));
+                if (c_kb == KB - 1) umma_commit(smem_u32(bars + STAGES + set));
+            }
+            if (i + 2 < total_it) {
+                if (half == 0) L.load(p, ra0, rb0);
+                else L.load(p, ra1, rb1);
+                L.advance(p);
+            }
+            if (pend_tile >= 0 && c_kb == 0) {
+                ok = epilogue(pend_tile, pend_count);
+                pend_tile = -1;
+                if (!ok) break;
+            }
+            if (c_kb == KB - 1) {
+                if (OP == OP_WGRAD) {
+                    // bias gradient: the eight chunk lanes of a row hold its partial sums
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        float s = bsum[r];
+                        s += __shfl_xor_sync(0xffffffffu, s, 1);
+                        s += __shfl_xor_sync(0xffffffffu, s, 2);
+                        s += __shfl_xor_sync(0xffffffffu, s, 4);
+                        const int split = c_tile / p.tiles_per_split, r2 = c_tile - split * p.tiles_per_split;
+                        const int m_tile = r2 / p.n_tiles, n_tile = r2 - m_tile * p.n_tiles;
+                        const int m = m_tile * BM + (tid >> 3) + 64 * r;
+                        if (p.bias_part && n_tile == 0 && (tid & 7) == 0 && m < p.M_total) p.bias_part[(size_t)m * p.splits + split] = s;
+                        bsum[r] = 0.f;
+                    }
+                }
+                if (p.sets == 2) {
+                    pend_tile = c_tile;
+                    pend_count = c_count;
+                } else {
+                    ok = epilogue(c_tile, c_count);
+                    if (!ok) break;
+                }
+                c_kb = 0;
+                c_tile += (int)gridDim.x;
+                ++c_count;
+            } else {
+                ++c_kb;
+            }
+        }
+    }
+    if (ok && pend_tile >= 0) ok = epilogue(pend_tile, pend_count);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+}  // namespace pw
+
+// ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
 
@@ -601,6 +1081,66 @@ static void wgrad_plan(int N, int C, int K, int kk, int oHW, int *bn, int *split
     *pix_blocks = ceil_div(oHW, BK);
 }
 
+
+// ---- pointwise path ----------------------------------------------------------------------------------
+static bool pw_applies(int kH, int kW, int dH, int dW, int padH, int padW)
+{
+    return kH == 1 && kW == 1 && dH == 1 && dW == 1 && padH == 0 && padW == 0;
+}
+static bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+typedef void (*PwKernel)(const pw::Params);
+template <int OP>
+static PwKernel pw_pick(int bn)
+{
+    switch (bn) {
+        case 32: return pw::pw_gemm_kernel<OP, 32>;
+        case 64: return pw::pw_gemm_kernel<OP, 64>;
+        default: return pw::pw_gemm_kernel<OP, 128>;
+    }
+}
+static int pw_bn_for(int n_total) { return n_total <= 32 ? 32 : (n_total <= 64 ? 64 : 128); }
+
+// Accumulators per tile and accumulator sets: k-blocks are dealt round-robin to `nacc` accumulators to keep the
+// tensor core's truncating accumulation chains short; two sets (epilogue overlapped with the next tile) when
+// they fit in the 512 TMEM columns.
+static void pw_accumulators(int bn, int kblocks, int *nacc, int *sets)
+{
+    if (bn == 128) {
+        if (kblocks <= 8) { *nacc = 2; *sets = 2; }
+        else { *nacc = 4; *sets = 1; }
+    } else if (bn == 64) {
+        if (kblocks <= 48) { *nacc = 4; *sets = 2; }
+        else { *nacc = 8; *sets = 1; }
+    } else {
+        *nacc = 8; *sets = 2;
+    }
+}
+
+static int pw_launch(PwKernel kern, pw::Params &p, cudaStream_t stream)
+{
+    const int grid = std::min(p.total_tiles, sm_count());
+    CUNN_CUDA(cudaFuncSetAttribute((const void *)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pw::SMEM));
+    void *args[] = {(void *)&p};
+    CUNN_CUDA(cudaLaunchKernel((const void *)kern, dim3(grid), dim3(pw::THREADS), args, pw::SMEM, stream));
+    return 0;
+}
+
+// Splits of the image range for the pointwise weight gradient: at most ~128 k-blocks per tile, and a tile count
+// that fills whole waves of the persistent grid.
+static void pw_wgrad_plan(int N, int C, int K, int HW, int *bn, int *splits, int *imgs_per_split)
+{
+    *bn = pw_bn_for(C);
+    const int tiles_mn = ceil_div(K, BM) * ceil_div(C, *bn);
+    const long long total_kb = ceil_div_ll((long long)N * HW, BK);
+    const long long s_min = std::max(1LL, ceil_div_ll(total_kb, 128));
+    const int grid = sm_count();
+    const long long waves = std::max(1LL, ceil_div_ll(tiles_mn * s_min, grid));
+    long long s = std::max(1LL, std::min((long long)N, waves * grid / tiles_mn));
+    *imgs_per_split = ceil_div(N, (int)s);
+    *splits = ceil_div(N, *imgs_per_split);
+}
+
 }  // namespace mm
 }  // namespace cunn
 
@@ -617,6 +1157,17 @@ extern "C" CUNN_API int cunn_b200_convmm_forward(const float *x, const float *we
     if (check(N, C, H, W, K, kH, kW, dH, dW, padH, padW, &oH, &oW)) return 1;
     if (N == 0) return 0;
     CUNN_CHECK_ARG(x && weight && y, "null tensor pointer");
+    if (pw_applies(kH, kW, dH, dW, padH, padW)) {
+        pw::Params q{};
+        q.a = x; q.b = weight; q.bias = bias; q.out = y; q.status = device_status_ptr();
+        q.HW = H * W; q.M_total = N * H * W; q.N_total = K; q.Kd = C; q.kblocks = ceil_div(C, BK);
+        const int bn = pw_bn_for(K);
+        q.n_tiles = ceil_div(K, bn); q.tiles_per_split = 0; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
+        q.n_img = N; q.imgs_per_split = N; q.splits = 1;
+        q.vec_a = (q.HW % 4 == 0) && aligned16(x); q.vec_b = (C % 4 == 0) && aligned16(weight);
+        pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
+        return pw_launch(pw_pick<OP_FWD>(bn), q, stream);
+    }
     GemmParams p{};
     p.a_src = x; p.b_src = weight; p.bias = bias; p.out = y; p.status = device_status_ptr();
     p.g_C = C; p.g_H = H; p.g_W = W; p.g_padH = padH; p.g_padW = padW; p.g_dH = dH; p.g_dW = dW; p.kH = kH; p.kW = kW;
@@ -637,6 +1188,17 @@ extern "C" CUNN_API int cunn_b200_convmm_grad_input(const float *gy, const float
     if (check(N, C, H, W, K, kH, kW, dH, dW, padH, padW, &oH, &oW)) return 1;
     if (N == 0) return 0;
     CUNN_CHECK_ARG(gy && weight && gx, "null tensor pointer");
+    if (pw_applies(kH, kW, dH, dW, padH, padW)) {
+        pw::Params q{};
+        q.a = gy; q.b = weight; q.bias = nullptr; q.out = gx; q.status = device_status_ptr();
+        q.HW = H * W; q.M_total = N * H * W; q.N_total = C; q.Kd = K; q.kblocks = ceil_div(K, BK);
+        const int bn = pw_bn_for(C);
+        q.n_tiles = ceil_div(C, bn); q.tiles_per_split = 0; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
+        q.n_img = N; q.imgs_per_split = N; q.splits = 1;
+        q.vec_a = (q.HW % 4 == 0) && aligned16(gy); q.vec_b = (C % 4 == 0) && aligned16(weight);
+        pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
+        return pw_launch(pw_pick<OP_DGRAD>(bn), q, stream);
+    }
     if (dH == 1 && dW == 1 && padH <= kH - 1 && padW <= kW - 1) {
         // stride 1: a convolution of gy with the kernel rotated by 180 degrees and padding k - 1 - pad
         GemmParams p{};
@@ -661,6 +1223,10 @@ extern "C" CUNN_API size_t cunn_b200_convmm_acc_grad_workspace(int N, int C, int
     int oH, oW;
     if (check(N, C, H, W, K, kH, kW, dH, dW, padH, padW, &oH, &oW) || N == 0) return 0;
     int bn, splits, ips, pb;
+    if (pw_applies(kH, kW, dH, dW, padH, padW)) {
+        pw_wgrad_plan(N, C, K, H * W, &bn, &splits, &ips);
+        return (size_t)splits * K * C * sizeof(float) + (size_t)K * splits * sizeof(float) + 256;
+    }
     wgrad_plan(N, C, K, kH * kW, oH * oW, &bn, &splits, &ips, &pb);
     const int chunks = std::max(1, std::min(N, ceil_div(sm_count() * 4, K)));
     return (size_t)splits * K * C * kH * kW * sizeof(float) + (size_t)K * chunks * sizeof(float) + 256;
@@ -683,6 +1249,28 @@ extern "C" CUNN_API int cunn_b200_convmm_acc_grad(const float *x, const float *g
                    workspace ? workspace_bytes : (size_t)0);
     int bn, splits, ips, pb;
     const int kk = kH * kW;
+    if (pw_applies(kH, kW, dH, dW, padH, padW)) {
+        pw_wgrad_plan(N, C, K, H * W, &bn, &splits, &ips);
+        const long long n = (long long)K * C;
+        pw::Params q{};
+        q.a = gy; q.b = x; q.bias = nullptr; q.out = (float *)workspace; q.status = device_status_ptr();
+        q.bias_part = grad_bias ? (float *)workspace + (size_t)splits * n : nullptr;
+        q.HW = H * W; q.M_total = K; q.N_total = C; q.Kd = 0;
+        q.kblocks = (int)ceil_div_ll((long long)ips * q.HW, BK);
+        q.n_tiles = ceil_div(C, bn); q.tiles_per_split = ceil_div(K, BM) * q.n_tiles; q.total_tiles = q.tiles_per_split * splits;
+        q.n_img = N; q.imgs_per_split = ips; q.splits = splits;
+        q.vec_a = (q.HW % 4 == 0) && aligned16(gy); q.vec_b = (q.HW % 4 == 0) && aligned16(x);
+        pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
+        if (pw_launch(pw_pick<OP_WGRAD>(bn), q, stream)) return 1;
+        const int rblocks = (int)std::max(1LL, std::min(ceil_div_ll(n, 256), (long long)sm_count() * 8));
+        wgrad_reduce_kernel<<<rblocks, 256, 0, stream>>>((const float *)workspace, grad_weight, n, splits, scale);
+        CUNN_LAUNCH_CHECK("convmm acc grad reduce");
+        if (grad_bias) {
+            bias_finish_kernel<<<ceil_div(K, 128), 128, 0, stream>>>(q.bias_part, grad_bias, K, splits, scale);
+            CUNN_LAUNCH_CHECK("convmm bias gradient finish");
+        }
+        return 0;
+    }
     wgrad_plan(N, C, K, kk, oH * oW, &bn, &splits, &ips, &pb);
     GemmParams p{};
     p.a_src = gy; p.b_src = x; p.bias = nullptr; p.out = (float *)workspace; p.status = device_status_ptr();

@@ -86,6 +86,13 @@ def test_convmm_golden(F, name):
     (2, 5, 10, 10, 7, 5, 2, 2, True),        # 5x5 stride 2 (generic k decomposition, gather dgrad)
     (2, 130, 6, 6, 20, 3, 1, 1, True),       # Kd = 1170: many k-blocks, ragged tail
     (9, 4, 5, 5, 4, 1, 2, 0, True),          # 1x1 stride 2
+    (8, 32, 56, 56, 64, 1, 1, 0, True),      # pointwise, one k-block, more tiles than SMs (persistent loop)
+    (16, 128, 28, 28, 128, 1, 1, 0, True),   # pointwise, four k-blocks, two accumulator sets
+    (2, 1024, 14, 14, 192, 1, 1, 0, False),  # pointwise, long reduction, ragged second column tile
+    (2, 30, 6, 6, 50, 1, 1, 0, True),        # pointwise, channel counts not multiples of 4
+    (3, 20, 5, 5, 36, 1, 1, 0, True),        # pointwise, 25-pixel planes (scalar loads)
+    (40, 512, 7, 7, 96, 1, 1, 0, True),      # pointwise, 49-pixel planes, several row tiles
+    (64, 1024, 1, 1, 1000, 1, 1, 0, True),   # classifier geometry: one pixel per image
 ])
 def test_convmm_shapes(F, ref64, shape):
     N, C, H, W, K, k, d, pad, bias = shape
