@@ -12,7 +12,7 @@
 //
 // One CTA computes a 128 x BN tile of D.  All 256 threads gather operand values from global memory
 // (coalesced along pixels, two k-blocks in flight in registers), split them and store 16-byte pieces
-// into K-major, non-swizzled core-matrix layout (8 rows x 16 bytes); one thread then issues the MMAs of
+// into K-major tiles in the 128-byte swizzle; one thread then issues the MMAs of
 // the k-block and commits them to the mbarrier that frees the stage.  The epilogue reads the
 // accumulator with tcgen05.ld (lane = tile row) and writes coalesced NCHW rows.  Every wait is bounded.
 //
@@ -30,8 +30,7 @@ enum Op : int { OP_FWD = 0, OP_DGRAD = 1, OP_WGRAD = 2 };
 constexpr int BM = 128;       // tile rows (TMEM lanes)
 constexpr int BK = 32;        // k-block: 8 chunks of 4 values (16 bytes)
 constexpr int THREADS = 256;
-constexpr int LBO = 128;      // bytes between the two 16-byte K chunks of an MMA (adjacent core matrices)
-constexpr int SBO = 1024;     // bytes between 8-row groups: 8 chunks x 128 bytes
+constexpr int SBO = 1024;     // bytes between 8-row groups of a K-major tile (rows of 128 bytes = one k-block)
 
 struct GemmParams {
     const float *a_src;   // FWD: x; DGRAD: gy; WGRAD: gy
@@ -112,10 +111,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// Shared-memory matrix descriptor: K-major, no swizzle, core matrices of 8 rows x 16 bytes.
+// Shared-memory matrix descriptor: K-major tile in the 128-byte swizzle (row r holds its eight 16-byte chunks
+// at positions chunk ^ (r & 7); groups of 8 rows are 1024 bytes apart).  The tensor core reads this form without
+// bank conflicts; the unswizzled 8 x 16-byte core-matrix form measured about 20 % slower.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr)
 {
-    return (uint64_t)((addr >> 4) & 0x3fff) | ((uint64_t)(LBO >> 4) << 16) | ((uint64_t)(SBO >> 4) << 32) | (1ull << 46);
+    return (uint64_t)((addr >> 4) & 0x3fff) | ((uint64_t)1 << 16) | ((uint64_t)(SBO >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 // Instruction descriptor of kind::tf32: fp32 accumulator, tf32 A and B, both K-major, M = 128, N = BN.
 __host__ __device__ constexpr uint32_t instr_desc(int n)
@@ -133,7 +134,7 @@ __device__ __forceinline__ void split_tf32(float v, float &hi, float &lo)
 }
 
 // Byte offset of the 16-byte piece (row, chunk) inside an operand tile.
-__device__ __forceinline__ uint32_t piece_offset(int row, int kc) { return (uint32_t)((row >> 3) * SBO + kc * LBO + (row & 7) * 16); }
+__device__ __forceinline__ uint32_t piece_offset(int row, int kc) { return (uint32_t)(row * 128 + ((kc ^ (row & 7)) << 4)); }
 
 __device__ __forceinline__ void store_split(unsigned char *hi_tile, unsigned char *lo_tile, int row, int kc, const float4 &v)
 {
@@ -364,7 +365,7 @@ conv_gemm_kernel(const GemmParams p)
         constexpr uint32_t idesc = instr_desc(BN < 16 ? 16 : BN);
 #pragma unroll
         for (int j = 0; j < BK / 8; ++j) {
-            const uint32_t koff = (uint32_t)j * 2 * LBO;      // two 16-byte chunks per MMA
+            const uint32_t koff = (uint32_t)j * 32;           // two 16-byte chunks per MMA; the swizzle is applied to the address
             const uint64_t ah = smem_desc(sa_hi + koff), al = smem_desc(sa_lo + koff);
             const uint64_t bh = smem_desc(sb_hi + koff), bl = smem_desc(sb_lo + koff);
             umma_tf32(d_tmem, al, bh, idesc, (first && j == 0) ? 0u : 1u);
@@ -557,17 +558,16 @@ dgrad_gather_kernel(const float *__restrict__ gy, const float *__restrict__ w, f
 // have been issued, so the tensor core and the memory system keep working through it.
 namespace pw {
 
-constexpr int THREADS = 512;
-constexpr int PITCH = 144;               // K-major tile: bytes between neighbouring 16-byte k chunks: 128 + 16 of padding, so
-                                         // that eight neighbouring lanes storing 16 bytes each fall into 32 different banks
-constexpr int ROWGROUP = 8 * PITCH;      // K-major tile: bytes of one group of 8 rows (8 chunks of 4 k values)
-constexpr int TILE = 16 * ROWGROUP;      // 128 rows x 32 k values, K-major with padding; an M/N-major tile (16 KiB) fits too
+constexpr int PRODUCERS = 512;           // threads that copy, split and run the epilogue (16 warps)
+constexpr int THREADS = PRODUCERS + 32;  // + one warp that only issues the MMAs
+constexpr int TILE = 128 * 128;          // 128 rows x 32 k values (16 KiB) in either layout
 constexpr int MN_ATOM = 512;             // M/N-major tile: bytes of one swizzle atom (32 rows x 4 k values)
 constexpr int MN_KATOM = 4 * MN_ATOM;    // ... bytes from one group of 4 k values to the next (4 atoms cover 128 rows)
-constexpr int STAGE = 4 * TILE;          // A hi, A lo, B hi, B lo
-constexpr int STAGES = 3;
-constexpr size_t SMEM = (size_t)STAGES * STAGE + 1024;
-static_assert(8 * MN_KATOM <= TILE, "an M/N-major tile fits the stage slot");
+constexpr int RAW_STAGES = 4;            // raw fp32 tiles (A, B) filled by asynchronous copies; split in place they become the hi tiles
+constexpr int LO_BUFS = 2;               // lo tiles (A, B) of the k-blocks whose MMAs are in flight
+constexpr int PREFETCH = 3;              // k-blocks the copies run ahead of the MMAs
+constexpr size_t SMEM = (size_t)(RAW_STAGES + LO_BUFS) * 2 * TILE + 1024;
+static_assert(8 * MN_KATOM == TILE, "both layouts fill the tile");
 
 struct Params {
     const float *a, *b, *bias;
@@ -615,6 +615,19 @@ __host__ __device__ constexpr uint32_t idesc_of(int n, bool a_mn, bool b_mn)
 }
 __device__ __forceinline__ float4 ldg4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
 __device__ __forceinline__ float4 zero4() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+
+// Asynchronous 16- and 4-byte copies global -> shared; `on` false writes zeros without reading `src`.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool on)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(on ? 16u : 0u) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, bool on)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(on ? 4u : 0u) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // Where the operand loads of one thread stand: tile, k-block and the thread's element offsets inside that tile.
 // M/N-major pieces: lane = group of 4 rows, k = warp + 16 i.  K-major pieces: chunk kc = tid & 7, rows (tid >> 3) + 64 i.
@@ -699,22 +712,28 @@ struct Loader {
         }
     }
 
-    // Four consecutive pixels of one row starting at (image i0, pixel p0); rows are HW long, images `stride` apart.
-    __device__ __forceinline__ float4 row_chunk(const Params &p, const float *base, int stride, bool vec) const
+    // Copies four consecutive pixels of one row, starting at this thread's (image, pixel), to shared memory.
+    __device__ __forceinline__ void row_chunk(const Params &p, uint32_t dst, const float *base, int stride, bool vec, bool on) const
     {
-        if (vec) return img < img_end ? ldg4(base + (size_t)img * stride + pix) : zero4();
-        float v[4];
+        if (vec) {
+            const bool ok = on && img < img_end;
+            cp_async16(dst, ok ? base + (size_t)img * stride + pix : base, ok);
+            return;
+        }
         int ij = img, pj = pix;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             while (pj >= p.HW) { pj -= p.HW; ++ij; }
-            v[j] = ij < img_end ? __ldg(base + (size_t)ij * stride + pj) : 0.f;
+            const bool ok = on && ij < img_end;
+            cp_async4(dst + 4 * j, ok ? base + (size_t)ij * stride + pj : base, ok);
             ++pj;
         }
-        return make_float4(v[0], v[1], v[2], v[3]);
     }
 
-    __device__ __forceinline__ void load(const Params &p, float4 (&ra)[2], float4 (&rb)[2]) const
+    // Issues the asynchronous copies of this thread's pieces of the current k-block into the raw tiles at
+    // shared-memory addresses sa / sb (+ the piece offsets); masked pieces are zero-filled.
+    __device__ __forceinline__ void issue(const Params &p, uint32_t sa, uint32_t sb, const uint32_t (&a_so)[2],
+                                          const uint32_t (&b_so)[2], const bool (&b_store)[2]) const
     {
         const int tid = threadIdx.x, warp = tid >> 5;
         if (tile >= p.total_tiles) return;
@@ -722,61 +741,60 @@ struct Loader {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int k = kb * BK + warp + 16 * i;
-                float4 v = zero4();
-                if (k < p.Kd && a_mask) {
-                    if (p.vec_a) {
-                        v = ldg4(p.a + a_off[0] + k * p.HW);
-                    } else {
-                        float t[4];
+                const bool kok = k < p.Kd;
+                if (p.vec_a) {
+                    const bool ok = kok && a_mask;
+                    cp_async16(sa + a_so[i], ok ? p.a + a_off[0] + k * p.HW : p.a, ok);
+                } else {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) t[j] = (a_mask >> j & 1u) ? __ldg(p.a + a_off[j] + k * p.HW) : 0.f;
-                        v = make_float4(t[0], t[1], t[2], t[3]);
+                    for (int j = 0; j < 4; ++j) {
+                        const bool ok = kok && (a_mask >> j & 1u);
+                        cp_async4(sa + a_so[i] + 4 * j, ok ? p.a + a_off[j] + k * p.HW : p.a, ok);
                     }
                 }
-                ra[i] = v;
             }
             if (OP == OP_FWD) {
                 const int k0 = kb * BK + (tid & 7) * 4;
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
-                    float4 v = zero4();
-                    if ((b_mask >> i & 1u) && k0 < p.Kd) {
-                        const float *src = p.b + b_off[i] + kb * BK;
-                        if (p.vec_b) {
-                            v = ldg4(src);
-                        } else {
-                            float t[4];
+                    if (!b_store[i]) continue;
+                    const float *src = p.b + b_off[i] + kb * BK;
+                    const bool rok = (b_mask >> i & 1u) != 0;
+                    if (p.vec_b) {
+                        const bool ok = rok && k0 < p.Kd;
+                        cp_async16(sb + b_so[i], ok ? src : p.b, ok);
+                    } else {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) t[j] = (k0 + j < p.Kd) ? __ldg(src + j) : 0.f;
-                            v = make_float4(t[0], t[1], t[2], t[3]);
+                        for (int j = 0; j < 4; ++j) {
+                            const bool ok = rok && k0 + j < p.Kd;
+                            cp_async4(sb + b_so[i] + 4 * j, ok ? src + j : p.b, ok);
                         }
                     }
-                    rb[i] = v;
                 }
             } else {
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
+                    if (!b_store[i]) continue;
                     const int k = kb * BK + warp + 16 * i;
-                    float4 v = zero4();
-                    if (k < p.Kd && b_mask) {
-                        const float *src = p.b + (size_t)k * p.N_total + b_off[0];
-                        if (p.vec_b) {
-                            v = ldg4(src);
-                        } else {
-                            float t[4];
+                    const bool kok = k < p.Kd;
+                    const float *src = p.b + (size_t)(kok ? k : 0) * p.N_total + b_off[0];
+                    if (p.vec_b) {
+                        const bool ok = kok && b_mask;
+                        cp_async16(sb + b_so[i], ok ? src : p.b, ok);
+                    } else {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) t[j] = (b_mask >> j & 1u) ? __ldg(src + j) : 0.f;
-                            v = make_float4(t[0], t[1], t[2], t[3]);
+                        for (int j = 0; j < 4; ++j) {
+                            const bool ok = kok && (b_mask >> j & 1u);
+                            cp_async4(sb + b_so[i] + 4 * j, ok ? src + j : p.b, ok);
                         }
                     }
-                    rb[i] = v;
                 }
             }
         } else {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                ra[i] = (a_mask >> i & 1u) ? row_chunk(p, p.a + a_off[i], p.M_total * p.HW, p.vec_a != 0) : zero4();
-                rb[i] = (b_mask >> i & 1u) ? row_chunk(p, p.b + b_off[i], p.N_total * p.HW, p.vec_b != 0) : zero4();
+                row_chunk(p, sa + a_so[i], p.a + a_off[i], p.M_total * p.HW, p.vec_a != 0, (a_mask >> i & 1u) != 0);
+                if (b_store[i]) row_chunk(p, sb + b_so[i], p.b + b_off[i], p.N_total * p.HW, p.vec_b != 0, (b_mask >> i & 1u) != 0);
             }
         }
     }
@@ -793,12 +811,14 @@ pw_gemm_kernel(const Params p)
     constexpr uint32_t idesc = idesc_of(BN, A_MN, B_MN);
 
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ uint64_t bars[STAGES + 2];     // stage-free barriers, then one accumulators-ready barrier per set
+    __shared__ uint64_t bars[RAW_STAGES + 2]; // MMAs-of-this-stage-done barriers, then one accumulators-ready barrier per set
+    __shared__ uint64_t full[RAW_STAGES];     // stage split and visible to the tensor core: one arrival per producer warp
     __shared__ uint32_t tmem_base_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int s = 0; s < STAGES + 2; ++s) mbar_init(smem_u32(bars + s), 1);
+        for (int s = 0; s < RAW_STAGES + 2; ++s) mbar_init(smem_u32(bars + s), 1);
+        for (int s = 0; s < RAW_STAGES; ++s) mbar_init(smem_u32(full + s), PRODUCERS / 32);
         mbar_fence_init();
     }
     if (warp == 0) tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
@@ -824,34 +844,41 @@ pw_gemm_kernel(const Params p)
         // XORed with the row index (the tensor core's 128B-base-32B swizzle, the only M/N-major form for tf32)
         const uint32_t mn = (uint32_t)((lane >> 3) * MN_ATOM + (k >> 2) * MN_KATOM + (k & 3) * 128 +
                                        ((((lane & 7) >> 1) ^ (k & 3)) << 5) + ((lane & 1) << 4));
-        const uint32_t km = (uint32_t)((row >> 3) * ROWGROUP + (tid & 7) * PITCH + (row & 7) * 16);
+        const uint32_t km = piece_offset(row, tid & 7);   // K-major: 128-byte swizzle
         a_so[i] = A_MN ? mn : km;
         b_so[i] = B_MN ? mn : km;
         b_store[i] = B_MN ? (lane * 4 < BN) : (row < BN);
     }
 
     float bsum[2] = {0.f, 0.f};                         // WGRAD: running row sums of gy (bias gradient)
-    auto store_block = [&](int stage, const float4 (&ra)[2], const float4 (&rb)[2]) {
-        unsigned char *sa_hi = smem + (size_t)stage * STAGE;
-        unsigned char *sa_lo = sa_hi + TILE, *sb_hi = sa_lo + TILE, *sb_lo = sb_hi + TILE;
+    unsigned char *const lo_base = smem + (size_t)RAW_STAGES * 2 * TILE;
+    // Splits this thread's own pieces of raw stage `rs` (its copies have landed): hi overwrites the raw value,
+    // lo goes to the same offset of lo buffer `lb`.
+    auto split_block = [&](int rs, int lb) {
+        unsigned char *a_hi = smem + (size_t)rs * 2 * TILE, *b_hi = a_hi + TILE;
+        unsigned char *a_lo = lo_base + (size_t)lb * 2 * TILE, *b_lo = a_lo + TILE;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            store_split_at(sa_hi, sa_lo, a_so[i], ra[i]);
-            if (b_store[i]) store_split_at(sb_hi, sb_lo, b_so[i], rb[i]);
-            if (OP == OP_WGRAD) bsum[i] += (ra[i].x + ra[i].y) + (ra[i].z + ra[i].w);
+            const float4 va = *reinterpret_cast<const float4 *>(a_hi + a_so[i]);
+            store_split_at(a_hi, a_lo, a_so[i], va);
+            if (OP == OP_WGRAD) bsum[i] += (va.x + va.y) + (va.z + va.w);
+            if (b_store[i]) {
+                const float4 vb = *reinterpret_cast<const float4 *>(b_hi + b_so[i]);
+                store_split_at(b_hi, b_lo, b_so[i], vb);
+            }
         }
     };
-    auto issue_mmas = [&](int stage, uint32_t d_tmem, bool first) {
-        const uint32_t sa_hi = smem_u32(smem + (size_t)stage * STAGE);
-        const uint32_t sa_lo = sa_hi + TILE, sb_hi = sa_lo + TILE, sb_lo = sb_hi + TILE;
+    auto issue_mmas = [&](int rs, int lb, uint32_t d_tmem, bool first) {
+        const uint32_t sa_hi = smem_u32(smem + (size_t)rs * 2 * TILE), sb_hi = sa_hi + TILE;
+        const uint32_t sa_lo = smem_u32(lo_base + (size_t)lb * 2 * TILE), sb_lo = sa_lo + TILE;
 #pragma unroll
         for (int j = 0; j < BK / 8; ++j) {
-            const uint32_t ao = A_MN ? (uint32_t)(j * 2 * MN_KATOM) : (uint32_t)(j * 2 * PITCH);
-            const uint32_t bo = B_MN ? (uint32_t)(j * 2 * MN_KATOM) : (uint32_t)(j * 2 * PITCH);
-            const uint64_t ah = A_MN ? desc_mn(sa_hi + ao) : desc_of(sa_hi + ao, PITCH, ROWGROUP);
-            const uint64_t al = A_MN ? desc_mn(sa_lo + ao) : desc_of(sa_lo + ao, PITCH, ROWGROUP);
-            const uint64_t bh = B_MN ? desc_mn(sb_hi + bo) : desc_of(sb_hi + bo, PITCH, ROWGROUP);
-            const uint64_t bl = B_MN ? desc_mn(sb_lo + bo) : desc_of(sb_lo + bo, PITCH, ROWGROUP);
+            const uint32_t ao = A_MN ? (uint32_t)(j * 2 * MN_KATOM) : (uint32_t)(j * 32);
+            const uint32_t bo = B_MN ? (uint32_t)(j * 2 * MN_KATOM) : (uint32_t)(j * 32);
+            const uint64_t ah = A_MN ? desc_mn(sa_hi + ao) : smem_desc(sa_hi + ao);
+            const uint64_t al = A_MN ? desc_mn(sa_lo + ao) : smem_desc(sa_lo + ao);
+            const uint64_t bh = B_MN ? desc_mn(sb_hi + bo) : smem_desc(sb_hi + bo);
+            const uint64_t bl = B_MN ? desc_mn(sb_lo + bo) : smem_desc(sb_lo + bo);
             umma_tf32(d_tmem, al, bh, idesc, (first && j == 0) ? 0u : 1u);
             umma_tf32(d_tmem, ah, bl, idesc, 1u);
             umma_tf32(d_tmem, ah, bh, idesc, 1u);
@@ -861,7 +888,7 @@ pw_gemm_kernel(const Params p)
     auto epilogue = [&](int t, int count) -> bool {
         const int set = (p.sets == 2) ? (count & 1) : 0;
         const uint32_t parity = (uint32_t)(((p.sets == 2) ? (count >> 1) : count) & 1);
-        if (!mbar_wait(smem_u32(bars + STAGES + set), parity, p.status)) return false;
+        if (!mbar_wait(smem_u32(bars + RAW_STAGES + set), parity, p.status)) return false;
         tc_fence_after();
         const int quarter = warp & 3, cc = (warp >> 2) * 32;     // TMEM lanes of this warp, its 32 columns
         if (cc < BN) {
@@ -925,42 +952,66 @@ pw_gemm_kernel(const Params p)
         return true;
     };
 
-    Loader<OP, BN> L;
-    L.tile = (int)blockIdx.x;
-    L.kb = 0;
-    if (my_tiles > 0) L.setup(p, L.tile);
-    float4 ra0[2], rb0[2], ra1[2], rb1[2];
-    if (total_it > 0) { L.load(p, ra0, rb0); L.advance(p); }
-    if (total_it > 1) { L.load(p, ra1, rb1); L.advance(p); }
-
-    int c_tile = (int)blockIdx.x, c_kb = 0, c_count = 0;   // tile, k-block and tile ordinal of the block being stored / issued
-    int pend_tile = -1, pend_count = 0;                    // tile whose epilogue is still to run (two accumulator sets)
     bool ok = true;
-    for (int it = 0; it < total_it && ok; it += 2) {
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const int i = it + half;
-            if (i >= total_it) break;
-            const int stage = i % STAGES;
-            if (i >= STAGES) {
-                if (!mbar_wait(smem_u32(bars + stage), (uint32_t)(((i / STAGES) - 1) & 1), p.status)) { ok = false; break; }
-            }
-            if (half == 0) store_block(stage, ra0, rb0);
-            else store_block(stage, ra1, rb1);
-            fence_async_smem();
-            __syncthreads();
-            if (tid == 0) {
+    if (warp == PRODUCERS / 32) {
+        // ---- MMA warp: waits for a split stage, issues its twelve MMAs, commits them to the stage's barrier ----
+        int kb = 0, count = 0;
+        for (int i = 0; i < total_it; ++i) {
+            const int rs = i % RAW_STAGES, lb = i % LO_BUFS;
+            if (!mbar_wait(smem_u32(full + rs), (uint32_t)((i / RAW_STAGES) & 1), p.status)) { ok = false; break; }
+            if (lane == 0) {
                 tc_fence_after();
-                const int set = (p.sets == 2) ? (c_count & 1) : 0;
-                issue_mmas(stage, tmem_base + (uint32_t)set * set_cols + (uint32_t)((c_kb % p.nacc) * ACC_COLS), c_kb < p.nacc);
-                umma_commit(smem_u32(bars + stage));
-                if (c_kb == KB - 1) umma_commit(smem_u32(bars + STAGES + set));
+                const int set = (p.sets == 2) ? (count & 1) : 0;
+                issue_mmas(rs, lb, tmem_base + (uint32_t)set * set_cols + (uint32_t)((kb % p.nacc) * ACC_COLS), kb < p.nacc);
+                umma_commit(smem_u32(bars + rs));
+                if (kb == KB - 1) umma_commit(smem_u32(bars + RAW_STAGES + set));
             }
-            if (i + 2 < total_it) {
-                if (half == 0) L.load(p, ra0, rb0);
-                else L.load(p, ra1, rb1);
+            __syncwarp();
+            if (++kb == KB) { kb = 0; ++count; }
+        }
+    } else {
+        Loader<OP, BN> L;
+        L.tile = (int)blockIdx.x;
+        L.kb = 0;
+        if (my_tiles > 0) L.setup(p, L.tile);
+        const uint32_t smem_a0 = smem_u32(smem);
+        // copies of the first PREFETCH k-blocks; one commit group per k-block, empty ones included, so that
+        // "all but the newest PREFETCH - 1 groups" always means "k-block i has landed"
+    #pragma unroll
+        for (int i = 0; i < PREFETCH; ++i) {
+            if (i < total_it) {
+                L.issue(p, smem_a0 + (uint32_t)(i * 2 * TILE), smem_a0 + (uint32_t)(i * 2 * TILE + TILE), a_so, b_so, b_store);
                 L.advance(p);
             }
+            cp_async_commit();
+        }
+
+        int c_tile = (int)blockIdx.x, c_kb = 0, c_count = 0;   // tile, k-block and tile ordinal of the block being split / issued
+        int pend_tile = -1, pend_count = 0;                    // tile whose epilogue is still to run (two accumulator sets)
+        for (int i = 0; i < total_it; ++i) {
+            const int rs = i % RAW_STAGES, lb = i % LO_BUFS;
+            cp_async_wait<PREFETCH - 1>();                     // this thread's pieces of k-block i are in shared memory
+            if (i >= LO_BUFS) {
+                // the MMAs of k-block i - 2 read this lo buffer
+                const int j = i - LO_BUFS;
+                if (!mbar_wait(smem_u32(bars + j % RAW_STAGES), (uint32_t)((j / RAW_STAGES) & 1), p.status)) { ok = false; break; }
+            }
+            split_block(rs, lb);
+            fence_async_smem();                                // generic-proxy stores -> visible to the tensor core's async proxy
+            tc_fence_before();                                 // orders this warp's earlier TMEM reads (epilogue) before the arrival
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(full + rs));
+            // refill the raw stage that k-block i - 1 used with k-block i + PREFETCH, once its MMAs have read it
+            if (i + PREFETCH < total_it) {
+                if (i >= 1) {
+                    const int j = i - 1;
+                    if (!mbar_wait(smem_u32(bars + j % RAW_STAGES), (uint32_t)((j / RAW_STAGES) & 1), p.status)) { ok = false; break; }
+                }
+                const int ns = (i + PREFETCH) % RAW_STAGES;
+                L.issue(p, smem_a0 + (uint32_t)(ns * 2 * TILE), smem_a0 + (uint32_t)(ns * 2 * TILE + TILE), a_so, b_so, b_store);
+                L.advance(p);
+            }
+            cp_async_commit();
             if (pend_tile >= 0 && c_kb == 0) {
                 ok = epilogue(pend_tile, pend_count);
                 pend_tile = -1;
@@ -971,14 +1022,14 @@ pw_gemm_kernel(const Params p)
                     // bias gradient: the eight chunk lanes of a row hold its partial sums
 #pragma unroll
                     for (int r = 0; r < 2; ++r) {
-                        float s = bsum[r];
-                        s += __shfl_xor_sync(0xffffffffu, s, 1);
-                        s += __shfl_xor_sync(0xffffffffu, s, 2);
-                        s += __shfl_xor_sync(0xffffffffu, s, 4);
+                        float sum = bsum[r];
+                        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
                         const int split = c_tile / p.tiles_per_split, r2 = c_tile - split * p.tiles_per_split;
                         const int m_tile = r2 / p.n_tiles, n_tile = r2 - m_tile * p.n_tiles;
                         const int m = m_tile * BM + (tid >> 3) + 64 * r;
-                        if (p.bias_part && n_tile == 0 && (tid & 7) == 0 && m < p.M_total) p.bias_part[(size_t)m * p.splits + split] = s;
+                        if (p.bias_part && n_tile == 0 && (tid & 7) == 0 && m < p.M_total) p.bias_part[(size_t)m * p.splits + split] = sum;
                         bsum[r] = 0.f;
                     }
                 }
@@ -996,8 +1047,9 @@ pw_gemm_kernel(const Params p)
                 ++c_kb;
             }
         }
+        cp_async_wait<0>();
+        if (ok && pend_tile >= 0) ok = epilogue(pend_tile, pend_count);
     }
-    if (ok && pend_tile >= 0) ok = epilogue(pend_tile, pend_count);
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
