@@ -63,23 +63,27 @@ stats_kernel(const float *__restrict__ x, ChunkStat *__restrict__ part, int N, i
     const float k = __ldg(x + ((size_t)n0 * C + c) * S);
     float s1 = 0.f, s2 = 0.f;
     const bool vec = (S % 4 == 0) && (((uintptr_t)x & 15) == 0);
-    for (int n = n0; n < n1; ++n) {
-        const float *p = x + ((size_t)n * C + c) * S;
-        if (vec) {
-            const float4 *p4 = reinterpret_cast<const float4 *>(p);
-#pragma unroll 4
-            for (int i = threadIdx.x; i < S / 4; i += blockDim.x) {
-                const float4 v = __ldg(p4 + i);
-                const float a = v.x - k, b = v.y - k, d = v.z - k, e = v.w - k;
-                s1 += (a + b) + (d + e);
-                s2 = fmaf(a, a, s2); s2 = fmaf(b, b, s2); s2 = fmaf(d, d, s2); s2 = fmaf(e, e, s2);
-            }
-        } else {
-            for (int i = threadIdx.x; i < S; i += blockDim.x) {
-                const float a = __ldg(p + i) - k;
-                s1 += a;
-                s2 = fmaf(a, a, s2);
-            }
+    // The chunk's planes are walked as one flat sequence of 16-byte (or 4-byte) items, so that every lane has
+    // work whatever the plane size; (n, i) = image and item inside its plane, advanced without divisions.
+    const int L = vec ? S / 4 : S;
+    const int qstep = (int)blockDim.x / L, rstep = (int)blockDim.x % L;
+    int n = n0 + (int)threadIdx.x / L, i = (int)threadIdx.x % L;
+    if (vec) {
+        while (n < n1) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(x + ((size_t)n * C + c) * S) + i);
+            const float a = v.x - k, b = v.y - k, d = v.z - k, e = v.w - k;
+            s1 += (a + b) + (d + e);
+            s2 = fmaf(a, a, s2); s2 = fmaf(b, b, s2); s2 = fmaf(d, d, s2); s2 = fmaf(e, e, s2);
+            n += qstep; i += rstep;
+            if (i >= L) { i -= L; ++n; }
+        }
+    } else {
+        while (n < n1) {
+            const float a = __ldg(x + ((size_t)n * C + c) * S + i) - k;
+            s1 += a;
+            s2 = fmaf(a, a, s2);
+            n += qstep; i += rstep;
+            if (i >= L) { i -= L; ++n; }
         }
     }
     s1 = block_sum(s1, sh);
@@ -123,7 +127,8 @@ stats_finish_kernel(const ChunkStat *__restrict__ part, int C, int chunks, float
 
 // y = gamma * (x - mean) * invstd + beta, per plane.  Training reads mean / invstd from save_*, inference
 // derives them from the running statistics.
-template <bool RELU>
+// GROUP threads (a warp for small planes, the whole CTA for large ones) share a plane.
+template <bool RELU, int GROUP>
 __global__ void __launch_bounds__(256)
 apply_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__restrict__ weight,
              const float *__restrict__ bias, const float *__restrict__ mean_v, const float *__restrict__ std_or_var,
@@ -131,8 +136,9 @@ apply_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__
 {
     auto act = [](float v) { return RELU ? (v > 0.f ? v : 0.f) : v; };
     const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)y) & 15) == 0);
-    // a CTA walks planes; threads walk the plane
-    for (long long pl = blockIdx.x; pl < planes; pl += gridDim.x) {
+    constexpr int PER_CTA = 256 / GROUP;
+    const int sub = (int)threadIdx.x / GROUP, t = (int)threadIdx.x % GROUP;
+    for (long long pl = (long long)blockIdx.x * PER_CTA + sub; pl < planes; pl += (long long)gridDim.x * PER_CTA) {
         const int c = (int)(pl % C);
         const float mean = __ldg(mean_v + c);
         const float invstd = train ? __ldg(std_or_var + c) : 1.f / sqrtf(__ldg(std_or_var + c) + eps);
@@ -144,7 +150,7 @@ apply_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__
             const float4 *x4 = reinterpret_cast<const float4 *>(xp);
             float4 *y4 = reinterpret_cast<float4 *>(yp);
 #pragma unroll 4
-            for (int i = threadIdx.x; i < S / 4; i += blockDim.x) {
+            for (int i = t; i < S / 4; i += GROUP) {
                 const float4 v = __ldg(x4 + i);
                 float4 o;
                 o.x = act(g * (v.x - mean) * invstd + b);
@@ -154,7 +160,7 @@ apply_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__
                 y4[i] = o;
             }
         } else {
-            for (int i = threadIdx.x; i < S; i += blockDim.x) yp[i] = act(g * (__ldg(xp + i) - mean) * invstd + b);
+            for (int i = t; i < S; i += GROUP) yp[i] = act(g * (__ldg(xp + i) - mean) * invstd + b);
         }
     }
 }
@@ -172,30 +178,33 @@ grad_stats_kernel(const float *__restrict__ x, const float *__restrict__ gy, con
     const float mean = __ldg(mean_v + c);
     float s = 0.f, d = 0.f;
     const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)gy | (uintptr_t)yact) & 15) == 0);
-    for (int n = n0; n < n1; ++n) {
-        const size_t off = ((size_t)n * C + c) * S;
-        if (vec) {
-            const float4 *x4 = reinterpret_cast<const float4 *>(x + off);
-            const float4 *g4 = reinterpret_cast<const float4 *>(gy + off);
-#pragma unroll 4
-            for (int i = threadIdx.x; i < S / 4; i += blockDim.x) {
-                const float4 v = __ldg(x4 + i);
-                float4 g = __ldg(g4 + i);
-                if (RELU) {   // gradient of the fused ReLU: pass only where the activation was positive
-                    const float4 a = __ldg(reinterpret_cast<const float4 *>(yact + off) + i);
-                    g.x = a.x > 0.f ? g.x : 0.f; g.y = a.y > 0.f ? g.y : 0.f; g.z = a.z > 0.f ? g.z : 0.f; g.w = a.w > 0.f ? g.w : 0.f;
-                }
-                s += (g.x + g.y) + (g.z + g.w);
-                d = fmaf(g.x, v.x - mean, d); d = fmaf(g.y, v.y - mean, d);
-                d = fmaf(g.z, v.z - mean, d); d = fmaf(g.w, v.w - mean, d);
+    const int L = vec ? S / 4 : S;
+    const int qstep = (int)blockDim.x / L, rstep = (int)blockDim.x % L;
+    int n = n0 + (int)threadIdx.x / L, i = (int)threadIdx.x % L;
+    if (vec) {
+        while (n < n1) {
+            const size_t off = ((size_t)n * C + c) * S;
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(x + off) + i);
+            float4 g = __ldg(reinterpret_cast<const float4 *>(gy + off) + i);
+            if (RELU) {   // gradient of the fused ReLU: pass only where the activation was positive
+                const float4 a = __ldg(reinterpret_cast<const float4 *>(yact + off) + i);
+                g.x = a.x > 0.f ? g.x : 0.f; g.y = a.y > 0.f ? g.y : 0.f; g.z = a.z > 0.f ? g.z : 0.f; g.w = a.w > 0.f ? g.w : 0.f;
             }
-        } else {
-            for (int i = threadIdx.x; i < S; i += blockDim.x) {
-                float g = __ldg(gy + off + i);
-                if (RELU) g = __ldg(yact + off + i) > 0.f ? g : 0.f;
-                s += g;
-                d = fmaf(g, __ldg(x + off + i) - mean, d);
-            }
+            s += (g.x + g.y) + (g.z + g.w);
+            d = fmaf(g.x, v.x - mean, d); d = fmaf(g.y, v.y - mean, d);
+            d = fmaf(g.z, v.z - mean, d); d = fmaf(g.w, v.w - mean, d);
+            n += qstep; i += rstep;
+            if (i >= L) { i -= L; ++n; }
+        }
+    } else {
+        while (n < n1) {
+            const size_t off = ((size_t)n * C + c) * S + i;
+            float g = __ldg(gy + off);
+            if (RELU) g = __ldg(yact + off) > 0.f ? g : 0.f;
+            s += g;
+            d = fmaf(g, __ldg(x + off) - mean, d);
+            n += qstep; i += rstep;
+            if (i >= L) { i -= L; ++n; }
         }
     }
     s = block_sum(s, sh);
@@ -240,13 +249,15 @@ grad_finish_kernel(const float2 *__restrict__ part, int C, int chunks, long long
 }
 
 // Backward, pass 3: the input gradient.
-template <bool RELU>
+template <bool RELU, int GROUP>
 __global__ void __launch_bounds__(256)
 grad_apply_kernel(const float *__restrict__ x, const float *__restrict__ gy, const float *__restrict__ yact,
                   float *__restrict__ gx, const GradCoef *__restrict__ coef, int train, int C, int S, long long planes)
 {
     const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)gy | (uintptr_t)gx | (uintptr_t)yact) & 15) == 0);
-    for (long long pl = blockIdx.x; pl < planes; pl += gridDim.x) {
+    constexpr int PER_CTA = 256 / GROUP;
+    const int sub = (int)threadIdx.x / GROUP, t = (int)threadIdx.x % GROUP;
+    for (long long pl = (long long)blockIdx.x * PER_CTA + sub; pl < planes; pl += (long long)gridDim.x * PER_CTA) {
         const GradCoef k = coef[pl % C];
         const float *xp = x + pl * S;
         const float *gp = gy + pl * S;
@@ -256,7 +267,7 @@ grad_apply_kernel(const float *__restrict__ x, const float *__restrict__ gy, con
             const float4 *g4 = reinterpret_cast<const float4 *>(gp);
             float4 *o4 = reinterpret_cast<float4 *>(op);
 #pragma unroll 4
-            for (int i = threadIdx.x; i < S / 4; i += blockDim.x) {
+            for (int i = t; i < S / 4; i += GROUP) {
                 float4 g = __ldg(g4 + i);
                 if (RELU) {
                     const float4 a = __ldg(reinterpret_cast<const float4 *>(yact + pl * S) + i);
@@ -275,7 +286,7 @@ grad_apply_kernel(const float *__restrict__ x, const float *__restrict__ gy, con
                 o4[i] = o;
             }
         } else {
-            for (int i = threadIdx.x; i < S; i += blockDim.x) {
+            for (int i = t; i < S; i += GROUP) {
                 float g = __ldg(gp + i);
                 if (RELU) g = __ldg(yact + pl * S + i) > 0.f ? g : 0.f;
                 op[i] = train ? (g - (__ldg(xp + i) - k.mean) * k.proj - k.gmean) * k.gscale : g * k.gscale;
@@ -291,10 +302,28 @@ static int pick_chunks(int N, int C)
     return std::max(1, std::min(N, want));
 }
 
-static int plane_grid(long long planes)
+// Planes of up to 1024 elements are handled by one warp each, larger ones by a whole CTA.
+static bool small_planes(int S) { return S <= 1024; }
+static int plane_grid(long long planes, int S)
 {
     const long long cap = (long long)sm_count() * 16;
-    return (int)std::max(1LL, std::min(planes, cap));
+    const long long per_cta = small_planes(S) ? 8 : 1;
+    return (int)std::max(1LL, std::min((planes + per_cta - 1) / per_cta, cap));
+}
+
+template <bool RELU>
+static void launch_apply(const float *x, float *y, const float *weight, const float *bias, const float *mean_v,
+                         const float *std_or_var, int train, float eps, int C, int S, long long planes, cudaStream_t stream)
+{
+    if (small_planes(S)) apply_kernel<RELU, 32><<<plane_grid(planes, S), 256, 0, stream>>>(x, y, weight, bias, mean_v, std_or_var, train, eps, C, S, planes);
+    else apply_kernel<RELU, 256><<<plane_grid(planes, S), 256, 0, stream>>>(x, y, weight, bias, mean_v, std_or_var, train, eps, C, S, planes);
+}
+template <bool RELU>
+static void launch_grad_apply(const float *x, const float *gy, const float *yact, float *gx, const GradCoef *coef, int train,
+                              int C, int S, long long planes, cudaStream_t stream)
+{
+    if (small_planes(S)) grad_apply_kernel<RELU, 32><<<plane_grid(planes, S), 256, 0, stream>>>(x, gy, yact, gx, coef, train, C, S, planes);
+    else grad_apply_kernel<RELU, 256><<<plane_grid(planes, S), 256, 0, stream>>>(x, gy, yact, gx, coef, train, C, S, planes);
 }
 
 }  // namespace bn
@@ -335,11 +364,11 @@ static int bn_forward_impl(const float *x, float *y, const float *weight, const 
         stats_finish_kernel<<<ceil_div(C, 128), 128, 0, stream>>>(part, C, chunks, running_mean, running_var, save_mean,
                                                                  save_std, momentum, eps);
         CUNN_LAUNCH_CHECK("batch norm statistics finish");
-        if (relu) apply_kernel<true><<<plane_grid(planes), 256, 0, stream>>>(x, y, weight, bias, save_mean, save_std, 1, (float)eps, C, S, planes);
-        else apply_kernel<false><<<plane_grid(planes), 256, 0, stream>>>(x, y, weight, bias, save_mean, save_std, 1, (float)eps, C, S, planes);
+        if (relu) launch_apply<true>(x, y, weight, bias, save_mean, save_std, 1, (float)eps, C, S, planes, stream);
+        else launch_apply<false>(x, y, weight, bias, save_mean, save_std, 1, (float)eps, C, S, planes, stream);
     } else {
-        if (relu) apply_kernel<true><<<plane_grid(planes), 256, 0, stream>>>(x, y, weight, bias, running_mean, running_var, 0, (float)eps, C, S, planes);
-        else apply_kernel<false><<<plane_grid(planes), 256, 0, stream>>>(x, y, weight, bias, running_mean, running_var, 0, (float)eps, C, S, planes);
+        if (relu) launch_apply<true>(x, y, weight, bias, running_mean, running_var, 0, (float)eps, C, S, planes, stream);
+        else launch_apply<false>(x, y, weight, bias, running_mean, running_var, 0, (float)eps, C, S, planes, stream);
     }
     CUNN_LAUNCH_CHECK("batch norm apply");
     return 0;
@@ -402,8 +431,8 @@ static int bn_backward_impl(const float *x, const float *gy, const float *yact, 
                                                             eps, scale, grad_weight, grad_bias, coef);
     CUNN_LAUNCH_CHECK("batch norm gradient finish");
     if (gx) {
-        if (yact) grad_apply_kernel<true><<<plane_grid(planes), 256, 0, stream>>>(x, gy, yact, gx, coef, train, C, S, planes);
-        else grad_apply_kernel<false><<<plane_grid(planes), 256, 0, stream>>>(x, gy, nullptr, gx, coef, train, C, S, planes);
+        if (yact) launch_grad_apply<true>(x, gy, yact, gx, coef, train, C, S, planes, stream);
+        else launch_grad_apply<false>(x, gy, nullptr, gx, coef, train, C, S, planes, stream);
         CUNN_LAUNCH_CHECK("batch norm input gradient");
     }
     return 0;

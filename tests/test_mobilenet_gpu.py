@@ -114,7 +114,8 @@ def test_mobilenet_step_matches_oracle(ref64, ref32):
     # SGD update: p -= lr * g
     before = rep.params.clone()
     rep.sgd(0.1)
-    assert torch.allclose(rep.params, before - 0.1 * rep.grads, rtol=0, atol=1e-7)
+    # the kernel may contract p - lr * g into one fused multiply-add: allow one rounding of the result
+    assert torch.allclose(rep.params, before - 0.1 * rep.grads, rtol=2e-7, atol=1e-7)
 
 
 def test_mobilenet_layout_matches_reference_parameter_count():
