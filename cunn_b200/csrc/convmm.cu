@@ -19,6 +19,7 @@
 // Input gradients for stride > 1 use a plain gather kernel (no network on the benchmarked path needs
 // them: a strided first layer has no input gradient).
 #include "common.cuh"
+#include "stemconv.h"
 
 #include <algorithm>
 
@@ -1209,6 +1210,7 @@ extern "C" CUNN_API int cunn_b200_convmm_forward(const float *x, const float *we
     if (check(N, C, H, W, K, kH, kW, dH, dW, padH, padW, &oH, &oW)) return 1;
     if (N == 0) return 0;
     CUNN_CHECK_ARG(x && weight && y, "null tensor pointer");
+    if (stem::applies(C, K, kH, kW)) return stem::forward(x, weight, bias, y, N, H, W, oH, oW, dH, dW, padH, padW, stream);
     if (pw_applies(kH, kW, dH, dW, padH, padW)) {
         pw::Params q{};
         q.a = x; q.b = weight; q.bias = bias; q.out = y; q.status = device_status_ptr();
@@ -1274,6 +1276,7 @@ extern "C" CUNN_API size_t cunn_b200_convmm_acc_grad_workspace(int N, int C, int
 {
     int oH, oW;
     if (check(N, C, H, W, K, kH, kW, dH, dW, padH, padW, &oH, &oW) || N == 0) return 0;
+    if (stem::applies(C, K, kH, kW)) return stem::wgrad_workspace_bytes();
     int bn, splits, ips, pb;
     if (pw_applies(kH, kW, dH, dW, padH, padW)) {
         pw_wgrad_plan(N, C, K, H * W, &bn, &splits, &ips);
@@ -1301,6 +1304,20 @@ extern "C" CUNN_API int cunn_b200_convmm_acc_grad(const float *x, const float *g
                    workspace ? workspace_bytes : (size_t)0);
     int bn, splits, ips, pb;
     const int kk = kH * kW;
+    if (stem::applies(C, K, kH, kW)) {
+        const int ctas = stem::wgrad_ctas();
+        const long long n = (long long)K * C * kk;
+        float *partial = (float *)workspace, *bias_part = partial + (size_t)ctas * n;
+        if (stem::weight_grad_partials(x, gy, partial, grad_bias ? bias_part : nullptr, N, H, W, oH, oW, dH, dW, padH, padW, stream)) return 1;
+        const int rblocks = (int)std::max(1LL, std::min(ceil_div_ll(n, 256), (long long)sm_count() * 8));
+        wgrad_reduce_kernel<<<rblocks, 256, 0, stream>>>(partial, grad_weight, n, ctas, scale);
+        CUNN_LAUNCH_CHECK("convmm acc grad reduce");
+        if (grad_bias) {
+            bias_finish_kernel<<<ceil_div(K, 128), 128, 0, stream>>>(bias_part, grad_bias, K, ctas, scale);
+            CUNN_LAUNCH_CHECK("convmm bias gradient finish");
+        }
+        return 0;
+    }
     if (pw_applies(kH, kW, dH, dW, padH, padW)) {
         pw_wgrad_plan(N, C, K, H * W, &bn, &splits, &ips);
         const long long n = (long long)K * C;

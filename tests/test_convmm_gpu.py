@@ -86,6 +86,9 @@ def test_convmm_golden(F, name):
     (2, 5, 10, 10, 7, 5, 2, 2, True),        # 5x5 stride 2 (generic k decomposition, gather dgrad)
     (2, 130, 6, 6, 20, 3, 1, 1, True),       # Kd = 1170: many k-blocks, ragged tail
     (9, 4, 5, 5, 4, 1, 2, 0, True),          # 1x1 stride 2
+    (3, 3, 17, 19, 32, 3, 1, 1, True),       # first-layer kernels: stride 1, odd sizes
+    (2, 3, 16, 16, 32, 3, 2, 0, False),      # first-layer kernels: no padding, no bias
+    (80, 3, 64, 64, 32, 3, 2, 1, True),      # first-layer kernels: more pixel tiles than CTAs
     (8, 32, 56, 56, 64, 1, 1, 0, True),      # pointwise, one k-block, more tiles than SMs (persistent loop)
     (16, 128, 28, 28, 128, 1, 1, 0, True),   # pointwise, four k-blocks, two accumulator sets
     (2, 1024, 14, 14, 192, 1, 1, 0, False),  # pointwise, long reduction, ragged second column tile
