@@ -125,6 +125,13 @@ stats_finish_kernel(const ChunkStat *__restrict__ part, int C, int chunks, float
     running_var[c] = (float)((1.0 - momentum) * (double)running_var[c] + momentum * (double)unbiased);
 }
 
+// gamma * (x - mean) * invstd + beta with every rounding pinned (no fused multiply-add), so that the backward
+// kernels can recompute the sign of the forward value bit for bit.
+__device__ __forceinline__ float bn_value(float v, float mean, float invstd, float g, float b)
+{
+    return __fadd_rn(__fmul_rn(__fmul_rn(g, __fsub_rn(v, mean)), invstd), b);
+}
+
 // y = gamma * (x - mean) * invstd + beta, per plane.  Training reads mean / invstd from save_*, inference
 // derives them from the running statistics.
 // GROUP threads (a warp for small planes, the whole CTA for large ones) share a plane.
@@ -153,14 +160,14 @@ apply_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__
             for (int i = t; i < S / 4; i += GROUP) {
                 const float4 v = __ldg(x4 + i);
                 float4 o;
-                o.x = act(g * (v.x - mean) * invstd + b);
-                o.y = act(g * (v.y - mean) * invstd + b);
-                o.z = act(g * (v.z - mean) * invstd + b);
-                o.w = act(g * (v.w - mean) * invstd + b);
+                o.x = act(bn_value(v.x, mean, invstd, g, b));
+                o.y = act(bn_value(v.y, mean, invstd, g, b));
+                o.z = act(bn_value(v.z, mean, invstd, g, b));
+                o.w = act(bn_value(v.w, mean, invstd, g, b));
                 y4[i] = o;
             }
         } else {
-            for (int i = t; i < S; i += GROUP) yp[i] = act(g * (__ldg(xp + i) - mean) * invstd + b);
+            for (int i = t; i < S; i += GROUP) yp[i] = act(bn_value(__ldg(xp + i), mean, invstd, g, b));
         }
     }
 }
@@ -168,16 +175,24 @@ apply_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__
 // Backward, pass 1: per (channel, chunk) sums of gy and gy * (x - mean).
 template <bool RELU>
 __global__ void __launch_bounds__(256)
-grad_stats_kernel(const float *__restrict__ x, const float *__restrict__ gy, const float *__restrict__ yact,
-                  float2 *__restrict__ part, const float *__restrict__ mean_v, int N, int C, int S, int chunks)
+grad_stats_kernel(const float *__restrict__ x, const float *__restrict__ gy, float2 *__restrict__ part,
+                  const float *__restrict__ mean_v, const float *__restrict__ std_or_var, const float *__restrict__ weight,
+                  const float *__restrict__ bias, int train, float eps, int N, int C, int S, int chunks)
 {
     __shared__ float sh[8];
     const int c = blockIdx.x / chunks, j = blockIdx.x % chunks;
     int n0, n1;
     chunk_range(N, chunks, j, &n0, &n1);
     const float mean = __ldg(mean_v + c);
+    // fused ReLU: the gradient passes only where the forward value was positive; its sign is recomputed from x
+    float invstd = 0.f, gam = 1.f, bet = 0.f;
+    if (RELU) {
+        invstd = train ? __ldg(std_or_var + c) : 1.f / sqrtf(__ldg(std_or_var + c) + eps);
+        gam = weight ? __ldg(weight + c) : 1.f;
+        bet = bias ? __ldg(bias + c) : 0.f;
+    }
     float s = 0.f, d = 0.f;
-    const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)gy | (uintptr_t)yact) & 15) == 0);
+    const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)gy) & 15) == 0);
     const int L = vec ? S / 4 : S;
     const int qstep = (int)blockDim.x / L, rstep = (int)blockDim.x % L;
     int n = n0 + (int)threadIdx.x / L, i = (int)threadIdx.x % L;
@@ -186,9 +201,11 @@ grad_stats_kernel(const float *__restrict__ x, const float *__restrict__ gy, con
             const size_t off = ((size_t)n * C + c) * S;
             const float4 v = __ldg(reinterpret_cast<const float4 *>(x + off) + i);
             float4 g = __ldg(reinterpret_cast<const float4 *>(gy + off) + i);
-            if (RELU) {   // gradient of the fused ReLU: pass only where the activation was positive
-                const float4 a = __ldg(reinterpret_cast<const float4 *>(yact + off) + i);
-                g.x = a.x > 0.f ? g.x : 0.f; g.y = a.y > 0.f ? g.y : 0.f; g.z = a.z > 0.f ? g.z : 0.f; g.w = a.w > 0.f ? g.w : 0.f;
+            if (RELU) {
+                g.x = bn_value(v.x, mean, invstd, gam, bet) > 0.f ? g.x : 0.f;
+                g.y = bn_value(v.y, mean, invstd, gam, bet) > 0.f ? g.y : 0.f;
+                g.z = bn_value(v.z, mean, invstd, gam, bet) > 0.f ? g.z : 0.f;
+                g.w = bn_value(v.w, mean, invstd, gam, bet) > 0.f ? g.w : 0.f;
             }
             s += (g.x + g.y) + (g.z + g.w);
             d = fmaf(g.x, v.x - mean, d); d = fmaf(g.y, v.y - mean, d);
@@ -200,9 +217,10 @@ grad_stats_kernel(const float *__restrict__ x, const float *__restrict__ gy, con
         while (n < n1) {
             const size_t off = ((size_t)n * C + c) * S + i;
             float g = __ldg(gy + off);
-            if (RELU) g = __ldg(yact + off) > 0.f ? g : 0.f;
+            const float v = __ldg(x + off);
+            if (RELU) g = bn_value(v, mean, invstd, gam, bet) > 0.f ? g : 0.f;
             s += g;
-            d = fmaf(g, __ldg(x + off) - mean, d);
+            d = fmaf(g, v - mean, d);
             n += qstep; i += rstep;
             if (i >= L) { i -= L; ++n; }
         }
@@ -218,11 +236,12 @@ grad_stats_kernel(const float *__restrict__ x, const float *__restrict__ gy, con
 //   gx = gy * gscale                                     (inference)
 struct GradCoef {
     float mean, proj, gmean, gscale;
+    float invstd, gamma, beta, pad;     // forward coefficients, for the sign of the fused ReLU's input
 };
 
 __global__ void __launch_bounds__(128)
 grad_finish_kernel(const float2 *__restrict__ part, int C, int chunks, long long count,
-                   const float *__restrict__ weight, const float *__restrict__ mean_v,
+                   const float *__restrict__ weight, const float *__restrict__ bias, const float *__restrict__ mean_v,
                    const float *__restrict__ std_or_var, int train, double eps, double scale,
                    float *__restrict__ grad_weight, float *__restrict__ grad_bias, GradCoef *__restrict__ coef)
 {
@@ -243,6 +262,10 @@ grad_finish_kernel(const float2 *__restrict__ part, int C, int chunks, long long
     k.gmean = (float)(s * norm);
     k.proj = (float)(d * norm * (double)stdv * (double)stdv);
     k.gscale = stdv * w;
+    k.invstd = train ? std_or_var[c] : 1.f / sqrtf(std_or_var[c] + (float)eps);   // as the forward kernel computes it
+    k.gamma = w;
+    k.beta = bias ? bias[c] : 0.f;
+    k.pad = 0.f;
     coef[c] = k;
     if (grad_weight) grad_weight[c] = (float)((double)grad_weight[c] + scale * d * (double)stdv);
     if (grad_bias) grad_bias[c] = (float)((double)grad_bias[c] + scale * s);
@@ -251,10 +274,10 @@ grad_finish_kernel(const float2 *__restrict__ part, int C, int chunks, long long
 // Backward, pass 3: the input gradient.
 template <bool RELU, int GROUP>
 __global__ void __launch_bounds__(256)
-grad_apply_kernel(const float *__restrict__ x, const float *__restrict__ gy, const float *__restrict__ yact,
-                  float *__restrict__ gx, const GradCoef *__restrict__ coef, int train, int C, int S, long long planes)
+grad_apply_kernel(const float *__restrict__ x, const float *__restrict__ gy, float *__restrict__ gx,
+                  const GradCoef *__restrict__ coef, int train, int C, int S, long long planes)
 {
-    const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)gy | (uintptr_t)gx | (uintptr_t)yact) & 15) == 0);
+    const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)gy | (uintptr_t)gx) & 15) == 0);
     constexpr int PER_CTA = 256 / GROUP;
     const int sub = (int)threadIdx.x / GROUP, t = (int)threadIdx.x % GROUP;
     for (long long pl = (long long)blockIdx.x * PER_CTA + sub; pl < planes; pl += (long long)gridDim.x * PER_CTA) {
@@ -269,13 +292,16 @@ grad_apply_kernel(const float *__restrict__ x, const float *__restrict__ gy, con
 #pragma unroll 4
             for (int i = t; i < S / 4; i += GROUP) {
                 float4 g = __ldg(g4 + i);
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (RELU || train) v = __ldg(x4 + i);
                 if (RELU) {
-                    const float4 a = __ldg(reinterpret_cast<const float4 *>(yact + pl * S) + i);
-                    g.x = a.x > 0.f ? g.x : 0.f; g.y = a.y > 0.f ? g.y : 0.f; g.z = a.z > 0.f ? g.z : 0.f; g.w = a.w > 0.f ? g.w : 0.f;
+                    g.x = bn_value(v.x, k.mean, k.invstd, k.gamma, k.beta) > 0.f ? g.x : 0.f;
+                    g.y = bn_value(v.y, k.mean, k.invstd, k.gamma, k.beta) > 0.f ? g.y : 0.f;
+                    g.z = bn_value(v.z, k.mean, k.invstd, k.gamma, k.beta) > 0.f ? g.z : 0.f;
+                    g.w = bn_value(v.w, k.mean, k.invstd, k.gamma, k.beta) > 0.f ? g.w : 0.f;
                 }
                 float4 o;
                 if (train) {
-                    const float4 v = __ldg(x4 + i);
                     o.x = (g.x - (v.x - k.mean) * k.proj - k.gmean) * k.gscale;
                     o.y = (g.y - (v.y - k.mean) * k.proj - k.gmean) * k.gscale;
                     o.z = (g.z - (v.z - k.mean) * k.proj - k.gmean) * k.gscale;
@@ -288,8 +314,9 @@ grad_apply_kernel(const float *__restrict__ x, const float *__restrict__ gy, con
         } else {
             for (int i = t; i < S; i += GROUP) {
                 float g = __ldg(gp + i);
-                if (RELU) g = __ldg(yact + pl * S + i) > 0.f ? g : 0.f;
-                op[i] = train ? (g - (__ldg(xp + i) - k.mean) * k.proj - k.gmean) * k.gscale : g * k.gscale;
+                const float v = (RELU || train) ? __ldg(xp + i) : 0.f;
+                if (RELU) g = bn_value(v, k.mean, k.invstd, k.gamma, k.beta) > 0.f ? g : 0.f;
+                op[i] = train ? (g - (v - k.mean) * k.proj - k.gmean) * k.gscale : g * k.gscale;
             }
         }
     }
@@ -319,11 +346,11 @@ static void launch_apply(const float *x, float *y, const float *weight, const fl
     else apply_kernel<RELU, 256><<<plane_grid(planes, S), 256, 0, stream>>>(x, y, weight, bias, mean_v, std_or_var, train, eps, C, S, planes);
 }
 template <bool RELU>
-static void launch_grad_apply(const float *x, const float *gy, const float *yact, float *gx, const GradCoef *coef, int train,
-                              int C, int S, long long planes, cudaStream_t stream)
+static void launch_grad_apply(const float *x, const float *gy, float *gx, const GradCoef *coef, int train, int C, int S,
+                              long long planes, cudaStream_t stream)
 {
-    if (small_planes(S)) grad_apply_kernel<RELU, 32><<<plane_grid(planes, S), 256, 0, stream>>>(x, gy, yact, gx, coef, train, C, S, planes);
-    else grad_apply_kernel<RELU, 256><<<plane_grid(planes, S), 256, 0, stream>>>(x, gy, yact, gx, coef, train, C, S, planes);
+    if (small_planes(S)) grad_apply_kernel<RELU, 32><<<plane_grid(planes, S), 256, 0, stream>>>(x, gy, gx, coef, train, C, S, planes);
+    else grad_apply_kernel<RELU, 256><<<plane_grid(planes, S), 256, 0, stream>>>(x, gy, gx, coef, train, C, S, planes);
 }
 
 }  // namespace bn
@@ -394,7 +421,7 @@ extern "C" CUNN_API int cunn_b200_batchnorm_relu_forward(const float *x, float *
                            workspace, workspace_bytes, stream, true);
 }
 
-static int bn_backward_impl(const float *x, const float *gy, const float *yact, float *gx, float *grad_weight,
+static int bn_backward_impl(const float *x, const float *gy, bool relu, const float *bias, float *gx, float *grad_weight,
                             float *grad_bias, const float *weight, const float *running_mean, const float *running_var,
                             const float *save_mean, const float *save_std, int N, int C, int S, int train, double scale,
                             double eps, void *workspace, size_t workspace_bytes, cunn_stream_t stream_)
@@ -421,18 +448,18 @@ static int bn_backward_impl(const float *x, const float *gy, const float *yact, 
     // inference-mode input gradient needs no sums; they are still required for gradWeight / gradBias
     const bool need_sums = train || grad_weight || grad_bias;
     if (need_sums) {
-        if (yact) grad_stats_kernel<true><<<C * chunks, 256, 0, stream>>>(x, gy, yact, part, mean_v, N, C, S, chunks);
-        else grad_stats_kernel<false><<<C * chunks, 256, 0, stream>>>(x, gy, nullptr, part, mean_v, N, C, S, chunks);
+        if (relu) grad_stats_kernel<true><<<C * chunks, 256, 0, stream>>>(x, gy, part, mean_v, sv, weight, bias, train, (float)eps, N, C, S, chunks);
+        else grad_stats_kernel<false><<<C * chunks, 256, 0, stream>>>(x, gy, part, mean_v, sv, weight, bias, train, (float)eps, N, C, S, chunks);
         CUNN_LAUNCH_CHECK("batch norm gradient sums");
     } else {
         CUNN_CUDA(cudaMemsetAsync(part, 0, (size_t)C * chunks * sizeof(float2), stream));
     }
-    grad_finish_kernel<<<ceil_div(C, 128), 128, 0, stream>>>(part, C, chunks, (long long)N * S, weight, mean_v, sv, train,
+    grad_finish_kernel<<<ceil_div(C, 128), 128, 0, stream>>>(part, C, chunks, (long long)N * S, weight, bias, mean_v, sv, train,
                                                             eps, scale, grad_weight, grad_bias, coef);
     CUNN_LAUNCH_CHECK("batch norm gradient finish");
     if (gx) {
-        if (yact) launch_grad_apply<true>(x, gy, yact, gx, coef, train, C, S, planes, stream);
-        else launch_grad_apply<false>(x, gy, nullptr, gx, coef, train, C, S, planes, stream);
+        if (relu) launch_grad_apply<true>(x, gy, gx, coef, train, C, S, planes, stream);
+        else launch_grad_apply<false>(x, gy, gx, coef, train, C, S, planes, stream);
         CUNN_LAUNCH_CHECK("batch norm input gradient");
     }
     return 0;
@@ -445,19 +472,17 @@ extern "C" CUNN_API int cunn_b200_batchnorm_backward(const float *x, const float
                                                      double eps, void *workspace, size_t workspace_bytes,
                                                      cunn_stream_t stream)
 {
-    return bn_backward_impl(x, gy, nullptr, gx, grad_weight, grad_bias, weight, running_mean, running_var, save_mean, save_std,
+    return bn_backward_impl(x, gy, false, nullptr, gx, grad_weight, grad_bias, weight, running_mean, running_var, save_mean, save_std,
                             N, C, S, train, scale, eps, workspace, workspace_bytes, stream);
 }
 
-extern "C" CUNN_API int cunn_b200_batchnorm_relu_backward(const float *x, const float *y, const float *gy, float *gx,
-                                                          float *grad_weight, float *grad_bias, const float *weight,
+extern "C" CUNN_API int cunn_b200_batchnorm_relu_backward(const float *x, const float *gy, float *gx, float *grad_weight,
+                                                          float *grad_bias, const float *weight, const float *bias,
                                                           const float *running_mean, const float *running_var,
                                                           const float *save_mean, const float *save_std, int N, int C,
                                                           int S, int train, double scale, double eps, void *workspace,
                                                           size_t workspace_bytes, cunn_stream_t stream)
 {
-    clear_error();
-    CUNN_CHECK_ARG(y || N == 0, "the fused BN+ReLU backward needs the forward output y");
-    return bn_backward_impl(x, gy, y, gx, grad_weight, grad_bias, weight, running_mean, running_var, save_mean, save_std, N, C,
+    return bn_backward_impl(x, gy, true, bias, gx, grad_weight, grad_bias, weight, running_mean, running_var, save_mean, save_std, N, C,
                             S, train, scale, eps, workspace, workspace_bytes, stream);
 }

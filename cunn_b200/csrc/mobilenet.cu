@@ -243,10 +243,10 @@ extern "C" CUNN_API int cunn_b200_mobilenet_step(const cunn_b200_mobilenet_confi
     STEP(cunn_b200_avgpool_backward(F(a.gpooled), g, B, m.feat, fh, fh, 1, 1, fh, fh, 1, 1, 0, 0, 1, stream));
     for (int i = nl - 1; i >= 0; --i) {
         const Layer &L = m.layers[i];
-        float *co = F(a.conv_out[i]), *ac = F(a.act[i]), *sv = F(a.save[i]);
+        float *co = F(a.conv_out[i]), *sv = F(a.save[i]);
         const float *xin = (i == 0) ? images : F(a.act[i - 1]);
-        STEP(cunn_b200_batchnorm_relu_backward(co, ac, g, g2, grads + L.g_off, grads + L.beta_off, params + L.g_off,
-                                               bn_running + L.bn_off, bn_running + L.bn_off + L.cout, sv, sv + L.cout, B,
+        STEP(cunn_b200_batchnorm_relu_backward(co, g, g2, grads + L.g_off, grads + L.beta_off, params + L.g_off,
+                                               params + L.beta_off, bn_running + L.bn_off, bn_running + L.bn_off + L.cout, sv, sv + L.cout, B,
                                                L.cout, L.hout * L.hout, 1, 1.0, eps, work, wbytes, stream));
         // g2 = gradient w.r.t. the convolution output
         if (L.kind == KIND_DW) {

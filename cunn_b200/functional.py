@@ -277,15 +277,15 @@ def batchnorm_relu_forward(x, weight, bias, running_mean, running_var, train, mo
     return out, save_mean, save_std
 
 
-def batchnorm_relu_backward(x, y, gy, weight, running_mean, running_var, save_mean, save_std, train, scale=1.0, eps=1e-5,
+def batchnorm_relu_backward(x, gy, weight, bias, running_mean, running_var, save_mean, save_std, train, scale=1.0, eps=1e-5,
                             grad_weight=None, grad_bias=None):
-    """Backward of batchnorm_relu_forward given its output y; accumulates into grad_weight / grad_bias."""
-    _chk(x, y, gy, weight, grad_weight, grad_bias)
+    """Backward of batchnorm_relu_forward (same x, weight, bias and statistics); accumulates into grad_weight / grad_bias."""
+    _chk(x, gy, weight, bias, grad_weight, grad_bias)
     N, C, S = _bn_dims(x)
     out = torch.empty_like(x)
     ws = workspace(lib.cunn_b200_batchnorm_workspace(N, C), x.device)
-    check(lib.cunn_b200_batchnorm_relu_backward(_ptr(x), _ptr(y), _ptr(gy), _ptr(out), _ptr(grad_weight), _ptr(grad_bias),
-                                                _ptr(weight), _ptr(running_mean), _ptr(running_var), _ptr(save_mean),
+    check(lib.cunn_b200_batchnorm_relu_backward(_ptr(x), _ptr(gy), _ptr(out), _ptr(grad_weight), _ptr(grad_bias),
+                                                _ptr(weight), _ptr(bias), _ptr(running_mean), _ptr(running_var), _ptr(save_mean),
                                                 _ptr(save_std), N, C, S, int(train), scale, eps, _ptr(ws), ws.numel(),
                                                 _stream()))
     return out

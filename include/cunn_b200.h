@@ -169,16 +169,17 @@ CUNN_API int cunn_b200_batchnorm_backward(const float *x, const float *gy, float
                                           int N, int C, int S, int train, double scale, double eps,
                                           void *workspace, size_t workspace_bytes, cunn_stream_t stream);
 
-/* BatchNormalization followed by ReLU in one pass (y = max(0, BN(x))), and its backward given that y: the
- * caller-side fusion of nn.SpatialBatchNormalization + nn.ReLU, which saves two full activation passes per
- * layer in each direction.  No counterpart in the reference (it runs BatchNormalization.cu and Threshold.cu
- * as separate kernels); results equal the two separate calls exactly. */
+/* BatchNormalization followed by ReLU in one pass (y = max(0, BN(x))), and its backward: the caller-side
+ * fusion of nn.SpatialBatchNormalization + nn.ReLU, which saves two full activation passes per layer in each
+ * direction.  The backward needs x, the affine parameters and the statistics only: it recomputes the sign of
+ * BN(x) with the forward's exact arithmetic instead of reading y.  No counterpart in the reference (it runs
+ * BatchNormalization.cu and Threshold.cu as separate kernels); results equal the two separate calls exactly. */
 CUNN_API int cunn_b200_batchnorm_relu_forward(const float *x, float *y, const float *weight, const float *bias,
                                               float *running_mean, float *running_var, float *save_mean, float *save_std,
                                               int N, int C, int S, int train, double momentum, double eps,
                                               void *workspace, size_t workspace_bytes, cunn_stream_t stream);
-CUNN_API int cunn_b200_batchnorm_relu_backward(const float *x, const float *y, const float *gy, float *gx,
-                                               float *grad_weight, float *grad_bias, const float *weight,
+CUNN_API int cunn_b200_batchnorm_relu_backward(const float *x, const float *gy, float *gx, float *grad_weight,
+                                               float *grad_bias, const float *weight, const float *bias,
                                                const float *running_mean, const float *running_var,
                                                const float *save_mean, const float *save_std, int N, int C, int S,
                                                int train, double scale, double eps, void *workspace,

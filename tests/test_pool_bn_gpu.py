@@ -233,5 +233,5 @@ def test_bn_relu_fused_equals_separate_calls(F, shape):
     assert torch.equal(y, y_ref) and torch.equal(sm, sm2) and torch.equal(ss, ss2) and torch.equal(rm1, rm2)
     gw1, gb1, gw2, gb2 = (torch.zeros(C, device="cuda") for _ in range(4))
     gx_ref = F.batchnorm_backward(x, F.threshold_backward(z, gy), w, rm1, rv1, sm, ss, True, grad_weight=gw1, grad_bias=gb1)
-    gx = F.batchnorm_relu_backward(x, y, gy, w, rm2, rv2, sm2, ss2, True, grad_weight=gw2, grad_bias=gb2)
+    gx = F.batchnorm_relu_backward(x, gy, w, b, rm2, rv2, sm2, ss2, True, grad_weight=gw2, grad_bias=gb2)
     assert torch.equal(gx, gx_ref) and torch.equal(gw1, gw2) and torch.equal(gb1, gb2)
