@@ -584,21 +584,13 @@ struct Params {
     int nacc, sets;    // accumulators per tile (k-blocks are dealt round-robin), accumulator sets in TMEM (1 or 2)
 };
 
-// hi = v rounded to tf32 (round half away, done in integer arithmetic), lo = v - hi.
-__device__ __forceinline__ void split_rn(float v, float &hi, float &lo)
+// 3xTF32 split of a raw fp32 tile in place.  The tensor core reads only the upper 19 bits of a tf32 operand,
+// so the raw value itself serves as hi = v with the low 13 mantissa bits dropped; lo = v - hi is exact in fp32
+// and is the only tile that has to be written.
+__device__ __forceinline__ float lo_part(float v) { return v - __uint_as_float(__float_as_uint(v) & 0xffffe000u); }
+__device__ __forceinline__ void store_lo_at(unsigned char *lo_tile, uint32_t off, const float4 &v)
 {
-    hi = __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xffffe000u);
-    lo = v - hi;
-}
-__device__ __forceinline__ void store_split_at(unsigned char *hi_tile, unsigned char *lo_tile, uint32_t off, const float4 &v)
-{
-    float4 h, l;
-    split_rn(v.x, h.x, l.x);
-    split_rn(v.y, h.y, l.y);
-    split_rn(v.z, h.z, l.z);
-    split_rn(v.w, h.w, l.w);
-    *reinterpret_cast<float4 *>(hi_tile + off) = h;
-    *reinterpret_cast<float4 *>(lo_tile + off) = l;
+    *reinterpret_cast<float4 *>(lo_tile + off) = make_float4(lo_part(v.x), lo_part(v.y), lo_part(v.z), lo_part(v.w));
 }
 __device__ __forceinline__ uint64_t desc_of(uint32_t addr, uint32_t lbo, uint32_t sbo)
 {
@@ -853,7 +845,7 @@ pw_gemm_kernel(const Params p)
 
     float bsum[2] = {0.f, 0.f};                         // WGRAD: running row sums of gy (bias gradient)
     unsigned char *const lo_base = smem + (size_t)RAW_STAGES * 2 * TILE;
-    // Splits this thread's own pieces of raw stage `rs` (its copies have landed): hi overwrites the raw value,
+    // Splits this thread's own pieces of raw stage `rs` (its copies have landed): the raw tile is the hi tile,
     // lo goes to the same offset of lo buffer `lb`.
     auto split_block = [&](int rs, int lb) {
         unsigned char *a_hi = smem + (size_t)rs * 2 * TILE, *b_hi = a_hi + TILE;
@@ -861,11 +853,11 @@ pw_gemm_kernel(const Params p)
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const float4 va = *reinterpret_cast<const float4 *>(a_hi + a_so[i]);
-            store_split_at(a_hi, a_lo, a_so[i], va);
+            store_lo_at(a_lo, a_so[i], va);
             if (OP == OP_WGRAD) bsum[i] += (va.x + va.y) + (va.z + va.w);
             if (b_store[i]) {
                 const float4 vb = *reinterpret_cast<const float4 *>(b_hi + b_so[i]);
-                store_split_at(b_hi, b_lo, b_so[i], vb);
+                store_lo_at(b_lo, b_so[i], vb);
             }
         }
     };
