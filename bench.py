@@ -36,8 +36,8 @@ METRIC = "dwconv_fwd_bwd_hbm_gbs"
 
 # DRAM traffic (read + write, MB) of one launch of the kernels that can top the per-launch time, from the
 # ncu capture summarised in profiles/dwconv_stack_ncu_sections.md (key: "<op>_<layer>").
-NCU_TRAFFIC_MB = {"wgrad_2": 264.3, "wgrad_1": 210.2, "fwd_2": 238.0, "dgrad_2": 200.7, "fwd_1": 154.6,
-                  "wgrad_3": 211.1}
+NCU_TRAFFIC_MB = {"wgrad_2": 261.3, "wgrad_1": 209.7, "fwd_2": 239.1, "dgrad_2": 199.1, "fwd_1": 155.1, "dgrad_1": 154.6,
+                  "wgrad_3": 209.9, "fwd_3": 153.7, "dgrad_3": 153.2}
 
 
 def out_size(hw, stride):
