@@ -581,6 +581,9 @@ struct Params {
     int kblocks;       // k-blocks per tile
     int n_img, imgs_per_split, splits;
     int vec_a, vec_b;  // 16-byte global loads allowed for A / B
+    // kernels larger than 1x1 (KS != 1): the unfolded operand is gathered from a [g_C, g_H, g_W] image tensor, the
+    // pixel grid that drives the gather is pix_W wide (HW = its size)
+    int g_C, g_H, g_W, kH, kW, dH, dW, padH, padW, pix_W;
     int nacc, sets;    // accumulators per tile (k-blocks are dealt round-robin), accumulator sets in TMEM (1 or 2)
 };
 
@@ -624,13 +627,20 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 // Where the operand loads of one thread stand: tile, k-block and the thread's element offsets inside that tile.
 // M/N-major pieces: lane = group of 4 rows, k = warp + 16 i.  K-major pieces: chunk kc = tid & 7, rows (tid >> 3) + 64 i.
-template <int OP, int BN>
+// KS = 1: pointwise.  KS = 3 / 0: 3x3 / any kernel of up to 32 taps, any stride and padding: the same tiles, but
+// the unfolded operand is gathered with 4-byte copies (zero-filled outside the image).
+template <int OP, int BN, int KS>
 struct Loader {
     int tile, kb;
     int a_off[4];       // FWD/DGRAD: element offsets of the thread's 4 pixels (channel 0); WGRAD: [0..1] row offsets
     int b_off[2];       // FWD: offsets of the thread's two filter rows (+ chunk); DGRAD: [0] first column; WGRAD: row offsets
     unsigned a_mask, b_mask;
     int img, pix, img_end;   // WGRAD: image and pixel of the thread's chunk in the current k-block
+    unsigned tapmask[4];     // KS != 1, FWD/DGRAD: bit t set when tap t of pixel j lies inside the image
+    int b_tap[2];            // KS != 1, WGRAD: kh | kw << 8 of the thread's two unfolded rows
+
+    __device__ __forceinline__ int taps(const Params &p) const { return KS == 3 ? 9 : p.kH * p.kW; }
+    __device__ __forceinline__ int kcols(const Params &p) const { return KS == 3 ? 3 : p.kW; }
 
     __device__ __forceinline__ void setup(const Params &p, int t)
     {
@@ -641,7 +651,25 @@ struct Loader {
         if (OP != OP_WGRAD) {
             const int m_tile = t / p.n_tiles, n_tile = t - m_tile * p.n_tiles;
             const int m = m_tile * BM + lane * 4, n0 = n_tile * BN;
-            if (p.vec_a) {
+            if (KS != 1) {
+                const int kk = taps(p), kw_n = kcols(p);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    a_off[j] = 0;
+                    tapmask[j] = 0;
+                    if (m + j < p.M_total) {
+                        const int im = (m + j) / p.HW, r = (m + j) - im * p.HW;
+                        const int ph = r / p.pix_W, pw_ = r - ph * p.pix_W;
+                        const int ih0 = ph * p.dH - p.padH, iw0 = pw_ * p.dW - p.padW;
+                        a_off[j] = im * p.g_C * p.g_H * p.g_W + ih0 * p.g_W + iw0;
+                        a_mask |= 1u << j;
+                        for (int t2 = 0; t2 < kk; ++t2) {
+                            const int kh = t2 / kw_n, kw = t2 - kh * kw_n;
+                            if ((unsigned)(ih0 + kh) < (unsigned)p.g_H && (unsigned)(iw0 + kw) < (unsigned)p.g_W) tapmask[j] |= 1u << t2;
+                        }
+                    }
+                }
+            } else if (p.vec_a) {
                 if (m < p.M_total) {
                     const int im = m / p.HW;
                     a_off[0] = im * p.Kd * p.HW + (m - im * p.HW);
@@ -682,6 +710,13 @@ struct Loader {
                 const int m = m_tile * BM + row, n = n_tile * BN + row;
                 a_off[i] = m * p.HW;
                 b_off[i] = n * p.HW;
+                if (KS != 1) {
+                    // unfolded row n = (channel, kh, kw): offset of its tap inside an image
+                    const int kk = taps(p), kw_n = kcols(p);
+                    const int c = n / kk, t2 = n - c * kk, kh = t2 / kw_n, kw = t2 - kh * kw_n;
+                    b_off[i] = (c * p.g_H + kh) * p.g_W + kw;
+                    b_tap[i] = kh | (kw << 8);
+                }
                 if (m < p.M_total) a_mask |= 1u << i;
                 if (row < BN && n < p.N_total) b_mask |= 1u << i;
             }
@@ -735,7 +770,16 @@ struct Loader {
             for (int i = 0; i < 2; ++i) {
                 const int k = kb * BK + warp + 16 * i;
                 const bool kok = k < p.Kd;
-                if (p.vec_a) {
+                if (KS != 1) {
+                    const int kk = taps(p), kw_n = kcols(p);
+                    const int c = k / kk, t2 = k - c * kk, kh = t2 / kw_n, kw = t2 - kh * kw_n;
+                    const int koff = (c * p.g_H + kh) * p.g_W + kw;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const bool ok = kok && (tapmask[j] >> t2 & 1u);
+                        cp_async4(sa + a_so[i] + 4 * j, ok ? p.a + (a_off[j] + koff) : p.a, ok);
+                    }
+                } else if (p.vec_a) {
                     const bool ok = kok && a_mask;
                     cp_async16(sa + a_so[i], ok ? p.a + a_off[0] + k * p.HW : p.a, ok);
                 } else {
@@ -770,6 +814,17 @@ struct Loader {
                     if (!b_store[i]) continue;
                     const int k = kb * BK + warp + 16 * i;
                     const bool kok = k < p.Kd;
+                    if (KS != 1) {
+                        // B[c][(ko, kh, kw)] = W[ko][c][kH-1-kh][kW-1-kw]: the tap index runs backwards
+                        const int kk = taps(p);
+                        const int ko = k / kk, t2 = k - ko * kk;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const bool ok = kok && (b_mask >> j & 1u);
+                            cp_async4(sb + b_so[i] + 4 * j, ok ? p.b + ((size_t)(ko * p.N_total + b_off[0] + j) * kk + (kk - 1 - t2)) : p.b, ok);
+                        }
+                        continue;
+                    }
                     const float *src = p.b + (size_t)(kok ? k : 0) * p.N_total + b_off[0];
                     if (p.vec_b) {
                         const bool ok = kok && b_mask;
@@ -787,13 +842,30 @@ struct Loader {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 row_chunk(p, sa + a_so[i], p.a + a_off[i], p.M_total * p.HW, p.vec_a != 0, (a_mask >> i & 1u) != 0);
-                if (b_store[i]) row_chunk(p, sb + b_so[i], p.b + b_off[i], p.N_total * p.HW, p.vec_b != 0, (b_mask >> i & 1u) != 0);
+                if (KS == 1) {
+                    if (b_store[i]) row_chunk(p, sb + b_so[i], p.b + b_off[i], p.N_total * p.HW, p.vec_b != 0, (b_mask >> i & 1u) != 0);
+                } else if (b_store[i]) {
+                    // four consecutive output pixels of the unfolded row: x[img][c][oh * dH - padH + kh][ow * dW - padW + kw]
+                    const bool on = (b_mask >> i & 1u) != 0;
+                    const int kh = b_tap[i] & 255, kw = b_tap[i] >> 8;
+                    int ij = img, oh = pix / p.pix_W, ow = pix - oh * p.pix_W;
+                    const int rows = p.HW / p.pix_W;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (ow >= p.pix_W) { ow = 0; ++oh; }
+                        if (oh >= rows) { oh = 0; ++ij; }
+                        const int ih = oh * p.dH - p.padH, iw = ow * p.dW - p.padW;
+                        const bool ok = on && ij < img_end && (unsigned)(ih + kh) < (unsigned)p.g_H && (unsigned)(iw + kw) < (unsigned)p.g_W;
+                        cp_async4(sb + b_so[i] + 4 * j, ok ? p.b + ((size_t)ij * p.g_C * p.g_H * p.g_W + b_off[i] + ih * p.g_W + iw) : p.b, ok);
+                        ++ow;
+                    }
+                }
             }
         }
     }
 };
 
-template <int OP, int BN>
+template <int OP, int BN, int KS>
 __global__ void __launch_bounds__(THREADS, 1)
 pw_gemm_kernel(const Params p)
 {
@@ -963,7 +1035,7 @@ pw_gemm_kernel(const Params p)
             if (++kb == KB) { kb = 0; ++count; }
         }
     } else {
-        Loader<OP, BN> L;
+        Loader<OP, BN, KS> L;
         L.tile = (int)blockIdx.x;
         L.kb = 0;
         if (my_tiles > 0) L.setup(p, L.tile);
@@ -1135,14 +1207,30 @@ static bool pw_applies(int kH, int kW, int dH, int dW, int padH, int padW)
 static bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
 typedef void (*PwKernel)(const pw::Params);
-template <int OP>
-static PwKernel pw_pick(int bn)
+template <int OP, int KS>
+static PwKernel pw_pick_bn(int bn)
 {
     switch (bn) {
-        case 32: return pw::pw_gemm_kernel<OP, 32>;
-        case 64: return pw::pw_gemm_kernel<OP, 64>;
-        default: return pw::pw_gemm_kernel<OP, 128>;
+        case 32: return pw::pw_gemm_kernel<OP, 32, KS>;
+        case 64: return pw::pw_gemm_kernel<OP, 64, KS>;
+        default: return pw::pw_gemm_kernel<OP, 128, KS>;
     }
+}
+template <int OP>
+static PwKernel pw_pick(int bn, int ks = 1)
+{
+    if (ks == 1) return pw_pick_bn<OP, 1>(bn);
+    if (ks == 3) return pw_pick_bn<OP, 3>(bn);
+    return pw_pick_bn<OP, 0>(bn);
+}
+// Kernels of up to 32 taps run on the same persistent kernel with a gathering loader.
+static bool gather_applies(int kH, int kW) { return kH * kW <= 32; }
+// loader variant of the gathering path: 3x3 has its own instantiation, everything else (a strided or padded 1x1
+// included) the one with run-time kernel sizes
+static int gather_ks(int kH, int kW) { return (kH == 3 && kW == 3) ? 3 : 0; }
+static void set_geometry(pw::Params &q, int gC, int gH, int gW, int kH, int kW, int dH, int dW, int padH, int padW, int pixW)
+{
+    q.g_C = gC; q.g_H = gH; q.g_W = gW; q.kH = kH; q.kW = kW; q.dH = dH; q.dW = dW; q.padH = padH; q.padW = padW; q.pix_W = pixW;
 }
 static int pw_bn_for(int n_total) { return n_total <= 32 ? 32 : (n_total <= 64 ? 64 : 128); }
 
@@ -1214,6 +1302,18 @@ extern "C" CUNN_API int cunn_b200_convmm_forward(const float *x, const float *we
         pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
         return pw_launch(pw_pick<OP_FWD>(bn), q, stream);
     }
+    if (gather_applies(kH, kW)) {
+        pw::Params q{};
+        q.a = x; q.b = weight; q.bias = bias; q.out = y; q.status = device_status_ptr();
+        q.HW = oH * oW; q.M_total = N * oH * oW; q.N_total = K; q.Kd = C * kH * kW; q.kblocks = ceil_div(q.Kd, BK);
+        set_geometry(q, C, H, W, kH, kW, dH, dW, padH, padW, oW);
+        const int bn = pw_bn_for(K);
+        q.n_tiles = ceil_div(K, bn); q.tiles_per_split = 0; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
+        q.n_img = N; q.imgs_per_split = N; q.splits = 1;
+        q.vec_a = 0; q.vec_b = (q.Kd % 4 == 0) && aligned16(weight);
+        pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
+        return pw_launch(pw_pick<OP_FWD>(bn, gather_ks(kH, kW)), q, stream);
+    }
     GemmParams p{};
     p.a_src = x; p.b_src = weight; p.bias = bias; p.out = y; p.status = device_status_ptr();
     p.g_C = C; p.g_H = H; p.g_W = W; p.g_padH = padH; p.g_padW = padW; p.g_dH = dH; p.g_dW = dW; p.kH = kH; p.kW = kW;
@@ -1247,6 +1347,18 @@ extern "C" CUNN_API int cunn_b200_convmm_grad_input(const float *gy, const float
     }
     if (dH == 1 && dW == 1 && padH <= kH - 1 && padW <= kW - 1) {
         // stride 1: a convolution of gy with the kernel rotated by 180 degrees and padding k - 1 - pad
+        if (gather_applies(kH, kW)) {
+            pw::Params q{};
+            q.a = gy; q.b = weight; q.bias = nullptr; q.out = gx; q.status = device_status_ptr();
+            q.HW = H * W; q.M_total = N * H * W; q.N_total = C; q.Kd = K * kH * kW; q.kblocks = ceil_div(q.Kd, BK);
+            set_geometry(q, K, oH, oW, kH, kW, 1, 1, kH - 1 - padH, kW - 1 - padW, W);
+            const int bn = pw_bn_for(C);
+            q.n_tiles = ceil_div(C, bn); q.tiles_per_split = 0; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
+            q.n_img = N; q.imgs_per_split = N; q.splits = 1;
+            q.vec_a = 0; q.vec_b = 0;
+            pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
+            return pw_launch(pw_pick<OP_DGRAD>(bn, gather_ks(kH, kW)), q, stream);
+        }
         GemmParams p{};
         p.a_src = gy; p.b_src = weight; p.bias = nullptr; p.out = gx; p.status = device_status_ptr();
         p.g_C = K; p.g_H = oH; p.g_W = oW; p.g_padH = kH - 1 - padH; p.g_padW = kW - 1 - padW; p.g_dH = 1; p.g_dW = 1;
@@ -1273,6 +1385,10 @@ extern "C" CUNN_API size_t cunn_b200_convmm_acc_grad_workspace(int N, int C, int
     if (pw_applies(kH, kW, dH, dW, padH, padW)) {
         pw_wgrad_plan(N, C, K, H * W, &bn, &splits, &ips);
         return (size_t)splits * K * C * sizeof(float) + (size_t)K * splits * sizeof(float) + 256;
+    }
+    if (gather_applies(kH, kW)) {
+        pw_wgrad_plan(N, C * kH * kW, K, oH * oW, &bn, &splits, &ips);
+        return (size_t)splits * K * C * kH * kW * sizeof(float) + (size_t)K * splits * sizeof(float) + 256;
     }
     wgrad_plan(N, C, K, kH * kW, oH * oW, &bn, &splits, &ips, &pb);
     const int chunks = std::max(1, std::min(N, ceil_div(sm_count() * 4, K)));
@@ -1323,6 +1439,30 @@ extern "C" CUNN_API int cunn_b200_convmm_acc_grad(const float *x, const float *g
         q.vec_a = (q.HW % 4 == 0) && aligned16(gy); q.vec_b = (q.HW % 4 == 0) && aligned16(x);
         pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
         if (pw_launch(pw_pick<OP_WGRAD>(bn), q, stream)) return 1;
+        const int rblocks = (int)std::max(1LL, std::min(ceil_div_ll(n, 256), (long long)sm_count() * 8));
+        wgrad_reduce_kernel<<<rblocks, 256, 0, stream>>>((const float *)workspace, grad_weight, n, splits, scale);
+        CUNN_LAUNCH_CHECK("convmm acc grad reduce");
+        if (grad_bias) {
+            bias_finish_kernel<<<ceil_div(K, 128), 128, 0, stream>>>(q.bias_part, grad_bias, K, splits, scale);
+            CUNN_LAUNCH_CHECK("convmm bias gradient finish");
+        }
+        return 0;
+    }
+    if (gather_applies(kH, kW)) {
+        const int oHW = oH * oW;
+        pw_wgrad_plan(N, C * kk, K, oHW, &bn, &splits, &ips);
+        const long long n = (long long)K * C * kk;
+        pw::Params q{};
+        q.a = gy; q.b = x; q.bias = nullptr; q.out = (float *)workspace; q.status = device_status_ptr();
+        q.bias_part = grad_bias ? (float *)workspace + (size_t)splits * n : nullptr;
+        q.HW = oHW; q.M_total = K; q.N_total = C * kk; q.Kd = 0;
+        q.kblocks = (int)ceil_div_ll((long long)ips * oHW, BK);
+        set_geometry(q, C, H, W, kH, kW, dH, dW, padH, padW, oW);
+        q.n_tiles = ceil_div(C * kk, bn); q.tiles_per_split = ceil_div(K, BM) * q.n_tiles; q.total_tiles = q.tiles_per_split * splits;
+        q.n_img = N; q.imgs_per_split = ips; q.splits = splits;
+        q.vec_a = (oHW % 4 == 0) && aligned16(gy); q.vec_b = 0;
+        pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
+        if (pw_launch(pw_pick<OP_WGRAD>(bn, gather_ks(kH, kW)), q, stream)) return 1;
         const int rblocks = (int)std::max(1LL, std::min(ceil_div_ll(n, 256), (long long)sm_count() * 8));
         wgrad_reduce_kernel<<<rblocks, 256, 0, stream>>>((const float *)workspace, grad_weight, n, splits, scale);
         CUNN_LAUNCH_CHECK("convmm acc grad reduce");

@@ -86,6 +86,8 @@ def test_convmm_golden(F, name):
     (2, 5, 10, 10, 7, 5, 2, 2, True),        # 5x5 stride 2 (generic k decomposition, gather dgrad)
     (2, 130, 6, 6, 20, 3, 1, 1, True),       # Kd = 1170: many k-blocks, ragged tail
     (9, 4, 5, 5, 4, 1, 2, 0, True),          # 1x1 stride 2
+    (2, 3, 20, 20, 8, 7, 2, 3, True),        # 7x7 (49 taps): the kernel for more than 32 taps
+    (2, 6, 12, 12, 10, 7, 1, 3, False),      # 7x7 stride 1: tensor-core input gradient of that kernel
     (3, 3, 17, 19, 32, 3, 1, 1, True),       # first-layer kernels: stride 1, odd sizes
     (2, 3, 16, 16, 32, 3, 2, 0, False),      # first-layer kernels: no padding, no bias
     (80, 3, 64, 64, 32, 3, 2, 1, True),      # first-layer kernels: more pixel tiles than CTAs
