@@ -127,3 +127,31 @@ def test_convmm_empty_batch_and_errors(F):
     with pytest.raises(CunnError, match="Output size is too small"):
         F.convmm_forward(torch.zeros((1, 4, 2, 2), device="cuda"), torch.zeros((8, 4, 5, 5), device="cuda"), None,
                          1, 1, 0, 0, out=torch.zeros(1, device="cuda"))
+
+
+@pytest.mark.parametrize("cfg", [(128, 256, 256, 14, 3, 1), (128, 1024, 256, 14, 1, 0)])
+def test_convmm_full_size_adjoint_identities(F, cfg):
+    # BASELINE config 3 at full size, where the CPU oracle is too slow: the three passes are the three partial
+    # derivatives of one trilinear form, so <conv(x, W), gy> == <x, dgrad(gy, W)> == <wgrad(x, gy), W>, and the
+    # bias gradient is the plain sum of gy.  Inner products are taken in fp64; 1e-4 is the GEMM-path bar.
+    N, C, K, HW, k, pad = cfg
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn((N, C, HW, HW), device="cuda", generator=g)
+    w = torch.randn((K, C, k, k), device="cuda", generator=g) * (2.0 / (C * k * k)) ** 0.5
+    gy = torch.randn((N, K, HW, HW), device="cuda", generator=g)
+    y = F.convmm_forward(x, w, None, 1, 1, pad, pad)
+    gx = F.convmm_grad_input(gy, w, HW, HW, 1, 1, pad, pad)
+    gw, gb = torch.zeros_like(w), torch.zeros(K, device="cuda")
+    F.convmm_acc_grad(x, gy, gw, gb, 1, 1, pad, pad, 1.0)
+    a = float((y.double() * gy.double()).sum())
+    b = float((x.double() * gx.double()).sum())
+    c = float((gw.double() * w.double()).sum())
+    scale = float((y.double().abs() * gy.double().abs()).sum())
+    assert abs(a - b) < 1e-6 * scale and abs(a - c) < 1e-6 * scale
+    ref_gb = gy.double().sum((0, 2, 3))
+    assert float((gb.double() - ref_gb).abs().max()) < 1e-4 * float(ref_gb.abs().max())
+    # linearity in x at full size: conv(2 x1 - 3 x2) == 2 conv(x1) - 3 conv(x2)
+    x2 = torch.randn((N, C, HW, HW), device="cuda", generator=g)
+    lhs = F.convmm_forward(2 * x - 3 * x2, w, None, 1, 1, pad, pad)
+    rhs = 2 * y - 3 * F.convmm_forward(x2, w, None, 1, 1, pad, pad)
+    assert float((lhs - rhs).abs().max()) < 1e-4 * float(rhs.abs().max())

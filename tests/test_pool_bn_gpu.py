@@ -235,3 +235,30 @@ def test_bn_relu_fused_equals_separate_calls(F, shape):
     gx_ref = F.batchnorm_backward(x, F.threshold_backward(z, gy), w, rm1, rv1, sm, ss, True, grad_weight=gw1, grad_bias=gb1)
     gx = F.batchnorm_relu_backward(x, gy, w, b, rm2, rv2, sm2, ss2, True, grad_weight=gw2, grad_bias=gb2)
     assert torch.equal(gx, gx_ref) and torch.equal(gw1, gw2) and torch.equal(gb1, gb2)
+
+
+def test_bn_full_size_properties(F):
+    # BASELINE config 4 geometry at reduced batch (N = 64: 822 MB would not leave room on a shared test box):
+    # with gamma = 1, beta = 0 the training output has zero mean and unit biased variance per channel, the
+    # saved statistics are those of x, and the input gradient is orthogonal to 1 and to (x - mean).
+    g = torch.Generator(device="cuda").manual_seed(8)
+    N, C, HW = 64, 64, 112
+    x = torch.randn((N, C, HW, HW), device="cuda", generator=g) * 2 + 0.5
+    rm, rv = torch.zeros(C, device="cuda"), torch.ones(C, device="cuda")
+    y, sm, ss = F.batchnorm_forward(x, None, None, rm, rv, True, 0.1, 1e-5)
+    xd = x.double()
+    mean = xd.mean((0, 2, 3))
+    var = xd.var((0, 2, 3), unbiased=False)
+    assert float((sm.double() - mean).abs().max()) < 1e-5 * float(mean.abs().max())
+    assert float((ss.double() - 1 / torch.sqrt(var + 1e-5)).abs().max()) < 1e-5
+    yd = y.double()
+    assert float(yd.mean((0, 2, 3)).abs().max()) < 1e-5
+    assert float((yd.var((0, 2, 3), unbiased=False) - 1).abs().max()) < 1e-4
+    n = N * HW * HW
+    assert float((rv.double() - (0.9 + 0.1 * var * n / (n - 1))).abs().max()) < 1e-5 * float(var.max())
+    gy = torch.randn((N, C, HW, HW), device="cuda", generator=g)
+    gx = F.batchnorm_backward(x, gy, None, rm, rv, sm, ss, True)
+    gxd = gx.double()
+    scale = float(gxd.abs().sum((0, 2, 3)).max())
+    assert float(gxd.sum((0, 2, 3)).abs().max()) < 1e-5 * scale
+    assert float((gxd * (xd - mean.view(1, C, 1, 1))).sum((0, 2, 3)).abs().max()) < 1e-5 * scale * 2
