@@ -314,18 +314,42 @@ def mobilenet_bench(args, dev, world, rank, dist):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / timed
-    # end to end: images from pinned host memory, loss back to the host, every step
+    # end to end: images from pinned host memory, loss back to the host, every step.  Two device buffers: the
+    # copy of step i + 1's images runs on a second stream under step i's kernels, as an input pipeline would do it.
     himg = images.cpu().pin_memory()
     hlab = labels.cpu().pin_memory()
     hloss = torch.zeros(1).pin_memory()
+    bufs = [(images, labels), (torch.empty_like(images), torch.empty_like(labels))]
+    s_cmp, s_in = torch.cuda.current_stream(), torch.cuda.Stream(device=dev)
+    ready = [torch.cuda.Event(), torch.cuda.Event()]      # buffer filled
+    freed = [torch.cuda.Event(), torch.cuda.Event()]      # buffer consumed by the step that used it
+
+    def fetch(i):
+        b = i & 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(freed[b])
+            bufs[b][0].copy_(himg, non_blocking=True)
+            bufs[b][1].copy_(hlab, non_blocking=True)
+            ready[b].record(s_in)
+
+    for e in freed:
+        e.record(s_cmp)
+    torch.cuda.synchronize()
     t0 = time.perf_counter()
-    for _ in range(timed):
-        images.copy_(himg, non_blocking=True)
-        labels.copy_(hlab, non_blocking=True)
-        loss = step.train_step(images, labels, gb, 0.01)
+    fetch(0)
+    for i in range(timed):
+        if i + 1 < timed:
+            fetch(i + 1)
+        b = i & 1
+        s_cmp.wait_event(ready[b])
+        loss = step.train_step(bufs[b][0], bufs[b][1], gb, 0.01)
+        freed[b].record(s_cmp)
         hloss.copy_(loss, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        s_cmp.synchronize()
     ems = (time.perf_counter() - t0) * 1e3 / timed
+    if dist is not None:
+        dist.all_reduce(loss)                             # the shards' scaled loss sums add up to the batch mean
+        hloss.copy_(loss)
     if dist is not None:
         tt = torch.tensor([ms, ems], device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)

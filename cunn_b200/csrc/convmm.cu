@@ -2,22 +2,26 @@
 //
 // The reference unfolds every image into a column buffer and calls SGEMM per image.  Here the three
 // passes are implicit GEMMs — no column buffer exists — computed by tcgen05.mma.kind::tf32 with a
-// 3xTF32 split: every fp32 operand value v is written to shared memory twice, as hi = tf32(v) and
-// lo = v - hi, and each K step issues hi*hi + hi*lo + lo*hi into one fp32 TMEM accumulator.  The
-// dropped lo*lo term and the tf32 rounding of lo are ~2^-21 relative, i.e. fp32-class accuracy.
+// 3xTF32 split: every fp32 operand value v is used as hi (its upper 19 bits) and lo = v - hi, and each
+// K step issues lo*hi + hi*lo + hi*hi into fp32 TMEM accumulators.  The dropped lo*lo term and the tf32
+// truncation of lo are ~2^-20 relative, i.e. fp32-class accuracy.
 //
 //   forward      D[pixel, k_out]        = sum_{c,kh,kw}  x(pixel; c,kh,kw)   * W[k_out][c,kh,kw]
 //   input grad   D[pixel, c]            = sum_{k,kh,kw}  gy(pixel; k,kh,kw)  * W[k][c][flipped kh,kw]   (stride 1)
 //   weight grad  D[k_out, (c,kh,kw)]    = sum_{img,pix}  gy[img][k_out][pix] * x(pix; c,kh,kw)          (split over images)
 //
-// One CTA computes a 128 x BN tile of D.  All 256 threads gather operand values from global memory
-// (coalesced along pixels, two k-blocks in flight in registers), split them and store 16-byte pieces
-// into K-major tiles in the 128-byte swizzle; one thread then issues the MMAs of
-// the k-block and commits them to the mbarrier that frees the stage.  The epilogue reads the
-// accumulator with tcgen05.ld (lane = tile row) and writes coalesced NCHW rows.  Every wait is bounded.
-//
-// Input gradients for stride > 1 use a plain gather kernel (no network on the benchmarked path needs
-// them: a strided first layer has no input gradient).
+// Three kernel families share these roles:
+//   * pw::pw_gemm_kernel<OP, BN, KS> — the persistent, warp-specialised kernel (further down): KS = 1 for 1x1
+//     stride-1 convolutions whose operands are plain matrices in memory, KS = 3 / 0 for 3x3 / any kernel of up to
+//     32 taps gathered element by element with asynchronous copies;
+//   * conv_gemm_kernel<OP, KS, BN> (next) — one CTA per 128 x BN tile for kernels of more than 32 taps: all 256
+//     threads gather operand values (two k-blocks in flight in registers), split them and store 16-byte pieces
+//     into K-major tiles in the 128-byte swizzle; one thread issues the MMAs of the k-block and commits them to
+//     the mbarrier that frees the stage; the epilogue reads the accumulator with tcgen05.ld (lane = tile row)
+//     and writes coalesced NCHW rows;
+//   * stemconv.cu — fp32-pipe kernels for the 3-channel 3x3 first layer.
+// Every wait is bounded.  Input gradients for stride > 1 use a plain gather kernel (no network on the
+// benchmarked path needs them: a strided first layer has no input gradient).
 #include "common.cuh"
 #include "stemconv.h"
 
@@ -553,8 +557,8 @@ dgrad_gather_kernel(const float *__restrict__ gy, const float *__restrict__ w, f
 //                                                                        k runs over (image, pixel) of this tile's image range
 //
 // tcgen05.mma takes M/N-major operands through the major bits of the instruction descriptor, so a 16-byte
-// global load becomes one 16-byte shared-memory store per tf32 half with no transposition.  One CTA per SM
-// walks a strided list of tiles; operand loads run two k-blocks ahead of the MMAs ACROSS tile boundaries, and
+// asynchronous copy lands an operand piece in shared memory in its final place, no transposition.  One CTA per SM
+// walks a strided list of tiles; operand copies run three k-blocks ahead of the MMAs ACROSS tile boundaries, and
 // when the accumulators fit twice in TMEM the epilogue of a tile runs after the first MMAs of the next tile
 // have been issued, so the tensor core and the memory system keep working through it.
 namespace pw {
