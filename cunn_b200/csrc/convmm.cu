@@ -559,19 +559,22 @@ dgrad_gather_kernel(const float *__restrict__ gy, const float *__restrict__ w, f
 // tcgen05.mma takes M/N-major operands through the major bits of the instruction descriptor, so a 16-byte
 // asynchronous copy lands an operand piece in shared memory in its final place, no transposition.  One CTA per SM
 // walks a strided list of tiles; operand copies run three k-blocks ahead of the MMAs ACROSS tile boundaries, and
-// when the accumulators fit twice in TMEM the epilogue of a tile runs after the first MMAs of the next tile
-// have been issued, so the tensor core and the memory system keep working through it.
+// four epilogue warps drain finished accumulators to global memory while the next tile is being produced (when the
+// accumulators fit twice in TMEM the MMAs of the next tile run under it as well).
 namespace pw {
 
 constexpr int PRODUCERS = 512;           // threads that copy, split and run the epilogue (16 warps)
-constexpr int THREADS = PRODUCERS + 32;  // + one warp that only issues the MMAs
+constexpr int EPILOGUE_WARPS = 4;         // warps that only drain accumulators: TMEM -> registers -> global memory
+constexpr int THREADS = PRODUCERS + 32 + 32 * EPILOGUE_WARPS;   // + one warp that only issues the MMAs
 constexpr int TILE = 128 * 128;          // 128 rows x 32 k values (16 KiB) in either layout
 constexpr int MN_ATOM = 512;             // M/N-major tile: bytes of one swizzle atom (32 rows x 4 k values)
 constexpr int MN_KATOM = 4 * MN_ATOM;    // ... bytes from one group of 4 k values to the next (4 atoms cover 128 rows)
 constexpr int RAW_STAGES = 4;            // raw fp32 tiles (A, B) filled by asynchronous copies; split in place they become the hi tiles
 constexpr int LO_BUFS = 2;               // lo tiles (A, B) of the k-blocks whose MMAs are in flight
 constexpr int PREFETCH = 3;              // k-blocks the copies run ahead of the MMAs
-constexpr size_t SMEM = (size_t)(RAW_STAGES + LO_BUFS) * 2 * TILE + 1024;
+constexpr int STAGE_COLS = 64;           // output columns staged at a time for the bulk-store epilogue (x 128 rows x 4 bytes)
+constexpr size_t OUT_STAGE = (size_t)STAGE_COLS * BM * 4;
+constexpr size_t SMEM = (size_t)(RAW_STAGES + LO_BUFS) * 2 * TILE + OUT_STAGE + 1024;
 static_assert(8 * MN_KATOM == TILE, "both layouts fill the tile");
 
 struct Params {
@@ -588,7 +591,8 @@ struct Params {
     // kernels larger than 1x1 (KS != 1): the unfolded operand is gathered from a [g_C, g_H, g_W] image tensor, the
     // pixel grid that drives the gather is pix_W wide (HW = its size)
     int g_C, g_H, g_W, kH, kW, dH, dW, padH, padW, pix_W;
-    int nacc, sets;    // accumulators per tile (k-blocks are dealt round-robin), accumulator sets in TMEM (1 or 2)
+    int nacc, sets;    // accumulators per tile (nacc - 1 for the hi*hi products, k-blocks round-robin, + 1 for the cross terms), accumulator sets in TMEM (1 or 2)
+    int bulk_out;      // FWD/DGRAD: planes of >= 1024 pixels (a multiple of 4), 16-byte aligned output: the columns of a tile leave as bulk stores
 };
 
 // 3xTF32 split of a raw fp32 tile in place.  The tensor core reads only the upper 19 bits of a tf32 operand,
@@ -628,6 +632,16 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, bool on
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// 1-D bulk copy shared -> global through the TMA unit (16-byte aligned addresses, size a multiple of 16 bytes).
+__device__ __forceinline__ void bulk_s2g_nocommit(void *dst, uint32_t src_smem, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Barrier among the epilogue warps only (hardware barrier 1; barrier 0 is __syncthreads).
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * EPILOGUE_WARPS) : "memory"); }
 
 // Where the operand loads of one thread stand: tile, k-block and the thread's element offsets inside that tile.
 // M/N-major pieces: lane = group of 4 rows, k = warp + 16 i.  K-major pieces: chunk kc = tid & 7, rows (tid >> 3) + 64 i.
@@ -882,12 +896,14 @@ pw_gemm_kernel(const Params p)
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint64_t bars[RAW_STAGES + 2]; // MMAs-of-this-stage-done barriers, then one accumulators-ready barrier per set
     __shared__ uint64_t full[RAW_STAGES];     // stage split and visible to the tensor core: one arrival per producer warp
+    __shared__ uint64_t accfree[2];           // accumulator set drained: one arrival per epilogue warp
     __shared__ uint32_t tmem_base_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int s = 0; s < RAW_STAGES + 2; ++s) mbar_init(smem_u32(bars + s), 1);
         for (int s = 0; s < RAW_STAGES; ++s) mbar_init(smem_u32(full + s), PRODUCERS / 32);
+        for (int s = 0; s < 2; ++s) mbar_init(smem_u32(accfree + s), EPILOGUE_WARPS);
         mbar_fence_init();
     }
     if (warp == 0) tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
@@ -899,7 +915,7 @@ pw_gemm_kernel(const Params p)
     const int KB = p.kblocks;
     const int my_tiles = ((int)blockIdx.x < p.total_tiles) ? (p.total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
     const int total_it = my_tiles * KB;
-    const int nacc_used = KB < p.nacc ? KB : p.nacc;
+    const int nhi_used = KB < p.nacc - 1 ? KB : p.nacc - 1;   // hi accumulators that received a k-block; the lo one always did
     const uint32_t set_cols = (uint32_t)(p.nacc * ACC_COLS);
 
     // shared-memory offsets of this thread's pieces (same for every stage)
@@ -937,7 +953,10 @@ pw_gemm_kernel(const Params p)
             }
         }
     };
-    auto issue_mmas = [&](int rs, int lb, uint32_t d_tmem, bool first) {
+    // hi*hi products go to accumulator d_hi, the two small cross terms to d_lo: the tensor core truncates when it
+    // accumulates, and the error of a chain scales with the magnitude it carries, so the large terms get the short
+    // chains (k-blocks round-robin over nacc - 1 accumulators) and all cross terms share one.
+    auto issue_mmas = [&](int rs, int lb, uint32_t d_hi, bool first_hi, uint32_t d_lo, bool first_lo) {
         const uint32_t sa_hi = smem_u32(smem + (size_t)rs * 2 * TILE), sb_hi = sa_hi + TILE;
         const uint32_t sa_lo = smem_u32(lo_base + (size_t)lb * 2 * TILE), sb_lo = sa_lo + TILE;
 #pragma unroll
@@ -948,76 +967,121 @@ pw_gemm_kernel(const Params p)
             const uint64_t al = A_MN ? desc_mn(sa_lo + ao) : smem_desc(sa_lo + ao);
             const uint64_t bh = B_MN ? desc_mn(sb_hi + bo) : smem_desc(sb_hi + bo);
             const uint64_t bl = B_MN ? desc_mn(sb_lo + bo) : smem_desc(sb_lo + bo);
-            umma_tf32(d_tmem, al, bh, idesc, (first && j == 0) ? 0u : 1u);
-            umma_tf32(d_tmem, ah, bl, idesc, 1u);
-            umma_tf32(d_tmem, ah, bh, idesc, 1u);
+            umma_tf32(d_lo, al, bh, idesc, (first_lo && j == 0) ? 0u : 1u);
+            umma_tf32(d_lo, ah, bl, idesc, 1u);
+            umma_tf32(d_hi, ah, bh, idesc, (first_hi && j == 0) ? 0u : 1u);
         }
     };
-    // Reads the accumulators of tile `t` (the `count`-th tile of this CTA) and writes its part of the output.
+    // Epilogue warps: reads the accumulators of tile `t` (the `count`-th tile of this CTA), writes the warp's 32
+    // rows of the output and hands the accumulator set back to the MMA warp.
     auto epilogue = [&](int t, int count) -> bool {
         const int set = (p.sets == 2) ? (count & 1) : 0;
         const uint32_t parity = (uint32_t)(((p.sets == 2) ? (count >> 1) : count) & 1);
         if (!mbar_wait(smem_u32(bars + RAW_STAGES + set), parity, p.status)) return false;
         tc_fence_after();
-        const int quarter = warp & 3, cc = (warp >> 2) * 32;     // TMEM lanes of this warp, its 32 columns
-        if (cc < BN) {
-            const int row = quarter * 32 + lane;
-            int m, n_base;
-            size_t dst_off = 0;
-            if (OP != OP_WGRAD) {
-                const int m_tile = t / p.n_tiles, n_tile = t - m_tile * p.n_tiles;
-                m = m_tile * BM + row;
-                n_base = n_tile * BN + cc;
-                if (m < p.M_total) {
-                    const int im = m / p.HW;
-                    dst_off = (size_t)im * p.N_total * p.HW + (m - im * p.HW) + (size_t)n_base * p.HW;
-                }
-            } else {
-                const int split = t / p.tiles_per_split, r2 = t - split * p.tiles_per_split;
-                const int m_tile = r2 / p.n_tiles, n_tile = r2 - m_tile * p.n_tiles;
-                m = m_tile * BM + row;
-                n_base = n_tile * BN + cc;
-                dst_off = ((size_t)split * p.M_total + m) * p.N_total + n_base;
+        const int quarter = warp & 3;                            // the TMEM lanes this warp may read
+        const int row = quarter * 32 + lane;
+        int m, n_tile0;
+        size_t dst_off = 0;
+        if (OP != OP_WGRAD) {
+            const int m_tile = t / p.n_tiles, n_tile = t - m_tile * p.n_tiles;
+            m = m_tile * BM + row;
+            n_tile0 = n_tile * BN;
+            if (m < p.M_total) {
+                const int im = m / p.HW;
+                dst_off = (size_t)im * p.N_total * p.HW + (m - im * p.HW) + (size_t)n_tile0 * p.HW;
             }
+        } else {
+            const int split = t / p.tiles_per_split, r2 = t - split * p.tiles_per_split;
+            const int m_tile = r2 / p.n_tiles, n_tile = r2 - m_tile * p.n_tiles;
+            m = m_tile * BM + row;
+            n_tile0 = n_tile * BN;
+            dst_off = ((size_t)split * p.M_total + m) * p.N_total + n_tile0;
+        }
+        if (OP != OP_WGRAD) {
+            // Whole tile inside the problem and planes long enough: stage 64 columns x 128 pixels in shared memory
+            // ([column][pixel], so a column is 512 contiguous bytes of one output plane) and let the TMA unit write
+            // each column as one bulk store (two when the tile crosses into the next image).
+            const int m_tile0 = (t / p.n_tiles) * BM;
+            if (p.bulk_out && m_tile0 + BM <= p.M_total) {
+                float *stage = reinterpret_cast<float *>(smem + (size_t)(RAW_STAGES + LO_BUFS) * 2 * TILE);
+                const int e = tid - (PRODUCERS + 32);            // 0 .. 127
+                const int im0 = m_tile0 / p.HW, pix0 = m_tile0 - im0 * p.HW;
+                const int len0 = min(BM, p.HW - pix0);
+#pragma unroll 1
+                for (int cbase = 0; cbase < BN; cbase += STAGE_COLS) {
+                    bulk_wait_read_all();                        // this thread's earlier bulk stores have left the buffer
+                    epilogue_sync();
+#pragma unroll 1
+                    for (int c0 = cbase; c0 < cbase + STAGE_COLS && c0 < BN; c0 += 16) {
+                        float acc[16];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {        // two passes of 16 columns keep the register count down
-                float acc[16];
+                        for (int j = 0; j < 16; ++j) acc[j] = (OP == OP_FWD && p.bias && n_tile0 + c0 + j < p.N_total) ? __ldg(p.bias + n_tile0 + c0 + j) : 0.f;
+                        for (int a2 = 0; a2 <= nhi_used; ++a2) {
+                            const int a = a2 < nhi_used ? a2 : p.nacc - 1;
+                            uint32_t r[16];
+                            tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)set * set_cols + (uint32_t)(a * ACC_COLS + c0), r);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-                for (int a = 0; a < nacc_used; ++a) {
-                    uint32_t r[16];
-                    tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)set * set_cols + (uint32_t)(a * ACC_COLS + cc + 16 * h), r);
+                            for (int j = 0; j < 16; ++j) acc[j] += __uint_as_float(r[j]);
+                        }
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) acc[j] += __uint_as_float(r[j]);
+                        for (int j = 0; j < 16; ++j) stage[(c0 - cbase + j) * BM + row] = acc[j];
+                    }
+                    fence_async_smem();                          // staged values -> visible to the bulk copy engine
+                    epilogue_sync();
+                    const int col = cbase + e, n = n_tile0 + col;
+                    if (e < STAGE_COLS && col < BN && n < p.N_total) {
+                        const uint32_t src = smem_u32(stage + e * BM);
+                        float *dst = p.out + ((size_t)im0 * p.N_total + n) * p.HW + pix0;
+                        bulk_s2g_nocommit(dst, src, (uint32_t)len0 * 4u);
+                        if (len0 < BM) bulk_s2g_nocommit(p.out + ((size_t)(im0 + 1) * p.N_total + n) * p.HW, src + (uint32_t)len0 * 4u, (uint32_t)(BM - len0) * 4u);
+                        bulk_commit();
+                    }
                 }
-                if (m < p.M_total) {
-                    const int n0 = n_base + 16 * h;
-                    if (OP != OP_WGRAD) {
-                        float *dst = p.out + dst_off + (size_t)(16 * h) * p.HW;
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(accfree + set));
+                return true;
+            }
+        }
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {                    // 16 columns at a time keeps the register count down
+            float acc[16];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if (n0 + j < p.N_total) {
-                                float v = acc[j];
-                                if (OP == OP_FWD && p.bias) v += __ldg(p.bias + n0 + j);
-                                dst[(size_t)j * p.HW] = v;
-                            }
-                        }
+            for (int j = 0; j < 16; ++j)                         // the bias loads are in flight while TMEM is read
+                acc[j] = (OP == OP_FWD && p.bias && n_tile0 + c0 + j < p.N_total) ? __ldg(p.bias + n_tile0 + c0 + j) : 0.f;
+            for (int a2 = 0; a2 <= nhi_used; ++a2) {
+                const int a = a2 < nhi_used ? a2 : p.nacc - 1;
+                uint32_t r[16];
+                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)set * set_cols + (uint32_t)(a * ACC_COLS + c0), r);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j] += __uint_as_float(r[j]);
+            }
+            if (m < p.M_total) {
+                const int n0 = n_tile0 + c0;
+                if (OP != OP_WGRAD) {
+                    float *dst = p.out + dst_off + (size_t)c0 * p.HW;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (n0 + j < p.N_total) dst[(size_t)j * p.HW] = acc[j];
+                    }
+                } else {
+                    float *dst = p.out + dst_off + c0;
+                    if ((p.N_total & 3) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4)
+                            if (n0 + j < p.N_total) *reinterpret_cast<float4 *>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
                     } else {
-                        float *dst = p.out + dst_off + 16 * h;
-                        if ((p.N_total & 3) == 0) {
 #pragma unroll
-                            for (int j = 0; j < 16; j += 4)
-                                if (n0 + j < p.N_total) *reinterpret_cast<float4 *>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (n0 + j < p.N_total) dst[j] = acc[j];
-                        }
+                        for (int j = 0; j < 16; ++j)
+                            if (n0 + j < p.N_total) dst[j] = acc[j];
                     }
                 }
             }
         }
-        tc_fence_before();
+        tc_fence_before();                                       // the TMEM reads above are ordered before the arrival
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(accfree + set));
         return true;
     };
 
@@ -1028,16 +1092,30 @@ pw_gemm_kernel(const Params p)
         for (int i = 0; i < total_it; ++i) {
             const int rs = i % RAW_STAGES, lb = i % LO_BUFS;
             if (!mbar_wait(smem_u32(full + rs), (uint32_t)((i / RAW_STAGES) & 1), p.status)) { ok = false; break; }
+            if (kb == 0 && count >= p.sets) {
+                // the epilogue warps must have drained the tile that used this accumulator set before
+                const int set = (p.sets == 2) ? (count & 1) : 0;
+                const int use = (p.sets == 2) ? (count >> 1) : count;
+                if (!mbar_wait(smem_u32(accfree + set), (uint32_t)((use - 1) & 1), p.status)) { ok = false; break; }
+            }
             if (lane == 0) {
                 tc_fence_after();
                 const int set = (p.sets == 2) ? (count & 1) : 0;
-                issue_mmas(rs, lb, tmem_base + (uint32_t)set * set_cols + (uint32_t)((kb % p.nacc) * ACC_COLS), kb < p.nacc);
+                const uint32_t acc0 = tmem_base + (uint32_t)set * set_cols;
+                const int nhi = p.nacc - 1;
+                issue_mmas(rs, lb, acc0 + (uint32_t)((kb % nhi) * ACC_COLS), kb < nhi, acc0 + (uint32_t)(nhi * ACC_COLS), kb == 0);
                 umma_commit(smem_u32(bars + rs));
                 if (kb == KB - 1) umma_commit(smem_u32(bars + RAW_STAGES + set));
             }
             __syncwarp();
             if (++kb == KB) { kb = 0; ++count; }
         }
+    } else if (warp > PRODUCERS / 32) {
+        // ---- epilogue warps: one pass over this CTA's tiles ----
+        for (int count = 0; count < my_tiles; ++count) {
+            if (!epilogue((int)blockIdx.x + count * (int)gridDim.x, count)) { ok = false; break; }
+        }
+        bulk_wait_read_all();                                    // shared memory must outlive the last bulk stores' reads
     } else {
         Loader<OP, BN, KS> L;
         L.tile = (int)blockIdx.x;
@@ -1055,8 +1133,7 @@ pw_gemm_kernel(const Params p)
             cp_async_commit();
         }
 
-        int c_tile = (int)blockIdx.x, c_kb = 0, c_count = 0;   // tile, k-block and tile ordinal of the block being split / issued
-        int pend_tile = -1, pend_count = 0;                    // tile whose epilogue is still to run (two accumulator sets)
+        int c_tile = (int)blockIdx.x, c_kb = 0;                // tile and k-block of the block being split
         for (int i = 0; i < total_it; ++i) {
             const int rs = i % RAW_STAGES, lb = i % LO_BUFS;
             cp_async_wait<PREFETCH - 1>();                     // this thread's pieces of k-block i are in shared memory
@@ -1067,7 +1144,6 @@ pw_gemm_kernel(const Params p)
             }
             split_block(rs, lb);
             fence_async_smem();                                // generic-proxy stores -> visible to the tensor core's async proxy
-            tc_fence_before();                                 // orders this warp's earlier TMEM reads (epilogue) before the arrival
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(full + rs));
             // refill the raw stage that k-block i - 1 used with k-block i + PREFETCH, once its MMAs have read it
@@ -1081,11 +1157,6 @@ pw_gemm_kernel(const Params p)
                 L.advance(p);
             }
             cp_async_commit();
-            if (pend_tile >= 0 && c_kb == 0) {
-                ok = epilogue(pend_tile, pend_count);
-                pend_tile = -1;
-                if (!ok) break;
-            }
             if (c_kb == KB - 1) {
                 if (OP == OP_WGRAD) {
                     // bias gradient: the eight chunk lanes of a row hold its partial sums
@@ -1102,22 +1173,13 @@ pw_gemm_kernel(const Params p)
                         bsum[r] = 0.f;
                     }
                 }
-                if (p.sets == 2) {
-                    pend_tile = c_tile;
-                    pend_count = c_count;
-                } else {
-                    ok = epilogue(c_tile, c_count);
-                    if (!ok) break;
-                }
                 c_kb = 0;
                 c_tile += (int)gridDim.x;
-                ++c_count;
             } else {
                 ++c_kb;
             }
         }
         cp_async_wait<0>();
-        if (ok && pend_tile >= 0) ok = epilogue(pend_tile, pend_count);
     }
     tc_fence_before();
     __syncthreads();
@@ -1238,13 +1300,20 @@ static void set_geometry(pw::Params &q, int gC, int gH, int gW, int kH, int kW, 
 }
 static int pw_bn_for(int n_total) { return n_total <= 32 ? 32 : (n_total <= 64 ? 64 : 128); }
 
-// Accumulators per tile and accumulator sets: k-blocks are dealt round-robin to `nacc` accumulators to keep the
-// tensor core's truncating accumulation chains short; two sets (epilogue overlapped with the next tile) when
+// Accumulators per tile and accumulator sets: the hi*hi products of the k-blocks are dealt round-robin to `nacc - 1`
+// accumulators to keep the tensor core's truncating accumulation chains short, the cross terms share the last one; two sets (epilogue overlapped with the next tile) when
 // they fit in the 512 TMEM columns.
-static void pw_accumulators(int bn, int kblocks, int *nacc, int *sets)
+static void pw_accumulators(int bn, int kblocks, int *nacc, int *sets, bool wgrad = false)
 {
-    if (bn == 128) {
+    if (bn == 128 && wgrad) {
+        // sums over pixels of random-sign products cancel: the weight gradient is the pass most sensitive to the
+        // accumulation chains, and its long k loops make the epilogue a small share anyway
         if (kblocks <= 8) { *nacc = 2; *sets = 2; }
+        else { *nacc = 4; *sets = 1; }
+    } else if (bn == 128) {
+        // two sets let the MMAs of the next tile run while the epilogue warps drain this one; beyond 16 k-blocks the
+        // chains (12 MMAs per k-block and accumulator) get long enough to need four accumulators for the 1e-4 bar
+        if (kblocks <= 16) { *nacc = 2; *sets = 2; }
         else { *nacc = 4; *sets = 1; }
     } else if (bn == 64) {
         if (kblocks <= 48) { *nacc = 4; *sets = 2; }
@@ -1303,6 +1372,7 @@ extern "C" CUNN_API int cunn_b200_convmm_forward(const float *x, const float *we
         q.n_tiles = ceil_div(K, bn); q.tiles_per_split = 0; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
         q.n_img = N; q.imgs_per_split = N; q.splits = 1;
         q.vec_a = (q.HW % 4 == 0) && aligned16(x); q.vec_b = (C % 4 == 0) && aligned16(weight);
+        q.bulk_out = (q.HW % 4 == 0) && q.HW >= 8 * BM && aligned16(y);
         pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
         return pw_launch(pw_pick<OP_FWD>(bn), q, stream);
     }
@@ -1315,6 +1385,7 @@ extern "C" CUNN_API int cunn_b200_convmm_forward(const float *x, const float *we
         q.n_tiles = ceil_div(K, bn); q.tiles_per_split = 0; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
         q.n_img = N; q.imgs_per_split = N; q.splits = 1;
         q.vec_a = 0; q.vec_b = (q.Kd % 4 == 0) && aligned16(weight);
+        q.bulk_out = (q.HW % 4 == 0) && q.HW >= 8 * BM && aligned16(y);
         pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
         return pw_launch(pw_pick<OP_FWD>(bn, gather_ks(kH, kW)), q, stream);
     }
@@ -1346,6 +1417,7 @@ extern "C" CUNN_API int cunn_b200_convmm_grad_input(const float *gy, const float
         q.n_tiles = ceil_div(C, bn); q.tiles_per_split = 0; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
         q.n_img = N; q.imgs_per_split = N; q.splits = 1;
         q.vec_a = (q.HW % 4 == 0) && aligned16(gy); q.vec_b = (C % 4 == 0) && aligned16(weight);
+        q.bulk_out = (q.HW % 4 == 0) && q.HW >= 8 * BM && aligned16(gx);
         pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
         return pw_launch(pw_pick<OP_DGRAD>(bn), q, stream);
     }
@@ -1360,6 +1432,7 @@ extern "C" CUNN_API int cunn_b200_convmm_grad_input(const float *gy, const float
             q.n_tiles = ceil_div(C, bn); q.tiles_per_split = 0; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
             q.n_img = N; q.imgs_per_split = N; q.splits = 1;
             q.vec_a = 0; q.vec_b = 0;
+            q.bulk_out = (q.HW % 4 == 0) && q.HW >= 8 * BM && aligned16(gx);
             pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
             return pw_launch(pw_pick<OP_DGRAD>(bn, gather_ks(kH, kW)), q, stream);
         }
@@ -1441,7 +1514,7 @@ extern "C" CUNN_API int cunn_b200_convmm_acc_grad(const float *x, const float *g
         q.n_tiles = ceil_div(C, bn); q.tiles_per_split = ceil_div(K, BM) * q.n_tiles; q.total_tiles = q.tiles_per_split * splits;
         q.n_img = N; q.imgs_per_split = ips; q.splits = splits;
         q.vec_a = (q.HW % 4 == 0) && aligned16(gy); q.vec_b = (q.HW % 4 == 0) && aligned16(x);
-        pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
+        pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets, true);
         if (pw_launch(pw_pick<OP_WGRAD>(bn), q, stream)) return 1;
         const int rblocks = (int)std::max(1LL, std::min(ceil_div_ll(n, 256), (long long)sm_count() * 8));
         wgrad_reduce_kernel<<<rblocks, 256, 0, stream>>>((const float *)workspace, grad_weight, n, splits, scale);
@@ -1465,7 +1538,7 @@ extern "C" CUNN_API int cunn_b200_convmm_acc_grad(const float *x, const float *g
         q.n_tiles = ceil_div(C * kk, bn); q.tiles_per_split = ceil_div(K, BM) * q.n_tiles; q.total_tiles = q.tiles_per_split * splits;
         q.n_img = N; q.imgs_per_split = ips; q.splits = splits;
         q.vec_a = (oHW % 4 == 0) && aligned16(gy); q.vec_b = 0;
-        pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
+        pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets, true);
         if (pw_launch(pw_pick<OP_WGRAD>(bn, gather_ks(kH, kW)), q, stream)) return 1;
         const int rblocks = (int)std::max(1LL, std::min(ceil_div_ll(n, 256), (long long)sm_count() * 8));
         wgrad_reduce_kernel<<<rblocks, 256, 0, stream>>>((const float *)workspace, grad_weight, n, splits, scale);
