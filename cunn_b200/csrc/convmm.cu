@@ -670,13 +670,16 @@ struct Loader {
             const int m_tile = t / p.n_tiles, n_tile = t - m_tile * p.n_tiles;
             const int m = m_tile * BM + lane * 4, n0 = n_tile * BN;
             if (KS != 1) {
+                // gathered operand: this lane's four rows are lane, lane + 32, lane + 64, lane + 96, so that one copy
+                // instruction of the warp covers 32 consecutive pixels (and 128 consecutive bytes of shared memory)
                 const int kk = taps(p), kw_n = kcols(p);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     a_off[j] = 0;
                     tapmask[j] = 0;
-                    if (m + j < p.M_total) {
-                        const int im = (m + j) / p.HW, r = (m + j) - im * p.HW;
+                    const int mj = m_tile * BM + lane + 32 * j;
+                    if (mj < p.M_total) {
+                        const int im = mj / p.HW, r = mj - im * p.HW;
                         const int ph = r / p.pix_W, pw_ = r - ph * p.pix_W;
                         const int ih0 = ph * p.dH - p.padH, iw0 = pw_ * p.dW - p.padW;
                         a_off[j] = im * p.g_C * p.g_H * p.g_W + ih0 * p.g_W + iw0;
@@ -713,11 +716,18 @@ struct Loader {
                     if (row < BN && n < p.N_total) b_mask |= 1u << i;
                 }
             } else {
-                const int col = n0 + lane * 4;
-                b_off[0] = col;
+                if (KS != 1) {
+                    b_off[0] = n0 + lane;                  // gathered: columns lane + 32 j
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (lane * 4 < BN && col + j < p.N_total) b_mask |= 1u << j;
+                    for (int j = 0; j < 4; ++j)
+                        if (lane + 32 * j < BN && n0 + lane + 32 * j < p.N_total) b_mask |= 1u << j;
+                } else {
+                    const int col = n0 + lane * 4;
+                    b_off[0] = col;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (lane * 4 < BN && col + j < p.N_total) b_mask |= 1u << j;
+                }
             }
         } else {
             const int split = t / p.tiles_per_split, r = t - split * p.tiles_per_split;
@@ -779,7 +789,7 @@ struct Loader {
     // Issues the asynchronous copies of this thread's pieces of the current k-block into the raw tiles at
     // shared-memory addresses sa / sb (+ the piece offsets); masked pieces are zero-filled.
     __device__ __forceinline__ void issue(const Params &p, uint32_t sa, uint32_t sb, const uint32_t (&a_so)[2],
-                                          const uint32_t (&b_so)[2], const bool (&b_store)[2]) const
+                                          const uint32_t (&b_so)[2], const bool (&b_store)[2], const uint32_t (&g_so)[2]) const
     {
         const int tid = threadIdx.x, warp = tid >> 5;
         if (tile >= p.total_tiles) return;
@@ -795,7 +805,7 @@ struct Loader {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const bool ok = kok && (tapmask[j] >> t2 & 1u);
-                        cp_async4(sa + a_so[i] + 4 * j, ok ? p.a + (a_off[j] + koff) : p.a, ok);
+                        cp_async4(sa + g_so[i] + MN_ATOM * j, ok ? p.a + (a_off[j] + koff) : p.a, ok);
                     }
                 } else if (p.vec_a) {
                     const bool ok = kok && a_mask;
@@ -829,7 +839,6 @@ struct Loader {
             } else {
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
-                    if (!b_store[i]) continue;
                     const int k = kb * BK + warp + 16 * i;
                     const bool kok = k < p.Kd;
                     if (KS != 1) {
@@ -839,10 +848,11 @@ struct Loader {
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const bool ok = kok && (b_mask >> j & 1u);
-                            cp_async4(sb + b_so[i] + 4 * j, ok ? p.b + ((size_t)(ko * p.N_total + b_off[0] + j) * kk + (kk - 1 - t2)) : p.b, ok);
+                            cp_async4(sb + g_so[i] + MN_ATOM * j, ok ? p.b + ((size_t)(ko * p.N_total + b_off[0] + 32 * j) * kk + (kk - 1 - t2)) : p.b, ok);
                         }
                         continue;
                     }
+                    if (!b_store[i]) continue;
                     const float *src = p.b + (size_t)(kok ? k : 0) * p.N_total + b_off[0];
                     if (p.vec_b) {
                         const bool ok = kok && b_mask;
@@ -919,7 +929,7 @@ pw_gemm_kernel(const Params p)
     const uint32_t set_cols = (uint32_t)(p.nacc * ACC_COLS);
 
     // shared-memory offsets of this thread's pieces (same for every stage)
-    uint32_t a_so[2], b_so[2];
+    uint32_t a_so[2], b_so[2], g_so[2];
     bool b_store[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -933,6 +943,9 @@ pw_gemm_kernel(const Params p)
         a_so[i] = A_MN ? mn : km;
         b_so[i] = B_MN ? mn : km;
         b_store[i] = B_MN ? (lane * 4 < BN) : (row < BN);
+        // gathered M/N-major operand (KS != 1): this lane copies element (row = lane + 32 j, k), 4 bytes each; j adds
+        // one 512-byte atom.  The 32 lanes of one copy instruction fill one 128-byte row of an atom.
+        g_so[i] = (uint32_t)((k >> 2) * MN_KATOM + (k & 3) * 128 + (((lane >> 3) ^ (k & 3)) << 5) + (((lane >> 2) & 1) << 4) + (lane & 3) * 4);
     }
 
     float bsum[2] = {0.f, 0.f};                         // WGRAD: running row sums of gy (bias gradient)
@@ -1127,7 +1140,7 @@ pw_gemm_kernel(const Params p)
     #pragma unroll
         for (int i = 0; i < PREFETCH; ++i) {
             if (i < total_it) {
-                L.issue(p, smem_a0 + (uint32_t)(i * 2 * TILE), smem_a0 + (uint32_t)(i * 2 * TILE + TILE), a_so, b_so, b_store);
+                L.issue(p, smem_a0 + (uint32_t)(i * 2 * TILE), smem_a0 + (uint32_t)(i * 2 * TILE + TILE), a_so, b_so, b_store, g_so);
                 L.advance(p);
             }
             cp_async_commit();
@@ -1142,6 +1155,7 @@ pw_gemm_kernel(const Params p)
                 const int j = i - LO_BUFS;
                 if (!mbar_wait(smem_u32(bars + j % RAW_STAGES), (uint32_t)((j / RAW_STAGES) & 1), p.status)) { ok = false; break; }
             }
+            if (KS != 1) __syncwarp();                         // gathered pieces were filled by several lanes of this warp
             split_block(rs, lb);
             fence_async_smem();                                // generic-proxy stores -> visible to the tensor core's async proxy
             __syncwarp();
@@ -1153,7 +1167,7 @@ pw_gemm_kernel(const Params p)
                     if (!mbar_wait(smem_u32(bars + j % RAW_STAGES), (uint32_t)((j / RAW_STAGES) & 1), p.status)) { ok = false; break; }
                 }
                 const int ns = (i + PREFETCH) % RAW_STAGES;
-                L.issue(p, smem_a0 + (uint32_t)(ns * 2 * TILE), smem_a0 + (uint32_t)(ns * 2 * TILE + TILE), a_so, b_so, b_store);
+                L.issue(p, smem_a0 + (uint32_t)(ns * 2 * TILE), smem_a0 + (uint32_t)(ns * 2 * TILE + TILE), a_so, b_so, b_store, g_so);
                 L.advance(p);
             }
             cp_async_commit();
