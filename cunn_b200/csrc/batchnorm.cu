@@ -48,61 +48,16 @@ __device__ __forceinline__ void chunk_range(int N, int chunks, int j, int *n0, i
     *n1 = *n0 + per + (j < extra ? 1 : 0);
 }
 
-// grid = C * chunks.  One partial statistic per CTA.
-__global__ void __launch_bounds__(256)
-stats_kernel(const float *__restrict__ x, ChunkStat *__restrict__ part, int N, int C, int S, int chunks)
-{
-    __shared__ float sh[8];
-    const int c = blockIdx.x / chunks, j = blockIdx.x % chunks;
-    int n0, n1;
-    chunk_range(N, chunks, j, &n0, &n1);
-    if (n0 >= n1) {
-        if (threadIdx.x == 0) part[blockIdx.x] = ChunkStat{0.f, 0.f, 0.f, 0.f};
-        return;
-    }
-    const float k = __ldg(x + ((size_t)n0 * C + c) * S);
-    float s1 = 0.f, s2 = 0.f;
-    const bool vec = (S % 4 == 0) && (((uintptr_t)x & 15) == 0);
-    // The chunk's planes are walked as one flat sequence of 16-byte (or 4-byte) items, so that every lane has
-    // work whatever the plane size; (n, i) = image and item inside its plane, advanced without divisions.
-    const int L = vec ? S / 4 : S;
-    const int qstep = (int)blockDim.x / L, rstep = (int)blockDim.x % L;
-    int n = n0 + (int)threadIdx.x / L, i = (int)threadIdx.x % L;
-    if (vec) {
-        while (n < n1) {
-            const float4 v = __ldg(reinterpret_cast<const float4 *>(x + ((size_t)n * C + c) * S) + i);
-            const float a = v.x - k, b = v.y - k, d = v.z - k, e = v.w - k;
-            s1 += (a + b) + (d + e);
-            s2 = fmaf(a, a, s2); s2 = fmaf(b, b, s2); s2 = fmaf(d, d, s2); s2 = fmaf(e, e, s2);
-            n += qstep; i += rstep;
-            if (i >= L) { i -= L; ++n; }
-        }
-    } else {
-        while (n < n1) {
-            const float a = __ldg(x + ((size_t)n * C + c) * S + i) - k;
-            s1 += a;
-            s2 = fmaf(a, a, s2);
-            n += qstep; i += rstep;
-            if (i >= L) { i -= L; ++n; }
-        }
-    }
-    s1 = block_sum(s1, sh);
-    s2 = block_sum(s2, sh);
-    if (threadIdx.x == 0) part[blockIdx.x] = ChunkStat{k, s1, s2, (float)((long long)(n1 - n0) * S)};
-}
-
-// One thread per channel: merge the chunk statistics in fp64, publish mean / inverse std, update
+// Merges the chunk statistics of channel c in fp64 (Chan's formula), publishes mean / inverse std and updates
 // the running statistics.
-__global__ void __launch_bounds__(128)
-stats_finish_kernel(const ChunkStat *__restrict__ part, int C, int chunks, float *__restrict__ running_mean,
-                    float *__restrict__ running_var, float *__restrict__ save_mean, float *__restrict__ save_std,
-                    double momentum, double eps)
+__device__ __forceinline__ void finish_stats_channel(const ChunkStat *part, int c, int chunks, float *running_mean,
+                                                     float *running_var, float *save_mean, float *save_std,
+                                                     double momentum, double eps)
 {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
     double n = 0.0, mean = 0.0, m2 = 0.0;
     for (int j = 0; j < chunks; ++j) {
-        const ChunkStat p = part[c * chunks + j];
+        const float4 raw = __ldcg(reinterpret_cast<const float4 *>(part + c * chunks + j));   // written by other CTAs
+        const ChunkStat p{raw.x, raw.y, raw.z, raw.w};
         if (p.n <= 0.f) continue;
         const double nb = p.n;
         const double mb = (double)p.k + (double)p.s1 / nb;
@@ -123,6 +78,80 @@ stats_finish_kernel(const ChunkStat *__restrict__ part, int C, int chunks, float
     save_std[c] = invstd;
     running_mean[c] = (float)((1.0 - momentum) * (double)running_mean[c] + momentum * (double)meanf);
     running_var[c] = (float)((1.0 - momentum) * (double)running_var[c] + momentum * (double)unbiased);
+}
+
+// The CTA that hands in the last partial of a channel finishes the channel: ticket counter per channel, zero
+// before the launch and zero again after it.  Returns true in thread 0 of that CTA.
+__device__ __forceinline__ bool last_cta_of_channel(unsigned int *counters, int c, int chunks, int *flag)
+{
+    if (threadIdx.x == 0) {
+        __threadfence();                                  // this CTA's partial is visible before its ticket
+        *flag = atomicAdd(counters + c, 1u) == (unsigned int)(chunks - 1);
+    }
+    __syncthreads();
+    const bool last = *flag != 0 && threadIdx.x == 0;
+    if (last) __threadfence();                            // the other CTAs' partials are visible after their tickets
+    return last;
+}
+
+// grid = C * chunks.  One partial statistic per CTA; with `counters` the last CTA of a channel also merges the
+// partials (no second launch).
+__global__ void __launch_bounds__(256)
+stats_kernel(const float *__restrict__ x, ChunkStat *__restrict__ part, int N, int C, int S, int chunks,
+             unsigned int *__restrict__ counters, float *__restrict__ running_mean, float *__restrict__ running_var,
+             float *__restrict__ save_mean, float *__restrict__ save_std, double momentum, double eps)
+{
+    __shared__ float sh[8];
+    __shared__ int flag;
+    const int c = blockIdx.x / chunks, j = blockIdx.x % chunks;
+    int n0, n1;
+    chunk_range(N, chunks, j, &n0, &n1);
+    float k = 0.f, s1 = 0.f, s2 = 0.f;
+    if (n0 < n1) {
+        k = __ldg(x + ((size_t)n0 * C + c) * S);
+        const bool vec = (S % 4 == 0) && (((uintptr_t)x & 15) == 0);
+        // The chunk's planes are walked as one flat sequence of 16-byte (or 4-byte) items, so that every lane has
+        // work whatever the plane size; (n, i) = image and item inside its plane, advanced without divisions.
+        const int L = vec ? S / 4 : S;
+        const int qstep = (int)blockDim.x / L, rstep = (int)blockDim.x % L;
+        int n = n0 + (int)threadIdx.x / L, i = (int)threadIdx.x % L;
+        if (vec) {
+            while (n < n1) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(x + ((size_t)n * C + c) * S) + i);
+                const float a = v.x - k, b = v.y - k, d = v.z - k, e = v.w - k;
+                s1 += (a + b) + (d + e);
+                s2 = fmaf(a, a, s2); s2 = fmaf(b, b, s2); s2 = fmaf(d, d, s2); s2 = fmaf(e, e, s2);
+                n += qstep; i += rstep;
+                if (i >= L) { i -= L; ++n; }
+            }
+        } else {
+            while (n < n1) {
+                const float a = __ldg(x + ((size_t)n * C + c) * S + i) - k;
+                s1 += a;
+                s2 = fmaf(a, a, s2);
+                n += qstep; i += rstep;
+                if (i >= L) { i -= L; ++n; }
+            }
+        }
+        s1 = block_sum(s1, sh);
+        s2 = block_sum(s2, sh);
+    }
+    if (threadIdx.x == 0) part[blockIdx.x] = ChunkStat{k, s1, s2, n0 < n1 ? (float)((long long)(n1 - n0) * S) : 0.f};
+    if (!counters) return;
+    if (last_cta_of_channel(counters, c, chunks, &flag)) {
+        finish_stats_channel(part, c, chunks, running_mean, running_var, save_mean, save_std, momentum, eps);
+        counters[c] = 0u;
+    }
+}
+
+// One thread per channel: the merge as a separate launch (more channels than ticket counters).
+__global__ void __launch_bounds__(128)
+stats_finish_kernel(const ChunkStat *__restrict__ part, int C, int chunks, float *__restrict__ running_mean,
+                    float *__restrict__ running_var, float *__restrict__ save_mean, float *__restrict__ save_std,
+                    double momentum, double eps)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < C) finish_stats_channel(part, c, chunks, running_mean, running_var, save_mean, save_std, momentum, eps);
 }
 
 // gamma * (x - mean) * invstd + beta with every rounding pinned (no fused multiply-add), so that the backward
@@ -172,14 +201,66 @@ apply_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__
     }
 }
 
+// Per-channel coefficients of the input gradient:
+//   gx = (gy - (x - mean) * proj - gmean) * gscale      (training)
+//   gx = gy * gscale                                     (inference)
+struct GradCoef {
+    float mean, proj, gmean, gscale;
+    float invstd, gamma, beta, pad;     // forward coefficients, for the sign of the fused ReLU's input
+};
+
+// Backward, pass 2 for channel c: totals the chunk sums in fp64, accumulates gradWeight / gradBias and publishes
+// the coefficients of the input gradient.
+__device__ __forceinline__ void finish_grad_channel(const float2 *part, int c, int chunks, long long count, const float *weight,
+                                                    const float *bias, const float *mean_v, const float *std_or_var,
+                                                    int train, double eps, double scale, float *grad_weight,
+                                                    float *grad_bias, GradCoef *coef)
+{
+    double s = 0.0, d = 0.0;
+    for (int j = 0; j < chunks; ++j) {
+        const float2 p = __ldcg(part + c * chunks + j);   // written by other CTAs
+        s += (double)p.x;
+        d += (double)p.y;
+    }
+    const float mean = mean_v[c];
+    const float stdv = train ? std_or_var[c] : (float)(1.0 / sqrt((double)std_or_var[c] + eps));
+    const float w = weight ? weight[c] : 1.f;
+    const double norm = 1.0 / (double)count;
+    GradCoef k;
+    k.mean = mean;
+    k.gmean = (float)(s * norm);
+    k.proj = (float)(d * norm * (double)stdv * (double)stdv);
+    k.gscale = stdv * w;
+    k.invstd = train ? std_or_var[c] : 1.f / sqrtf(std_or_var[c] + (float)eps);   // as the forward kernel computes it
+    k.gamma = w;
+    k.beta = bias ? bias[c] : 0.f;
+    k.pad = 0.f;
+    coef[c] = k;
+    if (grad_weight) grad_weight[c] = (float)((double)grad_weight[c] + scale * d * (double)stdv);
+    if (grad_bias) grad_bias[c] = (float)((double)grad_bias[c] + scale * s);
+}
+
+__global__ void __launch_bounds__(128)
+grad_finish_kernel(const float2 *__restrict__ part, int C, int chunks, long long count,
+                   const float *__restrict__ weight, const float *__restrict__ bias, const float *__restrict__ mean_v,
+                   const float *__restrict__ std_or_var, int train, double eps, double scale,
+                   float *__restrict__ grad_weight, float *__restrict__ grad_bias, GradCoef *__restrict__ coef)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < C) finish_grad_channel(part, c, chunks, count, weight, bias, mean_v, std_or_var, train, eps, scale, grad_weight, grad_bias, coef);
+}
+
 // Backward, pass 1: per (channel, chunk) sums of gy and gy * (x - mean).
 template <bool RELU>
 __global__ void __launch_bounds__(256)
 grad_stats_kernel(const float *__restrict__ x, const float *__restrict__ gy, float2 *__restrict__ part,
                   const float *__restrict__ mean_v, const float *__restrict__ std_or_var, const float *__restrict__ weight,
-                  const float *__restrict__ bias, int train, float eps, int N, int C, int S, int chunks)
+                  const float *__restrict__ bias, int train, float eps, int N, int C, int S, int chunks,
+                  unsigned int *__restrict__ counters, double eps_d, double scale, float *__restrict__ grad_weight,
+                  float *__restrict__ grad_bias, GradCoef *__restrict__ coef)
 {
     __shared__ float sh[8];
+    __shared__ int flag;
     const int c = blockIdx.x / chunks, j = blockIdx.x % chunks;
     int n0, n1;
     chunk_range(N, chunks, j, &n0, &n1);
@@ -228,47 +309,12 @@ grad_stats_kernel(const float *__restrict__ x, const float *__restrict__ gy, flo
     s = block_sum(s, sh);
     d = block_sum(d, sh);
     if (threadIdx.x == 0) part[blockIdx.x] = make_float2(s, d);
-}
-
-// Backward, pass 2 (one thread per channel): total the chunk sums in fp64, accumulate gradWeight /
-// gradBias, and publish the three per-channel coefficients of the input gradient:
-//   gx = (gy - (x - mean) * proj - gmean) * gscale      (training)
-//   gx = gy * gscale                                     (inference)
-struct GradCoef {
-    float mean, proj, gmean, gscale;
-    float invstd, gamma, beta, pad;     // forward coefficients, for the sign of the fused ReLU's input
-};
-
-__global__ void __launch_bounds__(128)
-grad_finish_kernel(const float2 *__restrict__ part, int C, int chunks, long long count,
-                   const float *__restrict__ weight, const float *__restrict__ bias, const float *__restrict__ mean_v,
-                   const float *__restrict__ std_or_var, int train, double eps, double scale,
-                   float *__restrict__ grad_weight, float *__restrict__ grad_bias, GradCoef *__restrict__ coef)
-{
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
-    double s = 0.0, d = 0.0;
-    for (int j = 0; j < chunks; ++j) {
-        const float2 p = part[c * chunks + j];
-        s += (double)p.x;
-        d += (double)p.y;
+    if (!counters) return;
+    if (last_cta_of_channel(counters, c, chunks, &flag)) {
+        finish_grad_channel(part, c, chunks, (long long)N * S, weight, bias, mean_v, std_or_var, train, eps_d, scale, grad_weight,
+                            grad_bias, coef);
+        counters[c] = 0u;
     }
-    const float mean = mean_v[c];
-    const float stdv = train ? std_or_var[c] : (float)(1.0 / sqrt((double)std_or_var[c] + eps));
-    const float w = weight ? weight[c] : 1.f;
-    const double norm = 1.0 / (double)count;
-    GradCoef k;
-    k.mean = mean;
-    k.gmean = (float)(s * norm);
-    k.proj = (float)(d * norm * (double)stdv * (double)stdv);
-    k.gscale = stdv * w;
-    k.invstd = train ? std_or_var[c] : 1.f / sqrtf(std_or_var[c] + (float)eps);   // as the forward kernel computes it
-    k.gamma = w;
-    k.beta = bias ? bias[c] : 0.f;
-    k.pad = 0.f;
-    coef[c] = k;
-    if (grad_weight) grad_weight[c] = (float)((double)grad_weight[c] + scale * d * (double)stdv);
-    if (grad_bias) grad_bias[c] = (float)((double)grad_bias[c] + scale * s);
 }
 
 // Backward, pass 3: the input gradient.
@@ -322,6 +368,11 @@ grad_apply_kernel(const float *__restrict__ x, const float *__restrict__ gy, flo
     }
 }
 
+// Ticket counters at the start of the workspace: one per channel for the forward statistics, one for the gradient
+// sums.  Zero when a call is enqueued, zero again when its kernels have run.
+constexpr int kMaxCounterChannels = 4096;
+constexpr size_t kCounterBytes = (size_t)2 * kMaxCounterChannels * sizeof(unsigned int);
+
 // Chunks per channel so that C * chunks CTAs fill the GPU a few times over, at most one chunk per image.
 static int pick_chunks(int N, int C)
 {
@@ -359,11 +410,12 @@ static void launch_grad_apply(const float *x, const float *gy, float *gx, const 
 using namespace cunn;
 using namespace cunn::bn;
 
+// Workspace layout: [ticket counters, kCounterBytes] [chunk partials] [gradient coefficients].
 extern "C" CUNN_API size_t cunn_b200_batchnorm_workspace(int N, int C)
 {
     if (N <= 0 || C <= 0) return 0;
     const size_t chunks = (size_t)pick_chunks(N, C);
-    return (size_t)C * chunks * sizeof(ChunkStat) + (size_t)C * sizeof(GradCoef) + 256;
+    return kCounterBytes + (((size_t)C * chunks * sizeof(ChunkStat) + 255) & ~(size_t)255) + (size_t)C * sizeof(GradCoef) + 256;
 }
 
 static int bn_forward_impl(const float *x, float *y, const float *weight, const float *bias, float *running_mean,
@@ -381,16 +433,20 @@ static int bn_forward_impl(const float *x, float *y, const float *weight, const 
     if (train) {
         CUNN_CHECK_ARG(save_mean && save_std, "training-mode batch norm needs save_mean and save_std");
         const int chunks = pick_chunks(N, C);
-        const size_t need = (size_t)C * chunks * sizeof(ChunkStat);
+        const size_t need = kCounterBytes + (size_t)C * chunks * sizeof(ChunkStat);
         CUNN_CHECK_ARG(workspace && workspace_bytes >= need && ((uintptr_t)workspace & 15) == 0,
                        "batch norm needs %zu bytes of 16-byte aligned workspace, got %zu", need,
                        workspace ? workspace_bytes : (size_t)0);
-        ChunkStat *part = (ChunkStat *)workspace;
-        stats_kernel<<<C * chunks, 256, 0, stream>>>(x, part, N, C, S, chunks);
+        unsigned int *counters = C <= kMaxCounterChannels ? (unsigned int *)workspace : nullptr;
+        ChunkStat *part = (ChunkStat *)((char *)workspace + kCounterBytes);
+        stats_kernel<<<C * chunks, 256, 0, stream>>>(x, part, N, C, S, chunks, counters, running_mean, running_var, save_mean,
+                                                     save_std, momentum, eps);
         CUNN_LAUNCH_CHECK("batch norm statistics");
-        stats_finish_kernel<<<ceil_div(C, 128), 128, 0, stream>>>(part, C, chunks, running_mean, running_var, save_mean,
-                                                                 save_std, momentum, eps);
-        CUNN_LAUNCH_CHECK("batch norm statistics finish");
+        if (!counters) {
+            stats_finish_kernel<<<ceil_div(C, 128), 128, 0, stream>>>(part, C, chunks, running_mean, running_var, save_mean,
+                                                                     save_std, momentum, eps);
+            CUNN_LAUNCH_CHECK("batch norm statistics finish");
+        }
         if (relu) launch_apply<true>(x, y, weight, bias, save_mean, save_std, 1, (float)eps, C, S, planes, stream);
         else launch_apply<false>(x, y, weight, bias, save_mean, save_std, 1, (float)eps, C, S, planes, stream);
     } else {
@@ -436,27 +492,32 @@ static int bn_backward_impl(const float *x, const float *gy, bool relu, const fl
                    "batch norm backward needs %s", train ? "save_mean and save_std" : "running_mean and running_var");
     const int chunks = pick_chunks(N, C);
     const size_t part_bytes = ((size_t)C * chunks * sizeof(ChunkStat) + 255) & ~(size_t)255;
-    const size_t need = part_bytes + (size_t)C * sizeof(GradCoef);
+    const size_t need = kCounterBytes + part_bytes + (size_t)C * sizeof(GradCoef);
     CUNN_CHECK_ARG(workspace && workspace_bytes >= need && ((uintptr_t)workspace & 15) == 0,
                    "batch norm backward needs %zu bytes of 16-byte aligned workspace, got %zu", need,
                    workspace ? workspace_bytes : (size_t)0);
-    float2 *part = (float2 *)workspace;
-    GradCoef *coef = (GradCoef *)((char *)workspace + part_bytes);
+    unsigned int *counters = C <= kMaxCounterChannels ? (unsigned int *)workspace + kMaxCounterChannels : nullptr;
+    float2 *part = (float2 *)((char *)workspace + kCounterBytes);
+    GradCoef *coef = (GradCoef *)((char *)workspace + kCounterBytes + part_bytes);
     const float *mean_v = train ? save_mean : running_mean;
     const float *sv = train ? save_std : running_var;
     const long long planes = (long long)N * C;
     // inference-mode input gradient needs no sums; they are still required for gradWeight / gradBias
     const bool need_sums = train || grad_weight || grad_bias;
     if (need_sums) {
-        if (relu) grad_stats_kernel<true><<<C * chunks, 256, 0, stream>>>(x, gy, part, mean_v, sv, weight, bias, train, (float)eps, N, C, S, chunks);
-        else grad_stats_kernel<false><<<C * chunks, 256, 0, stream>>>(x, gy, part, mean_v, sv, weight, bias, train, (float)eps, N, C, S, chunks);
+        if (relu) grad_stats_kernel<true><<<C * chunks, 256, 0, stream>>>(x, gy, part, mean_v, sv, weight, bias, train, (float)eps, N, C, S, chunks,
+                                                                          counters, eps, scale, grad_weight, grad_bias, coef);
+        else grad_stats_kernel<false><<<C * chunks, 256, 0, stream>>>(x, gy, part, mean_v, sv, weight, bias, train, (float)eps, N, C, S, chunks,
+                                                                       counters, eps, scale, grad_weight, grad_bias, coef);
         CUNN_LAUNCH_CHECK("batch norm gradient sums");
     } else {
         CUNN_CUDA(cudaMemsetAsync(part, 0, (size_t)C * chunks * sizeof(float2), stream));
     }
-    grad_finish_kernel<<<ceil_div(C, 128), 128, 0, stream>>>(part, C, chunks, (long long)N * S, weight, bias, mean_v, sv, train,
-                                                            eps, scale, grad_weight, grad_bias, coef);
-    CUNN_LAUNCH_CHECK("batch norm gradient finish");
+    if (!need_sums || !counters) {
+        grad_finish_kernel<<<ceil_div(C, 128), 128, 0, stream>>>(part, C, chunks, (long long)N * S, weight, bias, mean_v, sv, train,
+                                                                eps, scale, grad_weight, grad_bias, coef);
+        CUNN_LAUNCH_CHECK("batch norm gradient finish");
+    }
     if (gx) {
         if (relu) launch_grad_apply<true>(x, gy, gx, coef, train, C, S, planes, stream);
         else launch_grad_apply<false>(x, gy, gx, coef, train, C, S, planes, stream);

@@ -512,6 +512,27 @@ bias_finish_kernel(const float *__restrict__ part, float *__restrict__ gb, int K
     gb[k] = (float)((double)gb[k] + (double)scale * s);
 }
 
+// Both reductions of a weight-gradient pass in one launch: gW[i] += scale * sum_s partial[s][i] for i < n, and
+// gb[k] += scale * sum_j bias_part[k][j] for the K threads after them (bias_part may be null).
+__global__ void __launch_bounds__(256)
+wgrad_bias_reduce_kernel(const float *__restrict__ partial, float *__restrict__ gw, long long n, int splits, float scale,
+                         const float *__restrict__ bias_part, float *__restrict__ gb, int K)
+{
+    const long long total = n + (bias_part ? K : 0);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        if (i < n) {
+            float s = 0.f;
+            for (int k = 0; k < splits; ++k) s += __ldg(partial + (size_t)k * n + i);
+            gw[i] += scale * s;
+        } else {
+            const int k = (int)(i - n);
+            double s = 0.0;
+            for (int j = 0; j < splits; ++j) s += (double)bias_part[(size_t)k * splits + j];
+            gb[k] = (float)((double)gb[k] + (double)scale * s);
+        }
+    }
+}
+
 // Input gradient for any stride: gather form, one thread per input pixel (correctness path).
 __global__ void __launch_bounds__(256)
 dgrad_gather_kernel(const float *__restrict__ gy, const float *__restrict__ w, float *__restrict__ gx, int C, int H, int W,
@@ -1508,13 +1529,9 @@ extern "C" CUNN_API int cunn_b200_convmm_acc_grad(const float *x, const float *g
         const long long n = (long long)K * C * kk;
         float *partial = (float *)workspace, *bias_part = partial + (size_t)ctas * n;
         if (stem::weight_grad_partials(x, gy, partial, grad_bias ? bias_part : nullptr, N, H, W, oH, oW, dH, dW, padH, padW, stream)) return 1;
-        const int rblocks = (int)std::max(1LL, std::min(ceil_div_ll(n, 256), (long long)sm_count() * 8));
-        wgrad_reduce_kernel<<<rblocks, 256, 0, stream>>>(partial, grad_weight, n, ctas, scale);
+        const int rblocks = (int)std::max(1LL, std::min(ceil_div_ll(n + K, 256), (long long)sm_count() * 8));
+        wgrad_bias_reduce_kernel<<<rblocks, 256, 0, stream>>>(partial, grad_weight, n, ctas, scale, grad_bias ? bias_part : nullptr, grad_bias, K);
         CUNN_LAUNCH_CHECK("convmm acc grad reduce");
-        if (grad_bias) {
-            bias_finish_kernel<<<ceil_div(K, 128), 128, 0, stream>>>(bias_part, grad_bias, K, ctas, scale);
-            CUNN_LAUNCH_CHECK("convmm bias gradient finish");
-        }
         return 0;
     }
     if (pw_applies(kH, kW, dH, dW, padH, padW)) {
@@ -1530,13 +1547,9 @@ extern "C" CUNN_API int cunn_b200_convmm_acc_grad(const float *x, const float *g
         q.vec_a = (q.HW % 4 == 0) && aligned16(gy); q.vec_b = (q.HW % 4 == 0) && aligned16(x);
         pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets, true);
         if (pw_launch(pw_pick<OP_WGRAD>(bn), q, stream)) return 1;
-        const int rblocks = (int)std::max(1LL, std::min(ceil_div_ll(n, 256), (long long)sm_count() * 8));
-        wgrad_reduce_kernel<<<rblocks, 256, 0, stream>>>((const float *)workspace, grad_weight, n, splits, scale);
+        const int rblocks = (int)std::max(1LL, std::min(ceil_div_ll(n + K, 256), (long long)sm_count() * 8));
+        wgrad_bias_reduce_kernel<<<rblocks, 256, 0, stream>>>((const float *)workspace, grad_weight, n, splits, scale, q.bias_part, grad_bias, K);
         CUNN_LAUNCH_CHECK("convmm acc grad reduce");
-        if (grad_bias) {
-            bias_finish_kernel<<<ceil_div(K, 128), 128, 0, stream>>>(q.bias_part, grad_bias, K, splits, scale);
-            CUNN_LAUNCH_CHECK("convmm bias gradient finish");
-        }
         return 0;
     }
     if (gather_applies(kH, kW)) {
@@ -1554,13 +1567,9 @@ extern "C" CUNN_API int cunn_b200_convmm_acc_grad(const float *x, const float *g
         q.vec_a = (oHW % 4 == 0) && aligned16(gy); q.vec_b = 0;
         pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets, true);
         if (pw_launch(pw_pick<OP_WGRAD>(bn, gather_ks(kH, kW)), q, stream)) return 1;
-        const int rblocks = (int)std::max(1LL, std::min(ceil_div_ll(n, 256), (long long)sm_count() * 8));
-        wgrad_reduce_kernel<<<rblocks, 256, 0, stream>>>((const float *)workspace, grad_weight, n, splits, scale);
+        const int rblocks = (int)std::max(1LL, std::min(ceil_div_ll(n + K, 256), (long long)sm_count() * 8));
+        wgrad_bias_reduce_kernel<<<rblocks, 256, 0, stream>>>((const float *)workspace, grad_weight, n, splits, scale, q.bias_part, grad_bias, K);
         CUNN_LAUNCH_CHECK("convmm acc grad reduce");
-        if (grad_bias) {
-            bias_finish_kernel<<<ceil_div(K, 128), 128, 0, stream>>>(q.bias_part, grad_bias, K, splits, scale);
-            CUNN_LAUNCH_CHECK("convmm bias gradient finish");
-        }
         return 0;
     }
     wgrad_plan(N, C, K, kk, oH * oW, &bn, &splits, &ips, &pb);

@@ -78,16 +78,16 @@ static size_t align_up(size_t v) { return (v + 255) & ~(size_t)255; }
 // Arena layout (bytes from the base), computed identically by the size query and the step.
 struct Arena {
     std::vector<size_t> conv_out, act, save;   // per layer: pre-BN output, post-ReLU output, save_mean|save_std
-    size_t pooled = 0, logits = 0, logprob = 0, glogits = 0, gpooled = 0, loss2 = 0, gA = 0, gB = 0, work = 0, dwwork = 0, total = 0;
-    size_t work_bytes = 0, dwwork_bytes = 0;   // dwwork: scratch of the depthwise parameter gradient, whose ticket
-                                               // counters must stay zero between calls, so nothing else may use it
+    size_t pooled = 0, logits = 0, logprob = 0, glogits = 0, gpooled = 0, loss2 = 0, gA = 0, gB = 0, work = 0, dwwork = 0, bnwork = 0, total = 0;
+    size_t work_bytes = 0, dwwork_bytes = 0, bnwork_bytes = 0;   // dwwork / bnwork: scratch of the depthwise parameter gradient and of
+                                               // batch normalisation, whose ticket counters must stay zero between calls, so nothing else may use them
 };
 
 static void plan(const Model &m, int B, Arena &a)
 {
     size_t off = 0;
     size_t max_act = 0;
-    size_t work = 1 << 20, dwwork = 1 << 20;
+    size_t work = 1 << 20, dwwork = 1 << 20, bnwork = 1 << 20;
     for (const Layer &L : m.layers) {
         const size_t n = (size_t)B * L.cout * L.hout * L.hout * sizeof(float);
         a.conv_out.push_back(off); off = align_up(off + n);
@@ -95,7 +95,7 @@ static void plan(const Model &m, int B, Arena &a)
         a.save.push_back(off); off = align_up(off + 2 * (size_t)L.cout * sizeof(float));
         max_act = std::max(max_act, n);
         max_act = std::max(max_act, (size_t)B * L.cin * L.hin * L.hin * sizeof(float));
-        work = std::max(work, cunn_b200_batchnorm_workspace(B, L.cout));
+        bnwork = std::max(bnwork, cunn_b200_batchnorm_workspace(B, L.cout));
         if (L.kind == KIND_DW)
             dwwork = std::max(dwwork, cunn_b200_dwconv_acc_grad_workspace(B, L.cin, L.hin, L.hin, 1, 3, 3, L.stride, L.stride, 1, 1));
         else if (L.kind == KIND_PW)
@@ -114,6 +114,7 @@ static void plan(const Model &m, int B, Arena &a)
     a.gB = off; off = align_up(off + max_act);
     a.work = off; a.work_bytes = align_up(work); off += a.work_bytes;
     a.dwwork = off; a.dwwork_bytes = align_up(dwwork); off += a.dwwork_bytes;
+    a.bnwork = off; a.bnwork_bytes = align_up(bnwork); off += a.bnwork_bytes;
     a.total = off;
 }
 
@@ -200,6 +201,10 @@ extern "C" CUNN_API int cunn_b200_mobilenet_step(const cunn_b200_mobilenet_confi
     // the depthwise parameter-gradient kernel keeps ticket counters in the first 64 KiB of its workspace
     void *dwwork = base + a.dwwork;
     CUNN_CUDA(cudaMemsetAsync(dwwork, 0, 64 << 10, (cudaStream_t)stream));
+    // batch normalisation keeps its ticket counters in the first 32 KiB of its own workspace
+    void *bnwork = base + a.bnwork;
+    const size_t bnbytes = a.bnwork_bytes;
+    CUNN_CUDA(cudaMemsetAsync(bnwork, 0, 32 << 10, (cudaStream_t)stream));
 
     // ---------------- forward ----------------
     const float *x = images;
@@ -216,7 +221,7 @@ extern "C" CUNN_API int cunn_b200_mobilenet_step(const cunn_b200_mobilenet_confi
         // BN + ReLU in one pass (the caller-side fusion of nn.SpatialBatchNormalization + nn.ReLU)
         STEP(cunn_b200_batchnorm_relu_forward(co, ac, params + L.g_off, params + L.beta_off, bn_running + L.bn_off,
                                               bn_running + L.bn_off + L.cout, sv, sv + L.cout, B, L.cout, L.hout * L.hout,
-                                              1, momentum, eps, work, wbytes, stream));
+                                              1, momentum, eps, bnwork, bnbytes, stream));
         x = ac;
     }
     const int fh = m.final_hw;
@@ -247,7 +252,7 @@ extern "C" CUNN_API int cunn_b200_mobilenet_step(const cunn_b200_mobilenet_confi
         const float *xin = (i == 0) ? images : F(a.act[i - 1]);
         STEP(cunn_b200_batchnorm_relu_backward(co, g, g2, grads + L.g_off, grads + L.beta_off, params + L.g_off,
                                                params + L.beta_off, bn_running + L.bn_off, bn_running + L.bn_off + L.cout, sv, sv + L.cout, B,
-                                               L.cout, L.hout * L.hout, 1, 1.0, eps, work, wbytes, stream));
+                                               L.cout, L.hout * L.hout, 1, 1.0, eps, bnwork, bnbytes, stream));
         // g2 = gradient w.r.t. the convolution output
         if (L.kind == KIND_DW) {
             STEP(cunn_b200_dwconv_acc_grad(xin, g2, grads + L.w_off, grads + L.b_off, B, L.cin, L.hin, L.hin, 1, 3, 3,

@@ -16,10 +16,10 @@ struct THCState {
     THCUNN_b200_error_fn handler = nullptr;
     void *handler_ctx = nullptr;
     std::string last_error;
-    // grow-only scratch owned by the state: [0] general, [1] depthwise parameter gradient (zero-filled, its
-    // ticket counters must stay zero between calls)
-    void *scratch[2] = {nullptr, nullptr};
-    size_t scratch_bytes[2] = {0, 0};
+    // grow-only scratch owned by the state: [0] general, [1] depthwise parameter gradient, [2] batch normalisation
+    // (zero-filled: their ticket counters must stay zero between calls, so each has a buffer of its own)
+    void *scratch[3] = {nullptr, nullptr, nullptr};
+    size_t scratch_bytes[3] = {0, 0, 0};
 };
 
 namespace {
@@ -252,7 +252,7 @@ extern "C" CUNN_API THCState *THCState_b200_new(void) { return new THCState(); }
 extern "C" CUNN_API void THCState_b200_free(THCState *s)
 {
     if (!s) return;
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < 3; ++i)
         if (s->scratch[i]) cudaFree(s->scratch[i]);
     delete s;
 }
@@ -493,7 +493,7 @@ extern "C" CUNN_API void THNN_CudaBatchNormalization_updateOutput(
     if (x && tensor_resize(s, output_, input_->nDimension, input_->size, 4)) {
         const long c1[1] = {C};
         if (!train || (tensor_resize(s, saveMean_, 1, c1, 4) && tensor_resize(s, saveStd_, 1, c1, 4))) {
-            void *ws = state_scratch(s, 0, cunn_b200_batchnorm_workspace((int)N, (int)C));
+            void *ws = state_scratch(s, 2, cunn_b200_batchnorm_workspace((int)N, (int)C));
             if (ws)
                 TH_CALL(s, cunn_b200_batchnorm_forward(tdata<float>(x), tdata<float>(output_), weight_ ? tdata<float>(weight_) : nullptr,
                                                        bias_ ? tdata<float>(bias_) : nullptr, tdata<float>(runningMean_), tdata<float>(runningVar_),
@@ -516,7 +516,7 @@ extern "C" CUNN_API void THNN_CudaBatchNormalization_backward(
              size_desc(input_).c_str(), size_desc(gradOutput_).c_str());
     THCudaTensor *x = new_contiguous(s, input_), *gy = new_contiguous(s, gradOutput_);
     if (x && gy && (!gradInput_ || tensor_resize(s, gradInput_, input_->nDimension, input_->size, 4))) {
-        void *ws = state_scratch(s, 0, cunn_b200_batchnorm_workspace((int)N, (int)C));
+        void *ws = state_scratch(s, 2, cunn_b200_batchnorm_workspace((int)N, (int)C));
         if (ws)
             TH_CALL(s, cunn_b200_batchnorm_backward(tdata<float>(x), tdata<float>(gy), gradInput_ ? tdata<float>(gradInput_) : nullptr,
                                                     gradWeight_ ? tdata<float>(gradWeight_) : nullptr, gradBias_ ? tdata<float>(gradBias_) : nullptr,

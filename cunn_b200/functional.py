@@ -29,8 +29,9 @@ def _ptr(t):
 
 def workspace(nbytes, device, tag="scratch"):
     """Grow-only, zero-initialised scratch buffer per (device, stream, tag).  The depthwise parameter
-    gradient keeps ticket counters in its buffer (tag "dwconv") that must stay zero between calls, so no
-    other operator may write there; everything else shares the "scratch" buffer."""
+    gradient (tag "dwconv") and batch normalisation (tag "batchnorm") keep ticket counters in their buffers
+    that must stay zero between calls, so no other operator may write there; everything else shares the
+    "scratch" buffer."""
     key = (device.index, torch.cuda.current_stream().cuda_stream, tag)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
@@ -126,7 +127,7 @@ def batchnorm_forward(x, weight, bias, running_mean, running_var, train, momentu
         save_mean = torch.empty(C, dtype=torch.float32, device=x.device)
     if save_std is None:
         save_std = torch.empty(C, dtype=torch.float32, device=x.device)
-    ws = workspace(lib.cunn_b200_batchnorm_workspace(N, C), x.device)
+    ws = workspace(lib.cunn_b200_batchnorm_workspace(N, C), x.device, "batchnorm")
     check(lib.cunn_b200_batchnorm_forward(_ptr(x), _ptr(out), _ptr(weight), _ptr(bias), _ptr(running_mean),
                                           _ptr(running_var), _ptr(save_mean), _ptr(save_std), N, C, S, int(train),
                                           momentum, eps, _ptr(ws), ws.numel(), _stream()))
@@ -140,7 +141,7 @@ def batchnorm_backward(x, gy, weight, running_mean, running_var, save_mean, save
     N, C, S = _bn_dims(x)
     if want_gx and out is None:
         out = torch.empty_like(x)
-    ws = workspace(lib.cunn_b200_batchnorm_workspace(N, C), x.device)
+    ws = workspace(lib.cunn_b200_batchnorm_workspace(N, C), x.device, "batchnorm")
     check(lib.cunn_b200_batchnorm_backward(_ptr(x), _ptr(gy), _ptr(out) if want_gx else None, _ptr(grad_weight),
                                            _ptr(grad_bias), _ptr(weight), _ptr(running_mean), _ptr(running_var),
                                            _ptr(save_mean), _ptr(save_std), N, C, S, int(train), scale, eps,
@@ -270,7 +271,7 @@ def batchnorm_relu_forward(x, weight, bias, running_mean, running_var, train, mo
         out = torch.empty_like(x)
     save_mean = torch.empty(C, dtype=torch.float32, device=x.device)
     save_std = torch.empty(C, dtype=torch.float32, device=x.device)
-    ws = workspace(lib.cunn_b200_batchnorm_workspace(N, C), x.device)
+    ws = workspace(lib.cunn_b200_batchnorm_workspace(N, C), x.device, "batchnorm")
     check(lib.cunn_b200_batchnorm_relu_forward(_ptr(x), _ptr(out), _ptr(weight), _ptr(bias), _ptr(running_mean),
                                                _ptr(running_var), _ptr(save_mean), _ptr(save_std), N, C, S, int(train),
                                                momentum, eps, _ptr(ws), ws.numel(), _stream()))
@@ -283,7 +284,7 @@ def batchnorm_relu_backward(x, gy, weight, bias, running_mean, running_var, save
     _chk(x, gy, weight, bias, grad_weight, grad_bias)
     N, C, S = _bn_dims(x)
     out = torch.empty_like(x)
-    ws = workspace(lib.cunn_b200_batchnorm_workspace(N, C), x.device)
+    ws = workspace(lib.cunn_b200_batchnorm_workspace(N, C), x.device, "batchnorm")
     check(lib.cunn_b200_batchnorm_relu_backward(_ptr(x), _ptr(gy), _ptr(out), _ptr(grad_weight), _ptr(grad_bias),
                                                 _ptr(weight), _ptr(bias), _ptr(running_mean), _ptr(running_var), _ptr(save_mean),
                                                 _ptr(save_std), N, C, S, int(train), scale, eps, _ptr(ws), ws.numel(),

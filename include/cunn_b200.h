@@ -150,7 +150,10 @@ CUNN_API int cunn_b200_maxpool_backward(const float *gy, const int64_t *indices,
  * save_mean = mean, save_std = invstd = 1/sqrt(var + eps); running_mean/var updated with `momentum`,
  * running_var from the UNBIASED variance.  Inference: uses the running statistics and leaves them alone.
  * weight / bias may be NULL (gamma = 1, beta = 0).  `workspace`: caller-owned scratch of at least
- * cunn_b200_batchnorm_workspace(N, C) bytes, 16-byte aligned, contents irrelevant.
+ * cunn_b200_batchnorm_workspace(N, C) bytes, 16-byte aligned.  Its first 32 KiB hold per-channel ticket counters
+ * (the CTA that hands in a channel's last partial sum finishes the channel, which saves a launch): they must be
+ * zero when a call is enqueued and every call leaves them zero, so zero the buffer once and let no other
+ * operator write there; the rest of the buffer needs no initialisation.
  * Replaces THNN_(BatchNormalization_updateOutput) (lib/THCUNN/generic/BatchNormalization.cu:34-66,
  * kernels lib/THCUNN/BatchNormalization.cu:141-212). */
 CUNN_API size_t cunn_b200_batchnorm_workspace(int N, int C);
