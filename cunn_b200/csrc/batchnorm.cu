@@ -3,7 +3,7 @@
 // The reference runs one 512-thread CTA per channel, which leaves most of a 148-SM GPU idle when C is
 // small and reads the input three times.  Here every pass is spread over (channel x chunk) CTAs:
 //   * statistics: each CTA reduces a contiguous run of planes of one channel with 16-byte loads.  Sums
-//     are taken of (x - K) and (x - K)^2 with K the first element of the chunk, which keeps fp32
+//     are taken of (x - K) and (x - K)^2 with K the mean of the chunk's first elements, which keeps fp32
 //     accumulation accurate even when |mean| >> std; chunks are merged in fp64 (Chan's formula) by a
 //     small second kernel that also writes save_mean / save_std and updates the running statistics;
 //   * normalisation / gradient: one grid-stride pass with 16-byte loads and stores.
@@ -156,9 +156,24 @@ stats_kernel(const float *__restrict__ x, ChunkStat *__restrict__ part, int N, i
     const int c = blockIdx.x / chunks, j = blockIdx.x % chunks;
     int n0, n1;
     chunk_range(N, chunks, j, &n0, &n1);
+    __shared__ float k_s;
     float k = 0.f, s1 = 0.f, s2 = 0.f;
     if (n0 < n1) {
-        k = __ldg(x + ((size_t)n0 * C + c) * S);
+        // shift K = mean of the chunk's first (up to) 32 elements: close to the channel mean, so the sums of
+        // (x - K) stay small and keep their fp32 accuracy even when a single element is an outlier
+        if (threadIdx.x < 32) {
+            const long long cnt = (long long)(n1 - n0) * S;
+            const int m = cnt < 32 ? (int)cnt : 32;
+            float v = 0.f;
+            if ((int)threadIdx.x < m) {
+                const int e = (int)threadIdx.x, pn = n0 + e / S;
+                v = __ldg(x + ((size_t)pn * C + c) * S + (e - (e / S) * S));
+            }
+            v = warp_sum(v);
+            if (threadIdx.x == 0) k_s = v / (float)m;
+        }
+        __syncthreads();
+        k = k_s;
         const bool vec = (S % 4 == 0) && (((uintptr_t)x & 15) == 0);
         // The chunk's planes are walked as one flat sequence of 16-byte (or 4-byte) items, so that every lane has
         // work whatever the plane size; (n, i) = image and item inside its plane, advanced without divisions.

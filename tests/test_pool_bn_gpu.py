@@ -181,6 +181,8 @@ def test_bn_golden(F, name):
     ((300, 3, 2, 2), True),        # more images than chunks
     ((2, 1024, 7, 7), True),
     ((4, 8, 2, 3), True),          # 24 elements per channel
+    ((16, 4100, 2, 2), True),      # more channels than ticket counters: the merge runs as a separate launch
+    ((40, 2, 16, 16), True),       # 40 chunks per channel: more than one warp-lane round in the merge
 ])
 def test_bn_shapes(F, ref64, shape, affine):
     rng = np.random.default_rng(abs(hash(shape)) % 99991)
