@@ -536,7 +536,7 @@ wgrad_bias_reduce_kernel(const float *__restrict__ partial, float *__restrict__ 
 // Input gradient for any stride: gather form, one thread per input pixel (correctness path).
 __global__ void __launch_bounds__(256)
 dgrad_gather_kernel(const float *__restrict__ gy, const float *__restrict__ w, float *__restrict__ gx, int C, int H, int W,
-                    int K, int kH, int kW, int dH, int dW, int padH, int padW, int oH, int oW, long long total)
+                    int K, int kH, int kW, int dH, int dW, int padH, int padW, int dilH, int dilW, int oH, int oW, long long total)
 {
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
         const int wi = (int)(idx % W);
@@ -547,12 +547,12 @@ dgrad_gather_kernel(const float *__restrict__ gy, const float *__restrict__ w, f
         const long long n = t / C;
         float s = 0.f;
         for (int kh = 0; kh < kH; ++kh) {
-            const int a = h + padH - kh;
+            const int a = h + padH - kh * dilH;
             if (a < 0 || a % dH) continue;
             const int oh = a / dH;
             if (oh >= oH) continue;
             for (int kw = 0; kw < kW; ++kw) {
-                const int b = wi + padW - kw;
+                const int b = wi + padW - kw * dilW;
                 if (b < 0 || b % dW) continue;
                 const int ow = b / dW;
                 if (ow >= oW) continue;
@@ -612,6 +612,7 @@ struct Params {
     // kernels larger than 1x1 (KS != 1): the unfolded operand is gathered from a [g_C, g_H, g_W] image tensor, the
     // pixel grid that drives the gather is pix_W wide (HW = its size)
     int g_C, g_H, g_W, kH, kW, dH, dW, padH, padW, pix_W;
+    int dilH, dilW;    // distance between kernel taps (SpatialDilatedConvolution; 1 for SpatialConvolutionMM)
     int nacc, sets;    // accumulators per tile (nacc - 1 for the hi*hi products, k-blocks round-robin, + 1 for the cross terms), accumulator sets in TMEM (1 or 2)
     int bulk_out;      // FWD/DGRAD: planes of >= 1024 pixels (a multiple of 4), 16-byte aligned output: the columns of a tile leave as bulk stores
 };
@@ -676,7 +677,7 @@ struct Loader {
     unsigned a_mask, b_mask;
     int img, pix, img_end;   // WGRAD: image and pixel of the thread's chunk in the current k-block
     unsigned tapmask[4];     // KS != 1, FWD/DGRAD: bit t set when tap t of pixel j lies inside the image
-    int b_tap[2];            // KS != 1, WGRAD: kh | kw << 8 of the thread's two unfolded rows
+    int b_tap[2];            // KS != 1, WGRAD: row and column offset (kh * dilH | kw * dilW << 16) of the thread's two unfolded rows
 
     __device__ __forceinline__ int taps(const Params &p) const { return KS == 3 ? 9 : p.kH * p.kW; }
     __device__ __forceinline__ int kcols(const Params &p) const { return KS == 3 ? 3 : p.kW; }
@@ -707,7 +708,7 @@ struct Loader {
                         a_mask |= 1u << j;
                         for (int t2 = 0; t2 < kk; ++t2) {
                             const int kh = t2 / kw_n, kw = t2 - kh * kw_n;
-                            if ((unsigned)(ih0 + kh) < (unsigned)p.g_H && (unsigned)(iw0 + kw) < (unsigned)p.g_W) tapmask[j] |= 1u << t2;
+                            if ((unsigned)(ih0 + kh * p.dilH) < (unsigned)p.g_H && (unsigned)(iw0 + kw * p.dilW) < (unsigned)p.g_W) tapmask[j] |= 1u << t2;
                         }
                     }
                 }
@@ -763,8 +764,8 @@ struct Loader {
                     // unfolded row n = (channel, kh, kw): offset of its tap inside an image
                     const int kk = taps(p), kw_n = kcols(p);
                     const int c = n / kk, t2 = n - c * kk, kh = t2 / kw_n, kw = t2 - kh * kw_n;
-                    b_off[i] = (c * p.g_H + kh) * p.g_W + kw;
-                    b_tap[i] = kh | (kw << 8);
+                    b_off[i] = (c * p.g_H + kh * p.dilH) * p.g_W + kw * p.dilW;
+                    b_tap[i] = (kh * p.dilH) | ((kw * p.dilW) << 16);
                 }
                 if (m < p.M_total) a_mask |= 1u << i;
                 if (row < BN && n < p.N_total) b_mask |= 1u << i;
@@ -822,7 +823,7 @@ struct Loader {
                 if (KS != 1) {
                     const int kk = taps(p), kw_n = kcols(p);
                     const int c = k / kk, t2 = k - c * kk, kh = t2 / kw_n, kw = t2 - kh * kw_n;
-                    const int koff = (c * p.g_H + kh) * p.g_W + kw;
+                    const int koff = (c * p.g_H + kh * p.dilH) * p.g_W + kw * p.dilW;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const bool ok = kok && (tapmask[j] >> t2 & 1u);
@@ -896,7 +897,7 @@ struct Loader {
                 } else if (b_store[i]) {
                     // four consecutive output pixels of the unfolded row: x[img][c][oh * dH - padH + kh][ow * dW - padW + kw]
                     const bool on = (b_mask >> i & 1u) != 0;
-                    const int kh = b_tap[i] & 255, kw = b_tap[i] >> 8;
+                    const int kh = b_tap[i] & 0xffff, kw = b_tap[i] >> 16;          // tap offsets in pixels (dilation applied)
                     int ij = img, oh = pix / p.pix_W, ow = pix - oh * p.pix_W;
                     const int rows = p.HW / p.pix_W;
 #pragma unroll
@@ -1271,14 +1272,18 @@ static int launch(GemmKernel kern, const GemmParams &p, dim3 grid, int bn, cudaS
     return 0;
 }
 
-static int check(int N, int C, int H, int W, int K, int kH, int kW, int dH, int dW, int padH, int padW, int *oH, int *oW)
+static int check(int N, int C, int H, int W, int K, int kH, int kW, int dH, int dW, int padH, int padW, int *oH, int *oW,
+                 int dilH = 1, int dilW = 1)
 {
     CUNN_CHECK_ARG(kW > 0 && kH > 0, "kernel size should be greater than zero, but got kH: %d kW: %d", kH, kW);
     CUNN_CHECK_ARG(dW > 0 && dH > 0, "stride should be greater than zero, but got dH: %d dW: %d", dH, dW);
+    CUNN_CHECK_ARG(dilW > 0 && dilH > 0, "dilation should be greater than zero, but got dilationH: %d, dilationW: %d", dilH, dilW);
     CUNN_CHECK_ARG(N >= 0 && C > 0 && K > 0 && H > 0 && W > 0 && padH >= 0 && padW >= 0, "bad convolution sizes");
-    *oH = (H + 2 * padH - kH) / dH + 1;
-    *oW = (W + 2 * padW - kW) / dW + 1;
-    CUNN_CHECK_ARG(H + 2 * padH >= kH && W + 2 * padW >= kW && *oH >= 1 && *oW >= 1,
+    const int spanH = dilH * (kH - 1) + 1, spanW = dilW * (kW - 1) + 1;   // extent of the dilated kernel
+    CUNN_CHECK_ARG(spanH < (1 << 15) && spanW < (1 << 15), "dilated kernel extent too large");
+    *oH = (H + 2 * padH - spanH) / dH + 1;
+    *oW = (W + 2 * padW - spanW) / dW + 1;
+    CUNN_CHECK_ARG(H + 2 * padH >= spanH && W + 2 * padW >= spanW && *oH >= 1 && *oW >= 1,
                    "Given input size: (%d x %d x %d). Calculated output size: (%d x %d x %d). Output size is too small", C, H,
                    W, K, *oH, *oW);
     CUNN_CHECK_ARG((long long)N * C * (long long)H * W < (1LL << 31) && (long long)N * K * (long long)(*oH) * (*oW) < (1LL << 31) &&
@@ -1329,9 +1334,11 @@ static bool gather_applies(int kH, int kW) { return kH * kW <= 32; }
 // loader variant of the gathering path: 3x3 has its own instantiation, everything else (a strided or padded 1x1
 // included) the one with run-time kernel sizes
 static int gather_ks(int kH, int kW) { return (kH == 3 && kW == 3) ? 3 : 0; }
-static void set_geometry(pw::Params &q, int gC, int gH, int gW, int kH, int kW, int dH, int dW, int padH, int padW, int pixW)
+static void set_geometry(pw::Params &q, int gC, int gH, int gW, int kH, int kW, int dH, int dW, int padH, int padW, int pixW,
+                         int dilH, int dilW)
 {
     q.g_C = gC; q.g_H = gH; q.g_W = gW; q.kH = kH; q.kW = kW; q.dH = dH; q.dW = dW; q.padH = padH; q.padW = padW; q.pix_W = pixW;
+    q.dilH = dilH; q.dilW = dilW;
 }
 static int pw_bn_for(int n_total) { return n_total <= 32 ? 32 : (n_total <= 64 ? 64 : 128); }
 
@@ -1388,17 +1395,18 @@ static void pw_wgrad_plan(int N, int C, int K, int HW, int *bn, int *splits, int
 using namespace cunn;
 using namespace cunn::mm;
 
-extern "C" CUNN_API int cunn_b200_convmm_forward(const float *x, const float *weight, const float *bias, float *y, int N,
-                                                 int C, int H, int W, int K, int kH, int kW, int dH, int dW, int padH,
-                                                 int padW, cunn_stream_t stream_)
+static int conv_forward(const float *x, const float *weight, const float *bias, float *y, int N, int C, int H, int W, int K,
+                        int kH, int kW, int dH, int dW, int padH, int padW, int dilH, int dilW, cunn_stream_t stream_)
 {
     clear_error();
     cudaStream_t stream = (cudaStream_t)stream_;
     int oH, oW;
-    if (check(N, C, H, W, K, kH, kW, dH, dW, padH, padW, &oH, &oW)) return 1;
+    if (check(N, C, H, W, K, kH, kW, dH, dW, padH, padW, &oH, &oW, dilH, dilW)) return 1;
     if (N == 0) return 0;
     CUNN_CHECK_ARG(x && weight && y, "null tensor pointer");
-    if (stem::applies(C, K, kH, kW)) return stem::forward(x, weight, bias, y, N, H, W, oH, oW, dH, dW, padH, padW, stream);
+    const bool dilated = dilH != 1 || dilW != 1;
+    CUNN_CHECK_ARG(!dilated || gather_applies(kH, kW), "dilated kernels of more than 32 taps are not supported");
+    if (!dilated && stem::applies(C, K, kH, kW)) return stem::forward(x, weight, bias, y, N, H, W, oH, oW, dH, dW, padH, padW, stream);
     if (pw_applies(kH, kW, dH, dW, padH, padW)) {
         pw::Params q{};
         q.a = x; q.b = weight; q.bias = bias; q.out = y; q.status = device_status_ptr();
@@ -1415,7 +1423,7 @@ extern "C" CUNN_API int cunn_b200_convmm_forward(const float *x, const float *we
         pw::Params q{};
         q.a = x; q.b = weight; q.bias = bias; q.out = y; q.status = device_status_ptr();
         q.HW = oH * oW; q.M_total = N * oH * oW; q.N_total = K; q.Kd = C * kH * kW; q.kblocks = ceil_div(q.Kd, BK);
-        set_geometry(q, C, H, W, kH, kW, dH, dW, padH, padW, oW);
+        set_geometry(q, C, H, W, kH, kW, dH, dW, padH, padW, oW, dilH, dilW);
         const int bn = pw_bn_for(K);
         q.n_tiles = ceil_div(K, bn); q.tiles_per_split = 0; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
         q.n_img = N; q.imgs_per_split = N; q.splits = 1;
@@ -1434,16 +1442,16 @@ extern "C" CUNN_API int cunn_b200_convmm_forward(const float *x, const float *we
     return launch(pick_kernel<OP_FWD>(ks_of(kH, kW), bn), p, grid, bn, stream);
 }
 
-extern "C" CUNN_API int cunn_b200_convmm_grad_input(const float *gy, const float *weight, float *gx, int N, int C, int H,
-                                                    int W, int K, int kH, int kW, int dH, int dW, int padH, int padW,
-                                                    cunn_stream_t stream_)
+static int conv_grad_input(const float *gy, const float *weight, float *gx, int N, int C, int H, int W, int K, int kH, int kW,
+                           int dH, int dW, int padH, int padW, int dilH, int dilW, cunn_stream_t stream_)
 {
     clear_error();
     cudaStream_t stream = (cudaStream_t)stream_;
     int oH, oW;
-    if (check(N, C, H, W, K, kH, kW, dH, dW, padH, padW, &oH, &oW)) return 1;
+    if (check(N, C, H, W, K, kH, kW, dH, dW, padH, padW, &oH, &oW, dilH, dilW)) return 1;
     if (N == 0) return 0;
     CUNN_CHECK_ARG(gy && weight && gx, "null tensor pointer");
+    const bool dilated = dilH != 1 || dilW != 1;
     if (pw_applies(kH, kW, dH, dW, padH, padW)) {
         pw::Params q{};
         q.a = gy; q.b = weight; q.bias = nullptr; q.out = gx; q.status = device_status_ptr();
@@ -1456,13 +1464,13 @@ extern "C" CUNN_API int cunn_b200_convmm_grad_input(const float *gy, const float
         pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
         return pw_launch(pw_pick<OP_DGRAD>(bn), q, stream);
     }
-    if (dH == 1 && dW == 1 && padH <= kH - 1 && padW <= kW - 1) {
-        // stride 1: a convolution of gy with the kernel rotated by 180 degrees and padding k - 1 - pad
+    if (dH == 1 && dW == 1 && padH <= dilH * (kH - 1) && padW <= dilW * (kW - 1) && (!dilated || gather_applies(kH, kW))) {
+        // stride 1: a convolution of gy with the kernel rotated by 180 degrees and padding dil (k - 1) - pad
         if (gather_applies(kH, kW)) {
             pw::Params q{};
             q.a = gy; q.b = weight; q.bias = nullptr; q.out = gx; q.status = device_status_ptr();
             q.HW = H * W; q.M_total = N * H * W; q.N_total = C; q.Kd = K * kH * kW; q.kblocks = ceil_div(q.Kd, BK);
-            set_geometry(q, K, oH, oW, kH, kW, 1, 1, kH - 1 - padH, kW - 1 - padW, W);
+            set_geometry(q, K, oH, oW, kH, kW, 1, 1, dilH * (kH - 1) - padH, dilW * (kW - 1) - padW, W, dilH, dilW);
             const int bn = pw_bn_for(C);
             q.n_tiles = ceil_div(C, bn); q.tiles_per_split = 0; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
             q.n_img = N; q.imgs_per_split = N; q.splits = 1;
@@ -1482,17 +1490,18 @@ extern "C" CUNN_API int cunn_b200_convmm_grad_input(const float *gy, const float
     }
     const long long total = (long long)N * C * H * W;
     const int blocks = (int)std::max(1LL, std::min(ceil_div_ll(total, 256), (long long)sm_count() * 16));
-    dgrad_gather_kernel<<<blocks, 256, 0, stream>>>(gy, weight, gx, C, H, W, K, kH, kW, dH, dW, padH, padW, oH, oW, total);
+    dgrad_gather_kernel<<<blocks, 256, 0, stream>>>(gy, weight, gx, C, H, W, K, kH, kW, dH, dW, padH, padW, dilH, dilW, oH, oW, total);
     CUNN_LAUNCH_CHECK("convmm grad input (gather)");
     return 0;
 }
 
-extern "C" CUNN_API size_t cunn_b200_convmm_acc_grad_workspace(int N, int C, int H, int W, int K, int kH, int kW, int dH,
-                                                               int dW, int padH, int padW)
+static size_t conv_acc_grad_workspace(int N, int C, int H, int W, int K, int kH, int kW, int dH, int dW, int padH, int padW,
+                                      int dilH, int dilW)
 {
     int oH, oW;
-    if (check(N, C, H, W, K, kH, kW, dH, dW, padH, padW, &oH, &oW) || N == 0) return 0;
-    if (stem::applies(C, K, kH, kW)) return stem::wgrad_workspace_bytes();
+    if (check(N, C, H, W, K, kH, kW, dH, dW, padH, padW, &oH, &oW, dilH, dilW) || N == 0) return 0;
+    const bool dilated = dilH != 1 || dilW != 1;
+    if (!dilated && stem::applies(C, K, kH, kW)) return stem::wgrad_workspace_bytes();
     int bn, splits, ips, pb;
     if (pw_applies(kH, kW, dH, dW, padH, padW)) {
         pw_wgrad_plan(N, C, K, H * W, &bn, &splits, &ips);
@@ -1507,24 +1516,25 @@ extern "C" CUNN_API size_t cunn_b200_convmm_acc_grad_workspace(int N, int C, int
     return (size_t)splits * K * C * kH * kW * sizeof(float) + (size_t)K * chunks * sizeof(float) + 256;
 }
 
-extern "C" CUNN_API int cunn_b200_convmm_acc_grad(const float *x, const float *gy, float *grad_weight, float *grad_bias,
-                                                  int N, int C, int H, int W, int K, int kH, int kW, int dH, int dW,
-                                                  int padH, int padW, float scale, void *workspace, size_t workspace_bytes,
-                                                  cunn_stream_t stream_)
+static int conv_acc_grad(const float *x, const float *gy, float *grad_weight, float *grad_bias, int N, int C, int H, int W, int K,
+                         int kH, int kW, int dH, int dW, int padH, int padW, int dilH, int dilW, float scale, void *workspace,
+                         size_t workspace_bytes, cunn_stream_t stream_)
 {
     clear_error();
     cudaStream_t stream = (cudaStream_t)stream_;
     int oH, oW;
-    if (check(N, C, H, W, K, kH, kW, dH, dW, padH, padW, &oH, &oW)) return 1;
+    if (check(N, C, H, W, K, kH, kW, dH, dW, padH, padW, &oH, &oW, dilH, dilW)) return 1;
     if (N == 0) return 0;
     CUNN_CHECK_ARG(x && gy && grad_weight, "null tensor pointer");
-    const size_t need = cunn_b200_convmm_acc_grad_workspace(N, C, H, W, K, kH, kW, dH, dW, padH, padW);
+    const bool dilated = dilH != 1 || dilW != 1;
+    CUNN_CHECK_ARG(!dilated || gather_applies(kH, kW), "dilated kernels of more than 32 taps are not supported");
+    const size_t need = conv_acc_grad_workspace(N, C, H, W, K, kH, kW, dH, dW, padH, padW, dilH, dilW);
     CUNN_CHECK_ARG(workspace && workspace_bytes >= need && ((uintptr_t)workspace & 15) == 0,
                    "convmm acc_grad needs %zu bytes of 16-byte aligned workspace, got %zu", need,
                    workspace ? workspace_bytes : (size_t)0);
     int bn, splits, ips, pb;
     const int kk = kH * kW;
-    if (stem::applies(C, K, kH, kW)) {
+    if (!dilated && stem::applies(C, K, kH, kW)) {
         const int ctas = stem::wgrad_ctas();
         const long long n = (long long)K * C * kk;
         float *partial = (float *)workspace, *bias_part = partial + (size_t)ctas * n;
@@ -1561,7 +1571,7 @@ extern "C" CUNN_API int cunn_b200_convmm_acc_grad(const float *x, const float *g
         q.bias_part = grad_bias ? (float *)workspace + (size_t)splits * n : nullptr;
         q.HW = oHW; q.M_total = K; q.N_total = C * kk; q.Kd = 0;
         q.kblocks = (int)ceil_div_ll((long long)ips * oHW, BK);
-        set_geometry(q, C, H, W, kH, kW, dH, dW, padH, padW, oW);
+        set_geometry(q, C, H, W, kH, kW, dH, dW, padH, padW, oW, dilH, dilW);
         q.n_tiles = ceil_div(C * kk, bn); q.tiles_per_split = ceil_div(K, BM) * q.n_tiles; q.total_tiles = q.tiles_per_split * splits;
         q.n_img = N; q.imgs_per_split = ips; q.splits = splits;
         q.vec_a = (oHW % 4 == 0) && aligned16(gy); q.vec_b = 0;
@@ -1594,4 +1604,62 @@ extern "C" CUNN_API int cunn_b200_convmm_acc_grad(const float *x, const float *g
         CUNN_LAUNCH_CHECK("convmm bias gradient finish");
     }
     return 0;
+}
+
+extern "C" CUNN_API int cunn_b200_convmm_forward(const float *x, const float *weight, const float *bias, float *y, int N,
+                                                 int C, int H, int W, int K, int kH, int kW, int dH, int dW, int padH,
+                                                 int padW, cunn_stream_t stream)
+{
+    return conv_forward(x, weight, bias, y, N, C, H, W, K, kH, kW, dH, dW, padH, padW, 1, 1, stream);
+}
+
+extern "C" CUNN_API int cunn_b200_convmm_grad_input(const float *gy, const float *weight, float *gx, int N, int C, int H,
+                                                    int W, int K, int kH, int kW, int dH, int dW, int padH, int padW,
+                                                    cunn_stream_t stream)
+{
+    return conv_grad_input(gy, weight, gx, N, C, H, W, K, kH, kW, dH, dW, padH, padW, 1, 1, stream);
+}
+
+extern "C" CUNN_API size_t cunn_b200_convmm_acc_grad_workspace(int N, int C, int H, int W, int K, int kH, int kW, int dH,
+                                                               int dW, int padH, int padW)
+{
+    return conv_acc_grad_workspace(N, C, H, W, K, kH, kW, dH, dW, padH, padW, 1, 1);
+}
+
+extern "C" CUNN_API int cunn_b200_convmm_acc_grad(const float *x, const float *gy, float *grad_weight, float *grad_bias,
+                                                  int N, int C, int H, int W, int K, int kH, int kW, int dH, int dW,
+                                                  int padH, int padW, float scale, void *workspace, size_t workspace_bytes,
+                                                  cunn_stream_t stream)
+{
+    return conv_acc_grad(x, gy, grad_weight, grad_bias, N, C, H, W, K, kH, kW, dH, dW, padH, padW, 1, 1, scale, workspace,
+                         workspace_bytes, stream);
+}
+
+extern "C" CUNN_API int cunn_b200_dilated_conv_forward(const float *x, const float *weight, const float *bias, float *y, int N,
+                                                       int C, int H, int W, int K, int kH, int kW, int dH, int dW, int padH,
+                                                       int padW, int dilH, int dilW, cunn_stream_t stream)
+{
+    return conv_forward(x, weight, bias, y, N, C, H, W, K, kH, kW, dH, dW, padH, padW, dilH, dilW, stream);
+}
+
+extern "C" CUNN_API int cunn_b200_dilated_conv_grad_input(const float *gy, const float *weight, float *gx, int N, int C,
+                                                          int H, int W, int K, int kH, int kW, int dH, int dW, int padH,
+                                                          int padW, int dilH, int dilW, cunn_stream_t stream)
+{
+    return conv_grad_input(gy, weight, gx, N, C, H, W, K, kH, kW, dH, dW, padH, padW, dilH, dilW, stream);
+}
+
+extern "C" CUNN_API size_t cunn_b200_dilated_conv_acc_grad_workspace(int N, int C, int H, int W, int K, int kH, int kW,
+                                                                     int dH, int dW, int padH, int padW, int dilH, int dilW)
+{
+    return conv_acc_grad_workspace(N, C, H, W, K, kH, kW, dH, dW, padH, padW, dilH, dilW);
+}
+
+extern "C" CUNN_API int cunn_b200_dilated_conv_acc_grad(const float *x, const float *gy, float *grad_weight, float *grad_bias,
+                                                        int N, int C, int H, int W, int K, int kH, int kW, int dH, int dW,
+                                                        int padH, int padW, int dilH, int dilW, float scale, void *workspace,
+                                                        size_t workspace_bytes, cunn_stream_t stream)
+{
+    return conv_acc_grad(x, gy, grad_weight, grad_bias, N, C, H, W, K, kH, kW, dH, dW, padH, padW, dilH, dilW, scale, workspace,
+                         workspace_bytes, stream);
 }

@@ -390,8 +390,9 @@ done:
 // may be 2-D [K, C*kH*kW] or 4-D.
 static bool mm_prepare(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *weight, THCudaTensor *bias,
                        int kH, int kW, int dH, int dW, int padH, int padW, long *N, long *C, long *K, long *H, long *W,
-                       long *oH, long *oW)
+                       long *oH, long *oW, int dilH = 1, int dilW = 1)
 {
+    if (!(dilW > 0 && dilH > 0)) { raise(s, "dilation should be greater than zero, but got dilationH: %d, dilationW: %d", dilH, dilW); return false; }
     if (!(kW > 0 && kH > 0)) { raise(s, "kernel size should be greater than zero, but got kH: %d kW: %d", kH, kW); return false; }
     if (!(dW > 0 && dH > 0)) { raise(s, "stride should be greater than zero, but got dH: %d dW: %d", dH, dW); return false; }
     if (!is_contiguous(weight)) { raise(s, "weight tensor has to be contiguous"); return false; }
@@ -404,7 +405,7 @@ static bool mm_prepare(THCState *s, THCudaTensor *input, THCudaTensor *gradOutpu
     if (nd != 3 && nd != 4) { raise(s, "3D or 4D input tensor expected but got: %s", size_desc(input).c_str()); return false; }
     const int b = nd == 4;
     *N = b ? input->size[0] : 1; *H = input->size[b + 1]; *W = input->size[b + 2];
-    *oH = (*H + 2 * padH - kH) / dH + 1; *oW = (*W + 2 * padW - kW) / dW + 1;
+    *oH = (*H + 2 * padH - (dilH * (kH - 1) + 1)) / dH + 1; *oW = (*W + 2 * padW - (dilW * (kW - 1) + 1)) / dW + 1;
     if (*oW < 1 || *oH < 1) {
         raise(s, "Given input size: (%ld x %ld x %ld). Calculated output size: (%ld x %ld x %ld). Output size is too small", *C, *H, *W, *K, *oH, *oW);
         return false;
@@ -470,6 +471,70 @@ extern "C" CUNN_API void THNN_CudaSpatialConvolutionMM_accGradParameters(
     }
 done:
     tensor_free(x); tensor_free(gy);
+}
+
+// ---- SpatialDilatedConvolution (generic/SpatialDilatedConvolution.cu; decl generic/THCUNN.h:727-764): the same
+// implicit GEMM with taps dilation apart.  `columns` / `ones` / `gradColumns` are accepted and left untouched.
+extern "C" CUNN_API void THNN_CudaSpatialDilatedConvolution_updateOutput(
+    THCState *s, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias, THCudaTensor *,
+    THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH, int dilationW, int dilationH)
+{
+    long N, C, K, H, W, oH, oW;
+    if (!mm_prepare(s, input, nullptr, weight, bias, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW, dilationH, dilationW)) return;
+    THCudaTensor *x = new_contiguous(s, input);
+    if (x) {
+        const long sz4[4] = {N, K, oH, oW};
+        if (tensor_resize(s, output, 4, sz4, 4)) {
+            TH_CALL(s, cunn_b200_dilated_conv_forward(tdata<float>(x), tdata<float>(weight), bias ? tdata<float>(bias) : nullptr,
+                                                      tdata<float>(output), (int)N, (int)C, (int)H, (int)W, (int)K, kH, kW, dH, dW,
+                                                      padH, padW, dilationH, dilationW, s->stream));
+            if (input->nDimension == 3) tensor_resize(s, output, 3, sz4 + 1, 4);
+        }
+    }
+done:
+    tensor_free(x);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialDilatedConvolution_updateGradInput(
+    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight,
+    THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH, int dilationW, int dilationH)
+{
+    long N, C, K, H, W, oH, oW;
+    if (!mm_prepare(s, input, gradOutput, weight, nullptr, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW, dilationH, dilationW)) return;
+    THCudaTensor *gy = new_contiguous(s, gradOutput);
+    if (gy) {
+        const long sz4[4] = {N, C, H, W};
+        if (tensor_resize(s, gradInput, 4, sz4, 4)) {
+            TH_CALL(s, cunn_b200_dilated_conv_grad_input(tdata<float>(gy), tdata<float>(weight), tdata<float>(gradInput), (int)N, (int)C,
+                                                         (int)H, (int)W, (int)K, kH, kW, dH, dW, padH, padW, dilationH, dilationW,
+                                                         s->stream));
+            if (input->nDimension == 3) tensor_resize(s, gradInput, 3, sz4 + 1, 4);
+        }
+    }
+done:
+    tensor_free(gy);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialDilatedConvolution_accGradParameters(
+    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias,
+    THCudaTensor *, THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH, int dilationW, int dilationH,
+    float scale)
+{
+    long N, C, K, H, W, oH, oW;
+    if (!mm_prepare(s, input, gradOutput, gradWeight, gradBias, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW, dilationH, dilationW)) return;
+    THCudaTensor *x = new_contiguous(s, input), *gy = new_contiguous(s, gradOutput);
+    if (x && gy) {
+        const size_t need = cunn_b200_dilated_conv_acc_grad_workspace((int)N, (int)C, (int)H, (int)W, (int)K, kH, kW, dH, dW, padH, padW,
+                                                                       dilationH, dilationW);
+        void *ws = state_scratch(s, 0, need);
+        if (ws)
+            TH_CALL(s, cunn_b200_dilated_conv_acc_grad(tdata<float>(x), tdata<float>(gy), tdata<float>(gradWeight),
+                                                       gradBias ? tdata<float>(gradBias) : nullptr, (int)N, (int)C, (int)H, (int)W, (int)K,
+                                                       kH, kW, dH, dW, padH, padW, dilationH, dilationW, scale, ws, need, s->stream));
+    }
+done:
+    tensor_free(x);
+    tensor_free(gy);
 }
 
 // ---- BatchNormalization --------------------------------------------------------------------------------

@@ -185,6 +185,46 @@ def convmm_acc_grad(x, gy, grad_weight, grad_bias, dH, dW, padH, padW, scale=1.0
     return grad_weight, grad_bias
 
 
+def dilated_conv_out(size, k, d, pad, dil):
+    return (size + 2 * pad - (dil * (k - 1) + 1)) // d + 1 if d > 0 else 0
+
+
+def dilated_conv_forward(x, weight, bias, dH, dW, padH, padW, dilH, dilW, out=None):
+    """SpatialDilatedConvolution forward; weight [K, C, kH, kW]."""
+    _chk(x, weight, bias)
+    N, C, H, W = x.shape
+    K, _, kH, kW = weight.shape
+    oH, oW = dilated_conv_out(H, kH, dH, padH, dilH), dilated_conv_out(W, kW, dW, padW, dilW)
+    if out is None:
+        out = torch.empty((N, K, max(oH, 0), max(oW, 0)), dtype=torch.float32, device=x.device)
+    check(lib.cunn_b200_dilated_conv_forward(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), N, C, H, W, K, kH, kW,
+                                             dH, dW, padH, padW, dilH, dilW, _stream()))
+    return out
+
+
+def dilated_conv_grad_input(gy, weight, H, W, dH, dW, padH, padW, dilH, dilW, out=None):
+    _chk(gy, weight)
+    K, C, kH, kW = weight.shape
+    N = gy.shape[0]
+    if out is None:
+        out = torch.empty((N, C, H, W), dtype=torch.float32, device=gy.device)
+    check(lib.cunn_b200_dilated_conv_grad_input(_ptr(gy), _ptr(weight), _ptr(out), N, C, H, W, K, kH, kW,
+                                                dH, dW, padH, padW, dilH, dilW, _stream()))
+    return out
+
+
+def dilated_conv_acc_grad(x, gy, grad_weight, grad_bias, dH, dW, padH, padW, dilH, dilW, scale=1.0):
+    """Accumulates into grad_weight [K,C,kH,kW] and grad_bias [K] (may be None) in place."""
+    _chk(x, gy, grad_weight, grad_bias)
+    N, C, H, W = x.shape
+    K, _, kH, kW = grad_weight.shape
+    need = lib.cunn_b200_dilated_conv_acc_grad_workspace(N, C, H, W, K, kH, kW, dH, dW, padH, padW, dilH, dilW)
+    ws = workspace(need, x.device)
+    check(lib.cunn_b200_dilated_conv_acc_grad(_ptr(x), _ptr(gy), _ptr(grad_weight), _ptr(grad_bias), N, C, H, W, K, kH, kW,
+                                              dH, dW, padH, padW, dilH, dilW, scale, _ptr(ws), ws.numel(), _stream()))
+    return grad_weight, grad_bias
+
+
 def threshold_forward(x, threshold=0.0, value=0.0, out=None):
     _chk(x, out)
     if out is None:

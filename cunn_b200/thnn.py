@@ -52,6 +52,9 @@ _SIGS = {
     "SpatialConvolutionMM_updateOutput": [_T] * 6 + _CONV,
     "SpatialConvolutionMM_updateGradInput": [_T] * 6 + _CONV,
     "SpatialConvolutionMM_accGradParameters": [_T] * 6 + _CONV + [_F],
+    "SpatialDilatedConvolution_updateOutput": [_T] * 6 + _CONV + [ctypes.c_int, ctypes.c_int],
+    "SpatialDilatedConvolution_updateGradInput": [_T] * 5 + _CONV + [ctypes.c_int, ctypes.c_int],
+    "SpatialDilatedConvolution_accGradParameters": [_T] * 6 + _CONV + [ctypes.c_int, ctypes.c_int, _F],
     "BatchNormalization_updateOutput": [_T] * 8 + [_B, _D, _D],
     "BatchNormalization_backward": [_T] * 10 + [_B, _D, _D],
     "SpatialMaxPooling_updateOutput": [_T] * 3 + _CONV + [_B],
@@ -191,6 +194,37 @@ class THNN:
         hx, hg, hw, hb = self.wrap(x), self.wrap(gy), self.wrap(gw), self.wrap(gb)
         try:
             self.call("SpatialConvolutionMM_accGradParameters", hx, hg, hw, hb, None, None, kW, kH, dW, dH, padW, padH, scale)
+        finally:
+            self.free(hx, hg, hw, hb)
+
+    def SpatialDilatedConvolution_updateOutput(self, x, weight, bias, kW, kH, dW, dH, padW, padH, dilW, dilH):
+        b = x.dim() == 4
+        H, W = x.shape[b + 1], x.shape[b + 2]
+        oH = (H + 2 * padH - (dilH * (kH - 1) + 1)) // dH + 1
+        oW = (W + 2 * padW - (dilW * (kW - 1) + 1)) // dW + 1
+        cap = max(1, (x.shape[0] if b else 1) * weight.shape[0] * max(oH, 1) * max(oW, 1))
+        hx, hw, hb = self.wrap(x), self.wrap(weight), self.wrap(bias)
+        ho, buf = self.out(cap)
+        try:
+            self.call("SpatialDilatedConvolution_updateOutput", hx, ho, hw, hb, None, None, kW, kH, dW, dH, padW, padH, dilW, dilH)
+            return self.view(ho, buf)
+        finally:
+            self.free(hx, hw, hb, ho)
+
+    def SpatialDilatedConvolution_updateGradInput(self, x, gy, weight, kW, kH, dW, dH, padW, padH, dilW, dilH):
+        hx, hg, hw = self.wrap(x), self.wrap(gy), self.wrap(weight)
+        ho, buf = self.out(x.numel())
+        try:
+            self.call("SpatialDilatedConvolution_updateGradInput", hx, hg, ho, hw, None, kW, kH, dW, dH, padW, padH, dilW, dilH)
+            return self.view(ho, buf)
+        finally:
+            self.free(hx, hg, hw, ho)
+
+    def SpatialDilatedConvolution_accGradParameters(self, x, gy, gw, gb, kW, kH, dW, dH, padW, padH, dilW, dilH, scale):
+        hx, hg, hw, hb = self.wrap(x), self.wrap(gy), self.wrap(gw), self.wrap(gb)
+        try:
+            self.call("SpatialDilatedConvolution_accGradParameters", hx, hg, hw, hb, None, None, kW, kH, dW, dH, padW, padH,
+                      dilW, dilH, scale)
         finally:
             self.free(hx, hg, hw, hb)
 

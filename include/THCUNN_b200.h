@@ -91,6 +91,18 @@ CUNN_API void THNN_CudaSpatialConvolutionMM_accGradParameters(
     THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias,
     THCudaTensor *columns, THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH, float scale);
 
+CUNN_API void THNN_CudaSpatialDilatedConvolution_updateOutput(
+    THCState *state, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias,
+    THCudaTensor *columns, THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH, int dilationW,
+    int dilationH);
+CUNN_API void THNN_CudaSpatialDilatedConvolution_updateGradInput(
+    THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight,
+    THCudaTensor *gradColumns, int kW, int kH, int dW, int dH, int padW, int padH, int dilationW, int dilationH);
+CUNN_API void THNN_CudaSpatialDilatedConvolution_accGradParameters(
+    THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias,
+    THCudaTensor *columns, THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH, int dilationW,
+    int dilationH, float scale);
+
 CUNN_API void THNN_CudaBatchNormalization_updateOutput(
     THCState *state, THCudaTensor *input_, THCudaTensor *output_, THCudaTensor *weight_, THCudaTensor *bias_,
     THCudaTensor *runningMean_, THCudaTensor *runningVar_, THCudaTensor *saveMean_, THCudaTensor *saveStd_,

@@ -123,6 +123,25 @@ CUNN_API int cunn_b200_convmm_acc_grad(const float *x, const float *gy, float *g
                                        int dH, int dW, int padH, int padW, float scale,
                                        void *workspace, size_t workspace_bytes, cunn_stream_t stream);
 
+/* ---- SpatialDilatedConvolution -------------------------------------------------
+ * The same three passes with the kernel taps dilH x dilW apart: output size
+ * (in + 2 pad - (dil (k - 1) + 1)) / stride + 1 (lib/THCUNN/generic/SpatialDilatedConvolution.cu:49-50).
+ * Kernels of up to 32 taps; dilation 1 is SpatialConvolutionMM.  Replaces
+ * THNN_(SpatialDilatedConvolution_updateOutput / _updateGradInput / _accGradParameters)
+ * (lib/THCUNN/generic/SpatialDilatedConvolution.cu:88-200, 202-300, 302-450; decl generic/THCUNN.h:727-764). */
+CUNN_API int cunn_b200_dilated_conv_forward(const float *x, const float *weight, const float *bias, float *y,
+                                            int N, int C, int H, int W, int K, int kH, int kW, int dH, int dW,
+                                            int padH, int padW, int dilH, int dilW, cunn_stream_t stream);
+CUNN_API int cunn_b200_dilated_conv_grad_input(const float *gy, const float *weight, float *gx,
+                                               int N, int C, int H, int W, int K, int kH, int kW, int dH, int dW,
+                                               int padH, int padW, int dilH, int dilW, cunn_stream_t stream);
+CUNN_API size_t cunn_b200_dilated_conv_acc_grad_workspace(int N, int C, int H, int W, int K, int kH, int kW,
+                                                          int dH, int dW, int padH, int padW, int dilH, int dilW);
+CUNN_API int cunn_b200_dilated_conv_acc_grad(const float *x, const float *gy, float *grad_weight, float *grad_bias,
+                                             int N, int C, int H, int W, int K, int kH, int kW, int dH, int dW,
+                                             int padH, int padW, int dilH, int dilW, float scale,
+                                             void *workspace, size_t workspace_bytes, cunn_stream_t stream);
+
 /* ---- SpatialMaxPooling --------------------------------------------------------
  * x [N,C,H,W] -> y [N,C,oH,oW] and int64 indices of the same shape holding the flat position h*W + w of
  * the maximum inside its plane plus CUNN_B200_INDEX_BASE.  The window is scanned row-major with a strict

@@ -178,14 +178,18 @@ void FN(dwconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
 /* y [N,K,oH,oW].                                                            */
 /* ------------------------------------------------------------------------ */
 
+/* The three passes below take dilation factors: SpatialConvolutionMM is the case dilH = dilW = 1,
+ * SpatialDilatedConvolution (lib/THCUNN/generic/SpatialDilatedConvolution.cu:49-50,104-105: output size
+ * (in + 2 pad - (dil (k - 1) + 1)) / stride + 1; unfold with dilation, lib/THCUNN/im2col.h:18-37) the general one. */
+
 /* Forward: y_n = bias*ones + W * im2col(x_n)
- * (lib/THCUNN/generic/SpatialConvolutionMM.cu:129-194). */
-void FN(convmm_forward)(const float *x, const float *w, const float *bias, float *y,
-                        int N, int C, int H, int W, int K, int kH, int kW,
-                        int dH, int dW, int padH, int padW)
+ * (lib/THCUNN/generic/SpatialConvolutionMM.cu:129-194, SpatialDilatedConvolution.cu:140-196). */
+void FN(dilconv_forward)(const float *x, const float *w, const float *bias, float *y,
+                         int N, int C, int H, int W, int K, int kH, int kW,
+                         int dH, int dW, int padH, int padW, int dilH, int dilW)
 {
-    const int oH = (H + 2 * padH - kH) / dH + 1;
-    const int oW = (W + 2 * padW - kW) / dW + 1;
+    const int oH = (H + 2 * padH - (dilH * (kH - 1) + 1)) / dH + 1;
+    const int oW = (W + 2 * padW - (dilW * (kW - 1) + 1)) / dW + 1;
 #pragma omp parallel for collapse(2) schedule(static)
     for (int n = 0; n < N; ++n)
         for (int k = 0; k < K; ++k) {
@@ -198,10 +202,10 @@ void FN(convmm_forward)(const float *x, const float *w, const float *bias, float
                         const float *xp = x + ((size_t)n * C + c) * H * W;
                         const float *wp = w + ((size_t)k * C + c) * kH * kW;
                         for (int kh = 0; kh < kH; ++kh) {
-                            const int ih = oh * dH - padH + kh;
+                            const int ih = oh * dH - padH + kh * dilH;
                             if (ih < 0 || ih >= H) continue;
                             for (int kw = 0; kw < kW; ++kw) {
-                                const int iw = ow * dW - padW + kw;
+                                const int iw = ow * dW - padW + kw * dilW;
                                 if (iw < 0 || iw >= W) continue;
                                 s += (acc_t)wp[kh * kW + kw] * (acc_t)xp[ih * W + iw];
                             }
@@ -213,13 +217,13 @@ void FN(convmm_forward)(const float *x, const float *w, const float *bias, float
 }
 
 /* Input gradient: gx_n = col2im(W^T * gy_n)
- * (lib/THCUNN/generic/SpatialConvolutionMM.cu:272-308). */
-void FN(convmm_grad_input)(const float *gy, const float *w, float *gx,
-                           int N, int C, int H, int W, int K, int kH, int kW,
-                           int dH, int dW, int padH, int padW)
+ * (lib/THCUNN/generic/SpatialConvolutionMM.cu:272-308, SpatialDilatedConvolution.cu:244-290). */
+void FN(dilconv_grad_input)(const float *gy, const float *w, float *gx,
+                            int N, int C, int H, int W, int K, int kH, int kW,
+                            int dH, int dW, int padH, int padW, int dilH, int dilW)
 {
-    const int oH = (H + 2 * padH - kH) / dH + 1;
-    const int oW = (W + 2 * padW - kW) / dW + 1;
+    const int oH = (H + 2 * padH - (dilH * (kH - 1) + 1)) / dH + 1;
+    const int oW = (W + 2 * padW - (dilW * (kW - 1) + 1)) / dW + 1;
 #pragma omp parallel for collapse(2) schedule(static)
     for (int n = 0; n < N; ++n)
         for (int c = 0; c < C; ++c) {
@@ -228,12 +232,12 @@ void FN(convmm_grad_input)(const float *gy, const float *w, float *gx,
                 for (int wi = 0; wi < W; ++wi) {
                     acc_t s = 0;
                     for (int kh = 0; kh < kH; ++kh) {
-                        const int t = h + padH - kh;
+                        const int t = h + padH - kh * dilH;
                         if (t < 0 || t % dH) continue;
                         const int oh = t / dH;
                         if (oh >= oH) continue;
                         for (int kw = 0; kw < kW; ++kw) {
-                            const int u = wi + padW - kw;
+                            const int u = wi + padW - kw * dilW;
                             if (u < 0 || u % dW) continue;
                             const int ow = u / dW;
                             if (ow >= oW) continue;
@@ -248,13 +252,14 @@ void FN(convmm_grad_input)(const float *gy, const float *w, float *gx,
 }
 
 /* Parameter gradients, accumulated: gW += scale * sum_n gy_n * im2col(x_n)^T,
- * gb += scale * sum gy  (lib/THCUNN/generic/SpatialConvolutionMM.cu:396-470). */
-void FN(convmm_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
-                         int N, int C, int H, int W, int K, int kH, int kW,
-                         int dH, int dW, int padH, int padW, float scale)
+ * gb += scale * sum gy  (lib/THCUNN/generic/SpatialConvolutionMM.cu:396-470,
+ * SpatialDilatedConvolution.cu:350-440). */
+void FN(dilconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
+                          int N, int C, int H, int W, int K, int kH, int kW,
+                          int dH, int dW, int padH, int padW, int dilH, int dilW, float scale)
 {
-    const int oH = (H + 2 * padH - kH) / dH + 1;
-    const int oW = (W + 2 * padW - kW) / dW + 1;
+    const int oH = (H + 2 * padH - (dilH * (kH - 1) + 1)) / dH + 1;
+    const int oW = (W + 2 * padW - (dilW * (kW - 1) + 1)) / dW + 1;
 #pragma omp parallel for collapse(2) schedule(static)
     for (int k = 0; k < K; ++k)
         for (int c = 0; c < C; ++c) {
@@ -265,10 +270,10 @@ void FN(convmm_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
                         const float *xp = x + ((size_t)n * C + c) * H * W;
                         const float *gyp = gy + ((size_t)n * K + k) * oH * oW;
                         for (int oh = 0; oh < oH; ++oh) {
-                            const int ih = oh * dH - padH + kh;
+                            const int ih = oh * dH - padH + kh * dilH;
                             if (ih < 0 || ih >= H) continue;
                             for (int ow = 0; ow < oW; ++ow) {
-                                const int iw = ow * dW - padW + kw;
+                                const int iw = ow * dW - padW + kw * dilW;
                                 if (iw < 0 || iw >= W) continue;
                                 s += (acc_t)gyp[oh * oW + ow] * (acc_t)xp[ih * W + iw];
                             }
@@ -289,6 +294,27 @@ void FN(convmm_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
             gb[k] = (float)((acc_t)gb[k] + (acc_t)scale * s);
         }
     }
+}
+
+void FN(convmm_forward)(const float *x, const float *w, const float *bias, float *y,
+                        int N, int C, int H, int W, int K, int kH, int kW,
+                        int dH, int dW, int padH, int padW)
+{
+    FN(dilconv_forward)(x, w, bias, y, N, C, H, W, K, kH, kW, dH, dW, padH, padW, 1, 1);
+}
+
+void FN(convmm_grad_input)(const float *gy, const float *w, float *gx,
+                           int N, int C, int H, int W, int K, int kH, int kW,
+                           int dH, int dW, int padH, int padW)
+{
+    FN(dilconv_grad_input)(gy, w, gx, N, C, H, W, K, kH, kW, dH, dW, padH, padW, 1, 1);
+}
+
+void FN(convmm_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
+                         int N, int C, int H, int W, int K, int kH, int kW,
+                         int dH, int dW, int padH, int padW, float scale)
+{
+    FN(dilconv_acc_grad)(x, gy, gw, gb, N, C, H, W, K, kH, kW, dH, dW, padH, padW, 1, 1, scale);
 }
 
 /* ------------------------------------------------------------------------ */

@@ -107,6 +107,36 @@ class Ref:
                                     ctypes.c_float(scale))
         return gw, gb
 
+    # -- dilated convolution (SpatialDilatedConvolution; dilation 1 is SpatialConvolutionMM) -------
+    def dilconv_forward(self, x, w, b, dH, dW, padH, padW, dilH, dilW):
+        x, w = _f(x), _f(w)
+        b = None if b is None else _f(b)
+        N, C, H, W = x.shape
+        K, _, kH, kW = w.shape
+        oH = (H + 2 * padH - (dilH * (kH - 1) + 1)) // dH + 1
+        oW = (W + 2 * padW - (dilW * (kW - 1) + 1)) // dW + 1
+        y = np.empty((N, K, oH, oW), np.float32)
+        self._fn("dilconv_forward")(_p(x), _p(w), _p(b), _p(y), N, C, H, W, K, kH, kW, dH, dW, padH, padW, dilH, dilW)
+        return y
+
+    def dilconv_grad_input(self, gy, w, H, W, dH, dW, padH, padW, dilH, dilW):
+        gy, w = _f(gy), _f(w)
+        K, C, kH, kW = w.shape
+        N = gy.shape[0]
+        gx = np.empty((N, C, H, W), np.float32)
+        self._fn("dilconv_grad_input")(_p(gy), _p(w), _p(gx), N, C, H, W, K, kH, kW, dH, dW, padH, padW, dilH, dilW)
+        return gx
+
+    def dilconv_acc_grad(self, x, gy, gw, gb, dH, dW, padH, padW, dilH, dilW, scale):
+        x, gy = _f(x), _f(gy)
+        gw = _f(gw).copy()
+        gb = None if gb is None else _f(gb).copy()
+        N, C, H, W = x.shape
+        K, _, kH, kW = gw.shape
+        self._fn("dilconv_acc_grad")(_p(x), _p(gy), _p(gw), _p(gb), N, C, H, W, K, kH, kW, dH, dW, padH, padW,
+                                     dilH, dilW, ctypes.c_float(scale))
+        return gw, gb
+
     # -- batch norm --------------------------------------------------------------
     def bn_forward(self, x, weight, bias, running_mean, running_var, train, momentum, eps):
         """Returns y, running_mean', running_var', save_mean, save_std."""

@@ -85,6 +85,27 @@ def convmm_case(name, rng, N, C, H, W, K, k, d, pad, bias=True, scale=1.0):
     save(name, **arrs)
 
 
+def dilconv_case(name, rng, N, C, H, W, K, k, d, pad, dil, bias=True, scale=1.0):
+    """SpatialDilatedConvolution: torch.nn.functional.conv2d with dilation, forward and gradients."""
+    x = rng.standard_normal((N, C, H, W)).astype(np.float32)
+    w = (rng.standard_normal((K, C, k, k)) * np.sqrt(2.0 / (C * k * k))).astype(np.float32)
+    b = rng.uniform(-0.5, 0.5, K).astype(np.float32) if bias else None
+    oH = (H + 2 * pad - (dil * (k - 1) + 1)) // d + 1
+    oW = (W + 2 * pad - (dil * (k - 1) + 1)) // d + 1
+    gy = rng.standard_normal((N, K, oH, oW)).astype(np.float32)
+    gw0 = rng.standard_normal((K, C, k, k)).astype(np.float32)
+    gb0 = rng.standard_normal(K).astype(np.float32)
+    xt, wt = t(x, True), t(w, True)
+    bt = t(b, True) if bias else None
+    y = F.conv2d(xt, wt, bt, stride=d, padding=pad, dilation=dil)
+    y.backward(t(gy))
+    arrs = dict(x=x, w=w, gy=gy, y=y, gx=xt.grad, gw0=gw0, gb0=gb0, gw=t(gw0) + scale * wt.grad,
+                params=np.array([K, k, d, pad, dil, int(bias)]), scale=np.float32(scale))
+    if bias:
+        arrs.update(b=b, gb=t(gb0) + scale * bt.grad)
+    save(name, **arrs)
+
+
 def bn_case(name, rng, N, C, H, W, affine=True, momentum=0.1, eps=1e-5, scale=1.0):
     x = (0.5 + 2.0 * rng.standard_normal((N, C, H, W))).astype(np.float32)
     g = rng.uniform(0, 1, C).astype(np.float32) if affine else None
@@ -169,7 +190,19 @@ def main():
     maxpool_case("maxpool_ties", rng, 2, 3, 10, 10, 3, 2, 1, False, ties=True)
     maxpool_case("maxpool_2s2", rng, 1, 4, 9, 9, 2, 2, 0, True)
     support_case("support", rng)
+    dilated_cases()
+
+
+def dilated_cases():
+    # own generator: added after the fixtures above were committed, and must not shift their random streams
+    rng = np.random.default_rng(20240)
+    dilconv_case("dilconv_3x3_d2", rng, 2, 5, 11, 10, 8, 3, 1, 2, 2, scale=0.5)
+    dilconv_case("dilconv_3x3_d3_s2", rng, 2, 4, 15, 13, 6, 3, 2, 3, 3, bias=False)
 
 
 if __name__ == "__main__":
-    main()
+    import sys
+    if len(sys.argv) > 1 and sys.argv[1] == "dilated":
+        dilated_cases()                      # only the dilated-convolution fixtures
+    else:
+        main()

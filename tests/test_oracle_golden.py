@@ -171,3 +171,18 @@ def test_ref32_close_to_ref64(ref32, ref64):
     a = ref32.dwconv_forward(g["x"], g["w"], g["b"], 1, 1, 1, 1)
     b = ref64.dwconv_forward(g["x"], g["w"], g["b"], 1, 1, 1, 1)
     assert rel_err(a, b) < 1e-5
+
+
+@pytest.mark.parametrize("name", ["dilconv_3x3_d2", "dilconv_3x3_d3_s2"])
+def test_dilated_conv_oracle_vs_golden(ref64, name):
+    g = golden(name)
+    K, k, d, pad, dil, has_b = [int(v) for v in g["params"]]
+    H, W = g["x"].shape[2:]
+    b = g["b"] if has_b else None
+    assert rel_err(ref64.dilconv_forward(g["x"], g["w"], b, d, d, pad, pad, dil, dil), g["y"]) < 1e-6
+    assert rel_err(ref64.dilconv_grad_input(g["gy"], g["w"], H, W, d, d, pad, pad, dil, dil), g["gx"]) < 1e-6
+    gw, gb = ref64.dilconv_acc_grad(g["x"], g["gy"], g["gw0"], g["gb0"] if has_b else None, d, d, pad, pad, dil, dil,
+                                    float(g["scale"]))
+    assert rel_err(gw, g["gw"]) < 1e-6
+    if has_b:
+        assert rel_err(gb, g["gb"]) < 1e-6
