@@ -662,6 +662,8 @@ __device__ __forceinline__ void bulk_s2g_nocommit(void *dst, uint32_t src_smem, 
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Barrier among the producer warps only (hardware barrier 2).
+__device__ __forceinline__ void producers_sync() { asm volatile("bar.sync 2, %0;" ::"n"(PRODUCERS) : "memory"); }
 // Barrier among the epilogue warps only (hardware barrier 1; barrier 0 is __syncthreads).
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * EPILOGUE_WARPS) : "memory"); }
 
@@ -677,12 +679,14 @@ struct Loader {
     unsigned a_mask, b_mask;
     int img, pix, img_end;   // WGRAD: image and pixel of the thread's chunk in the current k-block
     unsigned tapmask[4];     // KS != 1, FWD/DGRAD: bit t set when tap t of pixel j lies inside the image
-    int b_tap[2];            // KS != 1, WGRAD: row and column offset (kh * dilH | kw * dilW << 16) of the thread's two unfolded rows
+    int img2, pix2;          // KS != 1, WGRAD: image and pixel of this lane's column (k = lane) of the unfolded operand
 
     __device__ __forceinline__ int taps(const Params &p) const { return KS == 3 ? 9 : p.kH * p.kW; }
     __device__ __forceinline__ int kcols(const Params &p) const { return KS == 3 ? 3 : p.kW; }
 
-    __device__ __forceinline__ void setup(const Params &p, int t)
+    // rowtab (KS != 1, WGRAD): shared table of the tile's 128 unfolded rows: x = offset of the row's tap inside an image
+    // (-1: row outside the problem), y = tap row offset | tap column offset << 16 (dilation applied)
+    __device__ __forceinline__ void setup(const Params &p, int t, int2 *rowtab)
     {
         const int tid = threadIdx.x, lane = tid & 31;
         tile = t;
@@ -760,33 +764,50 @@ struct Loader {
                 const int m = m_tile * BM + row, n = n_tile * BN + row;
                 a_off[i] = m * p.HW;
                 b_off[i] = n * p.HW;
-                if (KS != 1) {
-                    // unfolded row n = (channel, kh, kw): offset of its tap inside an image
-                    const int kk = taps(p), kw_n = kcols(p);
-                    const int c = n / kk, t2 = n - c * kk, kh = t2 / kw_n, kw = t2 - kh * kw_n;
-                    b_off[i] = (c * p.g_H + kh * p.dilH) * p.g_W + kw * p.dilW;
-                    b_tap[i] = (kh * p.dilH) | ((kw * p.dilW) << 16);
-                }
                 if (m < p.M_total) a_mask |= 1u << i;
                 if (row < BN && n < p.N_total) b_mask |= 1u << i;
             }
             img = split * p.imgs_per_split;
             img_end = min(p.n_img, img + p.imgs_per_split);
+            if (KS != 1) {
+                // every producer has issued the copies of the previous tile before the table changes
+                producers_sync();
+                if (tid < BM) {
+                    const int n = n_tile * BN + tid;
+                    int2 e = make_int2(-1, 0);
+                    if (tid < BN && n < p.N_total) {
+                        // unfolded row n = (channel, kh, kw)
+                        const int kk = taps(p), kw_n = kcols(p);
+                        const int c = n / kk, t2 = n - c * kk, kh = t2 / kw_n, kw = t2 - kh * kw_n;
+                        e.x = (c * p.g_H + kh * p.dilH) * p.g_W + kw * p.dilW;
+                        e.y = (kh * p.dilH) | ((kw * p.dilW) << 16);
+                    }
+                    rowtab[tid] = e;
+                }
+                producers_sync();
+                img2 = img;
+                pix2 = lane;
+                while (pix2 >= p.HW) { pix2 -= p.HW; ++img2; }
+            }
             pix = (tid & 7) * 4;
             while (pix >= p.HW) { pix -= p.HW; ++img; }
         }
     }
 
     // Moves to the next k-block of this CTA's tile list.
-    __device__ __forceinline__ void advance(const Params &p)
+    __device__ __forceinline__ void advance(const Params &p, int2 *rowtab)
     {
         if (++kb == p.kblocks) {
             const int t = tile + (int)gridDim.x;
-            if (t < p.total_tiles) setup(p, t);
+            if (t < p.total_tiles) setup(p, t, rowtab);
             else tile = t;
         } else if (OP == OP_WGRAD) {
             pix += BK;
             while (pix >= p.HW) { pix -= p.HW; ++img; }
+            if (KS != 1) {
+                pix2 += BK;
+                while (pix2 >= p.HW) { pix2 -= p.HW; ++img2; }
+            }
         }
     }
 
@@ -811,7 +832,8 @@ struct Loader {
     // Issues the asynchronous copies of this thread's pieces of the current k-block into the raw tiles at
     // shared-memory addresses sa / sb (+ the piece offsets); masked pieces are zero-filled.
     __device__ __forceinline__ void issue(const Params &p, uint32_t sa, uint32_t sb, const uint32_t (&a_so)[2],
-                                          const uint32_t (&b_so)[2], const bool (&b_store)[2], const uint32_t (&g_so)[2]) const
+                                          const uint32_t (&b_so)[2], const bool (&b_store)[2], const uint32_t (&g_so)[2],
+                                          const int2 *rowtab) const
     {
         const int tid = threadIdx.x, warp = tid >> 5;
         if (tile >= p.total_tiles) return;
@@ -892,23 +914,26 @@ struct Loader {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 row_chunk(p, sa + a_so[i], p.a + a_off[i], p.M_total * p.HW, p.vec_a != 0, (a_mask >> i & 1u) != 0);
-                if (KS == 1) {
-                    if (b_store[i]) row_chunk(p, sb + b_so[i], p.b + b_off[i], p.N_total * p.HW, p.vec_b != 0, (b_mask >> i & 1u) != 0);
-                } else if (b_store[i]) {
-                    // four consecutive output pixels of the unfolded row: x[img][c][oh * dH - padH + kh][ow * dW - padW + kw]
-                    const bool on = (b_mask >> i & 1u) != 0;
-                    const int kh = b_tap[i] & 0xffff, kw = b_tap[i] >> 16;          // tap offsets in pixels (dilation applied)
-                    int ij = img, oh = pix / p.pix_W, ow = pix - oh * p.pix_W;
-                    const int rows = p.HW / p.pix_W;
+                if (KS == 1 && b_store[i]) row_chunk(p, sb + b_so[i], p.b + b_off[i], p.N_total * p.HW, p.vec_b != 0, (b_mask >> i & 1u) != 0);
+            }
+            if (KS != 1) {
+                // unfolded operand: this lane owns column k = lane (one output pixel) of rows warp, warp + 16, ...:
+                // x[img][c][oh * dH - padH + kh * dilH][ow * dW - padW + kw * dilW]; one copy instruction of the warp
+                // fills the 128 bytes of one tile row
+                const int lane = tid & 31;
+                const int oh = pix2 / p.pix_W, ow = pix2 - oh * p.pix_W;
+                const int ih = oh * p.dH - p.padH, iw = ow * p.dW - p.padW;
+                const bool pix_ok = img2 < img_end;
+                const float *img_base = p.b + (size_t)(pix_ok ? img2 : 0) * p.g_C * p.g_H * p.g_W + (ih * p.g_W + iw);
+                const uint32_t dst0 = sb + (uint32_t)(warp * 128 + (((lane >> 2) ^ (warp & 7)) << 4) + (lane & 3) * 4);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (ow >= p.pix_W) { ow = 0; ++oh; }
-                        if (oh >= rows) { oh = 0; ++ij; }
-                        const int ih = oh * p.dH - p.padH, iw = ow * p.dW - p.padW;
-                        const bool ok = on && ij < img_end && (unsigned)(ih + kh) < (unsigned)p.g_H && (unsigned)(iw + kw) < (unsigned)p.g_W;
-                        cp_async4(sb + b_so[i] + 4 * j, ok ? p.b + ((size_t)ij * p.g_C * p.g_H * p.g_W + b_off[i] + ih * p.g_W + iw) : p.b, ok);
-                        ++ow;
-                    }
+                for (int q = 0; q < 8; ++q) {
+                    const int row = warp + 16 * q;
+                    if (row >= BN) break;
+                    const int2 e = rowtab[row];
+                    const bool ok = pix_ok && e.x >= 0 && (unsigned)(ih + (e.y & 0xffff)) < (unsigned)p.g_H &&
+                                    (unsigned)(iw + (e.y >> 16)) < (unsigned)p.g_W;
+                    cp_async4(dst0 + (uint32_t)q * 2048u, ok ? img_base + e.x : p.b, ok);
                 }
             }
         }
@@ -965,6 +990,13 @@ pw_gemm_kernel(const Params p)
         a_so[i] = A_MN ? mn : km;
         b_so[i] = B_MN ? mn : km;
         b_store[i] = B_MN ? (lane * 4 < BN) : (row < BN);
+        if (OP == OP_WGRAD && KS != 1) {
+            // gathered K-major operand: warp w copies rows w, w + 16, ... element by element, so it also splits them:
+            // this lane takes chunks (lane & 3) * 2 + i of row w + 16 * (lane >> 2)
+            const int grow = warp + 16 * (lane >> 2);
+            b_so[i] = piece_offset(grow, (lane & 3) * 2 + i);
+            b_store[i] = grow < BN;
+        }
         // gathered M/N-major operand (KS != 1): this lane copies element (row = lane + 32 j, k), 4 bytes each; j adds
         // one 512-byte atom.  The 32 lanes of one copy instruction fill one 128-byte row of an atom.
         g_so[i] = (uint32_t)((k >> 2) * MN_KATOM + (k & 3) * 128 + (((lane >> 3) ^ (k & 3)) << 5) + (((lane >> 2) & 1) << 4) + (lane & 3) * 4);
@@ -1155,15 +1187,16 @@ pw_gemm_kernel(const Params p)
         Loader<OP, BN, KS> L;
         L.tile = (int)blockIdx.x;
         L.kb = 0;
-        if (my_tiles > 0) L.setup(p, L.tile);
+        int2 *rowtab = reinterpret_cast<int2 *>(smem + (size_t)(RAW_STAGES + LO_BUFS) * 2 * TILE);   // in the output staging area, which the weight gradient does not use
+        if (my_tiles > 0) L.setup(p, L.tile, rowtab);
         const uint32_t smem_a0 = smem_u32(smem);
         // copies of the first PREFETCH k-blocks; one commit group per k-block, empty ones included, so that
         // "all but the newest PREFETCH - 1 groups" always means "k-block i has landed"
     #pragma unroll
         for (int i = 0; i < PREFETCH; ++i) {
             if (i < total_it) {
-                L.issue(p, smem_a0 + (uint32_t)(i * 2 * TILE), smem_a0 + (uint32_t)(i * 2 * TILE + TILE), a_so, b_so, b_store, g_so);
-                L.advance(p);
+                L.issue(p, smem_a0 + (uint32_t)(i * 2 * TILE), smem_a0 + (uint32_t)(i * 2 * TILE + TILE), a_so, b_so, b_store, g_so, rowtab);
+                L.advance(p, rowtab);
             }
             cp_async_commit();
         }
@@ -1189,8 +1222,8 @@ pw_gemm_kernel(const Params p)
                     if (!mbar_wait(smem_u32(bars + j % RAW_STAGES), (uint32_t)((j / RAW_STAGES) & 1), p.status)) { ok = false; break; }
                 }
                 const int ns = (i + PREFETCH) % RAW_STAGES;
-                L.issue(p, smem_a0 + (uint32_t)(ns * 2 * TILE), smem_a0 + (uint32_t)(ns * 2 * TILE + TILE), a_so, b_so, b_store, g_so);
-                L.advance(p);
+                L.issue(p, smem_a0 + (uint32_t)(ns * 2 * TILE), smem_a0 + (uint32_t)(ns * 2 * TILE + TILE), a_so, b_so, b_store, g_so, rowtab);
+                L.advance(p, rowtab);
             }
             cp_async_commit();
             if (c_kb == KB - 1) {
@@ -1374,19 +1407,28 @@ static int pw_launch(PwKernel kern, pw::Params &p, cudaStream_t stream)
     return 0;
 }
 
-// Splits of the image range for the pointwise weight gradient: at most ~128 k-blocks per tile, and a tile count
-// that fills whole waves of the persistent grid.
+// Splits of the image range for the weight gradient on the persistent kernel: every tile takes `imgs_per_split`
+// images.  Candidates are scored by (waves of the persistent grid) x (images per tile) — the time of the slowest
+// CTA — and tiles longer than ~128 k-blocks are avoided when a shorter choice exists (accumulation chains).
 static void pw_wgrad_plan(int N, int C, int K, int HW, int *bn, int *splits, int *imgs_per_split)
 {
     *bn = pw_bn_for(C);
-    const int tiles_mn = ceil_div(K, BM) * ceil_div(C, *bn);
-    const long long total_kb = ceil_div_ll((long long)N * HW, BK);
-    const long long s_min = std::max(1LL, ceil_div_ll(total_kb, 128));
+    const long long tiles_mn = (long long)ceil_div(K, BM) * ceil_div(C, *bn);
     const int grid = sm_count();
-    const long long waves = std::max(1LL, ceil_div_ll(tiles_mn * s_min, grid));
-    long long s = std::max(1LL, std::min((long long)N, waves * grid / tiles_mn));
-    *imgs_per_split = ceil_div(N, (int)s);
-    *splits = ceil_div(N, *imgs_per_split);
+    const long long kb_per_img = ceil_div_ll(HW, BK);
+    int best_ips = 1;
+    double best = -1.0;
+    for (int ips = 1; ips <= N; ++ips) {
+        const long long tiles = tiles_mn * ceil_div(N, ips);
+        const long long waves = ceil_div_ll(tiles, grid);
+        // in k-blocks: the tile's own loop + about six more for its prologue, its 64 KB of partial sums and their
+        // share of the final reduction
+        double cost = (double)waves * ((double)ips * kb_per_img + 6.0);
+        if (ips > 1 && (long long)ips * kb_per_img > 128) cost *= 1.0 + 0.25 * (double)((long long)ips * kb_per_img - 128) / 128.0;
+        if (best < 0.0 || cost < best * 0.999) { best = cost; best_ips = ips; }
+    }
+    *imgs_per_split = best_ips;
+    *splits = ceil_div(N, best_ips);
 }
 
 }  // namespace mm
