@@ -533,6 +533,14 @@ wgrad_bias_reduce_kernel(const float *__restrict__ partial, float *__restrict__ 
     }
 }
 
+// y[img][q][pix] += bias[q]: the bias of a transposed convolution, whose product comes out of the input-gradient kernels.
+__global__ void __launch_bounds__(256)
+add_plane_bias_kernel(float *__restrict__ y, const float *__restrict__ bias, int Q, int HW, long long total)
+{
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+        y[i] += __ldg(bias + (int)((i / HW) % Q));
+}
+
 // Input gradient for any stride: gather form, one thread per input pixel (correctness path).
 __global__ void __launch_bounds__(256)
 dgrad_gather_kernel(const float *__restrict__ gy, const float *__restrict__ w, float *__restrict__ gx, int C, int H, int W,
@@ -1704,4 +1712,104 @@ extern "C" CUNN_API int cunn_b200_dilated_conv_acc_grad(const float *x, const fl
 {
     return conv_acc_grad(x, gy, grad_weight, grad_bias, N, C, H, W, K, kH, kW, dH, dW, padH, padW, dilH, dilW, scale, workspace,
                          workspace_bytes, stream);
+}
+
+// ---------------------------------------------------------------------------
+// SpatialFullDilatedConvolution (transposed convolution): x [N,P,H,W], weight [P,Q,kH,kW], y [N,Q,OH,OW].
+// It is the adjoint of the convolution that maps [N,Q,OH,OW] to [N,P,H,W] with the same weight array read as
+// [K = P][C = Q][kH][kW], so its forward is that convolution's input gradient (plus bias), its input gradient is that
+// convolution's forward, and its weight gradient is that convolution's weight gradient with the roles of the
+// activations and the output gradient exchanged.
+// ---------------------------------------------------------------------------
+
+static int full_check(int N, int P, int H, int W, int Q, int kH, int kW, int dH, int dW, int padH, int padW, int dilH, int dilW,
+                      int adjH, int adjW, int *OH, int *OW)
+{
+    CUNN_CHECK_ARG(kW > 0 && kH > 0, "kernel size should be greater than zero, but got kH: %d kW: %d", kH, kW);
+    CUNN_CHECK_ARG(dW > 0 && dH > 0, "stride should be greater than zero, but got dH: %d dW: %d", dH, dW);
+    CUNN_CHECK_ARG(dilW > 0 && dilH > 0, "dilation should be greater than zero, but got dilationH: %d, dilationW: %d", dilH, dilW);
+    CUNN_CHECK_ARG(adjH >= 0 && adjW >= 0 && (adjW < dW || adjW < dilW) && (adjH < dH || adjH < dilH),
+                   "output padding must be smaller than either stride or dilation, but got adjH: %d adjW: %d dH: %d dW: %d "
+                   "dilationH: %d dilationW: %d", adjH, adjW, dH, dW, dilH, dilW);
+    CUNN_CHECK_ARG(adjH < dH && adjW < dW, "output padding of at least the stride is not supported (adjH: %d adjW: %d dH: %d dW: %d)",
+                   adjH, adjW, dH, dW);
+    CUNN_CHECK_ARG(N >= 0 && P > 0 && Q > 0 && H > 0 && W > 0 && padH >= 0 && padW >= 0, "bad convolution sizes");
+    const long long oh = (long long)(H - 1) * dH - 2 * padH + (dilH * (kH - 1) + 1) + adjH;
+    const long long ow = (long long)(W - 1) * dW - 2 * padW + (dilW * (kW - 1) + 1) + adjW;
+    CUNN_CHECK_ARG(oh >= 1 && ow >= 1 && oh < (1 << 24) && ow < (1 << 24),
+                   "Given input size: (%d x %d x %d). Calculated output size: (%d x %lld x %lld). Output size is too small", P, H, W,
+                   Q, oh, ow);
+    *OH = (int)oh; *OW = (int)ow;
+    return 0;
+}
+
+static int bias_chunks(int N, int Q) { return std::max(1, std::min(N, ceil_div(sm_count() * 4, Q))); }
+
+extern "C" CUNN_API int cunn_b200_full_conv_forward(const float *x, const float *weight, const float *bias, float *y, int N,
+                                                    int P, int H, int W, int Q, int kH, int kW, int dH, int dW, int padH,
+                                                    int padW, int dilH, int dilW, int adjH, int adjW, cunn_stream_t stream_)
+{
+    clear_error();
+    int OH, OW;
+    if (full_check(N, P, H, W, Q, kH, kW, dH, dW, padH, padW, dilH, dilW, adjH, adjW, &OH, &OW)) return 1;
+    if (conv_grad_input(x, weight, y, N, Q, OH, OW, P, kH, kW, dH, dW, padH, padW, dilH, dilW, stream_)) return 1;
+    if (bias && N > 0) {
+        const long long total = (long long)N * Q * OH * OW;
+        const int blocks = (int)std::max(1LL, std::min(ceil_div_ll(total, 256), (long long)sm_count() * 16));
+        add_plane_bias_kernel<<<blocks, 256, 0, (cudaStream_t)stream_>>>(y, bias, Q, OH * OW, total);
+        CUNN_LAUNCH_CHECK("full convolution bias");
+    }
+    return 0;
+}
+
+extern "C" CUNN_API int cunn_b200_full_conv_grad_input(const float *gy, const float *weight, float *gx, int N, int P, int H,
+                                                       int W, int Q, int kH, int kW, int dH, int dW, int padH, int padW,
+                                                       int dilH, int dilW, int adjH, int adjW, cunn_stream_t stream_)
+{
+    clear_error();
+    int OH, OW;
+    if (full_check(N, P, H, W, Q, kH, kW, dH, dW, padH, padW, dilH, dilW, adjH, adjW, &OH, &OW)) return 1;
+    return conv_forward(gy, weight, nullptr, gx, N, Q, OH, OW, P, kH, kW, dH, dW, padH, padW, dilH, dilW, stream_);
+}
+
+static size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+extern "C" CUNN_API size_t cunn_b200_full_conv_acc_grad_workspace(int N, int P, int H, int W, int Q, int kH, int kW, int dH,
+                                                                  int dW, int padH, int padW, int dilH, int dilW, int adjH,
+                                                                  int adjW)
+{
+    int OH, OW;
+    if (full_check(N, P, H, W, Q, kH, kW, dH, dW, padH, padW, dilH, dilW, adjH, adjW, &OH, &OW) || N == 0) return 0;
+    return round256(conv_acc_grad_workspace(N, Q, OH, OW, P, kH, kW, dH, dW, padH, padW, dilH, dilW)) +
+           (size_t)Q * bias_chunks(N, Q) * sizeof(float) + 256;
+}
+
+extern "C" CUNN_API int cunn_b200_full_conv_acc_grad(const float *x, const float *gy, float *grad_weight, float *grad_bias,
+                                                     int N, int P, int H, int W, int Q, int kH, int kW, int dH, int dW,
+                                                     int padH, int padW, int dilH, int dilW, int adjH, int adjW, float scale,
+                                                     void *workspace, size_t workspace_bytes, cunn_stream_t stream_)
+{
+    clear_error();
+    int OH, OW;
+    if (full_check(N, P, H, W, Q, kH, kW, dH, dW, padH, padW, dilH, dilW, adjH, adjW, &OH, &OW)) return 1;
+    if (N == 0) return 0;
+    const size_t conv_ws = round256(conv_acc_grad_workspace(N, Q, OH, OW, P, kH, kW, dH, dW, padH, padW, dilH, dilW));
+    const int chunks = bias_chunks(N, Q);
+    const size_t need = conv_ws + (size_t)Q * chunks * sizeof(float) + 256;
+    CUNN_CHECK_ARG(workspace && workspace_bytes >= need && ((uintptr_t)workspace & 15) == 0,
+                   "full convolution acc_grad needs %zu bytes of 16-byte aligned workspace, got %zu", need,
+                   workspace ? workspace_bytes : (size_t)0);
+    // the adjoint convolution's "input" is gy and its "output gradient" is x
+    if (conv_acc_grad(gy, x, grad_weight, nullptr, N, Q, OH, OW, P, kH, kW, dH, dW, padH, padW, dilH, dilW, scale, workspace,
+                      conv_ws, stream_))
+        return 1;
+    if (grad_bias) {
+        cudaStream_t stream = (cudaStream_t)stream_;
+        float *part = (float *)((char *)workspace + conv_ws);
+        bias_partial_kernel<<<Q * chunks, 256, 0, stream>>>(gy, part, N, Q, OH * OW, chunks);
+        CUNN_LAUNCH_CHECK("full convolution bias gradient");
+        bias_finish_kernel<<<ceil_div(Q, 128), 128, 0, stream>>>(part, grad_bias, Q, chunks, scale);
+        CUNN_LAUNCH_CHECK("full convolution bias gradient finish");
+    }
+    return 0;
 }

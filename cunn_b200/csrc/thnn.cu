@@ -537,6 +537,131 @@ done:
     tensor_free(gy);
 }
 
+// ---- SpatialFullDilatedConvolution / SpatialFullConvolution (transposed convolution) ----------------------
+// Shape rules of lib/THCUNN/generic/SpatialFullDilatedConvolution.cu:5-66: weight [nInputPlane, nOutputPlane, kH, kW]
+// (or 2-D [nInputPlane, nOutputPlane*kH*kW]), bias [nOutputPlane].
+static bool full_prepare(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *weight, THCudaTensor *bias,
+                         int kH, int kW, int dH, int dW, int padH, int padW, int dilH, int dilW, int adjH, int adjW, long *N,
+                         long *P, long *Q, long *H, long *W, long *OH, long *OW)
+{
+    if (!(kW > 0 && kH > 0)) { raise(s, "kernel size should be greater than zero, but got kH: %d kW: %d", kH, kW); return false; }
+    if (!(dW > 0 && dH > 0)) { raise(s, "stride should be greater than zero, but got dH: %d dW: %d", dH, dW); return false; }
+    if (!(dilW > 0 && dilH > 0)) { raise(s, "dilation should be greater than zero, but got dilationH: %d, dilationW: %d", dilH, dilW); return false; }
+    if (!((adjW < dW || adjW < dilW) && (adjH < dH || adjH < dilH))) {
+        raise(s, "output padding must be smaller than either stride or dilation, but got adjH: %d adjW: %d dH: %d dW: %d dilationH: %d dilationW: %d",
+              adjH, adjW, dH, dW, dilH, dilW);
+        return false;
+    }
+    if (!is_contiguous(weight)) { raise(s, "weight tensor has to be contiguous"); return false; }
+    if (bias && !is_contiguous(bias)) { raise(s, "bias tensor has to be contiguous"); return false; }
+    if (weight->nDimension != 2 && weight->nDimension != 4) { raise(s, "2D or 4D weight tensor expected, but got: %s", size_desc(weight).c_str()); return false; }
+    *P = weight->size[0];
+    *Q = weight->nDimension == 2 ? weight->size[1] / (kH * kW) : weight->size[1];
+    if (bias && !check_dim_size(s, bias, "bias", 1, 0, *Q)) return false;
+    const int nd = input->nDimension;
+    if (nd != 3 && nd != 4) { raise(s, "3D or 4D input tensor expected but got: %s", size_desc(input).c_str()); return false; }
+    const int b = nd == 4;
+    *N = b ? input->size[0] : 1; *H = input->size[b + 1]; *W = input->size[b + 2];
+    *OH = (*H - 1) * dH - 2 * padH + (dilH * (kH - 1) + 1) + adjH;
+    *OW = (*W - 1) * dW - 2 * padW + (dilW * (kW - 1) + 1) + adjW;
+    if (*OW < 1 || *OH < 1) {
+        raise(s, "Given input size: (%ld x %ld x %ld). Calculated output size: (%ld x %ld x %ld). Output size is too small", *P, *H, *W, *Q, *OH, *OW);
+        return false;
+    }
+    if (!check_dim_size(s, input, "input", nd, b, *P)) return false;
+    if (gradOutput && !(check_dim_size(s, gradOutput, "gradOutput", nd, b, *Q) && check_dim_size(s, gradOutput, "gradOutput", nd, b + 1, *OH) &&
+                        check_dim_size(s, gradOutput, "gradOutput", nd, b + 2, *OW))) return false;
+    return true;
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialFullDilatedConvolution_updateOutput(
+    THCState *s, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias, THCudaTensor *,
+    THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH, int dilationW, int dilationH, int adjW, int adjH)
+{
+    long N, P, Q, H, W, OH, OW;
+    if (!full_prepare(s, input, nullptr, weight, bias, kH, kW, dH, dW, padH, padW, dilationH, dilationW, adjH, adjW, &N, &P, &Q, &H, &W, &OH, &OW)) return;
+    THCudaTensor *x = new_contiguous(s, input);
+    if (x) {
+        const long sz4[4] = {N, Q, OH, OW};
+        if (tensor_resize(s, output, 4, sz4, 4)) {
+            TH_CALL(s, cunn_b200_full_conv_forward(tdata<float>(x), tdata<float>(weight), bias ? tdata<float>(bias) : nullptr,
+                                                   tdata<float>(output), (int)N, (int)P, (int)H, (int)W, (int)Q, kH, kW, dH, dW, padH,
+                                                   padW, dilationH, dilationW, adjH, adjW, s->stream));
+            if (input->nDimension == 3) tensor_resize(s, output, 3, sz4 + 1, 4);
+        }
+    }
+done:
+    tensor_free(x);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialFullDilatedConvolution_updateGradInput(
+    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight,
+    THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH, int dilationW, int dilationH, int adjW, int adjH)
+{
+    long N, P, Q, H, W, OH, OW;
+    if (!full_prepare(s, input, gradOutput, weight, nullptr, kH, kW, dH, dW, padH, padW, dilationH, dilationW, adjH, adjW, &N, &P, &Q, &H, &W, &OH, &OW)) return;
+    THCudaTensor *gy = new_contiguous(s, gradOutput);
+    if (gy) {
+        const long sz4[4] = {N, P, H, W};
+        if (tensor_resize(s, gradInput, 4, sz4, 4)) {
+            TH_CALL(s, cunn_b200_full_conv_grad_input(tdata<float>(gy), tdata<float>(weight), tdata<float>(gradInput), (int)N, (int)P,
+                                                      (int)H, (int)W, (int)Q, kH, kW, dH, dW, padH, padW, dilationH, dilationW, adjH,
+                                                      adjW, s->stream));
+            if (input->nDimension == 3) tensor_resize(s, gradInput, 3, sz4 + 1, 4);
+        }
+    }
+done:
+    tensor_free(gy);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialFullDilatedConvolution_accGradParameters(
+    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias,
+    THCudaTensor *, THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH, int dilationW, int dilationH,
+    int adjW, int adjH, float scale)
+{
+    long N, P, Q, H, W, OH, OW;
+    if (!full_prepare(s, input, gradOutput, gradWeight, gradBias, kH, kW, dH, dW, padH, padW, dilationH, dilationW, adjH, adjW, &N, &P, &Q, &H, &W, &OH, &OW)) return;
+    THCudaTensor *x = new_contiguous(s, input), *gy = new_contiguous(s, gradOutput);
+    if (x && gy) {
+        const size_t need = cunn_b200_full_conv_acc_grad_workspace((int)N, (int)P, (int)H, (int)W, (int)Q, kH, kW, dH, dW, padH, padW,
+                                                                    dilationH, dilationW, adjH, adjW);
+        void *ws = state_scratch(s, 0, need);
+        if (ws)
+            TH_CALL(s, cunn_b200_full_conv_acc_grad(tdata<float>(x), tdata<float>(gy), tdata<float>(gradWeight),
+                                                    gradBias ? tdata<float>(gradBias) : nullptr, (int)N, (int)P, (int)H, (int)W, (int)Q,
+                                                    kH, kW, dH, dW, padH, padW, dilationH, dilationW, adjH, adjW, scale, ws, need,
+                                                    s->stream));
+    }
+done:
+    tensor_free(x);
+    tensor_free(gy);
+}
+
+// SpatialFullConvolution is the same operator with dilation 1 (lib/THCUNN/generic/SpatialFullConvolution.cu).
+extern "C" CUNN_API void THNN_CudaSpatialFullConvolution_updateOutput(
+    THCState *s, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias, THCudaTensor *columns,
+    THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH, int adjW, int adjH)
+{
+    THNN_CudaSpatialFullDilatedConvolution_updateOutput(s, input, output, weight, bias, columns, ones, kW, kH, dW, dH, padW, padH, 1, 1,
+                                                        adjW, adjH);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialFullConvolution_updateGradInput(
+    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight,
+    THCudaTensor *gradColumns, int kW, int kH, int dW, int dH, int padW, int padH, int adjW, int adjH)
+{
+    THNN_CudaSpatialFullDilatedConvolution_updateGradInput(s, input, gradOutput, gradInput, weight, gradColumns, kW, kH, dW, dH, padW,
+                                                           padH, 1, 1, adjW, adjH);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialFullConvolution_accGradParameters(
+    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias,
+    THCudaTensor *columns, THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH, int adjW, int adjH, float scale)
+{
+    THNN_CudaSpatialFullDilatedConvolution_accGradParameters(s, input, gradOutput, gradWeight, gradBias, columns, ones, kW, kH, dW, dH,
+                                                             padW, padH, 1, 1, adjW, adjH, scale);
+}
+
 // ---- BatchNormalization --------------------------------------------------------------------------------
 // Any [N, C, ...] input is viewed as [N, C, S] (lib/THCUNN/generic/BatchNormalization.cu:8-32).
 static bool bn_dims(THCState *s, const THCudaTensor *t, long *N, long *C, long *S)

@@ -225,6 +225,46 @@ def dilated_conv_acc_grad(x, gy, grad_weight, grad_bias, dH, dW, padH, padW, dil
     return grad_weight, grad_bias
 
 
+def full_conv_out(size, k, d, pad, dil, adj):
+    return (size - 1) * d - 2 * pad + dil * (k - 1) + 1 + adj
+
+
+def full_conv_forward(x, weight, bias, dH, dW, padH, padW, dilH=1, dilW=1, adjH=0, adjW=0, out=None):
+    """SpatialFullDilatedConvolution (transposed convolution) forward; weight [P, Q, kH, kW], x [N, P, H, W]."""
+    _chk(x, weight, bias)
+    N, P, H, W = x.shape
+    _, Q, kH, kW = weight.shape
+    OH, OW = full_conv_out(H, kH, dH, padH, dilH, adjH), full_conv_out(W, kW, dW, padW, dilW, adjW)
+    if out is None:
+        out = torch.empty((N, Q, max(OH, 0), max(OW, 0)), dtype=torch.float32, device=x.device)
+    check(lib.cunn_b200_full_conv_forward(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), N, P, H, W, Q, kH, kW,
+                                          dH, dW, padH, padW, dilH, dilW, adjH, adjW, _stream()))
+    return out
+
+
+def full_conv_grad_input(gy, weight, H, W, dH, dW, padH, padW, dilH=1, dilW=1, adjH=0, adjW=0, out=None):
+    _chk(gy, weight)
+    P, Q, kH, kW = weight.shape
+    N = gy.shape[0]
+    if out is None:
+        out = torch.empty((N, P, H, W), dtype=torch.float32, device=gy.device)
+    check(lib.cunn_b200_full_conv_grad_input(_ptr(gy), _ptr(weight), _ptr(out), N, P, H, W, Q, kH, kW,
+                                             dH, dW, padH, padW, dilH, dilW, adjH, adjW, _stream()))
+    return out
+
+
+def full_conv_acc_grad(x, gy, grad_weight, grad_bias, dH, dW, padH, padW, dilH=1, dilW=1, adjH=0, adjW=0, scale=1.0):
+    """Accumulates into grad_weight [P,Q,kH,kW] and grad_bias [Q] (may be None) in place."""
+    _chk(x, gy, grad_weight, grad_bias)
+    N, P, H, W = x.shape
+    _, Q, kH, kW = grad_weight.shape
+    geo = (N, P, H, W, Q, kH, kW, dH, dW, padH, padW, dilH, dilW, adjH, adjW)
+    ws = workspace(lib.cunn_b200_full_conv_acc_grad_workspace(*geo), x.device)
+    check(lib.cunn_b200_full_conv_acc_grad(_ptr(x), _ptr(gy), _ptr(grad_weight), _ptr(grad_bias), *geo, scale,
+                                           _ptr(ws), ws.numel(), _stream()))
+    return grad_weight, grad_bias
+
+
 def threshold_forward(x, threshold=0.0, value=0.0, out=None):
     _chk(x, out)
     if out is None:

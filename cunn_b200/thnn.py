@@ -55,6 +55,12 @@ _SIGS = {
     "SpatialDilatedConvolution_updateOutput": [_T] * 6 + _CONV + [ctypes.c_int, ctypes.c_int],
     "SpatialDilatedConvolution_updateGradInput": [_T] * 5 + _CONV + [ctypes.c_int, ctypes.c_int],
     "SpatialDilatedConvolution_accGradParameters": [_T] * 6 + _CONV + [ctypes.c_int, ctypes.c_int, _F],
+    "SpatialFullDilatedConvolution_updateOutput": [_T] * 6 + _CONV + [_I] * 4,
+    "SpatialFullDilatedConvolution_updateGradInput": [_T] * 5 + _CONV + [_I] * 4,
+    "SpatialFullDilatedConvolution_accGradParameters": [_T] * 6 + _CONV + [_I] * 4 + [_F],
+    "SpatialFullConvolution_updateOutput": [_T] * 6 + _CONV + [_I] * 2,
+    "SpatialFullConvolution_updateGradInput": [_T] * 5 + _CONV + [_I] * 2,
+    "SpatialFullConvolution_accGradParameters": [_T] * 6 + _CONV + [_I] * 2 + [_F],
     "BatchNormalization_updateOutput": [_T] * 8 + [_B, _D, _D],
     "BatchNormalization_backward": [_T] * 10 + [_B, _D, _D],
     "SpatialMaxPooling_updateOutput": [_T] * 3 + _CONV + [_B],
@@ -227,6 +233,53 @@ class THNN:
                       dilW, dilH, scale)
         finally:
             self.free(hx, hg, hw, hb)
+
+    def SpatialFullDilatedConvolution_updateOutput(self, x, weight, bias, kW, kH, dW, dH, padW, padH, dilW, dilH, adjW, adjH):
+        b = x.dim() == 4
+        H, W = x.shape[b + 1], x.shape[b + 2]
+        OH = (H - 1) * dH - 2 * padH + dilH * (kH - 1) + 1 + adjH
+        OW = (W - 1) * dW - 2 * padW + dilW * (kW - 1) + 1 + adjW
+        cap = max(1, (x.shape[0] if b else 1) * weight.shape[1] * max(OH, 1) * max(OW, 1))
+        hx, hw, hb = self.wrap(x), self.wrap(weight), self.wrap(bias)
+        ho, buf = self.out(cap)
+        try:
+            self.call("SpatialFullDilatedConvolution_updateOutput", hx, ho, hw, hb, None, None, kW, kH, dW, dH, padW, padH,
+                      dilW, dilH, adjW, adjH)
+            return self.view(ho, buf)
+        finally:
+            self.free(hx, hw, hb, ho)
+
+    def SpatialFullDilatedConvolution_updateGradInput(self, x, gy, weight, kW, kH, dW, dH, padW, padH, dilW, dilH, adjW, adjH):
+        hx, hg, hw = self.wrap(x), self.wrap(gy), self.wrap(weight)
+        ho, buf = self.out(x.numel())
+        try:
+            self.call("SpatialFullDilatedConvolution_updateGradInput", hx, hg, ho, hw, None, kW, kH, dW, dH, padW, padH,
+                      dilW, dilH, adjW, adjH)
+            return self.view(ho, buf)
+        finally:
+            self.free(hx, hg, hw, ho)
+
+    def SpatialFullDilatedConvolution_accGradParameters(self, x, gy, gw, gb, kW, kH, dW, dH, padW, padH, dilW, dilH, adjW,
+                                                        adjH, scale):
+        hx, hg, hw, hb = self.wrap(x), self.wrap(gy), self.wrap(gw), self.wrap(gb)
+        try:
+            self.call("SpatialFullDilatedConvolution_accGradParameters", hx, hg, hw, hb, None, None, kW, kH, dW, dH, padW, padH,
+                      dilW, dilH, adjW, adjH, scale)
+        finally:
+            self.free(hx, hg, hw, hb)
+
+    def SpatialFullConvolution_updateOutput(self, x, weight, bias, kW, kH, dW, dH, padW, padH, adjW, adjH):
+        b = x.dim() == 4
+        OH = (x.shape[b + 1] - 1) * dH - 2 * padH + kH + adjH
+        OW = (x.shape[b + 2] - 1) * dW - 2 * padW + kW + adjW
+        cap = max(1, (x.shape[0] if b else 1) * weight.shape[1] * max(OH, 1) * max(OW, 1))
+        hx, hw, hb = self.wrap(x), self.wrap(weight), self.wrap(bias)
+        ho, buf = self.out(cap)
+        try:
+            self.call("SpatialFullConvolution_updateOutput", hx, ho, hw, hb, None, None, kW, kH, dW, dH, padW, padH, adjW, adjH)
+            return self.view(ho, buf)
+        finally:
+            self.free(hx, hw, hb, ho)
 
     def BatchNormalization_updateOutput(self, x, weight, bias, running_mean, running_var, train, momentum, eps):
         C = x.shape[1]

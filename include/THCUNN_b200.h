@@ -103,6 +103,30 @@ CUNN_API void THNN_CudaSpatialDilatedConvolution_accGradParameters(
     THCudaTensor *columns, THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH, int dilationW,
     int dilationH, float scale);
 
+/* lib/THCUNN/generic/THCUNN.h:766-806 (SpatialFullDilatedConvolution) and :849-886 (SpatialFullConvolution) */
+CUNN_API void THNN_CudaSpatialFullDilatedConvolution_updateOutput(
+    THCState *state, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias,
+    THCudaTensor *columns, THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH, int dilationW,
+    int dilationH, int adjW, int adjH);
+CUNN_API void THNN_CudaSpatialFullDilatedConvolution_updateGradInput(
+    THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight,
+    THCudaTensor *gradColumns, int kW, int kH, int dW, int dH, int padW, int padH, int dilationW, int dilationH,
+    int adjW, int adjH);
+CUNN_API void THNN_CudaSpatialFullDilatedConvolution_accGradParameters(
+    THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias,
+    THCudaTensor *columns, THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH, int dilationW,
+    int dilationH, int adjW, int adjH, float scale);
+CUNN_API void THNN_CudaSpatialFullConvolution_updateOutput(
+    THCState *state, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias,
+    THCudaTensor *columns, THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH, int adjW, int adjH);
+CUNN_API void THNN_CudaSpatialFullConvolution_updateGradInput(
+    THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight,
+    THCudaTensor *gradColumns, int kW, int kH, int dW, int dH, int padW, int padH, int adjW, int adjH);
+CUNN_API void THNN_CudaSpatialFullConvolution_accGradParameters(
+    THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias,
+    THCudaTensor *columns, THCudaTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH, int adjW, int adjH,
+    float scale);
+
 CUNN_API void THNN_CudaBatchNormalization_updateOutput(
     THCState *state, THCudaTensor *input_, THCudaTensor *output_, THCudaTensor *weight_, THCudaTensor *bias_,
     THCudaTensor *runningMean_, THCudaTensor *runningVar_, THCudaTensor *saveMean_, THCudaTensor *saveStd_,

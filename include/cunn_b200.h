@@ -142,6 +142,32 @@ CUNN_API int cunn_b200_dilated_conv_acc_grad(const float *x, const float *gy, fl
                                              int padH, int padW, int dilH, int dilW, float scale,
                                              void *workspace, size_t workspace_bytes, cunn_stream_t stream);
 
+/* ---- SpatialFullDilatedConvolution (transposed convolution) ----------------------
+ * x [N,P,H,W], weight [P,Q,kH,kW], bias [Q] or NULL -> y [N,Q,OH,OW] with
+ * OH = (H-1)*dH - 2*padH + dilH*(kH-1) + 1 + adjH (adjH < dH required here; the reference also admits
+ * adjH < dilH).  Runs on the kernels of the convolution it is the adjoint of: forward = that convolution's
+ * input gradient plus bias, input gradient = its forward, parameter gradient = its parameter gradient with
+ * activations and output gradient exchanged; dilation 1 is SpatialFullConvolution.  acc_grad accumulates
+ * (+= scale * g) and needs cunn_b200_full_conv_acc_grad_workspace(...) bytes of 16-byte aligned scratch.
+ * Replaces THNN_(SpatialFullDilatedConvolution_updateOutput / _updateGradInput / _accGradParameters)
+ * (lib/THCUNN/generic/SpatialFullDilatedConvolution.cu:68-209, 211-317, 319-461; decl generic/THCUNN.h:766-806)
+ * and THNN_(SpatialFullConvolution_*) (lib/THCUNN/generic/SpatialFullConvolution.cu). */
+CUNN_API int cunn_b200_full_conv_forward(const float *x, const float *weight, const float *bias, float *y,
+                                         int N, int P, int H, int W, int Q, int kH, int kW, int dH, int dW,
+                                         int padH, int padW, int dilH, int dilW, int adjH, int adjW,
+                                         cunn_stream_t stream);
+CUNN_API int cunn_b200_full_conv_grad_input(const float *gy, const float *weight, float *gx,
+                                            int N, int P, int H, int W, int Q, int kH, int kW, int dH, int dW,
+                                            int padH, int padW, int dilH, int dilW, int adjH, int adjW,
+                                            cunn_stream_t stream);
+CUNN_API size_t cunn_b200_full_conv_acc_grad_workspace(int N, int P, int H, int W, int Q, int kH, int kW,
+                                                       int dH, int dW, int padH, int padW, int dilH, int dilW,
+                                                       int adjH, int adjW);
+CUNN_API int cunn_b200_full_conv_acc_grad(const float *x, const float *gy, float *grad_weight, float *grad_bias,
+                                          int N, int P, int H, int W, int Q, int kH, int kW, int dH, int dW,
+                                          int padH, int padW, int dilH, int dilW, int adjH, int adjW, float scale,
+                                          void *workspace, size_t workspace_bytes, cunn_stream_t stream);
+
 /* ---- SpatialMaxPooling --------------------------------------------------------
  * x [N,C,H,W] -> y [N,C,oH,oW] and int64 indices of the same shape holding the flat position h*W + w of
  * the maximum inside its plane plus CUNN_B200_INDEX_BASE.  The window is scanned row-major with a strict

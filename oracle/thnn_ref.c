@@ -318,6 +318,116 @@ void FN(convmm_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
 }
 
 /* ------------------------------------------------------------------------ */
+/* Transposed ("full") dilated convolution: x [N,P,H,W], weight [P,Q,kH,kW],  */
+/* y [N,Q,OH,OW] with OH = (H-1)*dH - 2*padH + dilH*(kH-1) + 1 + adjH.         */
+/* ------------------------------------------------------------------------ */
+
+/* Forward: y_n = col2im(W^T * x_n) + bias
+ * (lib/THCUNN/generic/SpatialFullDilatedConvolution.cu:68-209; output size :51-52). */
+void FN(fullconv_forward)(const float *x, const float *w, const float *bias, float *y,
+                          int N, int P, int H, int W, int Q, int kH, int kW,
+                          int dH, int dW, int padH, int padW, int dilH, int dilW, int adjH, int adjW)
+{
+    const int OH = (H - 1) * dH - 2 * padH + dilH * (kH - 1) + 1 + adjH;
+    const int OW = (W - 1) * dW - 2 * padW + dilW * (kW - 1) + 1 + adjW;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int n = 0; n < N; ++n)
+        for (int q = 0; q < Q; ++q) {
+            float *yp = y + ((size_t)n * Q + q) * OH * OW;
+            for (int oh = 0; oh < OH; ++oh)
+                for (int ow = 0; ow < OW; ++ow) {
+                    acc_t s = bias ? (acc_t)bias[q] : (acc_t)0;
+                    for (int kh = 0; kh < kH; ++kh) {
+                        const int t = oh + padH - kh * dilH;
+                        if (t < 0 || t % dH || t / dH >= H) continue;
+                        for (int kw = 0; kw < kW; ++kw) {
+                            const int u = ow + padW - kw * dilW;
+                            if (u < 0 || u % dW || u / dW >= W) continue;
+                            for (int p = 0; p < P; ++p)
+                                s += (acc_t)w[((size_t)p * Q + q) * kH * kW + kh * kW + kw] *
+                                     (acc_t)x[(((size_t)n * P + p) * H + t / dH) * W + u / dW];
+                        }
+                    }
+                    yp[oh * OW + ow] = (float)s;
+                }
+        }
+}
+
+/* Input gradient: gx_n = W * im2col(gy_n)
+ * (lib/THCUNN/generic/SpatialFullDilatedConvolution.cu:211-317). */
+void FN(fullconv_grad_input)(const float *gy, const float *w, float *gx,
+                             int N, int P, int H, int W, int Q, int kH, int kW,
+                             int dH, int dW, int padH, int padW, int dilH, int dilW, int adjH, int adjW)
+{
+    const int OH = (H - 1) * dH - 2 * padH + dilH * (kH - 1) + 1 + adjH;
+    const int OW = (W - 1) * dW - 2 * padW + dilW * (kW - 1) + 1 + adjW;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int n = 0; n < N; ++n)
+        for (int p = 0; p < P; ++p)
+            for (int ih = 0; ih < H; ++ih)
+                for (int iw = 0; iw < W; ++iw) {
+                    acc_t s = 0;
+                    for (int q = 0; q < Q; ++q) {
+                        const float *gyp = gy + ((size_t)n * Q + q) * OH * OW;
+                        const float *wp = w + ((size_t)p * Q + q) * kH * kW;
+                        for (int kh = 0; kh < kH; ++kh) {
+                            const int oh = ih * dH - padH + kh * dilH;
+                            if (oh < 0 || oh >= OH) continue;
+                            for (int kw = 0; kw < kW; ++kw) {
+                                const int ow = iw * dW - padW + kw * dilW;
+                                if (ow < 0 || ow >= OW) continue;
+                                s += (acc_t)wp[kh * kW + kw] * (acc_t)gyp[oh * OW + ow];
+                            }
+                        }
+                    }
+                    gx[(((size_t)n * P + p) * H + ih) * W + iw] = (float)s;
+                }
+}
+
+/* Parameter gradients, accumulated: gW += scale * sum_n x_n * im2col(gy_n)^T, gb += scale * sum gy
+ * (lib/THCUNN/generic/SpatialFullDilatedConvolution.cu:319-461). */
+void FN(fullconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
+                           int N, int P, int H, int W, int Q, int kH, int kW,
+                           int dH, int dW, int padH, int padW, int dilH, int dilW, int adjH, int adjW, float scale)
+{
+    const int OH = (H - 1) * dH - 2 * padH + dilH * (kH - 1) + 1 + adjH;
+    const int OW = (W - 1) * dW - 2 * padW + dilW * (kW - 1) + 1 + adjW;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int p = 0; p < P; ++p)
+        for (int q = 0; q < Q; ++q)
+            for (int kh = 0; kh < kH; ++kh)
+                for (int kw = 0; kw < kW; ++kw) {
+                    acc_t s = 0;
+                    for (int n = 0; n < N; ++n) {
+                        const float *xp = x + ((size_t)n * P + p) * H * W;
+                        const float *gyp = gy + ((size_t)n * Q + q) * OH * OW;
+                        for (int ih = 0; ih < H; ++ih) {
+                            const int oh = ih * dH - padH + kh * dilH;
+                            if (oh < 0 || oh >= OH) continue;
+                            for (int iw = 0; iw < W; ++iw) {
+                                const int ow = iw * dW - padW + kw * dilW;
+                                if (ow < 0 || ow >= OW) continue;
+                                s += (acc_t)xp[ih * W + iw] * (acc_t)gyp[oh * OW + ow];
+                            }
+                        }
+                    }
+                    float *g = gw + ((size_t)p * Q + q) * kH * kW + kh * kW + kw;
+                    *g = (float)((acc_t)*g + (acc_t)scale * s);
+                }
+    if (gb) {
+#pragma omp parallel for schedule(static)
+        for (int q = 0; q < Q; ++q) {
+            acc_t s = 0;
+            for (int n = 0; n < N; ++n) {
+                const float *gyp = gy + ((size_t)n * Q + q) * OH * OW;
+                for (int i = 0; i < OH * OW; ++i) s += (acc_t)gyp[i];
+            }
+            gb[q] = (float)((acc_t)gb[q] + (acc_t)scale * s);
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------ */
 /* Batch normalisation over [N,C,S] (S = H*W).                               */
 /* ------------------------------------------------------------------------ */
 

@@ -137,6 +137,42 @@ class Ref:
                                      dilH, dilW, ctypes.c_float(scale))
         return gw, gb
 
+    # -- transposed convolution (SpatialFullDilatedConvolution; weight [P, Q, kH, kW]) -------------
+    @staticmethod
+    def fullconv_out_size(H, W, kH, kW, dH, dW, padH, padW, dilH, dilW, adjH, adjW):
+        return ((H - 1) * dH - 2 * padH + dilH * (kH - 1) + 1 + adjH,
+                (W - 1) * dW - 2 * padW + dilW * (kW - 1) + 1 + adjW)
+
+    def fullconv_forward(self, x, w, b, dH, dW, padH, padW, dilH=1, dilW=1, adjH=0, adjW=0):
+        x, w = _f(x), _f(w)
+        b = None if b is None else _f(b)
+        N, P, H, W = x.shape
+        _, Q, kH, kW = w.shape
+        OH, OW = self.fullconv_out_size(H, W, kH, kW, dH, dW, padH, padW, dilH, dilW, adjH, adjW)
+        y = np.empty((N, Q, OH, OW), np.float32)
+        self._fn("fullconv_forward")(_p(x), _p(w), _p(b), _p(y), N, P, H, W, Q, kH, kW, dH, dW, padH, padW,
+                                     dilH, dilW, adjH, adjW)
+        return y
+
+    def fullconv_grad_input(self, gy, w, H, W, dH, dW, padH, padW, dilH=1, dilW=1, adjH=0, adjW=0):
+        gy, w = _f(gy), _f(w)
+        P, Q, kH, kW = w.shape
+        N = gy.shape[0]
+        gx = np.empty((N, P, H, W), np.float32)
+        self._fn("fullconv_grad_input")(_p(gy), _p(w), _p(gx), N, P, H, W, Q, kH, kW, dH, dW, padH, padW,
+                                        dilH, dilW, adjH, adjW)
+        return gx
+
+    def fullconv_acc_grad(self, x, gy, gw, gb, dH, dW, padH, padW, dilH=1, dilW=1, adjH=0, adjW=0, scale=1.0):
+        x, gy = _f(x), _f(gy)
+        gw = _f(gw).copy()
+        gb = None if gb is None else _f(gb).copy()
+        N, P, H, W = x.shape
+        _, Q, kH, kW = gw.shape
+        self._fn("fullconv_acc_grad")(_p(x), _p(gy), _p(gw), _p(gb), N, P, H, W, Q, kH, kW, dH, dW, padH, padW,
+                                      dilH, dilW, adjH, adjW, ctypes.c_float(scale))
+        return gw, gb
+
     # -- batch norm --------------------------------------------------------------
     def bn_forward(self, x, weight, bias, running_mean, running_var, train, momentum, eps):
         """Returns y, running_mean', running_var', save_mean, save_std."""

@@ -106,6 +106,25 @@ def dilconv_case(name, rng, N, C, H, W, K, k, d, pad, dil, bias=True, scale=1.0)
     save(name, **arrs)
 
 
+def fullconv_case(name, rng, N, P, H, W, Q, k, d, pad, dil, adj, bias=True, scale=1.0):
+    """SpatialFullDilatedConvolution: torch.nn.functional.conv_transpose2d, forward and gradients."""
+    x = rng.standard_normal((N, P, H, W)).astype(np.float32)
+    w = (rng.standard_normal((P, Q, k, k)) * np.sqrt(2.0 / (P * k * k))).astype(np.float32)
+    b = rng.uniform(-0.5, 0.5, Q).astype(np.float32) if bias else None
+    xt, wt = t(x, True), t(w, True)
+    bt = t(b, True) if bias else None
+    y = F.conv_transpose2d(xt, wt, bt, stride=d, padding=pad, output_padding=adj, dilation=dil)
+    gy = rng.standard_normal(tuple(y.shape)).astype(np.float32)
+    gw0 = rng.standard_normal((P, Q, k, k)).astype(np.float32)
+    gb0 = rng.standard_normal(Q).astype(np.float32)
+    y.backward(t(gy))
+    arrs = dict(x=x, w=w, gy=gy, y=y, gx=xt.grad, gw0=gw0, gb0=gb0, gw=t(gw0) + scale * wt.grad,
+                params=np.array([Q, k, d, pad, dil, adj, int(bias)]), scale=np.float32(scale))
+    if bias:
+        arrs.update(b=b, gb=t(gb0) + scale * bt.grad)
+    save(name, **arrs)
+
+
 def bn_case(name, rng, N, C, H, W, affine=True, momentum=0.1, eps=1e-5, scale=1.0):
     x = (0.5 + 2.0 * rng.standard_normal((N, C, H, W))).astype(np.float32)
     g = rng.uniform(0, 1, C).astype(np.float32) if affine else None
@@ -191,6 +210,7 @@ def main():
     maxpool_case("maxpool_2s2", rng, 1, 4, 9, 9, 2, 2, 0, True)
     support_case("support", rng)
     dilated_cases()
+    fullconv_cases()
 
 
 def dilated_cases():
@@ -200,9 +220,19 @@ def dilated_cases():
     dilconv_case("dilconv_3x3_d3_s2", rng, 2, 4, 15, 13, 6, 3, 2, 3, 3, bias=False)
 
 
+def fullconv_cases():
+    # own generator, for the same reason
+    rng = np.random.default_rng(20241)
+    fullconv_case("fullconv_3x3_s2", rng, 2, 6, 7, 6, 5, 3, 2, 1, 1, 1, scale=0.5)
+    fullconv_case("fullconv_4x4_s2", rng, 2, 4, 5, 6, 8, 4, 2, 1, 1, 0, bias=False)
+    fullconv_case("fullconv_3x3_d2", rng, 1, 3, 8, 9, 4, 3, 1, 2, 2, 0)
+
+
 if __name__ == "__main__":
     import sys
     if len(sys.argv) > 1 and sys.argv[1] == "dilated":
         dilated_cases()                      # only the dilated-convolution fixtures
+    elif len(sys.argv) > 1 and sys.argv[1] == "full":
+        fullconv_cases()                     # only the transposed-convolution fixtures
     else:
         main()

@@ -186,3 +186,19 @@ def test_dilated_conv_oracle_vs_golden(ref64, name):
     assert rel_err(gw, g["gw"]) < 1e-6
     if has_b:
         assert rel_err(gb, g["gb"]) < 1e-6
+
+
+@pytest.mark.parametrize("name", ["fullconv_3x3_s2", "fullconv_4x4_s2", "fullconv_3x3_d2"])
+def test_full_conv_oracle_vs_golden(ref64, name):
+    # SpatialFullDilatedConvolution restatement against PyTorch-CPU conv_transpose2d fixtures
+    g = golden(name)
+    Q, k, d, pad, dil, adj, has_b = [int(v) for v in g["params"]]
+    H, W = g["x"].shape[2:]
+    b = g["b"] if has_b else None
+    geo = (d, d, pad, pad, dil, dil, adj, adj)
+    assert rel_err(ref64.fullconv_forward(g["x"], g["w"], b, *geo), g["y"]) < 1e-6
+    assert rel_err(ref64.fullconv_grad_input(g["gy"], g["w"], H, W, *geo), g["gx"]) < 1e-6
+    gw, gb = ref64.fullconv_acc_grad(g["x"], g["gy"], g["gw0"], g["gb0"] if has_b else None, *geo, float(g["scale"]))
+    assert rel_err(gw, g["gw"]) < 1e-6
+    if has_b:
+        assert rel_err(gb, g["gb"]) < 1e-6
