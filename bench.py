@@ -202,8 +202,8 @@ def workload_config(n, world):
                                          "tensor is re-read only after >= 1.2 GB of other traffic",
             "parallelism": "dp%d (batch-sharded, NCCL all-reduce of depthwise weight gradients)" % world
                            if world > 1 else "single GPU",
-            "launch": "39 kernels per step replayed from CUDA graphs; with N > 1 the weight-gradient all-reduce "
-                      "overlaps the input-gradient kernels"}
+            "launch": "39 kernels per step replayed from CUDA graphs, consecutive (independent) layers on alternating "
+                      "streams; with N > 1 the weight-gradient all-reduce overlaps the input-gradient kernels"}
 
 
 def other_configs_bench(dev):
@@ -370,6 +370,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--graph-streams", type=int, default=2,
+                    help="streams the launches of the depthwise stack alternate between inside the CUDA graph")
     ap.add_argument("--no-mobilenet", action="store_true")
     ap.add_argument("--no-others", action="store_true", help="skip the config 3 / config 4 single-kernel timings")
     ap.add_argument("--mobilenet-batch", type=int, default=1024, help="global batch of the MobileNetV1 step")
@@ -436,15 +438,34 @@ def main():
     torch.cuda.set_stream(stream)
     kernels()                       # first call: workspace allocation, function attributes
     torch.cuda.synchronize()
+    # The layers of the stack are independent of each other, so inside a graph consecutive launches alternate
+    # between the capture stream and side streams: the ramp-up of one kernel overlaps the tail of the one before.
+    # Every stream has its own scratch buffer (cunn_b200.functional.workspace), allocated here, outside the capture.
+    side = [torch.cuda.Stream(device=dev) for _ in range(max(args.graph_streams, 1) - 1)]
+    for s2 in side:
+        with torch.cuda.stream(s2):
+            kernels()
+    torch.cuda.synchronize()
     # One CUDA graph per step on one GPU.  With several ranks the step is two graphs: forwards and
     # parameter gradients first, then the input gradients, so that the NCCL all-reduce of the flat
     # weight-gradient buffer (issued between them, on NCCL's own stream) overlaps the input-gradient kernels;
     # the step ends when both have finished.
-    def part(names):
+    def part(names, streams=()):
+        for s2 in streams:
+            s2.wait_stream(stream)
+        i = 0
         for name, op in OPS:
             if name in names:
                 for t in T:
-                    op(t)
+                    k = i % (len(streams) + 1)
+                    i += 1
+                    if k == 0:
+                        op(t)
+                    else:
+                        with torch.cuda.stream(streams[k - 1]):
+                            op(t)
+        for s2 in streams:
+            stream.wait_stream(s2)
 
     graphs = None
     if world > 1:
@@ -456,7 +477,7 @@ def main():
         for names in parts:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream):
-                part(names)
+                part(names, side)
             graphs.append(g)
 
     def step():
@@ -503,6 +524,46 @@ def main():
     ms_per_step = ms / steps
     value = step_bytes(BATCH) * world / (ms_per_step * 1e-3) / 1e9
 
+    # ---- the graphs compute what direct launches on one stream compute ------------------------------
+    verified = None
+    single_stream = None
+    if graphs:
+        flat_grad.zero_()
+        step()
+        torch.cuda.synchronize()
+        got = [(t["y"].clone(), t["gx"].clone()) for t in T]
+        got_grad = flat_grad.clone()
+        for t in T:
+            t["y"].zero_()
+            t["gx"].zero_()
+        flat_grad.zero_()
+        kernels()
+        torch.cuda.synchronize()
+        bad = [i + 1 for i, ((y, gx), t) in enumerate(zip(got, T)) if not (torch.equal(y, t["y"]) and torch.equal(gx, t["gx"]))]
+        # parameter gradients are summed with atomics in some layers: compare against the largest gradient
+        gerr = float((got_grad - flat_grad).abs().max() / flat_grad.abs().max()) if world == 1 else 0.0
+        verified = not bad and gerr < 1e-5   # with several ranks the graph step also sums the gradients over the ranks
+        del got, got_grad
+        if not verified:
+            raise SystemExit("bench: the graph replay and direct launches disagree (layers %s, gradient error %.3g)" % (bad, gerr))
+        if side and world == 1:
+            # the same step with every launch on one stream, for comparison
+            g1 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g1, stream=stream):
+                part(("fwd", "dgrad", "wgrad"))
+            for _ in range(warmup):
+                g1.replay()
+            torch.cuda.synchronize()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for _ in range(steps):
+                g1.replay()
+            s1.record()
+            torch.cuda.synchronize()
+            sms = s0.elapsed_time(s1) / steps
+            single_stream = {"ms_per_step": round(sms, 4), "value": round(step_bytes(BATCH) / (sms * 1e-3) / 1e9, 1),
+                             "unit": "GB/s"}
+
     # ---- per-kernel durations (CUDA events around every launch, same stream) ------------------------
     ksteps = min(steps, 10)
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(launches_per_step + 1)] for _ in range(ksteps)]
@@ -537,7 +598,9 @@ def main():
                 "step": {"achieved": round(step_bytes(BATCH) / (ms_per_step * 1e-3) / 1e9 if world == 1 else
                                            value / world, 1),
                          "frac": round((value / world) / peak, 4),
-                         "note": "all 39 launches: algorithmic bytes / graph-replay time per step"},
+                         "note": "all 39 launches: algorithmic bytes / graph-replay time per step; consecutive launches "
+                                 "alternate between %d streams inside the graph" % (len(side) + 1),
+                         "single_stream": single_stream, "matches_direct_launches": verified},
                 "per_kernel": [dict(op=k["op"], layer=k["layer"], us=round(k["ms"] * 1e3, 2),
                                     gbs=round(k["bytes"] / (k["ms"] * 1e-3) / 1e9, 0)) for k in per]}
 
