@@ -144,6 +144,91 @@ __device__ __forceinline__ void finish_stats_channel_warp(const ChunkStat *part,
     running_var[c] = (float)((1.0 - momentum) * (double)running_var[c] + momentum * (double)unbiased);
 }
 
+// Walks the planes [n0, n1) of channel c as one flat sequence of items of type T (float4 or float), blockDim.x items
+// apart per thread, and fetches them U at a time so that every thread keeps U loads in flight.  `mask` has bit u set
+// for every slot that was filled; items arrive in walk order, so sums taken slot by slot do not depend on U.
+template <typename T, int U>
+struct PlaneWalk {
+    const float *x;
+    int C, S, c, n1, L, qstep, rstep, n, i;
+    __device__ __forceinline__ void init(const float *x_, int C_, int S_, int c_, int n0, int n1_)
+    {
+        x = x_; C = C_; S = S_; c = c_; n1 = n1_;
+        L = S / (int)(sizeof(T) / sizeof(float));
+        qstep = (int)blockDim.x / L; rstep = (int)blockDim.x % L;
+        n = n0 + (int)threadIdx.x / L; i = (int)threadIdx.x % L;
+    }
+    // the same walk over a second tensor of the same shape
+    template <bool TWO>
+    __device__ __forceinline__ unsigned load(T (&v)[U], T (&w)[U], const float *y)
+    {
+        unsigned mask = 0;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (n < n1) {
+                const size_t off = ((size_t)n * C + c) * S;
+                v[u] = __ldg(reinterpret_cast<const T *>(x + off) + i);
+                if (TWO) w[u] = __ldg(reinterpret_cast<const T *>(y + off) + i);
+                mask |= 1u << u;
+                n += qstep; i += rstep;
+                if (i >= L) { i -= L; ++n; }
+            }
+        }
+        return mask;
+    }
+};
+
+// Shifted sums of one chunk: s1 = sum (x - k), s2 = sum (x - k)^2.  The shift k is the mean of the chunk's first (up to)
+// 32 elements: close to the channel mean, so the sums of (x - k) stay small and keep their fp32 accuracy even when a
+// single element is an outlier.  The first batch of loads is issued before the probe for k, so its latency is hidden.
+template <typename T, int U>
+__device__ __forceinline__ void chunk_sums(const float *x, int C, int S, int c, int n0, int n1, float *k_s, float *s1_out,
+                                           float *s2_out, float *k_out)
+{
+    PlaneWalk<T, U> w;
+    w.init(x, C, S, c, n0, n1);
+    T a[U], b[U];
+    unsigned ma = w.template load<false>(a, a, nullptr), mb = 0;
+    if (threadIdx.x < 32) {
+        const long long cnt = (long long)(n1 - n0) * S;
+        const int m = cnt < 32 ? (int)cnt : 32;
+        float v = 0.f;
+        if ((int)threadIdx.x < m) {
+            const int e = (int)threadIdx.x, pn = n0 + e / S;
+            v = __ldg(x + ((size_t)pn * C + c) * S + (e - (e / S) * S));
+        }
+        v = warp_sum(v);
+        if (threadIdx.x == 0) *k_s = v / (float)m;
+    }
+    __syncthreads();
+    const float k = *k_s;
+    float s1 = 0.f, s2 = 0.f;
+    auto acc1 = [&](float v) { const float t = v - k; s1 += t; s2 = fmaf(t, t, s2); };
+    auto acc = [&](const T (&v)[U], unsigned m) {
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (m >> u & 1u) {
+                if constexpr (sizeof(T) == 16) {
+                    const float4 q = *reinterpret_cast<const float4 *>(&v[u]);
+                    const float e = q.x - k, f = q.y - k, g = q.z - k, h = q.w - k;
+                    s1 += (e + f) + (g + h);
+                    s2 = fmaf(e, e, s2); s2 = fmaf(f, f, s2); s2 = fmaf(g, g, s2); s2 = fmaf(h, h, s2);
+                } else {
+                    acc1(*reinterpret_cast<const float *>(&v[u]));
+                }
+            }
+    };
+    for (;;) {
+        if (!ma) break;
+        mb = w.template load<false>(b, b, nullptr);
+        acc(a, ma);
+        if (!mb) break;
+        ma = w.template load<false>(a, a, nullptr);
+        acc(b, mb);
+    }
+    *s1_out = s1; *s2_out = s2; *k_out = k;
+}
+
 // grid = C * chunks.  One partial statistic per CTA; with `counters` the last CTA of a channel also merges the
 // partials (no second launch).
 __global__ void __launch_bounds__(256)
@@ -159,45 +244,9 @@ stats_kernel(const float *__restrict__ x, ChunkStat *__restrict__ part, int N, i
     __shared__ float k_s;
     float k = 0.f, s1 = 0.f, s2 = 0.f;
     if (n0 < n1) {
-        // shift K = mean of the chunk's first (up to) 32 elements: close to the channel mean, so the sums of
-        // (x - K) stay small and keep their fp32 accuracy even when a single element is an outlier
-        if (threadIdx.x < 32) {
-            const long long cnt = (long long)(n1 - n0) * S;
-            const int m = cnt < 32 ? (int)cnt : 32;
-            float v = 0.f;
-            if ((int)threadIdx.x < m) {
-                const int e = (int)threadIdx.x, pn = n0 + e / S;
-                v = __ldg(x + ((size_t)pn * C + c) * S + (e - (e / S) * S));
-            }
-            v = warp_sum(v);
-            if (threadIdx.x == 0) k_s = v / (float)m;
-        }
-        __syncthreads();
-        k = k_s;
         const bool vec = (S % 4 == 0) && (((uintptr_t)x & 15) == 0);
-        // The chunk's planes are walked as one flat sequence of 16-byte (or 4-byte) items, so that every lane has
-        // work whatever the plane size; (n, i) = image and item inside its plane, advanced without divisions.
-        const int L = vec ? S / 4 : S;
-        const int qstep = (int)blockDim.x / L, rstep = (int)blockDim.x % L;
-        int n = n0 + (int)threadIdx.x / L, i = (int)threadIdx.x % L;
-        if (vec) {
-            while (n < n1) {
-                const float4 v = __ldg(reinterpret_cast<const float4 *>(x + ((size_t)n * C + c) * S) + i);
-                const float a = v.x - k, b = v.y - k, d = v.z - k, e = v.w - k;
-                s1 += (a + b) + (d + e);
-                s2 = fmaf(a, a, s2); s2 = fmaf(b, b, s2); s2 = fmaf(d, d, s2); s2 = fmaf(e, e, s2);
-                n += qstep; i += rstep;
-                if (i >= L) { i -= L; ++n; }
-            }
-        } else {
-            while (n < n1) {
-                const float a = __ldg(x + ((size_t)n * C + c) * S + i) - k;
-                s1 += a;
-                s2 = fmaf(a, a, s2);
-                n += qstep; i += rstep;
-                if (i >= L) { i -= L; ++n; }
-            }
-        }
+        if (vec) chunk_sums<float4, 4>(x, C, S, c, n0, n1, &k_s, &s1, &s2, &k);
+        else chunk_sums<float, 8>(x, C, S, c, n0, n1, &k_s, &s1, &s2, &k);
         s1 = block_sum(s1, sh);
         s2 = block_sum(s2, sh);
     }
@@ -339,36 +388,58 @@ grad_stats_kernel(const float *__restrict__ x, const float *__restrict__ gy, flo
     }
     float s = 0.f, d = 0.f;
     const bool vec = (S % 4 == 0) && ((((uintptr_t)x | (uintptr_t)gy) & 15) == 0);
-    const int L = vec ? S / 4 : S;
-    const int qstep = (int)blockDim.x / L, rstep = (int)blockDim.x % L;
-    int n = n0 + (int)threadIdx.x / L, i = (int)threadIdx.x % L;
+    auto one = [&](float v, float g) {
+        if (RELU) g = bn_value(v, mean, invstd, gam, bet) > 0.f ? g : 0.f;
+        return g;
+    };
     if (vec) {
-        while (n < n1) {
-            const size_t off = ((size_t)n * C + c) * S;
-            const float4 v = __ldg(reinterpret_cast<const float4 *>(x + off) + i);
-            float4 g = __ldg(reinterpret_cast<const float4 *>(gy + off) + i);
-            if (RELU) {
-                g.x = bn_value(v.x, mean, invstd, gam, bet) > 0.f ? g.x : 0.f;
-                g.y = bn_value(v.y, mean, invstd, gam, bet) > 0.f ? g.y : 0.f;
-                g.z = bn_value(v.z, mean, invstd, gam, bet) > 0.f ? g.z : 0.f;
-                g.w = bn_value(v.w, mean, invstd, gam, bet) > 0.f ? g.w : 0.f;
-            }
-            s += (g.x + g.y) + (g.z + g.w);
-            d = fmaf(g.x, v.x - mean, d); d = fmaf(g.y, v.y - mean, d);
-            d = fmaf(g.z, v.z - mean, d); d = fmaf(g.w, v.w - mean, d);
-            n += qstep; i += rstep;
-            if (i >= L) { i -= L; ++n; }
+        constexpr int U = 2;
+        PlaneWalk<float4, U> w;
+        w.init(x, C, S, c, n0, n1);
+        float4 xa[U], ga[U], xb[U], gb[U];
+        auto acc = [&](const float4 (&xv)[U], const float4 (&gv)[U], unsigned m) {
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (m >> u & 1u) {
+                    const float4 v = xv[u];
+                    float4 g = gv[u];
+                    g.x = one(v.x, g.x); g.y = one(v.y, g.y); g.z = one(v.z, g.z); g.w = one(v.w, g.w);
+                    s += (g.x + g.y) + (g.z + g.w);
+                    d = fmaf(g.x, v.x - mean, d); d = fmaf(g.y, v.y - mean, d);
+                    d = fmaf(g.z, v.z - mean, d); d = fmaf(g.w, v.w - mean, d);
+                }
+        };
+        unsigned ma = w.load<true>(xa, ga, gy), mb = 0;
+        for (;;) {
+            if (!ma) break;
+            mb = w.load<true>(xb, gb, gy);
+            acc(xa, ga, ma);
+            if (!mb) break;
+            ma = w.load<true>(xa, ga, gy);
+            acc(xb, gb, mb);
         }
     } else {
-        while (n < n1) {
-            const size_t off = ((size_t)n * C + c) * S + i;
-            float g = __ldg(gy + off);
-            const float v = __ldg(x + off);
-            if (RELU) g = bn_value(v, mean, invstd, gam, bet) > 0.f ? g : 0.f;
-            s += g;
-            d = fmaf(g, v - mean, d);
-            n += qstep; i += rstep;
-            if (i >= L) { i -= L; ++n; }
+        constexpr int U = 4;
+        PlaneWalk<float, U> w;
+        w.init(x, C, S, c, n0, n1);
+        float xa[U], ga[U], xb[U], gb[U];
+        auto acc = [&](const float (&xv)[U], const float (&gv)[U], unsigned m) {
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (m >> u & 1u) {
+                    const float g = one(xv[u], gv[u]);
+                    s += g;
+                    d = fmaf(g, xv[u] - mean, d);
+                }
+        };
+        unsigned ma = w.load<true>(xa, ga, gy), mb = 0;
+        for (;;) {
+            if (!ma) break;
+            mb = w.load<true>(xb, gb, gy);
+            acc(xa, ga, ma);
+            if (!mb) break;
+            ma = w.load<true>(xa, ga, gy);
+            acc(xb, gb, mb);
         }
     }
     s = block_sum(s, sh);
