@@ -315,6 +315,58 @@ apply_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__
     }
 }
 
+// Planes whose size is not a multiple of 4 (7x7 = 49 elements): the tensor is walked as one flat array of 16-byte
+// items, four per thread and iteration; an item may straddle planes, so the channel is tracked element by element.
+template <bool RELU>
+__global__ void __launch_bounds__(256)
+apply_flat_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__restrict__ weight,
+                  const float *__restrict__ bias, const float *__restrict__ mean_v, const float *__restrict__ std_or_var,
+                  int train, float eps, unsigned C, unsigned S, unsigned total)
+{
+    auto act = [](float v) { return RELU ? (v > 0.f ? v : 0.f) : v; };
+    float mean = 0.f, invstd = 0.f, g = 1.f, b = 0.f;
+    auto fetch = [&](unsigned c) {
+        mean = __ldg(mean_v + c);
+        invstd = train ? __ldg(std_or_var + c) : 1.f / sqrtf(__ldg(std_or_var + c) + eps);
+        g = weight ? __ldg(weight + c) : 1.f;
+        b = bias ? __ldg(bias + c) : 0.f;
+    };
+    auto item = [&](unsigned q, const float4 v) {
+        const unsigned e = q * 4u, pl = e / S;
+        unsigned r = e - pl * S, c = pl % C;
+        fetch(c);
+        const float in[4] = {v.x, v.y, v.z, v.w};
+        float out[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            out[j] = act(bn_value(in[j], mean, invstd, g, b));
+            if (j < 3 && ++r == S) {
+                r = 0;
+                if (++c == C) c = 0;
+                fetch(c);
+            }
+        }
+        reinterpret_cast<float4 *>(y)[q] = make_float4(out[0], out[1], out[2], out[3]);
+    };
+    const unsigned items = total / 4u, stride = gridDim.x * blockDim.x, tid = blockIdx.x * blockDim.x + threadIdx.x;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x);
+    constexpr unsigned U = 4;
+    for (unsigned q = tid; q < items; q += U * stride) {
+        float4 v[U];
+#pragma unroll
+        for (unsigned u = 0; u < U; ++u)
+            if (q + u * stride < items) v[u] = __ldg(x4 + q + u * stride);
+#pragma unroll
+        for (unsigned u = 0; u < U; ++u)
+            if (q + u * stride < items) item(q + u * stride, v[u]);
+    }
+    if (tid < total - items * 4u) {
+        const unsigned e = items * 4u + tid;
+        fetch((e / S) % C);
+        y[e] = act(bn_value(__ldg(x + e), mean, invstd, g, b));
+    }
+}
+
 // Per-channel coefficients of the input gradient:
 //   gx = (gy - (x - mean) * proj - gmean) * gscale      (training)
 //   gx = gy * gscale                                     (inference)
@@ -506,6 +558,66 @@ grad_apply_kernel(const float *__restrict__ x, const float *__restrict__ gy, flo
     }
 }
 
+// The flat walk of apply_flat_kernel for the input gradient.
+template <bool RELU>
+__global__ void __launch_bounds__(256)
+grad_apply_flat_kernel(const float *__restrict__ x, const float *__restrict__ gy, float *__restrict__ gx,
+                       const GradCoef *__restrict__ coef, int train, unsigned C, unsigned S, unsigned total)
+{
+    GradCoef k;
+    auto fetch = [&](unsigned c) {
+        const float4 *p = reinterpret_cast<const float4 *>(coef + c);
+        const float4 a = __ldg(p), b = __ldg(p + 1);
+        k.mean = a.x; k.proj = a.y; k.gmean = a.z; k.gscale = a.w;
+        k.invstd = b.x; k.gamma = b.y; k.beta = b.z; k.pad = b.w;
+    };
+    auto one = [&](float v, float g) {
+        if (RELU) g = bn_value(v, k.mean, k.invstd, k.gamma, k.beta) > 0.f ? g : 0.f;
+        return train ? (g - (v - k.mean) * k.proj - k.gmean) * k.gscale : g * k.gscale;
+    };
+    auto item = [&](unsigned q, const float4 v, const float4 g) {
+        const unsigned e = q * 4u, pl = e / S;
+        unsigned r = e - pl * S, c = pl % C;
+        fetch(c);
+        const float vin[4] = {v.x, v.y, v.z, v.w}, gin[4] = {g.x, g.y, g.z, g.w};
+        float out[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            out[j] = one(vin[j], gin[j]);
+            if (j < 3 && ++r == S) {
+                r = 0;
+                if (++c == C) c = 0;
+                fetch(c);
+            }
+        }
+        reinterpret_cast<float4 *>(gx)[q] = make_float4(out[0], out[1], out[2], out[3]);
+    };
+    const unsigned items = total / 4u, stride = gridDim.x * blockDim.x, tid = blockIdx.x * blockDim.x + threadIdx.x;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x), *g4 = reinterpret_cast<const float4 *>(gy);
+    const bool need_x = RELU || train;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    constexpr unsigned U = 4;
+    for (unsigned q = tid; q < items; q += U * stride) {
+        float4 v[U], g[U];
+#pragma unroll
+        for (unsigned u = 0; u < U; ++u) {
+            v[u] = zero;
+            if (q + u * stride < items) {
+                g[u] = __ldg(g4 + q + u * stride);
+                if (need_x) v[u] = __ldg(x4 + q + u * stride);
+            }
+        }
+#pragma unroll
+        for (unsigned u = 0; u < U; ++u)
+            if (q + u * stride < items) item(q + u * stride, v[u], g[u]);
+    }
+    if (tid < total - items * 4u) {
+        const unsigned e = items * 4u + tid;
+        fetch((e / S) % C);
+        gx[e] = one(need_x ? __ldg(x + e) : 0.f, __ldg(gy + e));
+    }
+}
+
 // Ticket counters at the start of the workspace: one per channel for the forward statistics, one for the gradient
 // sums.  Zero when a call is enqueued, zero again when its kernels have run.
 constexpr int kMaxCounterChannels = 4096;
@@ -527,10 +639,25 @@ static int plane_grid(long long planes, int S)
     return (int)std::max(1LL, std::min((planes + per_cta - 1) / per_cta, cap));
 }
 
+// Planes that are not a multiple of 16 bytes take the flat kernels (32-bit element indices, 16-byte aligned tensors).
+static bool flat_applies(int S, long long planes, const void *a, const void *b, const void *c)
+{
+    return S % 4 != 0 && planes * S >= 4 && planes * S < (1LL << 32) && ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0);
+}
+static int flat_grid(unsigned total)
+{
+    return (int)std::max(1LL, std::min(ceil_div_ll((long long)(total / 4u), 1024), (long long)sm_count() * 8));
+}
+
 template <bool RELU>
 static void launch_apply(const float *x, float *y, const float *weight, const float *bias, const float *mean_v,
                          const float *std_or_var, int train, float eps, int C, int S, long long planes, cudaStream_t stream)
 {
+    if (flat_applies(S, planes, x, y, y)) {
+        const unsigned total = (unsigned)(planes * S);
+        apply_flat_kernel<RELU><<<flat_grid(total), 256, 0, stream>>>(x, y, weight, bias, mean_v, std_or_var, train, eps, (unsigned)C, (unsigned)S, total);
+        return;
+    }
     if (small_planes(S)) apply_kernel<RELU, 32><<<plane_grid(planes, S), 256, 0, stream>>>(x, y, weight, bias, mean_v, std_or_var, train, eps, C, S, planes);
     else apply_kernel<RELU, 256><<<plane_grid(planes, S), 256, 0, stream>>>(x, y, weight, bias, mean_v, std_or_var, train, eps, C, S, planes);
 }
@@ -538,6 +665,11 @@ template <bool RELU>
 static void launch_grad_apply(const float *x, const float *gy, float *gx, const GradCoef *coef, int train, int C, int S,
                               long long planes, cudaStream_t stream)
 {
+    if (flat_applies(S, planes, x, gy, gx)) {
+        const unsigned total = (unsigned)(planes * S);
+        grad_apply_flat_kernel<RELU><<<flat_grid(total), 256, 0, stream>>>(x, gy, gx, coef, train, (unsigned)C, (unsigned)S, total);
+        return;
+    }
     if (small_planes(S)) grad_apply_kernel<RELU, 32><<<plane_grid(planes, S), 256, 0, stream>>>(x, gy, gx, coef, train, C, S, planes);
     else grad_apply_kernel<RELU, 256><<<plane_grid(planes, S), 256, 0, stream>>>(x, gy, gx, coef, train, C, S, planes);
 }
