@@ -128,3 +128,38 @@ def test_mobilenet_layout_matches_reference_parameter_count():
     lay = mb.layout(cfg)
     assert len(lay) == 28 and lay[-1]["kind"] == mb.KIND_FC and lay[-1]["hin"] == 7
     assert [L["stride"] for L in lay if L["kind"] == mb.KIND_DW] == [1, 2, 1, 2, 1, 2, 1, 1, 1, 1, 1, 2, 1]
+
+
+def test_graph_replay_equals_direct_launches():
+    # DataParallelStep(use_graph=True): the first two uses of a buffer pair launch directly (the second also
+    # captures), the third replays the graph.  With learning rate 0 every step sees the same parameters, so the
+    # replayed step must reproduce the loss exactly (the forward pass is deterministic) and the gradients up to the
+    # summation order of the layers that add with atomics.
+    from cunn_b200 import mobilenet as mb, device_status
+    cfg = mb.Config(64, 8, 10)
+    params = mb.init_params(cfg, seed=11)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    B = 6
+    images = torch.randn((B, 3, 64, 64), device="cuda", generator=g)
+    labels = torch.randint(1, 11, (B,), device="cuda", dtype=torch.int64, generator=g)
+    rep = mb.MobileNetV1(cfg, torch.device("cuda"), params, max_batch=B)
+    step = mb.DataParallelStep(rep, None, use_graph=True)
+    losses, grads, bn = [], [], []
+    for _ in range(4):
+        losses.append(float(step.train_step(images, labels, B, 0.0)))
+        grads.append(rep.grads.clone())
+        bn.append(rep.bn_running.clone())
+    torch.cuda.synchronize()
+    assert device_status() == 0
+    assert len(step._graphs) == 1
+    assert losses[2] == losses[0] and losses[3] == losses[0]
+    scale = float(grads[0].abs().max())
+    assert float((grads[2] - grads[0]).abs().max()) < 1e-5 * scale
+    assert float((grads[3] - grads[0]).abs().max()) < 1e-5 * scale
+    # the running statistics keep moving towards the batch statistics: step 3 continues from step 2
+    assert not torch.equal(bn[2], bn[1]) and float((bn[3] - bn[2]).abs().max()) < float((bn[1] - bn[0]).abs().max()) * 1.0001
+    # and with a learning rate the replayed steps train the network
+    first = float(step.train_step(images, labels, B, 0.05))
+    for _ in range(5):
+        last = float(step.train_step(images, labels, B, 0.05))
+    assert last < first
