@@ -70,8 +70,6 @@ _decl("cunn_b200_fill", c_int, [c_void_p, c_longlong, c_float, c_void_p])
 _decl("cunn_b200_sgd_update", c_int, [c_void_p, c_void_p, c_longlong, c_float, c_void_p])
 _decl("cunn_b200_set_deterministic", None, [c_int])
 _decl("cunn_b200_get_deterministic", c_int, [])
-_decl("cunn_b200_dwconv_tuning", None, [ctypes.POINTER(c_int), c_int])
-_decl("cunn_b200_dwconv_describe_plan", c_int, [c_int] * 6 + [ctypes.c_char_p, c_int])
 
 
 class CunnError(RuntimeError):
@@ -85,15 +83,3 @@ def check(rc):
 
 def device_status():
     return lib.cunn_b200_device_status()
-
-
-def dwconv_tuning(*values):
-    """Overrides the depthwise fast-path tile plan (see cunn_b200_dwconv_tuning); no arguments resets it."""
-    arr = (c_int * max(len(values), 1))(*values)
-    lib.cunn_b200_dwconv_tuning(arr, len(values))
-
-
-def dwconv_describe_plan(mode, N, C, H, W, stride):
-    buf = ctypes.create_string_buffer(512)
-    lib.cunn_b200_dwconv_describe_plan(mode, N, C, H, W, stride, buf, 512)
-    return buf.value.decode()

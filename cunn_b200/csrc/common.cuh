@@ -96,7 +96,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *st
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
         if (clock64() - t0 > 2000000000LL) {
-            atomicExch(status, (int)STATUS_MBARRIER_TIMEOUT);
+            if (status) atomicExch(status, (int)STATUS_MBARRIER_TIMEOUT);
             return false;
         }
     }

@@ -1502,6 +1502,7 @@ static int conv_grad_input(const float *gy, const float *weight, float *gx, int 
     if (N == 0) return 0;
     CUNN_CHECK_ARG(gy && weight && gx, "null tensor pointer");
     const bool dilated = dilH != 1 || dilW != 1;
+    CUNN_CHECK_ARG(!dilated || gather_applies(kH, kW), "dilated kernels of more than 32 taps are not supported");
     if (pw_applies(kH, kW, dH, dW, padH, padW)) {
         pw::Params q{};
         q.a = gy; q.b = weight; q.bias = nullptr; q.out = gx; q.status = device_status_ptr();

@@ -1235,6 +1235,9 @@ static int grid_for(long long total)
 using namespace cunn;
 using namespace cunn::dw;
 
+// Developer hooks for tile-plan sweeps; not part of the library's interface and absent from the
+// default build (compile with -DCUNN_B200_DEV_HOOKS).
+#ifdef CUNN_B200_DEV_HOOKS
 extern "C" CUNN_API void cunn_b200_dwconv_tuning(const int *values, int count)
 {
     int v[10] = {0, 0, 0, 0, 0, 0, 0, 0, -1, -1};
@@ -1250,6 +1253,7 @@ extern "C" CUNN_API void cunn_b200_dwconv_tuning(const int *values, int count)
     g_tuning.stage_out = v[8];
     g_tuning.direct = v[9];
 }
+#endif  // CUNN_B200_DEV_HOOKS
 
 extern "C" int cunn_b200_dwconv_forward(const float *x, const float *weight, const float *bias, float *y, int N, int C,
                                         int H, int W, int M, int kH, int kW, int dH, int dW, int padH, int padW,
@@ -1353,6 +1357,9 @@ extern "C" int cunn_b200_dwconv_acc_grad(const float *x, const float *gy, float 
             CUNN_CHECK_ARG(workspace && workspace_bytes >= need && aligned16(workspace),
                            "dwconv acc_grad needs %zu bytes of 16-byte aligned workspace, got %zu", need,
                            workspace ? workspace_bytes : (size_t)0);
+            // The ticket counters return to zero when every CTA hands in its partials; a CTA that gave up on a
+            // bounded wait does not, so they are cleared here rather than trusted to be zero on entry.
+            CUNN_CUDA(cudaMemsetAsync(workspace, 0, (size_t)(C / pl.P) * sizeof(unsigned int), stream));
             fp.counters = (unsigned int *)workspace;
             fp.partials = (float *)((char *)workspace + wgrad_counter_bytes(C, pl));
             return launch_fast(fp, pl, stream, "dwconv acc grad (3x3)");
@@ -1365,6 +1372,7 @@ extern "C" int cunn_b200_dwconv_acc_grad(const float *x, const float *gy, float 
     return 0;
 }
 
+#ifdef CUNN_B200_DEV_HOOKS
 // Writes the tile plan the 3x3 fast path would use into buf (for tests, tuning and documentation).
 // mode: 0 forward, 1 stride-2 input gradient, 2 parameter gradient.
 extern "C" CUNN_API int cunn_b200_dwconv_describe_plan(int mode, int N, int C, int H, int W, int stride, char *buf, int buflen)
@@ -1380,6 +1388,7 @@ extern "C" CUNN_API int cunn_b200_dwconv_describe_plan(int mode, int N, int C, i
              pl.out_floats * 4, pl.smem);
     return pl.ok ? 0 : 1;
 }
+#endif  // CUNN_B200_DEV_HOOKS
 
 // ---------------------------------------------------------------------------
 // Parameter gradient without caller-provided scratch

@@ -4,290 +4,28 @@
 // strided inputs — and then calls the flat C ABI (cunn_b200.h) on the state's current stream.
 // Errors go through the state's error hook (TH's THError); if the hook returns, the entry point returns.
 #include "common.cuh"
-#include "../../include/THCUNN_b200.h"
+#include "../../include/THCUNN_b200.h"   // with CUNN_B200_USE_REAL_THC this pulls in cutorch's <THC/THC.h>
 
 #include <stdlib.h>
 #include <string.h>
 #include <string>
 #include <vector>
 
-struct THCState {
-    cudaStream_t stream = nullptr;
-    THCUNN_b200_error_fn handler = nullptr;
-    void *handler_ctx = nullptr;
-    std::string last_error;
-    // grow-only scratch owned by the state: [0] general, [1] depthwise parameter gradient, [2] batch normalisation
-    // (zero-filled: their ticket counters must stay zero between calls, so each has a buffer of its own)
-    void *scratch[3] = {nullptr, nullptr, nullptr};
-    size_t scratch_bytes[3] = {0, 0, 0};
-};
-
-namespace {
-
-const char kOwned = 1;     // storage flag: memory belongs to the storage (cudaMalloc'ed here)
-
-void raise(THCState *s, const char *fmt, ...)
-{
-    char buf[600];
-    va_list ap;
-    va_start(ap, fmt);
-    vsnprintf(buf, sizeof(buf), fmt, ap);
-    va_end(ap);
-    s->last_error = buf;
-    if (s->handler) s->handler(buf, s->handler_ctx);
-    else fprintf(stderr, "THCUNN error: %s\n", buf);
-}
-
-#define TH_CHECK(state, cond, ...)         \
-    do {                                   \
-        if (!(cond)) {                     \
-            raise(state, __VA_ARGS__);     \
-            return;                        \
-        }                                  \
-    } while (0)
-// a flat-ABI call failed: forward its message
-#define TH_CALL(state, call)                                  \
-    do {                                                      \
-        if ((call) != 0) {                                    \
-            raise(state, "%s", cunn_b200_last_error());      \
-            goto done;                                        \
-        }                                                     \
-    } while (0)
-
-ptrdiff_t nelem(const THCudaTensor *t)
-{
-    if (!t || t->nDimension == 0) return 0;
-    ptrdiff_t n = 1;
-    for (int i = 0; i < t->nDimension; ++i) n *= t->size[i];
-    return n;
-}
-
-bool is_contiguous(const THCudaTensor *t)
-{
-    long z = 1;
-    for (int d = t->nDimension - 1; d >= 0; --d) {
-        if (t->size[d] != 1) {
-            if (t->stride[d] != z) return false;
-            z *= t->size[d];
-        }
-    }
-    return true;
-}
-
-std::string size_desc(const THCudaTensor *t)
-{
-    std::string s = "[";
-    for (int i = 0; t && i < t->nDimension; ++i) {
-        s += std::to_string(t->size[i]);
-        if (i + 1 < t->nDimension) s += " x ";
-    }
-    return s + "]";
-}
-
-THCudaTensor *tensor_new()
-{
-    THCudaTensor *t = (THCudaTensor *)calloc(1, sizeof(THCudaTensor));
-    t->refcount = 1;
-    t->flag = 1;
-    return t;
-}
-
-void storage_release(THCudaStorage *st)
-{
-    if (!st) return;
-    if (--st->refcount > 0) return;
-    if ((st->flag & kOwned) && st->data) cudaFree(st->data);
-    free(st);
-}
-
-void tensor_free(THCudaTensor *t)
-{
-    if (!t) return;
-    if (--t->refcount > 0) return;
-    storage_release(t->storage);
-    free(t->size);
-    free(t->stride);
-    free(t);
-}
-
-// Gives t the contiguous shape `sizes`; grows its storage when needed.  elem = element size in bytes.
-bool tensor_resize(THCState *s, THCudaTensor *t, int nd, const long *sizes, int elem)
-{
-    ptrdiff_t n = nd ? 1 : 0;
-    for (int i = 0; i < nd; ++i) n *= sizes[i];
-    bool same = t->nDimension == nd;
-    for (int i = 0; same && i < nd; ++i) same = t->size[i] == sizes[i];
-    if (!(same && is_contiguous(t))) {
-        t->size = (long *)realloc(t->size, sizeof(long) * (nd ? nd : 1));
-        t->stride = (long *)realloc(t->stride, sizeof(long) * (nd ? nd : 1));
-        t->nDimension = nd;
-        long z = 1;
-        for (int d = nd - 1; d >= 0; --d) {
-            t->size[d] = sizes[d];
-            t->stride[d] = z;
-            z *= sizes[d];
-        }
-    }
-    const ptrdiff_t need = t->storageOffset + n;
-    if (!t->storage) {
-        t->storage = (THCudaStorage *)calloc(1, sizeof(THCudaStorage));
-        t->storage->refcount = 1;
-        t->storage->flag = kOwned;
-        cudaGetDevice(&t->storage->device);
-    }
-    if (need > t->storage->size) {
-        if (!(t->storage->flag & kOwned)) {
-            raise(s, "cannot resize a tensor over caller-owned memory from %td to %td elements", t->storage->size, need);
-            return false;
-        }
-        void *p = nullptr;
-        if (need > 0 && cudaMalloc(&p, (size_t)need * elem) != cudaSuccess) {
-            raise(s, "cudaMalloc of %zu bytes failed", (size_t)need * elem);
-            return false;
-        }
-        if (t->storage->data && t->storage->size > 0)
-            cudaMemcpyAsync(p, t->storage->data, (size_t)t->storage->size * elem, cudaMemcpyDeviceToDevice, s->stream);
-        if (t->storage->data) {
-            cudaStreamSynchronize(s->stream);
-            cudaFree(t->storage->data);
-        }
-        t->storage->data = p;
-        t->storage->size = need;
-    }
-    return true;
-}
-
-template <typename T>
-T *tdata(const THCudaTensor *t)
-{
-    if (!t || !t->storage || !t->storage->data) return nullptr;
-    return (T *)t->storage->data + t->storageOffset;
-}
-
-// dst (contiguous) = src (any strides), up to 5 dimensions, element size 4 or 8.
-template <typename T>
-__global__ void strided_copy_kernel(const T *__restrict__ src, T *__restrict__ dst, long long n, int nd, long s0, long s1,
-                                    long s2, long s3, long s4, long t0, long t1, long t2, long t3, long t4)
-{
-    const long size[5] = {s0, s1, s2, s3, s4};
-    const long stride[5] = {t0, t1, t2, t3, t4};
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        long long r = i, off = 0;
-        for (int d = nd - 1; d >= 0; --d) {
-            off += (r % size[d]) * stride[d];
-            r /= size[d];
-        }
-        dst[i] = src[off];
-    }
-}
-
-// A contiguous tensor with t's contents: t itself (retained) when already contiguous, else a copy.
-THCudaTensor *new_contiguous(THCState *s, THCudaTensor *t, int elem = 4)
-{
-    if (is_contiguous(t)) {
-        ++t->refcount;
-        return t;
-    }
-    if (t->nDimension > 5) {
-        raise(s, "non-contiguous tensors of more than 5 dimensions are not supported");
-        return nullptr;
-    }
-    THCudaTensor *c = tensor_new();
-    if (!tensor_resize(s, c, t->nDimension, t->size, elem)) {
-        tensor_free(c);
-        return nullptr;
-    }
-    long sz[5] = {1, 1, 1, 1, 1}, st[5] = {0, 0, 0, 0, 0};
-    for (int i = 0; i < t->nDimension; ++i) { sz[i] = t->size[i]; st[i] = t->stride[i]; }
-    const long long n = nelem(t);
-    if (n > 0) {
-        const int blocks = (int)std::min<long long>((n + 255) / 256, 65535);
-        if (elem == 4)
-            strided_copy_kernel<float><<<blocks, 256, 0, s->stream>>>(tdata<float>(t), tdata<float>(c), n, t->nDimension, sz[0], sz[1], sz[2], sz[3], sz[4], st[0], st[1], st[2], st[3], st[4]);
-        else
-            strided_copy_kernel<long long><<<blocks, 256, 0, s->stream>>>(tdata<long long>(t), tdata<long long>(c), n, t->nDimension, sz[0], sz[1], sz[2], sz[3], sz[4], st[0], st[1], st[2], st[3], st[4]);
-    }
-    return c;
-}
-
-void *state_scratch(THCState *s, int which, size_t bytes)
-{
-    if (bytes <= s->scratch_bytes[which]) return s->scratch[which];
-    const size_t want = std::max(bytes, (size_t)1 << 20);
-    void *p = nullptr;
-    if (cudaMalloc(&p, want) != cudaSuccess) {
-        raise(s, "cudaMalloc of %zu bytes of scratch failed", want);
-        return nullptr;
-    }
-    cudaMemsetAsync(p, 0, want, s->stream);
-    if (s->scratch[which]) {
-        cudaStreamSynchronize(s->stream);
-        cudaFree(s->scratch[which]);
-    }
-    s->scratch[which] = p;
-    s->scratch_bytes[which] = want;
-    return p;
-}
-
-bool check_dim_size(THCState *s, const THCudaTensor *t, const char *name, int dim, int dim_size, long size)
-{
-    if (t->nDimension != dim || t->size[dim_size] != size) {
-        raise(s, "Need %s of dimension %d and %s.size[%d] == %ld but got %s to be of shape: %s", name, dim, name, dim_size,
-              size, name, size_desc(t).c_str());
-        return false;
-    }
-    return true;
-}
-
-}  // namespace
+// Tensor and state access goes through one of two back-ends with the same helper names:
+//   thc_backend_builtin.inc  the library's own state and tensor struct (default; what the tests drive);
+//   thc_backend_real.inc     cutorch's libTHC (THCState_getCurrentStream, THCudaTensor_newContiguous,
+//                            THCudaTensor_resizeNd, THError ...), for a build inside a Lua-Torch install.
+#ifdef CUNN_B200_USE_REAL_THC
+#include "thc_backend_real.inc"
+#else
+#include "thc_backend_builtin.inc"
+#endif
 
 extern "C" void thcunn_b200_not_implemented(THCState *state, const char *name)
 {
     if (state) raise(state, "%s is not implemented in this build (only the convolutional hot path is)", name);
     else fprintf(stderr, "THCUNN error: %s is not implemented in this build\n", name);
 }
-
-// ---- harness helpers --------------------------------------------------------------------------------
-extern "C" CUNN_API THCState *THCState_b200_new(void) { return new THCState(); }
-extern "C" CUNN_API void THCState_b200_free(THCState *s)
-{
-    if (!s) return;
-    for (int i = 0; i < 3; ++i)
-        if (s->scratch[i]) cudaFree(s->scratch[i]);
-    delete s;
-}
-extern "C" CUNN_API void THCState_b200_setStream(THCState *s, cunn_stream_t stream) { s->stream = (cudaStream_t)stream; }
-extern "C" CUNN_API void THCState_b200_setErrorHandler(THCState *s, THCUNN_b200_error_fn fn, void *ctx)
-{
-    s->handler = fn;
-    s->handler_ctx = ctx;
-}
-extern "C" CUNN_API const char *THCState_b200_lastError(THCState *s) { return s->last_error.c_str(); }
-extern "C" CUNN_API THCudaTensor *THCudaTensor_b200_new(THCState *) { return tensor_new(); }
-extern "C" CUNN_API THCudaLongTensor *THCudaLongTensor_b200_new(THCState *) { return tensor_new(); }
-extern "C" CUNN_API THCudaTensor *THCudaTensor_b200_wrap(THCState *, void *data, ptrdiff_t capacity, int ndim,
-                                                         const long *sizes, const long *strides, int)
-{
-    THCudaTensor *t = tensor_new();
-    t->storage = (THCudaStorage *)calloc(1, sizeof(THCudaStorage));
-    t->storage->refcount = 1;
-    t->storage->flag = 0;   // caller-owned
-    t->storage->data = data;
-    t->storage->size = capacity;
-    cudaGetDevice(&t->storage->device);
-    t->nDimension = ndim;
-    t->size = (long *)malloc(sizeof(long) * (ndim ? ndim : 1));
-    t->stride = (long *)malloc(sizeof(long) * (ndim ? ndim : 1));
-    long z = 1;
-    for (int d = ndim - 1; d >= 0; --d) {
-        t->size[d] = sizes[d];
-        t->stride[d] = strides ? strides[d] : z;
-        z *= sizes[d];
-    }
-    return t;
-}
-extern "C" CUNN_API void THCudaTensor_b200_free(THCState *, THCudaTensor *t) { tensor_free(t); }
-extern "C" CUNN_API void *THCudaTensor_b200_data(THCState *, THCudaTensor *t) { return tdata<char>(t) ? (void *)((char *)t->storage->data) : nullptr; }
 
 // ---- SpatialDepthWiseConvolution -------------------------------------------------------------------
 // Shape rules of lib/THCUNN/generic/SpatialDepthWiseConvolution.cu:5-56.  A 2-D weight [M, C*kH*kW] is
@@ -337,12 +75,12 @@ extern "C" CUNN_API void THNN_CudaSpatialDepthWiseConvolution_updateOutput(
         const long sz4[4] = {N, C * M, oH, oW};
         if (tensor_resize(s, output, 4, sz4, 4)) {
             TH_CALL(s, cunn_b200_dwconv_forward(tdata<float>(x), tdata<float>(w), tdata<float>(b), tdata<float>(output), (int)N,
-                                                (int)C, (int)H, (int)W, (int)M, kH, kW, dH, dW, padH, padW, s->stream));
+                                                (int)C, (int)H, (int)W, (int)M, kH, kW, dH, dW, padH, padW, state_stream(s)));
             if (input->nDimension == 3) tensor_resize(s, output, 3, sz4 + 1, 4);
         }
     }
 done:
-    tensor_free(x); tensor_free(w); tensor_free(b);
+    tensor_free(s, x); tensor_free(s, w); tensor_free(s, b);
 }
 
 extern "C" CUNN_API void THNN_CudaSpatialDepthWiseConvolution_updateGradInput(
@@ -357,12 +95,12 @@ extern "C" CUNN_API void THNN_CudaSpatialDepthWiseConvolution_updateGradInput(
         const long sz4[4] = {N, C, H, W};
         if (tensor_resize(s, gradInput, 4, sz4, 4)) {
             TH_CALL(s, cunn_b200_dwconv_grad_input(tdata<float>(gy), tdata<float>(w), tdata<float>(gradInput), (int)N, (int)C,
-                                                   (int)H, (int)W, (int)M, kH, kW, dH, dW, padH, padW, s->stream));
+                                                   (int)H, (int)W, (int)M, kH, kW, dH, dW, padH, padW, state_stream(s)));
             if (input->nDimension == 3) tensor_resize(s, gradInput, 3, sz4 + 1, 4);
         }
     }
 done:
-    tensor_free(gy); tensor_free(w);
+    tensor_free(s, gy); tensor_free(s, w);
 }
 
 extern "C" CUNN_API void THNN_CudaSpatialDepthWiseConvolution_accGradParameters(
@@ -379,10 +117,10 @@ extern "C" CUNN_API void THNN_CudaSpatialDepthWiseConvolution_accGradParameters(
         if (!need || ws)
             TH_CALL(s, cunn_b200_dwconv_acc_grad(tdata<float>(x), tdata<float>(gy), tdata<float>(gradWeight), tdata<float>(gradBias),
                                                  (int)N, (int)C, (int)H, (int)W, (int)M, kH, kW, dH, dW, padH, padW, scale, ws,
-                                                 s->scratch_bytes[1], s->stream));
+                                                 state_scratch_bytes(s, 1), state_stream(s)));
     }
 done:
-    tensor_free(x); tensor_free(gy);
+    tensor_free(s, x); tensor_free(s, gy);
 }
 
 // ---- SpatialConvolutionMM ----------------------------------------------------------------------------
@@ -427,12 +165,12 @@ extern "C" CUNN_API void THNN_CudaSpatialConvolutionMM_updateOutput(
         const long sz4[4] = {N, K, oH, oW};
         if (tensor_resize(s, output, 4, sz4, 4)) {
             TH_CALL(s, cunn_b200_convmm_forward(tdata<float>(x), tdata<float>(weight), bias ? tdata<float>(bias) : nullptr, tdata<float>(output),
-                                                (int)N, (int)C, (int)H, (int)W, (int)K, kH, kW, dH, dW, padH, padW, s->stream));
+                                                (int)N, (int)C, (int)H, (int)W, (int)K, kH, kW, dH, dW, padH, padW, state_stream(s)));
             if (input->nDimension == 3) tensor_resize(s, output, 3, sz4 + 1, 4);
         }
     }
 done:
-    tensor_free(x);
+    tensor_free(s, x);
 }
 
 extern "C" CUNN_API void THNN_CudaSpatialConvolutionMM_updateGradInput(
@@ -446,12 +184,12 @@ extern "C" CUNN_API void THNN_CudaSpatialConvolutionMM_updateGradInput(
         const long sz4[4] = {N, C, H, W};
         if (tensor_resize(s, gradInput, 4, sz4, 4)) {
             TH_CALL(s, cunn_b200_convmm_grad_input(tdata<float>(gy), tdata<float>(weight), tdata<float>(gradInput), (int)N, (int)C, (int)H,
-                                                   (int)W, (int)K, kH, kW, dH, dW, padH, padW, s->stream));
+                                                   (int)W, (int)K, kH, kW, dH, dW, padH, padW, state_stream(s)));
             if (input->nDimension == 3) tensor_resize(s, gradInput, 3, sz4 + 1, 4);
         }
     }
 done:
-    tensor_free(gy);
+    tensor_free(s, gy);
 }
 
 extern "C" CUNN_API void THNN_CudaSpatialConvolutionMM_accGradParameters(
@@ -467,10 +205,10 @@ extern "C" CUNN_API void THNN_CudaSpatialConvolutionMM_accGradParameters(
         if (ws)
             TH_CALL(s, cunn_b200_convmm_acc_grad(tdata<float>(x), tdata<float>(gy), tdata<float>(gradWeight), gradBias ? tdata<float>(gradBias) : nullptr,
                                                  (int)N, (int)C, (int)H, (int)W, (int)K, kH, kW, dH, dW, padH, padW, scale, ws,
-                                                 s->scratch_bytes[0], s->stream));
+                                                 state_scratch_bytes(s, 0), state_stream(s)));
     }
 done:
-    tensor_free(x); tensor_free(gy);
+    tensor_free(s, x); tensor_free(s, gy);
 }
 
 // ---- SpatialDilatedConvolution (generic/SpatialDilatedConvolution.cu; decl generic/THCUNN.h:727-764): the same
@@ -487,12 +225,12 @@ extern "C" CUNN_API void THNN_CudaSpatialDilatedConvolution_updateOutput(
         if (tensor_resize(s, output, 4, sz4, 4)) {
             TH_CALL(s, cunn_b200_dilated_conv_forward(tdata<float>(x), tdata<float>(weight), bias ? tdata<float>(bias) : nullptr,
                                                       tdata<float>(output), (int)N, (int)C, (int)H, (int)W, (int)K, kH, kW, dH, dW,
-                                                      padH, padW, dilationH, dilationW, s->stream));
+                                                      padH, padW, dilationH, dilationW, state_stream(s)));
             if (input->nDimension == 3) tensor_resize(s, output, 3, sz4 + 1, 4);
         }
     }
 done:
-    tensor_free(x);
+    tensor_free(s, x);
 }
 
 extern "C" CUNN_API void THNN_CudaSpatialDilatedConvolution_updateGradInput(
@@ -507,12 +245,12 @@ extern "C" CUNN_API void THNN_CudaSpatialDilatedConvolution_updateGradInput(
         if (tensor_resize(s, gradInput, 4, sz4, 4)) {
             TH_CALL(s, cunn_b200_dilated_conv_grad_input(tdata<float>(gy), tdata<float>(weight), tdata<float>(gradInput), (int)N, (int)C,
                                                          (int)H, (int)W, (int)K, kH, kW, dH, dW, padH, padW, dilationH, dilationW,
-                                                         s->stream));
+                                                         state_stream(s)));
             if (input->nDimension == 3) tensor_resize(s, gradInput, 3, sz4 + 1, 4);
         }
     }
 done:
-    tensor_free(gy);
+    tensor_free(s, gy);
 }
 
 extern "C" CUNN_API void THNN_CudaSpatialDilatedConvolution_accGradParameters(
@@ -530,11 +268,11 @@ extern "C" CUNN_API void THNN_CudaSpatialDilatedConvolution_accGradParameters(
         if (ws)
             TH_CALL(s, cunn_b200_dilated_conv_acc_grad(tdata<float>(x), tdata<float>(gy), tdata<float>(gradWeight),
                                                        gradBias ? tdata<float>(gradBias) : nullptr, (int)N, (int)C, (int)H, (int)W, (int)K,
-                                                       kH, kW, dH, dW, padH, padW, dilationH, dilationW, scale, ws, need, s->stream));
+                                                       kH, kW, dH, dW, padH, padW, dilationH, dilationW, scale, ws, need, state_stream(s)));
     }
 done:
-    tensor_free(x);
-    tensor_free(gy);
+    tensor_free(s, x);
+    tensor_free(s, gy);
 }
 
 // ---- SpatialFullDilatedConvolution / SpatialFullConvolution (transposed convolution) ----------------------
@@ -586,12 +324,12 @@ extern "C" CUNN_API void THNN_CudaSpatialFullDilatedConvolution_updateOutput(
         if (tensor_resize(s, output, 4, sz4, 4)) {
             TH_CALL(s, cunn_b200_full_conv_forward(tdata<float>(x), tdata<float>(weight), bias ? tdata<float>(bias) : nullptr,
                                                    tdata<float>(output), (int)N, (int)P, (int)H, (int)W, (int)Q, kH, kW, dH, dW, padH,
-                                                   padW, dilationH, dilationW, adjH, adjW, s->stream));
+                                                   padW, dilationH, dilationW, adjH, adjW, state_stream(s)));
             if (input->nDimension == 3) tensor_resize(s, output, 3, sz4 + 1, 4);
         }
     }
 done:
-    tensor_free(x);
+    tensor_free(s, x);
 }
 
 extern "C" CUNN_API void THNN_CudaSpatialFullDilatedConvolution_updateGradInput(
@@ -606,12 +344,12 @@ extern "C" CUNN_API void THNN_CudaSpatialFullDilatedConvolution_updateGradInput(
         if (tensor_resize(s, gradInput, 4, sz4, 4)) {
             TH_CALL(s, cunn_b200_full_conv_grad_input(tdata<float>(gy), tdata<float>(weight), tdata<float>(gradInput), (int)N, (int)P,
                                                       (int)H, (int)W, (int)Q, kH, kW, dH, dW, padH, padW, dilationH, dilationW, adjH,
-                                                      adjW, s->stream));
+                                                      adjW, state_stream(s)));
             if (input->nDimension == 3) tensor_resize(s, gradInput, 3, sz4 + 1, 4);
         }
     }
 done:
-    tensor_free(gy);
+    tensor_free(s, gy);
 }
 
 extern "C" CUNN_API void THNN_CudaSpatialFullDilatedConvolution_accGradParameters(
@@ -630,11 +368,11 @@ extern "C" CUNN_API void THNN_CudaSpatialFullDilatedConvolution_accGradParameter
             TH_CALL(s, cunn_b200_full_conv_acc_grad(tdata<float>(x), tdata<float>(gy), tdata<float>(gradWeight),
                                                     gradBias ? tdata<float>(gradBias) : nullptr, (int)N, (int)P, (int)H, (int)W, (int)Q,
                                                     kH, kW, dH, dW, padH, padW, dilationH, dilationW, adjH, adjW, scale, ws, need,
-                                                    s->stream));
+                                                    state_stream(s)));
     }
 done:
-    tensor_free(x);
-    tensor_free(gy);
+    tensor_free(s, x);
+    tensor_free(s, gy);
 }
 
 // SpatialFullConvolution is the same operator with dilation 1 (lib/THCUNN/generic/SpatialFullConvolution.cu).
@@ -688,11 +426,11 @@ extern "C" CUNN_API void THNN_CudaBatchNormalization_updateOutput(
                 TH_CALL(s, cunn_b200_batchnorm_forward(tdata<float>(x), tdata<float>(output_), weight_ ? tdata<float>(weight_) : nullptr,
                                                        bias_ ? tdata<float>(bias_) : nullptr, tdata<float>(runningMean_), tdata<float>(runningVar_),
                                                        tdata<float>(saveMean_), tdata<float>(saveStd_), (int)N, (int)C, (int)S, train ? 1 : 0,
-                                                       momentum, eps, ws, s->scratch_bytes[0], s->stream));
+                                                       momentum, eps, ws, state_scratch_bytes(s, 2), state_stream(s)));
         }
     }
 done:
-    tensor_free(x);
+    tensor_free(s, x);
 }
 
 extern "C" CUNN_API void THNN_CudaBatchNormalization_backward(
@@ -712,10 +450,10 @@ extern "C" CUNN_API void THNN_CudaBatchNormalization_backward(
                                                     gradWeight_ ? tdata<float>(gradWeight_) : nullptr, gradBias_ ? tdata<float>(gradBias_) : nullptr,
                                                     weight_ ? tdata<float>(weight_) : nullptr, tdata<float>(runningMean_), tdata<float>(runningVar_),
                                                     tdata<float>(saveMean_), tdata<float>(saveStd_), (int)N, (int)C, (int)S, train ? 1 : 0, scale, eps,
-                                                    ws, s->scratch_bytes[0], s->stream));
+                                                    ws, state_scratch_bytes(s, 2), state_stream(s)));
     }
 done:
-    tensor_free(x); tensor_free(gy);
+    tensor_free(s, x); tensor_free(s, gy);
 }
 
 // ---- SpatialMaxPooling ------------------------------------------------------------------------------------
@@ -735,12 +473,12 @@ extern "C" CUNN_API void THNN_CudaSpatialMaxPooling_updateOutput(THCState *s, TH
         const long sz4[4] = {N, C, oH > 0 ? oH : 0, oW > 0 ? oW : 0};
         if (oH < 1 || oW < 1 || (tensor_resize(s, output, 4, sz4, 4) && tensor_resize(s, indices, 4, sz4, 8))) {
             TH_CALL(s, cunn_b200_maxpool_forward(tdata<float>(x), tdata<float>(output), tdata<int64_t>(indices), (int)N, (int)C, (int)H, (int)W, kH,
-                                                 kW, dH, dW, padH, padW, 1, 1, ceil_mode, s->stream));
+                                                 kW, dH, dW, padH, padW, 1, 1, ceil_mode, state_stream(s)));
             if (nd == 3) tensor_resize(s, output, 3, sz4 + 1, 4);   // indices stay 4-D, as in the reference
         }
     }
 done:
-    tensor_free(x);
+    tensor_free(s, x);
 }
 
 extern "C" CUNN_API void THNN_CudaSpatialMaxPooling_updateGradInput(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput,
@@ -759,9 +497,9 @@ extern "C" CUNN_API void THNN_CudaSpatialMaxPooling_updateGradInput(THCState *s,
     THCudaTensor *gy = new_contiguous(s, gradOutput);
     if (gy && tensor_resize(s, gradInput, nd, input->size, 4))
         TH_CALL(s, cunn_b200_maxpool_backward(tdata<float>(gy), tdata<int64_t>(indices), tdata<float>(gradInput), (int)N, (int)C, (int)H, (int)W,
-                                              kH, kW, dH, dW, padH, padW, 1, 1, ceil_mode, s->stream));
+                                              kH, kW, dH, dW, padH, padW, 1, 1, ceil_mode, state_stream(s)));
 done:
-    tensor_free(gy);
+    tensor_free(s, gy);
 }
 
 // ---- support operators ---------------------------------------------------------------------------------------
@@ -770,15 +508,15 @@ extern "C" CUNN_API void THNN_CudaThreshold_updateOutput(THCState *s, THCudaTens
 {
     if (inplace) {
         TH_CHECK(s, is_contiguous(input), "in-place Threshold needs a contiguous input");
-        if (cunn_b200_threshold_forward(tdata<float>(input), tdata<float>(input), nelem(input), threshold, val, s->stream)) raise(s, "%s", cunn_b200_last_error());
+        if (cunn_b200_threshold_forward(tdata<float>(input), tdata<float>(input), nelem(input), threshold, val, state_stream(s))) raise(s, "%s", cunn_b200_last_error());
         // the reference makes output share input's storage (THCTensor_set); callers keep using `input`
         return;
     }
     THCudaTensor *x = new_contiguous(s, input);
     if (x && tensor_resize(s, output, input->nDimension, input->size, 4))
-        TH_CALL(s, cunn_b200_threshold_forward(tdata<float>(x), tdata<float>(output), nelem(input), threshold, val, s->stream));
+        TH_CALL(s, cunn_b200_threshold_forward(tdata<float>(x), tdata<float>(output), nelem(input), threshold, val, state_stream(s)));
 done:
-    tensor_free(x);
+    tensor_free(s, x);
 }
 
 extern "C" CUNN_API void THNN_CudaThreshold_updateGradInput(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput,
@@ -789,13 +527,13 @@ extern "C" CUNN_API void THNN_CudaThreshold_updateGradInput(THCState *s, THCudaT
     if (x && gy) {
         if (inplace) {
             if (gy != gradOutput) raise(s, "in-place Threshold needs a contiguous gradOutput");
-            else TH_CALL(s, cunn_b200_threshold_backward(tdata<float>(x), tdata<float>(gy), tdata<float>(gy), nelem(input), threshold, s->stream));
+            else TH_CALL(s, cunn_b200_threshold_backward(tdata<float>(x), tdata<float>(gy), tdata<float>(gy), nelem(input), threshold, state_stream(s)));
         } else if (tensor_resize(s, gradInput, input->nDimension, input->size, 4)) {
-            TH_CALL(s, cunn_b200_threshold_backward(tdata<float>(x), tdata<float>(gy), tdata<float>(gradInput), nelem(input), threshold, s->stream));
+            TH_CALL(s, cunn_b200_threshold_backward(tdata<float>(x), tdata<float>(gy), tdata<float>(gradInput), nelem(input), threshold, state_stream(s)));
         }
     }
 done:
-    tensor_free(x); tensor_free(gy);
+    tensor_free(s, x); tensor_free(s, gy);
 }
 
 extern "C" CUNN_API void THNN_CudaSpatialAveragePooling_updateOutput(THCState *s, THCudaTensor *input, THCudaTensor *output, int kW,
@@ -813,11 +551,11 @@ extern "C" CUNN_API void THNN_CudaSpatialAveragePooling_updateOutput(THCState *s
     const long sz4[4] = {N, C, oH, oW};
     if (x && tensor_resize(s, output, 4, sz4, 4)) {
         TH_CALL(s, cunn_b200_avgpool_forward(tdata<float>(x), tdata<float>(output), (int)N, (int)C, (int)H, (int)W, (int)oH, (int)oW, kH, kW, dH, dW,
-                                             padH, padW, count_include_pad, s->stream));
+                                             padH, padW, count_include_pad, state_stream(s)));
         if (nd == 3) tensor_resize(s, output, 3, sz4 + 1, 4);
     }
 done:
-    tensor_free(x);
+    tensor_free(s, x);
 }
 
 extern "C" CUNN_API void THNN_CudaSpatialAveragePooling_updateGradInput(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput,
@@ -834,9 +572,9 @@ extern "C" CUNN_API void THNN_CudaSpatialAveragePooling_updateGradInput(THCState
     THCudaTensor *gy = new_contiguous(s, gradOutput);
     if (gy && tensor_resize(s, gradInput, nd, input->size, 4))
         TH_CALL(s, cunn_b200_avgpool_backward(tdata<float>(gy), tdata<float>(gradInput), (int)N, (int)C, (int)H, (int)W, (int)oH, (int)oW, kH, kW, dH,
-                                              dW, padH, padW, count_include_pad, s->stream));
+                                              dW, padH, padW, count_include_pad, state_stream(s)));
 done:
-    tensor_free(gy);
+    tensor_free(s, gy);
 }
 
 extern "C" CUNN_API void THNN_CudaLogSoftMax_updateOutput(THCState *s, THCudaTensor *input, THCudaTensor *output)
@@ -845,9 +583,9 @@ extern "C" CUNN_API void THNN_CudaLogSoftMax_updateOutput(THCState *s, THCudaTen
     const long B = input->nDimension == 2 ? input->size[0] : 1, D = input->size[input->nDimension - 1];
     THCudaTensor *x = new_contiguous(s, input);
     if (x && tensor_resize(s, output, input->nDimension, input->size, 4))
-        TH_CALL(s, cunn_b200_logsoftmax_forward(tdata<float>(x), tdata<float>(output), (int)B, (int)D, s->stream));
+        TH_CALL(s, cunn_b200_logsoftmax_forward(tdata<float>(x), tdata<float>(output), (int)B, (int)D, state_stream(s)));
 done:
-    tensor_free(x);
+    tensor_free(s, x);
 }
 
 extern "C" CUNN_API void THNN_CudaLogSoftMax_updateGradInput(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput,
@@ -858,10 +596,10 @@ extern "C" CUNN_API void THNN_CudaLogSoftMax_updateGradInput(THCState *s, THCuda
     const long B = output->nDimension == 2 ? output->size[0] : 1, D = output->size[output->nDimension - 1];
     THCudaTensor *y = new_contiguous(s, output), *gy = new_contiguous(s, gradOutput);
     if (y && gy && tensor_resize(s, gradInput, output->nDimension, output->size, 4))
-        TH_CALL(s, cunn_b200_logsoftmax_backward(tdata<float>(y), tdata<float>(gy), tdata<float>(gradInput), (int)B, (int)D, s->stream));
+        TH_CALL(s, cunn_b200_logsoftmax_backward(tdata<float>(y), tdata<float>(gy), tdata<float>(gradInput), (int)B, (int)D, state_stream(s)));
 done:
     (void)input;
-    tensor_free(y); tensor_free(gy);
+    tensor_free(s, y); tensor_free(s, gy);
 }
 
 extern "C" CUNN_API void THNN_CudaClassNLLCriterion_updateOutput(THCState *s, THCudaTensor *input, THCudaLongTensor *target,
@@ -879,12 +617,12 @@ extern "C" CUNN_API void THNN_CudaClassNLLCriterion_updateOutput(THCState *s, TH
     float *pair = (float *)state_scratch(s, 0, 16);
     if (!pair) return;
     if (cunn_b200_classnll_forward(tdata<float>(input), tdata<int64_t>(target), weights ? tdata<float>(weights) : nullptr, pair, (int)B, (int)D,
-                                   sizeAverage, ignore_index, s->stream)) {
+                                   sizeAverage, ignore_index, state_stream(s))) {
         raise(s, "%s", cunn_b200_last_error());
         return;
     }
-    cudaMemcpyAsync(tdata<float>(output), pair, 4, cudaMemcpyDeviceToDevice, s->stream);
-    cudaMemcpyAsync(tdata<float>(total_weight), pair + 1, 4, cudaMemcpyDeviceToDevice, s->stream);
+    cudaMemcpyAsync(tdata<float>(output), pair, 4, cudaMemcpyDeviceToDevice, state_stream(s));
+    cudaMemcpyAsync(tdata<float>(total_weight), pair + 1, 4, cudaMemcpyDeviceToDevice, state_stream(s));
 }
 
 extern "C" CUNN_API void THNN_CudaClassNLLCriterion_updateGradInput(THCState *s, THCudaTensor *input, THCudaLongTensor *target,
@@ -897,6 +635,6 @@ extern "C" CUNN_API void THNN_CudaClassNLLCriterion_updateGradInput(THCState *s,
     // gradInput is NOT zeroed here: nn.ClassNLLCriterion resizes and zeroes it before the call
     TH_CHECK(s, nelem(gradInput) == nelem(input) && is_contiguous(gradInput), "gradInput must be contiguous and of input's size");
     if (cunn_b200_classnll_backward(tdata<int64_t>(target), weights ? tdata<float>(weights) : nullptr, tdata<float>(total_weight), tdata<float>(gradInput),
-                                    (int)B, (int)D, sizeAverage, ignore_index, s->stream))
+                                    (int)B, (int)D, sizeAverage, ignore_index, state_stream(s)))
         raise(s, "%s", cunn_b200_last_error());
 }

@@ -38,7 +38,9 @@ lib.THCState_b200_setStream.argtypes = [c_void_p, c_void_p]
 lib.THCState_b200_setErrorHandler.argtypes = [c_void_p, _ERRFN, c_void_p]
 lib.THCudaTensor_b200_wrap.restype = _TP
 lib.THCudaTensor_b200_wrap.argtypes = [c_void_p, c_void_p, ctypes.c_ssize_t, c_int, ctypes.POINTER(c_long),
-                                       ctypes.POINTER(c_long), c_int]
+                                       ctypes.POINTER(c_long), c_int, ctypes.c_ssize_t]
+lib.THCudaTensor_b200_data.restype = c_void_p
+lib.THCudaTensor_b200_data.argtypes = [c_void_p, _TP, c_int]
 lib.THCudaTensor_b200_new.restype = _TP
 lib.THCudaTensor_b200_new.argtypes = [c_void_p]
 lib.THCudaTensor_b200_free.argtypes = [c_void_p, _TP]
@@ -105,8 +107,11 @@ class THNN:
         nd = t.dim()
         sizes = (c_long * max(nd, 1))(*t.shape)
         strides = (c_long * max(nd, 1))(*t.stride())
-        cap = t.untyped_storage().nbytes() // t.element_size() - t.storage_offset()
-        h = lib.THCudaTensor_b200_wrap(self.state, t.data_ptr(), cap, nd, sizes, strides, t.element_size())
+        # the storage starts at the torch storage's base; a view keeps its offset, as a Lua tensor would
+        st = t.untyped_storage()
+        cap = st.nbytes() // t.element_size()
+        h = lib.THCudaTensor_b200_wrap(self.state, st.data_ptr(), cap, nd, sizes, strides, t.element_size(),
+                                       t.storage_offset())
         self._keep.append(t)
         return h
 
@@ -114,7 +119,7 @@ class THNN:
         """An output tensor with no shape yet over `capacity` elements of torch memory: the callee resizes it."""
         buf = torch.empty(max(int(capacity), 1), dtype=dtype, device=device)
         sizes = (c_long * 1)(0)
-        h = lib.THCudaTensor_b200_wrap(self.state, buf.data_ptr(), buf.numel(), 0, sizes, None, buf.element_size())
+        h = lib.THCudaTensor_b200_wrap(self.state, buf.data_ptr(), buf.numel(), 0, sizes, None, buf.element_size(), 0)
         return h, buf
 
     @staticmethod

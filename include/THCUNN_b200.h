@@ -5,8 +5,9 @@
  *
  * The tensor and storage structs restate the public layout of cutorch 1.0's THCTensor.h / THCStorage.h.
  * cutorch is not part of the reference tree and is absent from this image, so binary compatibility with
- * a real Lua-Torch install could not be verified; inside a cutorch build compile the entry points against
- * the real <THC/THC.h> instead (define CUNN_B200_USE_REAL_THC before including this header).
+ * a real Lua-Torch install could not be verified; inside a cutorch build compile the library with
+ * -DCUNN_B200_USE_REAL_THC: this header then includes cutorch's <THC/THC.h> and the entry points reach
+ * the state and the tensors through libTHC (csrc/thc_backend_real.inc) instead of the structs below.
  *
  * The small THCudaTensor_* / THCState_* helper set below is what a C harness needs to drive the entry
  * points without cutorch; it is not a reimplementation of libTHC.
@@ -19,6 +20,10 @@
 #include <stdint.h>
 
 #include "cunn_b200.h"
+
+#ifdef CUNN_B200_USE_REAL_THC
+#include <THC/THC.h>   /* cutorch's THCState, THCudaTensor, THCudaLongTensor */
+#endif
 
 #ifdef __cplusplus
 extern "C" {
@@ -50,7 +55,8 @@ typedef THCudaTensor THCudaLongTensor;   /* same layout, 8-byte elements */
 typedef struct THCState THCState;        /* opaque here: current stream, error hook, scratch */
 #endif
 
-/* ---- harness helpers ---------------------------------------------------------------------------- */
+/* ---- harness helpers (built-in tensor layer only) ------------------------------------------------- */
+#ifndef CUNN_B200_USE_REAL_THC
 CUNN_API THCState *THCState_b200_new(void);
 CUNN_API void THCState_b200_free(THCState *state);
 CUNN_API void THCState_b200_setStream(THCState *state, cunn_stream_t stream);
@@ -64,11 +70,15 @@ CUNN_API const char *THCState_b200_lastError(THCState *state);
 CUNN_API THCudaTensor *THCudaTensor_b200_new(THCState *state);                    /* empty, 0 dimensions */
 CUNN_API THCudaLongTensor *THCudaLongTensor_b200_new(THCState *state);
 /* A tensor over caller-owned device memory (never freed or reallocated by the library; a resize that does
- * not fit raises an error).  sizes/strides in elements; strides == NULL means contiguous. */
+ * not fit raises an error).  sizes/strides in elements; strides == NULL means contiguous; `data` is the
+ * start of the storage and the view begins storage_offset_elems elements into it. */
 CUNN_API THCudaTensor *THCudaTensor_b200_wrap(THCState *state, void *data, ptrdiff_t capacity_elems, int ndim,
-                                              const long *sizes, const long *strides, int elem_size);
+                                              const long *sizes, const long *strides, int elem_size,
+                                              ptrdiff_t storage_offset_elems);
 CUNN_API void THCudaTensor_b200_free(THCState *state, THCudaTensor *t);
-CUNN_API void *THCudaTensor_b200_data(THCState *state, THCudaTensor *t);
+/* Device address of the view's first element (storage data + storageOffset * elem_size bytes). */
+CUNN_API void *THCudaTensor_b200_data(THCState *state, THCudaTensor *t, int elem_size);
+#endif
 
 /* ---- hot path (float) ---------------------------------------------------------------------------- */
 CUNN_API void THNN_CudaSpatialDepthWiseConvolution_updateOutput(

@@ -296,16 +296,6 @@ CUNN_API int cunn_b200_mobilenet_step(const cunn_b200_mobilenet_config *cfg, con
                                       float *bn_running, void *arena, size_t arena_bytes, float *loss,
                                       double momentum, double eps, cunn_stream_t stream);
 
-/* Tuning hook for sweeps and tests: overrides the tile plan of the 3x3 fast path for the calling
- * thread.  values[0..count) = {planes_per_tile, rows_per_tile, rows_per_strip, stages, ctas_per_sm,
- * force_generic, stage_budget_kb, vec, staged_stores(-1 auto)}; 0 keeps the automatic choice, missing
- * entries are reset.  force_generic != 0 routes every call to the shape-generic kernels. */
-CUNN_API void cunn_b200_dwconv_tuning(const int *values, int count);
-
-/* Writes a one-line description of the tile plan the fast path picks (mode 0 forward, 1 stride-2
- * input gradient, 2 parameter gradient) for a 3x3/pad-1 layer; returns 0 if the fast path applies. */
-CUNN_API int cunn_b200_dwconv_describe_plan(int mode, int N, int C, int H, int W, int stride, char *buf, int buflen);
-
 #ifdef __cplusplus
 }
 #endif

@@ -52,3 +52,32 @@ def test_no_cpu_fallback_message():
     from cunn_b200._lib import lib
     rc = lib.cunn_b200_threshold_forward(ctypes.c_void_p(16), ctypes.c_void_p(16), 4, 0.0, 0.0, None)
     assert rc != 0 and lib.cunn_b200_last_error()
+
+
+def test_cutorch_backend_of_the_entry_points_compiles(tmp_path):
+    """csrc/thnn.cu built with -DCUNN_B200_USE_REAL_THC against a header that only DECLARES cutorch's
+    functions (tests/thc_stub): the object must leave exactly the libTHC calls the reference's wrappers use
+    as undefined symbols, and still define every THNN_Cuda* entry point of the hot path."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        import pytest
+        pytest.skip("nvcc not available")
+    obj = str(tmp_path / "thnn_real.o")
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O0", "-std=c++17", "-ccbin", "/usr/bin/g++",
+           "-Xcompiler", "-fPIC", "-DCUNN_BUILDING=1", "-DCUNN_B200_USE_REAL_THC",
+           "-I", os.path.join(ROOT, "tests", "thc_stub"), "-c", os.path.join(ROOT, "cunn_b200", "csrc", "thnn.cu"), "-o", obj]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    syms = subprocess.run(["nm", obj], capture_output=True, text=True, check=True).stdout.splitlines()
+    undefined = {l.split()[-1] for l in syms if " U " in l}
+    defined = {l.split()[-1] for l in syms if " T " in l}
+    thc = {n for n in undefined if n.startswith(("THC", "_THError"))}
+    assert thc == {"THCState_getCurrentStream", "THCudaMalloc", "THCudaFree", "THCudaTensor_new", "THCudaTensor_free",
+                   "THCudaTensor_newContiguous", "THCudaTensor_resizeNd", "THCudaLongTensor_resizeNd", "_THError"} - \
+        ({"THCudaTensor_new"} - thc)
+    for n in ("THNN_CudaSpatialDepthWiseConvolution_updateOutput", "THNN_CudaSpatialConvolutionMM_accGradParameters",
+              "THNN_CudaBatchNormalization_backward", "THNN_CudaSpatialMaxPooling_updateOutput"):
+        assert n in defined
+    assert not any(n.startswith("THCState_b200") for n in defined)      # the harness layer is built-in only
