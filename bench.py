@@ -1,6 +1,6 @@
 #!/usr/bin/env python
-"""Benchmark of the depthwise-convolution hot path (BASELINE config 2: the 13 depthwise 3x3 layers of
-MobileNetV1, fp32 NCHW, batch 64 per GPU, forward + input gradient + parameter gradient per layer).
+"""Benchmark of the depthwise-convolution hot path: the 13 depthwise 3x3 layers of MobileNetV1, fp32 NCHW,
+batch 64 per GPU, forward + input gradient + parameter gradient per layer.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
@@ -10,10 +10,12 @@ With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank runs
 own batch of 64 images (weak scaling) and the ranks all-reduce the flat depthwise weight-gradient buffer
 over NCCL at the end of each step, as the batch-sharded DataParallelTable does.
 
-Prints ONE JSON line (rank 0).  `value` is whole-job algorithmic GB/s with inputs resident in HBM;
-`e2e` is the same metric through the C ABI with pinned host buffers, host<->device copies timed;
-`roofline` describes the kernel launch that takes the most time; `cpu_baseline` is the fp32 CPU port of
-the oracle timed on this box's host cores on a bounded sample.
+Prints ONE JSON line (rank 0).  `value` is whole-job algorithmic GB/s with inputs resident in HBM
+(`single_stream` beside it: the same launches in one stream, as a network with dependent layers sees
+them); `e2e` is the same metric through the THNN_Cuda* entry points with pinned host buffers,
+host<->device copies timed; `roofline` describes the kernel launch that takes the most time;
+`cpu_baseline` is the fp32 CPU port of the oracle timed on this box's host cores on the same 64 images;
+`parity` holds the error figures of the benchmarked kernels against the fp64 oracle.
 """
 import argparse
 import json
@@ -34,8 +36,8 @@ BATCH = 64
 SEED = 1234
 METRIC = "dwconv_fwd_bwd_hbm_gbs"
 
-# DRAM traffic (read + write, MB) of one launch of the kernels that can top the per-launch time, from the
-# ncu capture summarised in profiles/dwconv_stack_ncu_sections.md (key: "<op>_<layer>").
+# DRAM traffic (read + write, MB) of one launch of the kernels that can top the per-launch time, from an
+# ncu capture of this command's depthwise launches (key: "<op>_<layer>").
 NCU_TRAFFIC_MB = {"wgrad_2": 261.3, "wgrad_1": 209.7, "fwd_2": 239.1, "dgrad_2": 199.1, "fwd_1": 155.1, "dgrad_1": 154.6,
                   "wgrad_3": 209.9, "fwd_3": 153.7, "dgrad_3": 153.2}
 
@@ -140,15 +142,15 @@ def make_host_inputs(n):
 
 def run_reference(args):
     """--impl reference: the CPU arm.  torch/nn's CPU THNN (what the reference's tests compare with) is not
-    part of the reference tree and nothing of the reference compiles here, so this times the fp32 OpenMP
-    port of the oracle on all host cores, on a bounded sample (a few images per layer) of the workload."""
+    part of the reference tree and the reference's own depthwise path is GPU code, so this times the fp32
+    OpenMP port of the oracle on all host cores, on the full workload (64 images per layer), every step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    res = cpu_baseline(target_seconds=8.0, steps=args.steps, warmup=min(args.warmup, 1))
+    res = cpu_baseline(steps=args.steps, warmup=min(args.warmup, 1), budget_seconds=150.0)
     line = {
         "impl": "reference", "metric": METRIC, "value": res["value"], "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+        "steps": res["steps"], "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(res["sample_images"], 1),
         "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
@@ -158,13 +160,15 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def cpu_baseline(target_seconds=12.0, steps=1, warmup=0):
-    """Times the fp32 CPU port (oracle/thnn_ref.c, ref32_*) of the same 13-layer fwd+dgrad+wgrad stack on
-    `n` images per layer, with n chosen so one step takes about target_seconds / (steps + warmup)."""
+def cpu_baseline(steps=1, warmup=0, budget_seconds=30.0):
+    """Times the fp32 CPU port (oracle/thnn_ref.c, ref32_*) of the same 13-layer fwd+dgrad+wgrad stack on the
+    full batch of 64 images per layer, on every host core (the OpenMP thread count is set explicitly:
+    launchers export OMP_NUM_THREADS=1).  Runs `steps` steps, fewer only if they would exceed budget_seconds."""
     import numpy as np
     from oracle.thnn_ref import Ref
     ref = Ref("ref32_")
     cores = os.cpu_count() or 1
+    threads = ref.set_threads(cores)
 
     def one_step(data):
         for (C, HW, s), d in zip(LAYERS, data):
@@ -174,43 +178,83 @@ def cpu_baseline(target_seconds=12.0, steps=1, warmup=0):
         for (C, HW, s), d in zip(LAYERS, data):
             ref.dwconv_acc_grad(d["x"], d["gy"], np.zeros_like(d["w"]), np.zeros_like(d["b"]), s, s, 1, 1, 1.0)
 
-    probe = make_host_inputs(1)
-    one_step(probe)
+    n = BATCH
+    data = make_host_inputs(n)
     t0 = time.perf_counter()
-    one_step(probe)
-    t1 = time.perf_counter() - t0
-    per_step_budget = target_seconds / max(1, steps + warmup)
-    n = int(max(1, min(BATCH, per_step_budget / max(t1, 1e-4))))
-    data = make_host_inputs(n) if n > 1 else probe
-    for _ in range(warmup):
+    one_step(data)                                   # first touch of the pages, thread pool start
+    first = time.perf_counter() - t0
+    steps = int(max(1, min(steps, budget_seconds / max(first, 1e-3) - warmup - 1)))
+    for _ in range(max(warmup - 1, 0)):
         one_step(data)
     t0 = time.perf_counter()
     for _ in range(steps):
         one_step(data)
     dt = (time.perf_counter() - t0) / steps
-    return {"value": step_bytes(n) / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-            "sample": "13-layer depthwise stack fwd+dgrad+wgrad on %d image(s) per layer (of %d), fp32 OpenMP "
-                      "port of the oracle, %d step(s)" % (n, BATCH, steps),
-            "ms_per_step": dt * 1e3, "sample_images": n}
+    return {"value": step_bytes(n) / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": "13-layer depthwise stack fwd+dgrad+wgrad on all %d images per layer, fp32 OpenMP port of the "
+                      "oracle on %d threads, %d step(s)" % (n, threads, steps),
+            "ms_per_step": dt * 1e3, "sample_images": n, "steps": steps}
+
+
+def parity_check(T, fwd, dgrad, wgrad, layers=(7, 12, 13)):
+    """Runs three of the benchmarked layers (the 14x14 stride-1 and stride-2 and the 7x7 one, all 64 images) once
+    more and compares y, gx and the parameter gradients with the fp64 oracle: worst tensor-normalised error
+    max|got-want|/max|want| and worst element-wise relative error with a floor of 1e-3 max|want|."""
+    import numpy as np
+    import torch
+    from oracle.thnn_ref import Ref
+    ref = Ref("ref64_")
+    ref.set_threads(os.cpu_count() or 1)
+
+    def errs(got, want):
+        got, want = got.astype(np.float64), want.astype(np.float64)
+        m = float(np.max(np.abs(want)))
+        d = np.abs(got - want)
+        return float(d.max() / m), float(np.max(d / np.maximum(np.abs(want), 1e-3 * m)))
+
+    worst = {"fwd": [0.0, 0.0], "grad": [0.0, 0.0]}
+    for li in layers:
+        t = T[li - 1]
+        s, HW = t["s"], t["HW"]
+        t["gw"].zero_()
+        t["gb"].zero_()
+        fwd(t)
+        dgrad(t)
+        wgrad(t)
+        torch.cuda.synchronize()
+        x, w, b, gy = (t[k].cpu().numpy() for k in ("x", "w", "b", "gy"))
+        rgw, rgb = ref.dwconv_acc_grad(x, gy, np.zeros_like(w), np.zeros_like(b), s, s, 1, 1, 1.0)
+        pairs = [("fwd", t["y"].cpu().numpy(), ref.dwconv_forward(x, w, b, s, s, 1, 1)),
+                 ("grad", t["gx"].cpu().numpy(), ref.dwconv_grad_input(gy, w, HW, HW, s, s, 1, 1)),
+                 ("grad", t["gw"].cpu().numpy(), rgw), ("grad", t["gb"].cpu().numpy(), rgb)]
+        for kind, got, want in pairs:
+            n, r = errs(got, want)
+            worst[kind][0] = max(worst[kind][0], n)
+            worst[kind][1] = max(worst[kind][1], r)
+    return {"against": "fp64 CPU oracle, whole tensors, layers %s at batch %d" % (list(layers), BATCH),
+            "forward": {"norm_err": worst["fwd"][0], "rel_err_floor_1e-3": worst["fwd"][1], "bar": 1e-5},
+            "gradients": {"norm_err": worst["grad"][0], "rel_err_floor_1e-3": worst["grad"][1], "bar": 1e-4},
+            "ok": worst["fwd"][0] <= 1e-5 and worst["grad"][0] <= 1e-4}
 
 
 def workload_config(n, world):
     return {"workload": "MobileNetV1 depthwise stack: 13 SpatialDepthWiseConvolution 3x3 pad 1 layers, "
-                        "fwd + updateGradInput + accGradParameters each (BASELINE config 2)",
+                        "fwd + updateGradInput + accGradParameters each",
             "batch_per_gpu": n, "global_batch": n * world, "layers": len(LAYERS),
             "layout": "NCHW fp32", "l2": "inputs larger than L2: one step touches 2.5 GB of tensors per GPU and a "
                                          "tensor is re-read only after >= 1.2 GB of other traffic",
             "parallelism": "dp%d (batch-sharded, NCCL all-reduce of depthwise weight gradients)" % world
                            if world > 1 else "single GPU",
             "launch": "39 kernels per step replayed from CUDA graphs, consecutive (independent) layers on alternating "
-                      "streams; with N > 1 the weight-gradient all-reduce overlaps the input-gradient kernels"}
+                      "streams; with N > 1 the weight-gradient all-reduce overlaps the input-gradient kernels",
+            "timing": "rounds of exactly --steps steps, back to back for >= 1 s; ms_per_step is the mean over all rounds"}
 
 
 def other_configs_bench(dev):
     """The other single-GPU configurations of the path, one kernel at a time (device-resident inputs, CUDA events on
-    the launching stream, median of the repeats): im2col-GEMM convolution (BASELINE config 3, 3xTF32 on the
-    tensor cores; TFLOP/s are fp32-equivalent: 2*N*K*C*kH*kW*oH*oW per pass) and batch normalisation +
-    3x3/2 max pooling at 256x64x112x112 (config 4; GB/s are algorithmic bytes: BN 2 tensors forward and 3
+    the launching stream, median of the repeats): im2col-GEMM convolution (ResNet-shaped 3x3 and 1x1 layers at
+    batch 128, 3xTF32 on the tensor cores; TFLOP/s are fp32-equivalent: 2*N*K*C*kH*kW*oH*oW per pass) and batch
+    normalisation + 3x3/2 max pooling at 256x64x112x112 (GB/s are algorithmic bytes: BN 2 tensors forward and 3
     backward, pooling input + output + int64 indices).  Buffers rotate so that successive launches never
     find their operands in L2."""
     import torch
@@ -235,7 +279,7 @@ def other_configs_bench(dev):
         return sorted(ts)[len(ts) // 2]
 
     res = {}
-    # ---- config 3: SpatialConvolutionMM --------------------------------------------------------------
+    # ---- SpatialConvolutionMM --------------------------------------------------------------
     for name, (N, C, K, HW, k, pad) in (("convmm_3x3_256to256_14x14_n128", (128, 256, 256, 14, 3, 1)),
                                          ("convmm_1x1_1024to256_14x14_n128", (128, 1024, 256, 14, 1, 0))):
         nbuf = 6
@@ -255,7 +299,7 @@ def other_configs_bench(dev):
             res["%s_%s" % (name, op)] = {"us": round(ms * 1e3, 1), "value": round(flop / (ms * 1e-3) / 1e12, 1),
                                          "unit": "TFLOP/s fp32-equivalent (3xTF32 tcgen05)"}
         del xs, gys, ys, gxs
-    # ---- config 4: BatchNormalization and SpatialMaxPooling --------------------------------------------
+    # ---- BatchNormalization and SpatialMaxPooling --------------------------------------------
     N, C, HW = 256, 64, 112
     x = torch.randn((N, C, HW, HW), device=dev, generator=gen) * 2 + 0.5
     y = torch.empty_like(x)
@@ -373,13 +417,15 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--min-seconds", type=float, default=1.0,
+                    help="the timed region repeats rounds of --steps steps until it has lasted about this long")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--graph-streams", type=int, default=2,
                     help="streams the launches of the depthwise stack alternate between inside the CUDA graph")
     ap.add_argument("--no-mobilenet", action="store_true")
-    ap.add_argument("--no-others", action="store_true", help="skip the config 3 / config 4 single-kernel timings")
+    ap.add_argument("--no-others", action="store_true", help="skip the single-kernel timings of the GEMM convolution, batch norm and pooling")
     ap.add_argument("--mobilenet-batch", type=int, default=1024, help="global batch of the MobileNetV1 step")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -514,20 +560,42 @@ def main():
         sampler.uuid = "GPU-" + sampler.uuid if not sampler.uuid.startswith("GPU-") else sampler.uuid
         sampler.start()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
+    # The timed region is `rounds` back-to-back rounds of exactly `steps` steps each, enough rounds to last
+    # about args.min_seconds, so that the clocks are sampled over a sustained run; CUDA events bracket every
+    # round and the reported time per step is the mean over all of them.
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
     for _ in range(steps):
         step()
-    e1.record()
+    p1.record()
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
+    probe_ms = max(p0.elapsed_time(p1), 1e-3)
+    rounds = int(max(1, min(2000, -(-args.min_seconds * 1e3 // probe_ms))))
+    if world > 1:
+        rt = torch.tensor([rounds], device=dev)
+        dist.all_reduce(rt, op=dist.ReduceOp.MAX)
+        rounds = int(rt.item())
+        dist.barrier()
+    torch.cuda.synchronize()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(rounds + 1)]
+    marks[0].record()
+    for r in range(rounds):
+        for _ in range(steps):
+            step()
+        marks[r + 1].record()
+    torch.cuda.synchronize()
+    ms = marks[0].elapsed_time(marks[rounds])
+    round_ms = sorted(marks[r].elapsed_time(marks[r + 1]) / steps for r in range(rounds))
     clocks = sampler.stop() if sampler else None
     if world > 1:
         dist.barrier()
         tt = torch.tensor([ms], device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         ms = float(tt.item())
-    ms_per_step = ms / steps
+    ms_per_step = ms / (steps * rounds)
+    timed = {"rounds": rounds, "steps_per_round": steps, "total_ms": round(ms, 2),
+             "ms_per_step_best_round": round(round_ms[0], 4), "ms_per_step_median_round": round(round_ms[rounds // 2], 4),
+             "ms_per_step_worst_round": round(round_ms[-1], 4)}
     value = step_bytes(BATCH) * world / (ms_per_step * 1e-3) / 1e9
 
     # ---- the graphs compute what direct launches on one stream compute ------------------------------
@@ -562,13 +630,15 @@ def main():
             torch.cuda.synchronize()
             s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s0.record()
-            for _ in range(steps):
+            for _ in range(steps * rounds):
                 g1.replay()
             s1.record()
             torch.cuda.synchronize()
-            sms = s0.elapsed_time(s1) / steps
+            sms = s0.elapsed_time(s1) / (steps * rounds)
+            peak1, _ = measured_peaks()
             single_stream = {"ms_per_step": round(sms, 4), "value": round(step_bytes(BATCH) / (sms * 1e-3) / 1e9, 1),
-                             "unit": "GB/s"}
+                             "unit": "GB/s", "frac_of_peak": round(step_bytes(BATCH) / (sms * 1e-3) / 1e9 / peak1, 4),
+                             "note": "the same 39 launches replayed from a graph in ONE stream"}
 
     # ---- per-kernel durations (CUDA events around every launch, same stream) ------------------------
     ksteps = min(steps, 10)
@@ -610,11 +680,15 @@ def main():
                 "per_kernel": [dict(op=k["op"], layer=k["layer"], us=round(k["ms"] * 1e3, 2),
                                     gbs=round(k["bytes"] / (k["ms"] * 1e-3) / 1e9, 0)) for k in per]}
 
-    # ---- end to end through the C ABI with host buffers ----------------------------------------------
+    # ---- end to end through the THNN_Cuda* entry points with host buffers -----------------------------
+    # The calls a Lua module makes: THNN_CudaSpatialDepthWiseConvolution_updateOutput / _updateGradInput /
+    # _accGradParameters on tensor structs (lib/THCUNN/generic/THCUNN.h:667-702), outputs resized by the callee.
     e2e = None
     H = None
     if not args.no_e2e:
         import numpy as np
+        from cunn_b200 import thnn
+        nnb = thnn.THNN()
         esteps = max(1, min(steps, 3))
         H = []
         for t in T:
@@ -639,15 +713,18 @@ def main():
                     ev_in = torch.cuda.Event()
                     ev_in.record(s_in)
                 s_cmp.wait_event(ev_in)
-                fwd(t)
-                dgrad(t)
-                wgrad(t)
+                st = t["s"]
+                y = nnb.SpatialDepthWiseConvolution_updateOutput(t["x"], t["w"], t["b"], 3, 3, st, st, 1, 1)
+                gx = nnb.SpatialDepthWiseConvolution_updateGradInput(t["x"], t["gy"], t["w"], 3, 3, st, st, 1, 1)
+                nnb.SpatialDepthWiseConvolution_accGradParameters(t["x"], t["gy"], t["gw"], t["gb"], 3, 3, st, st, 1, 1, 1.0)
                 ev_c = torch.cuda.Event()
                 ev_c.record(s_cmp)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(ev_c)
-                    h["y"].copy_(t["y"], non_blocking=True)
-                    h["gx"].copy_(t["gx"], non_blocking=True)
+                    h["y"].copy_(y, non_blocking=True)
+                    h["gx"].copy_(gx, non_blocking=True)
+                    y.record_stream(s_out)
+                    gx.record_stream(s_out)
             if world > 1:
                 dist.all_reduce(flat_grad)
             hgrad.copy_(flat_grad, non_blocking=True)
@@ -670,11 +747,18 @@ def main():
             tt = torch.tensor([ems], device=dev)
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             ems = float(tt.item())
+        nnb.close()
         e2e = {"value": round(step_bytes(BATCH) * world / (ems / esteps * 1e-3) / 1e9, 2), "unit": "GB/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": esteps,
-               "ms_per_step": round(ems / esteps, 3)}
+               "ms_per_step": round(ems / esteps, 3),
+               "api": "THNN_CudaSpatialDepthWiseConvolution_updateOutput / _updateGradInput / _accGradParameters"}
 
-    # ---- MobileNetV1 training step, batch-sharded over the ranks (BASELINE config 5) ----------------
+    # ---- the benchmarked kernels against the fp64 oracle (checker only; part of the CPU leg) --------------
+    parity = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        parity = parity_check(T, fwd, dgrad, wgrad)
+
+    # ---- MobileNetV1 training step, batch-sharded over the ranks ------------------------------------
     mbn = None
     if not args.no_mobilenet:
         mbn = mobilenet_bench(args, dev, world, rank, dist if world > 1 else None)
@@ -688,14 +772,15 @@ def main():
     status = device_status()
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        c = cpu_baseline(target_seconds=12.0, steps=1, warmup=0)
+        c = cpu_baseline(steps=3, warmup=1, budget_seconds=30.0)
         cpu = {k: (round(c[k], 3) if isinstance(c[k], float) else c[k]) for k in ("value", "unit", "cores", "kind", "sample")}
 
     if rank == 0:
         line = {"metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": steps,
                 "warmup": warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(BATCH, world),
-                "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * steps,
+                "clocks": clocks, "timed": timed, "single_stream": single_stream, "e2e": e2e,
+                "gpu_launches": launches_per_step * steps * rounds, "parity": parity,
                 "roofline": roofline, "cpu_baseline": cpu, "mobilenet_v1": mbn, "other_configs": others, "device_status": status}
         print(json.dumps(line))
     if world > 1:

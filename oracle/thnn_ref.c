@@ -17,12 +17,16 @@
  *                                          THNN uses for float tensors.
  *
  * PARITY STATUS: the reference ships no golden vectors and its CPU comparison
- * library (torch/nn THNN) is absent from the reference tree, so this
- * restatement is pinned against (a) the reference's in-tree self-consistency
- * tests (depthwise == per-channel SpatialConvolution, average-pool known
- * answers) and (b) fixtures produced by PyTorch's CPU operators, a descendant
- * of the same THNN code.  Against the reference's own CPU library: parity
- * unpinned.
+ * library (torch/nn THNN) is absent from the reference tree.  This restatement
+ * is pinned against (a) the reference's OWN device kernels, compiled unchanged
+ * from the reference tree (oracle/_ref, see ref_kernels_*.cu): max and average
+ * pooling run on the host and must agree bit for bit (values, int64 indices);
+ * batch normalisation and the unfold + SGEMM convolution schedules ran on a
+ * B200 and their outputs are committed as tests/golden/refk_*.npz; (b) the
+ * reference's in-tree self-consistency tests (depthwise == per-channel
+ * SpatialConvolution, average-pool known answers); (c) fixtures produced by
+ * PyTorch's CPU operators, a descendant of the same THNN code.  Against
+ * torch/nn's CPU library itself: unpinned (absent).
  *
  * Each function cites the reference file:line whose arithmetic it follows
  * (paths relative to the reference project root).
@@ -53,6 +57,17 @@ typedef REF_ACC acc_t;
 #endif
 
 int FN(index_base)(void) { return REF_INDEX_BASE; }
+
+/* Number of OpenMP threads the routines below use from now on (launchers such as
+ * torch.distributed.run export OMP_NUM_THREADS=1, which the timed baseline must not inherit). */
+#ifdef _OPENMP
+#include <omp.h>
+void FN(set_threads)(int n) { if (n > 0) omp_set_num_threads(n); }
+int FN(max_threads)(void) { return omp_get_max_threads(); }
+#else
+void FN(set_threads)(int n) { (void)n; }
+int FN(max_threads)(void) { return 1; }
+#endif
 
 /* ------------------------------------------------------------------------ */
 /* Depthwise convolution.                                                   */

@@ -45,6 +45,11 @@ class Ref:
         self.prefix = prefix
         self.index_base = self._fn("index_base", ctypes.c_int)()
 
+    def set_threads(self, n):
+        """Fixes the OpenMP thread count of this library (both prefixes share one runtime); returns the count in use."""
+        self._fn("set_threads")(int(n))
+        return self._fn("max_threads", ctypes.c_int)()
+
     def _fn(self, name, restype=None):
         f = getattr(self.lib, self.prefix + name)
         f.restype = restype

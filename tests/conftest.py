@@ -87,7 +87,7 @@ def norm_err(got, want):
 
 # ---------------------------------------------------------------------------------------------
 # Parity bookkeeping: every assert_parity() call records both error figures; the table is printed
-# at the end of the run and, when the scratch folder for GPU runs exists, written there as JSON.
+# at the end of the run and written as JSON to the file the CUNN_PARITY_REPORT variable names, if set.
 _PARITY = []
 
 
@@ -123,8 +123,8 @@ def pytest_terminal_summary(terminalreporter):
         p = rec["fp32_port_rel_err_floor_1e-3"]
         tr.write_line("%-58s tol %.0e  %.2e  %.2e  %s" % (rec["name"][:58], rec["tol"], rec["norm_err"],
                                                          rec["rel_err_floor_1e-3"], "-" if p is None else "%.2e" % p))
-    out = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out):
+    out = os.environ.get("CUNN_PARITY_REPORT")
+    if out:
         import json
-        with open(os.path.join(out, "parity_report.json"), "w") as f:
+        with open(out, "w") as f:
             json.dump(_PARITY, f, indent=1)

@@ -131,7 +131,8 @@ def test_convmm_empty_batch_and_errors(F):
 
 @pytest.mark.parametrize("cfg", [(128, 256, 256, 14, 3, 1), (128, 1024, 256, 14, 1, 0)])
 def test_convmm_full_size_adjoint_identities(F, cfg):
-    # BASELINE config 3 at full size, where the CPU oracle is too slow: the three passes are the three partial
+    # The two benchmarked GEMM convolutions at full size (a size-independent property beside the whole-tensor
+    # oracle comparison of test_full_size_gpu.py): the three passes are the three partial
     # derivatives of one trilinear form, so <conv(x, W), gy> == <x, dgrad(gy, W)> == <wgrad(x, gy), W>, and the
     # bias gradient is the plain sum of gy.  Inner products are taken in fp64; 1e-4 is the GEMM-path bar.
     N, C, K, HW, k, pad = cfg

@@ -82,7 +82,7 @@ def test_dwconv_golden(F, name):
 
 
 def test_dwconv_config1(F, ref64):
-    # BASELINE config 1: N=8, C=32, 56x56, 3x3 s1 p1 m1; scale 1 and 0.5 on non-zero gradWeight
+    # the single-layer configuration: N=8, C=32, 56x56, 3x3 s1 p1 m1; scale 1 and 0.5 on non-zero gradWeight
     case = make_case(1234, 8, 32, 56, 56, 1, 3, 1, 1)
     check_against_oracle(ref64, F, *case, 1, 1, 1.0)
     check_against_oracle(ref64, F, *case, 1, 1, 0.5)
@@ -171,7 +171,7 @@ def test_dwconv_unaligned_pointers_take_generic_path(F, ref64):
 
 
 def test_dwconv_linearity_full_size(F):
-    # Size-independent property at a BASELINE config-2 layer (N=64, C=128, 56x56): conv is linear in x
+    # Size-independent property at a MobileNetV1 depthwise layer at batch 64 (C=128, 56x56): conv is linear in x
     # and in gy, and <gy, conv(x)> == <dgrad(gy), x> (adjointness ties forward and input gradient).
     torch.manual_seed(0)
     N, C, HW = 64, 128, 56

@@ -1,5 +1,7 @@
-"""The CPU oracle against the committed PyTorch-CPU fixtures and against the
-reference's own self-consistency tests.  No GPU needed."""
+"""The CPU oracle against the committed fixtures — outputs of the reference's own device kernels run on a
+B200 (tests/golden/refk_*.npz, made by tests/golden/make_golden_refkernels.py) and outputs of PyTorch's CPU
+operators (the other files, tests/golden/make_golden.py) — and against the reference's own self-consistency
+tests.  No GPU needed."""
 import numpy as np
 import pytest
 
@@ -202,3 +204,82 @@ def test_full_conv_oracle_vs_golden(ref64, name):
     assert rel_err(gw, g["gw"]) < 1e-6
     if has_b:
         assert rel_err(gb, g["gb"]) < 1e-6
+
+
+# ---------------------------------------------------------------------------------------------------
+# Fixtures computed by the reference's own kernels (fp32 arithmetic in the reference's summation order,
+# so agreement with the fp64 oracle is to fp32 rounding of these small cases, not to 1e-6).
+REFK_TOL = 2e-5
+
+
+@pytest.mark.parametrize("name", ["refk_convmm_3x3", "refk_convmm_5x5_s2", "refk_convmm_1x1"])
+def test_convmm_oracle_vs_refkernel_golden(ref64, name):
+    g = golden(name)
+    K, k, d, pad, has_b = [int(v) for v in g["params"]]
+    b = g["b"] if has_b else None
+    H, W = g["x"].shape[2:]
+    assert rel_err(ref64.convmm_forward(g["x"], g["w"], b, d, d, pad, pad), g["y"]) < REFK_TOL
+    assert rel_err(ref64.convmm_grad_input(g["gy"], g["w"], H, W, d, d, pad, pad), g["gx"]) < REFK_TOL
+    gw, gb = ref64.convmm_acc_grad(g["x"], g["gy"], g["gw0"], g["gb0"] if has_b else None, d, d, pad, pad, float(g["scale"]))
+    assert rel_err(gw, g["gw"]) < REFK_TOL
+    if has_b:
+        assert rel_err(gb, g["gb"]) < REFK_TOL
+
+
+@pytest.mark.parametrize("name", ["refk_dwconv_s1", "refk_dwconv_s2_m3", "refk_dwconv_k5_nobias"])
+def test_dwconv_oracle_vs_refkernel_golden(ref64, name):
+    g = golden(name)
+    M, k, d, pad, has_b = [int(v) for v in g["params"]]
+    b = g["b"] if has_b else None
+    H, W = g["x"].shape[2:]
+    assert rel_err(ref64.dwconv_forward(g["x"], g["w"], b, d, d, pad, pad), g["y"]) < REFK_TOL
+    assert rel_err(ref64.dwconv_grad_input(g["gy"], g["w"], H, W, d, d, pad, pad), g["gx"]) < REFK_TOL
+    gw, gb = ref64.dwconv_acc_grad(g["x"], g["gy"], g["gw0"], g["gb0"] if has_b else None, d, d, pad, pad, float(g["scale"]))
+    assert rel_err(gw, g["gw"]) < REFK_TOL
+    if has_b:
+        assert rel_err(gb, g["gb"]) < REFK_TOL
+
+
+@pytest.mark.parametrize("name", ["refk_bn_affine", "refk_bn_plain"])
+def test_bn_oracle_vs_refkernel_golden(ref64, name):
+    g = golden(name)
+    affine = int(g["params"][0])
+    w = g["g"] if affine else None
+    b = g["b"] if affine else None
+    mom, eps, scale = float(g["momentum"]), float(g["eps"]), float(g["scale"])
+    y, rm, rv, sm, ss = ref64.bn_forward(g["x"], w, b, g["rm0"], g["rv0"], True, mom, eps)
+    for got, key in ((y, "y_train"), (rm, "rm_train"), (rv, "rv_train"), (sm, "save_mean"), (ss, "save_std")):
+        assert rel_err(got, g[key]) < REFK_TOL, key
+    for train, sfx in ((True, "_train"), (False, "_eval")):
+        gx, gw, gb = ref64.bn_backward(g["x"], g["gy"], w, g["rm0"], g["rv0"], g["save_mean"], g["save_std"], train, scale, eps,
+                                       gw=g["gw0"], gb=g["gb0"])
+        assert rel_err(gx, g["gx" + sfx]) < REFK_TOL
+        assert rel_err(gw, g["gw" + sfx]) < REFK_TOL and rel_err(gb, g["gb" + sfx]) < REFK_TOL
+    assert rel_err(ref64.bn_forward(g["x"], w, b, g["rm0"], g["rv0"], False, mom, eps)[0], g["y_eval"]) < REFK_TOL
+
+
+@pytest.mark.parametrize("name", ["refk_unfold_3x3_s2", "refk_unfold_3x2_dil2"])
+def test_unfold_index_math_vs_refkernel_golden(name):
+    """im2col / col2im of the reference (lib/THCUNN/im2col.h:10-121) against a direct restatement of their index
+    arithmetic: col[(c*kH+i)*kW+j, oh*oW+ow] = x[c, oh*dH-padH+i*dilH, ow*dW-padW+j*dilW] (0 outside), and the
+    fold is its transpose.  Values are copied, so equality is exact for the unfold."""
+    g = golden(name)
+    kH, kW, padH, padW, dH, dW, dilH, dilW = [int(v) for v in g["params"]]
+    x = g["x"]
+    C, H, W = x.shape
+    oH = (H + 2 * padH - (dilH * (kH - 1) + 1)) // dH + 1
+    oW = (W + 2 * padW - (dilW * (kW - 1) + 1)) // dW + 1
+    col = np.zeros((C * kH * kW, oH * oW), np.float32)
+    folded = np.zeros((C, H, W), np.float64)
+    for c in range(C):
+        for i in range(kH):
+            for j in range(kW):
+                r = (c * kH + i) * kW + j
+                for oh in range(oH):
+                    for ow in range(oW):
+                        h, w_ = oh * dH - padH + i * dilH, ow * dW - padW + j * dilW
+                        if 0 <= h < H and 0 <= w_ < W:
+                            col[r, oh * oW + ow] = x[c, h, w_]
+                            folded[c, h, w_] += g["col_in"][r, oh * oW + ow]
+    assert np.array_equal(col, g["col"])
+    assert rel_err(folded, g["folded"]) < 5e-6      # the reference folds in fp32

@@ -43,7 +43,7 @@ def test_maxpool_golden(F, ref64, name):
 
 @pytest.mark.parametrize("shape", [
     # N, C, H, W, k, d, pad, ceil, ties
-    (2, 3, 112, 112, 3, 2, 1, False, False),   # fast path (BASELINE config 4 geometry)
+    (2, 3, 112, 112, 3, 2, 1, False, False),   # fast path (geometry of the benchmarked pooling layer)
     (2, 5, 32, 48, 3, 2, 1, False, True),      # fast path with many ties
     (3, 2, 31, 40, 3, 2, 1, False, True),      # fast path, odd height
     (2, 3, 112, 112, 3, 2, 1, True, False),    # ceil mode changes the output size -> generic
@@ -93,7 +93,7 @@ def test_maxpool_rejects_bad_arguments(F):
 
 
 def test_maxpool_full_size_properties(F):
-    # BASELINE config 4 geometry at reduced batch (N=32): the stored index must point at the stored value,
+    # the benchmarked geometry at reduced batch (N=32): the stored index must point at the stored value,
     # and backward must conserve the gradient mass: sum(gx) == sum(gy).
     torch.manual_seed(0)
     x = torch.randn((32, 64, 112, 112), device="cuda") * 2 + 0.5
@@ -175,7 +175,7 @@ def test_bn_golden(F, name):
 
 
 @pytest.mark.parametrize("shape,affine", [
-    ((4, 64, 112, 112), True),     # BASELINE config 4 geometry, reduced batch
+    ((4, 64, 112, 112), True),     # the benchmarked geometry, reduced batch
     ((7, 5, 9, 11), True),         # S not a multiple of 4 -> scalar path
     ((3, 16, 32, 32), False),      # H*W = 1024, the reference's extra case; no affine
     ((300, 3, 2, 2), True),        # more images than chunks
@@ -240,7 +240,7 @@ def test_bn_relu_fused_equals_separate_calls(F, shape):
 
 
 def test_bn_full_size_properties(F):
-    # BASELINE config 4 geometry at reduced batch (N = 64: 822 MB would not leave room on a shared test box):
+    # the benchmarked geometry at reduced batch (N = 64; test_full_size_gpu.py runs the full 256):
     # with gamma = 1, beta = 0 the training output has zero mean and unit biased variance per channel, the
     # saved statistics are those of x, and the input gradient is orthogonal to 1 and to (x - mean).
     g = torch.Generator(device="cuda").manual_seed(8)
