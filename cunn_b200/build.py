@@ -26,6 +26,10 @@ FLAGS = [
 ]
 
 
+if os.environ.get("CUNN_B200_DEV_HOOKS"):      # sweep builds only: tuning switches that are not part of the library
+    FLAGS.append("-DCUNN_B200_DEV_HOOKS=1")
+
+
 def _sources():
     return sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cpp")))
 
@@ -44,6 +48,10 @@ def _compile(src, obj, verbose):
 
 def build(force=False, verbose=False):
     os.makedirs(OBJDIR, exist_ok=True)
+    stamp = os.path.join(OBJDIR, "flags.txt")
+    flags = " ".join(FLAGS)
+    if not os.path.exists(stamp) or open(stamp).read() != flags:
+        force = True                                # objects built with other flags do not mix
     dep_t = _deps_mtime()
     jobs, objs = [], []
     for src in _sources():
@@ -57,6 +65,8 @@ def build(force=False, verbose=False):
                 sys.stderr.write(out)
             if rc:
                 raise RuntimeError("nvcc failed on " + src)
+    with open(stamp, "w") as f:
+        f.write(flags)
     if jobs or not os.path.exists(SO):
         cmd = [NVCC, "-shared", "-ccbin", "/usr/bin/g++", "-o", SO] + objs + ["--cudart", "static", "-Xlinker", "--no-undefined"]
         r = subprocess.run(cmd, capture_output=True, text=True)

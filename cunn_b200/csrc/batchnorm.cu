@@ -12,6 +12,7 @@
 #include "common.cuh"
 
 #include <algorithm>
+#include <stdlib.h>
 
 namespace cunn {
 namespace bn {
@@ -106,6 +107,7 @@ __device__ __forceinline__ void chan_merge(double &n, double &mean, double &m2, 
 
 // The same merge as finish_stats_channel, by one warp: every lane folds its share of the chunks, then the lanes are
 // merged pairwise (fp64 divisions are slow; 37 chunks in one thread took 10 us).
+// `part` points at the channel's first partial.
 __device__ __forceinline__ void finish_stats_channel_warp(const ChunkStat *part, int c, int chunks, float *running_mean,
                                                           float *running_var, float *save_mean, float *save_std,
                                                           double momentum, double eps)
@@ -113,7 +115,7 @@ __device__ __forceinline__ void finish_stats_channel_warp(const ChunkStat *part,
     const int lane = threadIdx.x & 31;
     double n = 0.0, mean = 0.0, m2 = 0.0;
     for (int j = lane; j < chunks; j += 32) {
-        const float4 raw = __ldcg(reinterpret_cast<const float4 *>(part + c * chunks + j));
+        const float4 raw = __ldcg(reinterpret_cast<const float4 *>(part + j));
         if (raw.w <= 0.f) continue;
         const double nb = raw.w;
         chan_merge(n, mean, m2, nb, (double)raw.x + (double)raw.y / nb, (double)raw.z - (double)raw.y * (double)raw.y / nb);
@@ -253,7 +255,7 @@ stats_kernel(const float *__restrict__ x, ChunkStat *__restrict__ part, int N, i
     if (threadIdx.x == 0) part[blockIdx.x] = ChunkStat{k, s1, s2, n0 < n1 ? (float)((long long)(n1 - n0) * S) : 0.f};
     if (!counters) return;
     if (last_cta_of_channel(counters, c, chunks, &flag)) {
-        if (threadIdx.x < 32) finish_stats_channel_warp(part, c, chunks, running_mean, running_var, save_mean, save_std, momentum, eps);
+        if (threadIdx.x < 32) finish_stats_channel_warp(part + (size_t)c * chunks, c, chunks, running_mean, running_var, save_mean, save_std, momentum, eps);
         if (threadIdx.x == 0) counters[c] = 0u;
     }
 }
@@ -384,7 +386,7 @@ __device__ __forceinline__ void finish_grad_channel(const float2 *part, int c, i
 {
     double s = 0.0, d = 0.0;
     for (int j = 0; j < chunks; ++j) {
-        const float2 p = __ldcg(part + c * chunks + j);   // written by other CTAs
+        const float2 p = __ldcg(part + j);                // the channel's partials, written by other CTAs
         s += (double)p.x;
         d += (double)p.y;
     }
@@ -406,6 +408,44 @@ __device__ __forceinline__ void finish_grad_channel(const float2 *part, int c, i
     if (grad_bias) grad_bias[c] = (float)((double)grad_bias[c] + scale * s);
 }
 
+// The same totals by one warp: lanes add strided subsets in fp64 and are then folded in a fixed order, so the
+// result does not depend on timing.  Lane 0 publishes.
+__device__ __forceinline__ void finish_grad_channel_warp(const float2 *part, int c, int chunks, long long count, const float *weight,
+                                                         const float *bias, const float *mean_v, const float *std_or_var,
+                                                         int train, double eps, double scale, float *grad_weight,
+                                                         float *grad_bias, GradCoef *coef)
+{
+    const int lane = threadIdx.x & 31;
+    double s = 0.0, d = 0.0;
+    for (int j = lane; j < chunks; j += 32) {
+        const float2 p = __ldcg(part + j);
+        s += (double)p.x;
+        d += (double)p.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        s += __shfl_down_sync(0xffffffffu, s, o);
+        d += __shfl_down_sync(0xffffffffu, d, o);
+    }
+    if (lane != 0) return;
+    const float mean = mean_v[c];
+    const float stdv = train ? std_or_var[c] : (float)(1.0 / sqrt((double)std_or_var[c] + eps));
+    const float w = weight ? weight[c] : 1.f;
+    const double norm = 1.0 / (double)count;
+    GradCoef k;
+    k.mean = mean;
+    k.gmean = (float)(s * norm);
+    k.proj = (float)(d * norm * (double)stdv * (double)stdv);
+    k.gscale = stdv * w;
+    k.invstd = train ? std_or_var[c] : 1.f / sqrtf(std_or_var[c] + (float)eps);
+    k.gamma = w;
+    k.beta = bias ? bias[c] : 0.f;
+    k.pad = 0.f;
+    coef[c] = k;
+    if (grad_weight) grad_weight[c] = (float)((double)grad_weight[c] + scale * d * (double)stdv);
+    if (grad_bias) grad_bias[c] = (float)((double)grad_bias[c] + scale * s);
+}
+
 __global__ void __launch_bounds__(128)
 grad_finish_kernel(const float2 *__restrict__ part, int C, int chunks, long long count,
                    const float *__restrict__ weight, const float *__restrict__ bias, const float *__restrict__ mean_v,
@@ -413,7 +453,7 @@ grad_finish_kernel(const float2 *__restrict__ part, int C, int chunks, long long
                    float *__restrict__ grad_weight, float *__restrict__ grad_bias, GradCoef *__restrict__ coef)
 {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c < C) finish_grad_channel(part, c, chunks, count, weight, bias, mean_v, std_or_var, train, eps, scale, grad_weight, grad_bias, coef);
+    if (c < C) finish_grad_channel(part + (size_t)c * chunks, c, chunks, count, weight, bias, mean_v, std_or_var, train, eps, scale, grad_weight, grad_bias, coef);
 }
 
 // Backward, pass 1: per (channel, chunk) sums of gy and gy * (x - mean).
@@ -500,7 +540,7 @@ grad_stats_kernel(const float *__restrict__ x, const float *__restrict__ gy, flo
     if (!counters) return;
     if (last_cta_of_channel(counters, c, chunks, &flag)) {
         if (threadIdx.x == 0) {
-            finish_grad_channel(part, c, chunks, (long long)N * S, weight, bias, mean_v, std_or_var, train, eps_d, scale, grad_weight,
+            finish_grad_channel(part + (size_t)c * chunks, c, chunks, (long long)N * S, weight, bias, mean_v, std_or_var, train, eps_d, scale, grad_weight,
                                 grad_bias, coef);
             counters[c] = 0u;
         }
@@ -618,10 +658,499 @@ grad_apply_flat_kernel(const float *__restrict__ x, const float *__restrict__ gy
     }
 }
 
-// Ticket counters at the start of the workspace: one per channel for the forward statistics, one for the gradient
-// sums.  Zero when a call is enqueued, zero again when its kernels have run.
+
+// ---------------------------------------------------------------------------------------------------------------
+// Grouped passes: statistics and normalisation in ONE launch, ordered so that the second read of x finds it in L2.
+//
+// The two-launch path above streams the whole tensor twice through HBM (3 tensor passes forward, 5 backward, for
+// 2 and 3 algorithmic ones): by the time the normalise kernel starts, the statistics kernel has pushed the start
+// of the tensor out of the 126 MB L2.  Here the channels are taken in groups whose slabs (N planes per channel)
+// fit in a fraction of L2, and a persistent grid of co-resident CTAs (cooperative launch) walks the groups.
+//
+// Every CTA is two halves — four consumer warps and one copy-issuing warp each — with a stream of their own:
+//   * the statistics half reduces group after group (reads carry an L2 evict_last policy), hands in one partial
+//     per (CTA, channel) and takes a ticket; the CTA that draws a channel's last ticket merges the partials in fp64
+//     (in CTA order: results do not depend on timing), publishes mean / inverse std (or the gradient coefficients)
+//     and raises the channel's ready flag.  It never waits for another CTA, so it keeps HBM busy;
+//   * the apply half follows: per channel it waits for the ready flag — with a cycle limit, after which it records
+//     STATUS_FLAG_TIMEOUT and the CTA leaves — re-reads the group (evict_first: finished data leaves L2 first) and
+//     writes the result with 16-byte stores.  The last reader of a flag lowers it again.
+// The statistics half stays at most two groups ahead of its own CTA's apply half, which bounds what must stay
+// resident in L2.  All counters and flags are zero before the launch and zero after it.
+//
+// Data movement: each half sees its launch as ONE stream of stages (a stage = up to P consecutive float4 items of
+// one channel's sequence, i.e. a few runs of whole or partial planes).  The half's producer warp keeps kStages stages
+// in flight with 1-D TMA bulk copies into a shared-memory ring (a full and an empty mbarrier per slot, bounded
+// waits), across group boundaries: bytes in flight do not depend on registers or on the occupancy of the arithmetic,
+// and issuing copies is off the consumers' critical path.
+//
+// Work split: inside a group, the float4 items of its channels form one sequence (channel-major, N*L items per
+// channel); CTA b takes the b-th of `grid` equal shares, which may span channel boundaries ("segments").
+//
+// Forward statistics use one shift K per channel (the mean of the first 32 elements of the channel's first plane,
+// read by every CTA): sums of (x - K) and (x - K)^2 keep their fp32 accuracy when |mean| >> std, and partials with
+// a common shift merge by plain fp64 addition.
+struct GroupPlan {
+    int N, C, S, L;         // L = S / 4: float4 items per plane
+    int G, groups;          // channels per group (the last group may be smaller), number of groups
+    int pstride;            // partial slots per channel
+    int lookahead;          // groups the statistics half may run ahead of its CTA's apply half
+    long long NL;           // items per channel
+};
+
+constexpr int kStages = 3;              // per half
+constexpr int kStageBytes = 16384;      // per slot: 1024 items of one tensor (forward) or 512 items of two (backward)
+constexpr int kHalf = 128;              // consumer threads per half (4 warps); each half has a fifth warp that only issues copies
+constexpr int kGroupedThreads = 2 * (kHalf + 32);
+
+__device__ __forceinline__ unsigned long long l2_policy_evict_last()
+{
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ unsigned long long l2_policy_evict_first()
+{
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void st_hint(float4 *p, const float4 v, unsigned long long pol)
+{
+    asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;"
+                 ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "l"(pol) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned *p)
+{
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_u32(unsigned *p, unsigned v)
+{
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Barrier among the 128 threads of one half (barrier 0 is __syncthreads).
+__device__ __forceinline__ void half_sync(int half)
+{
+    if (half == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+    else asm volatile("bar.sync 2, 128;" ::: "memory");
+}
+
+// Sum over one half; sh: 4 floats of that half.
+__device__ __forceinline__ float half_sum(float v, float *sh, int half)
+{
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, w = (threadIdx.x >> 5) & 3;
+    half_sync(half);
+    if (lane == 0) sh[w] = v;
+    half_sync(half);
+    return (sh[0] + sh[1]) + (sh[2] + sh[3]);
+}
+
+// The CTAs whose shares touch channel cl (local index in the group) of a group of W items: first and last.
+__device__ __forceinline__ void channel_ctas(long long W, long long NL, int cl, int grid, int *b_first, int *b_last)
+{
+    *b_first = (int)((((long long)cl * NL + 1) * grid + W - 1) / W) - 1;
+    *b_last = (int)((((long long)(cl + 1) * NL) * grid + W - 1) / W) - 1;
+}
+
+struct GroupCounters {
+    unsigned *tick, *ready, *done;
+};
+
+// One stage of a half's stream.
+struct Stage {
+    int g, cl, c;           // group, channel inside the group, channel
+    int q, len;             // first item (in the channel's sequence) and item count
+    bool seg_first, seg_last, group_last;
+    int seg_items;          // items of the whole segment
+};
+
+// Enumerates the stages of CTA b, group after group.  Pure integer arithmetic on uniform values: the producer warp
+// and the consumers each step a copy of their own.
+struct StageIter {
+    GroupPlan gp;
+    int grid, b, P;
+    int g, Gg, cl;
+    long long W, lo, hi, pos, seg_end;   // the CTA's share [lo, hi) of the group sequence; position; end of the segment
+    bool in_group;
+
+    __device__ __forceinline__ void init(const GroupPlan &gp_, int grid_, int b_, int P_)
+    {
+        gp = gp_; grid = grid_; b = b_; P = P_;
+        g = -1; in_group = false;
+    }
+    __device__ __forceinline__ void enter_group()
+    {
+        Gg = min(gp.G, gp.C - g * gp.G);
+        W = (long long)Gg * gp.NL;
+        lo = W * b / grid; hi = W * (b + 1) / grid;
+        pos = lo;
+        cl = (int)(lo / gp.NL);
+        seg_end = min(hi, (long long)(cl + 1) * gp.NL);
+        in_group = pos < hi;
+    }
+    __device__ __forceinline__ bool next(Stage &st)
+    {
+        while (!in_group) {
+            if (++g >= gp.groups) return false;
+            enter_group();
+        }
+        const long long cbeg = (long long)cl * gp.NL;
+        const long long seg_beg = max(lo, cbeg);
+        st.g = g; st.cl = cl; st.c = g * gp.G + cl;
+        st.q = (int)(pos - cbeg);
+        st.len = (int)min((long long)P, seg_end - pos);
+        st.seg_first = pos == seg_beg;
+        st.seg_items = (int)(seg_end - seg_beg);
+        pos += st.len;
+        st.seg_last = pos == seg_end;
+        st.group_last = false;
+        if (st.seg_last) {
+            if (pos >= hi) { in_group = false; st.group_last = true; }
+            else { ++cl; seg_end = min(hi, (long long)(cl + 1) * gp.NL); }
+        }
+        return true;
+    }
+};
+
+// One warp: copies stage st of `tensors` tensors into a ring slot (runs of whole or partial planes, one bulk copy
+// each, all counted on the slot's barrier).
+template <int TENSORS>
+__device__ __forceinline__ void issue_stage(const Stage &st, const GroupPlan &gp, const float4 *t0, const float4 *t1,
+                                            float4 *slot_mem, int P, uint32_t bar, unsigned long long pol)
+{
+    const int lane = threadIdx.x & 31;
+    if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)st.len * 16u * TENSORS);
+    __syncwarp();
+    const int L = gp.L;
+    const int n0 = st.q / L, i0 = st.q - n0 * L, end = st.q + st.len;
+    const int runs = (end - 1) / L - n0 + 1;
+    const long long CL = (long long)gp.C * L, cbase = (long long)st.c * L;
+    for (int r = lane; r < runs; r += 32) {
+        const int start = r == 0 ? st.q : (n0 + r) * L;
+        const int rlen = min(r == 0 ? L - i0 : L, end - start);
+        const long long goff = cbase + (long long)(n0 + r) * CL + (r == 0 ? i0 : 0);
+        bulk_g2s_hint(smem_u32(slot_mem + (start - st.q)), t0 + goff, (uint32_t)rlen * 16u, bar, pol);
+        if (TENSORS == 2) bulk_g2s_hint(smem_u32(slot_mem + P + (start - st.q)), t1 + goff, (uint32_t)rlen * 16u, bar, pol);
+    }
+}
+
+struct GroupedArgs {
+    const float *x, *gy;             // gy: backward only
+    float *out;                      // y (forward) or gx (backward)
+    const float *weight, *bias;
+    void *part;                      // float2 partials, pstride per channel
+    GroupCounters cn;
+    float *running_mean, *running_var, *save_mean, *save_std;     // forward: written
+    const float *mean_v, *std_or_var;                              // backward: saved or running statistics
+    float *grad_weight, *grad_bias;
+    GradCoef *coef;
+    double momentum, eps, scale;
+    int train;
+    GroupPlan gp;
+    int *status;
+};
+
+// Forward merge for channel c by one warp: partials (sum (x - K), sum (x - K)^2) share the shift K.
+__device__ __forceinline__ void finish_stats_shifted_warp(const float2 *part, int c, int cnt, float K, long long count,
+                                                          float *running_mean, float *running_var, float *save_mean,
+                                                          float *save_std, double momentum, double eps)
+{
+    const int lane = threadIdx.x & 31;
+    double s1 = 0.0, s2 = 0.0;
+    for (int j = lane; j < cnt; j += 32) {
+        const float2 p = __ldcg(part + j);
+        s1 += (double)p.x;
+        s2 += (double)p.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        s1 += __shfl_down_sync(0xffffffffu, s1, o);
+        s2 += __shfl_down_sync(0xffffffffu, s2, o);
+    }
+    if (lane != 0) return;
+    const double n = (double)count;
+    const double mean = (double)K + s1 / n;
+    double m2 = s2 - s1 * s1 / n;
+    if (m2 < 0.0) m2 = 0.0;
+    const float meanf = (float)mean;
+    const float varN = (float)m2;
+    float invstd = 0.f;
+    if (varN != 0.f || (float)eps != 0.f) invstd = 1.f / sqrtf((float)(m2 / n) + (float)eps);
+    const float unbiased = (float)(m2 / (n - 1.0));
+    save_mean[c] = meanf;
+    save_std[c] = invstd;
+    running_mean[c] = (float)((1.0 - momentum) * (double)running_mean[c] + momentum * (double)meanf);
+    running_var[c] = (float)((1.0 - momentum) * (double)running_var[c] + momentum * (double)unbiased);
+}
+
+template <bool BWD, bool RELU>
+__global__ void __launch_bounds__(kGroupedThreads, 2)
+grouped_kernel(const GroupedArgs a)
+{
+    constexpr int T = BWD ? 2 : 1;
+    constexpr int P = kStageBytes / 16 / T;
+    extern __shared__ __align__(128) unsigned char ring_raw[];
+    __shared__ __align__(8) unsigned long long full_s[2][kStages];      // slot filled (transaction bytes)
+    __shared__ __align__(8) unsigned long long empty_s[2][kStages];     // slot read by the half's four consumer warps
+    __shared__ float sums_s[2][4];
+    __shared__ float k_s;
+    __shared__ int flag_s[2];
+    __shared__ volatile int applied_s;       // groups this CTA's apply half has finished
+    __shared__ volatile int abort_s;         // a wait ran out somewhere in the CTA: everybody leaves
+
+    const GroupPlan gp = a.gp;
+    const int grid = (int)gridDim.x, b = (int)blockIdx.x;
+    const int warp = (int)threadIdx.x >> 5, lane = (int)threadIdx.x & 31;
+    const int half = warp / 5, wi = warp % 5;                           // wi == 4: the half's producer warp
+    const int ht = wi * 32 + lane;                                      // consumer index inside the half, 0..127
+    float4 *ring = reinterpret_cast<float4 *>(ring_raw) + (size_t)half * kStages * T * P;     // [kStages][T][P] of this half
+    unsigned long long *bars = full_s[half], *empties = empty_s[half];
+    float *sh = sums_s[half];
+    const float4 *x4 = reinterpret_cast<const float4 *>(a.x), *g4 = reinterpret_cast<const float4 *>(a.gy);
+    const unsigned long long pol = half == 0 ? l2_policy_evict_last() : l2_policy_evict_first();
+
+    if (threadIdx.x == 0) {
+        for (int h = 0; h < 2; ++h)
+            for (int s = 0; s < kStages; ++s) {
+                mbar_init(smem_u32(&full_s[h][s]), 1);
+                mbar_init(smem_u32(&empty_s[h][s]), 4);
+            }
+        mbar_fence_init();
+        applied_s = 0;
+        abort_s = 0;
+    }
+    __syncthreads();
+
+    // A bounded wait on a barrier phase that also gives up when another part of the CTA has.
+    auto wait_phase = [&](unsigned long long *bar, uint32_t parity) -> bool {
+        const uint32_t addr = smem_u32(bar);
+        if (mbar_try_wait(addr, parity)) return true;
+        const long long t0 = clock64();
+        while (!mbar_try_wait(addr, parity)) {
+            if (abort_s) return false;
+            if (clock64() - t0 > 2000000000LL) {
+                if (a.status) atomicExch(a.status, (int)STATUS_MBARRIER_TIMEOUT);
+                abort_s = 1;
+                return false;
+            }
+        }
+        return true;
+    };
+
+    if (wi == 4) {
+        // ------------------------------------------------ producer warp of this half -----------------------------------
+        // Issues every stage of the half's stream, kStages ahead of the consumers: a slot is refilled as soon as the four
+        // consumer warps have released it.  Before leaving it lets its last copies land (shared memory stays valid until
+        // the whole CTA has exited, but nothing may still be in flight when it does).
+        StageIter prod;
+        prod.init(gp, grid, b, P);
+        Stage ps;
+        int i = 0;
+        for (; prod.next(ps); ++i) {
+            const int slot = i % kStages;
+            if (i >= kStages && !wait_phase(empties + slot, (uint32_t)(((i / kStages) - 1) & 1))) break;
+            issue_stage<T>(ps, gp, x4, g4, ring + (size_t)slot * T * P, P, smem_u32(bars + slot), pol);
+        }
+        for (int j = max(0, i - kStages); j < i; ++j)
+            if (!wait_phase(bars + j % kStages, (uint32_t)((j / kStages) & 1))) break;
+        return;
+    }
+
+    StageIter cons;
+    cons.init(gp, grid, b, P);
+    Stage st;
+    // The consumers of a half are done with a slot: one arrival per warp.
+    auto release_slot = [&](int slot) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(empties + slot));
+    };
+    // Thread 0 of the half polls cond() with a cycle limit; the whole half learns the outcome.
+    auto bounded = [&](auto cond) -> bool {
+        if (ht == 0) {
+            int ok = 1;
+            if (!cond()) {
+                const long long t0 = clock64();
+                while (!cond()) {
+                    if (abort_s || clock64() - t0 > 2000000000LL) {
+                        if (!abort_s && a.status) atomicExch(a.status, (int)STATUS_FLAG_TIMEOUT);
+                        abort_s = 1;
+                        ok = 0;
+                        break;
+                    }
+                    __nanosleep(64);
+                }
+            }
+            flag_s[half] = ok;
+        }
+        half_sync(half);
+        const bool ok = flag_s[half] != 0;
+        half_sync(half);
+        return ok;
+    };
+    const int qstep = kHalf / gp.L, rstep = kHalf % gp.L;
+    const long long CL = (long long)gp.C * gp.L;
+
+    if (half == 0) {
+        // ------------------------------------------------ statistics half ------------------------------------------------
+        float K = 0.f, a1 = 0.f, a2 = 0.f;             // forward: shift, sum (x - K), sum (x - K)^2; backward: a1 = sum gy, a2 = sum gy (x - mean)
+        float mean = 0.f, invstd = 0.f, gam = 1.f, bet = 0.f;
+        for (int it = 0; cons.next(st); ++it) {
+            const int slot = it % kStages;
+            const float4 *sx = ring + (size_t)slot * T * P, *sg = sx + P;
+            const int c = st.c;
+            if (st.seg_first) {
+                // stay at most `lookahead` groups ahead of this CTA's apply half
+                if (st.g >= gp.lookahead && !bounded([&] { return applied_s >= st.g - gp.lookahead + 1; })) return;
+                a1 = 0.f; a2 = 0.f;
+                if (!BWD) {
+                    // the channel's shift: mean of the first 32 elements of its first plane (the same value in every CTA)
+                    if (ht < 32) {
+                        const int mm = min(32, gp.S);
+                        float e = ht < mm ? __ldg(a.x + (long long)c * gp.S + ht) : 0.f;
+                        e = warp_sum(e);
+                        if (ht == 0) k_s = e / (float)mm;
+                    }
+                    half_sync(0);
+                    K = k_s;
+                } else {
+                    mean = __ldg(a.mean_v + c);
+                    if (RELU) {
+                        invstd = a.train ? __ldg(a.std_or_var + c) : 1.f / sqrtf(__ldg(a.std_or_var + c) + (float)a.eps);
+                        gam = a.weight ? __ldg(a.weight + c) : 1.f;
+                        bet = a.bias ? __ldg(a.bias + c) : 0.f;
+                    }
+                }
+            }
+            if (!wait_phase(bars + slot, (uint32_t)((it / kStages) & 1))) return;
+            if (!BWD) {
+#pragma unroll 4
+                for (int j = ht; j < st.len; j += kHalf) {
+                    const float4 q = sx[j];
+                    const float e = q.x - K, f = q.y - K, gg = q.z - K, h = q.w - K;
+                    a1 += (e + f) + (gg + h);
+                    a2 = fmaf(e, e, a2); a2 = fmaf(f, f, a2); a2 = fmaf(gg, gg, a2); a2 = fmaf(h, h, a2);
+                }
+            } else {
+                auto one = [&](float v, float g_) { return RELU ? (bn_value(v, mean, invstd, gam, bet) > 0.f ? g_ : 0.f) : g_; };
+#pragma unroll 2
+                for (int j = ht; j < st.len; j += kHalf) {
+                    const float4 xv = sx[j];
+                    float4 gv = sg[j];
+                    gv.x = one(xv.x, gv.x); gv.y = one(xv.y, gv.y); gv.z = one(xv.z, gv.z); gv.w = one(xv.w, gv.w);
+                    a1 += (gv.x + gv.y) + (gv.z + gv.w);
+                    a2 = fmaf(gv.x, xv.x - mean, a2); a2 = fmaf(gv.y, xv.y - mean, a2);
+                    a2 = fmaf(gv.z, xv.z - mean, a2); a2 = fmaf(gv.w, xv.w - mean, a2);
+                }
+            }
+            release_slot(slot);
+            if (st.seg_last) {
+                // hand in this segment's partial; the CTA with the channel's last ticket merges and raises the flag
+                a1 = half_sum(a1, sh, 0);
+                a2 = half_sum(a2, sh, 0);
+                int bf, bl;
+                channel_ctas((long long)min(gp.G, gp.C - st.g * gp.G) * gp.NL, gp.NL, st.cl, grid, &bf, &bl);
+                const int cnt = bl - bf + 1;
+                float2 *pc = reinterpret_cast<float2 *>(a.part) + (size_t)c * gp.pstride;
+                if (ht == 0) {
+                    pc[b - bf] = make_float2(a1, a2);
+                    __threadfence();                                  // the partial is visible before the ticket
+                    flag_s[0] = atomicAdd(a.cn.tick + c, 1u) == (unsigned)(cnt - 1);
+                }
+                half_sync(0);
+                const bool last = flag_s[0] != 0;
+                half_sync(0);
+                if (last) {
+                    __threadfence();                                  // the other CTAs' partials are visible after their tickets
+                    if (ht < 32) {
+                        if (!BWD)
+                            finish_stats_shifted_warp(pc, c, cnt, K, (long long)gp.N * gp.S, a.running_mean, a.running_var, a.save_mean,
+                                                      a.save_std, a.momentum, a.eps);
+                        else
+                            finish_grad_channel_warp(pc, c, cnt, (long long)gp.N * gp.S, a.weight, a.bias, a.mean_v, a.std_or_var, a.train,
+                                                     a.eps, a.scale, a.grad_weight, a.grad_bias, a.coef);
+                        if (ht == 0) {
+                            a.cn.tick[c] = 0u;
+                            __threadfence();
+                            st_release_u32(a.cn.ready + c, 1u);
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        // -------------------------------------------------- apply half --------------------------------------------------
+        float4 *o4 = reinterpret_cast<float4 *>(a.out);
+        float mean = 0.f, invstd = 0.f, gam = 1.f, bet = 0.f;
+        GradCoef kf{};
+        const unsigned long long drop = pol;
+        for (int it = 0; cons.next(st); ++it) {
+            const int slot = it % kStages;
+            const float4 *sx = ring + (size_t)slot * T * P, *sg = sx + P;
+            const int c = st.c;
+            if (st.seg_first) {
+                // the statistics (or gradient coefficients) of this channel must have been merged
+                const unsigned *rf = a.cn.ready + c;
+                if (!bounded([&] { return ld_acquire_u32(rf) != 0u; })) return;
+                if (!BWD) {
+                    mean = __ldcg(a.save_mean + c); invstd = __ldcg(a.save_std + c);
+                    gam = a.weight ? __ldg(a.weight + c) : 1.f; bet = a.bias ? __ldg(a.bias + c) : 0.f;
+                } else {
+                    const float4 ca = __ldcg(reinterpret_cast<const float4 *>(a.coef + c)), cb = __ldcg(reinterpret_cast<const float4 *>(a.coef + c) + 1);
+                    kf.mean = ca.x; kf.proj = ca.y; kf.gmean = ca.z; kf.gscale = ca.w;
+                    kf.invstd = cb.x; kf.gamma = cb.y; kf.beta = cb.z; kf.pad = cb.w;
+                }
+                if (ht == 0) {
+                    // the last of the channel's readers lowers the flag again
+                    int bf, bl;
+                    channel_ctas((long long)min(gp.G, gp.C - st.g * gp.G) * gp.NL, gp.NL, st.cl, grid, &bf, &bl);
+                    if (atomicAdd(a.cn.done + c, 1u) == (unsigned)(bl - bf)) {
+                        a.cn.done[c] = 0u;
+                        st_release_u32(a.cn.ready + c, 0u);
+                    }
+                }
+            }
+            if (!wait_phase(bars + slot, (uint32_t)((it / kStages) & 1))) return;
+            // item j of the slot is item st.q + j of the channel's sequence: image (st.q + j) / L, offset (st.q + j) % L
+            int n = (st.q + ht) / gp.L, i = (st.q + ht) - n * gp.L;
+            float4 *obase = o4 + (long long)c * gp.L;
+            auto act = [](float t) { return RELU ? (t > 0.f ? t : 0.f) : t; };
+#pragma unroll 2
+            for (int j = ht; j < st.len; j += kHalf) {
+                const float4 v = sx[j];
+                float4 o;
+                if (!BWD) {
+                    o.x = act(bn_value(v.x, mean, invstd, gam, bet));
+                    o.y = act(bn_value(v.y, mean, invstd, gam, bet));
+                    o.z = act(bn_value(v.z, mean, invstd, gam, bet));
+                    o.w = act(bn_value(v.w, mean, invstd, gam, bet));
+                } else {
+                    const float4 q = sg[j];
+                    auto one = [&](float xv, float g_) {
+                        if (RELU) g_ = bn_value(xv, kf.mean, kf.invstd, kf.gamma, kf.beta) > 0.f ? g_ : 0.f;
+                        return a.train ? (g_ - (xv - kf.mean) * kf.proj - kf.gmean) * kf.gscale : g_ * kf.gscale;
+                    };
+                    o.x = one(v.x, q.x); o.y = one(v.y, q.y); o.z = one(v.z, q.z); o.w = one(v.w, q.w);
+                }
+                st_hint(obase + (long long)n * CL + i, o, drop);
+                n += qstep; i += rstep;
+                if (i >= gp.L) { i -= gp.L; ++n; }
+            }
+            release_slot(slot);
+            if (st.group_last && ht == 0) applied_s = st.g + 1;
+        }
+    }
+}
+
+// Counters at the start of the workspace, kMaxCounterChannels entries each: ticket counters of the forward
+// statistics and of the gradient sums, and for the grouped kernels a ready flag and a reader counter per channel,
+// forward and backward.  All zero when a call is enqueued, all zero again when its kernels have run (a kernel
+// that recorded STATUS_FLAG_TIMEOUT may leave them set: clear the workspace after a non-zero device status).
 constexpr int kMaxCounterChannels = 4096;
-constexpr size_t kCounterBytes = (size_t)2 * kMaxCounterChannels * sizeof(unsigned int);
+constexpr int kCounterArrays = 6;
+constexpr size_t kCounterBytes = (size_t)kCounterArrays * kMaxCounterChannels * sizeof(unsigned int);
 
 // Chunks per channel so that C * chunks CTAs fill the GPU a few times over, at most one chunk per image.
 static int pick_chunks(int N, int C)
@@ -680,12 +1209,81 @@ static void launch_grad_apply(const float *x, const float *gy, float *gx, const 
 using namespace cunn;
 using namespace cunn::bn;
 
-// Workspace layout: [ticket counters, kCounterBytes] [chunk partials] [gradient coefficients].
+// ---- grouped path: planning and launch ---------------------------------------------------------------------
+// Bytes of one group's slabs.  Two groups are in flight (one waiting to be normalised, one being reduced) beside
+// the output being written, and a B200's L2 serves each half of the chip from its own half of the 126 MB.
+static size_t g_group_bytes = (size_t)28 << 20;
+// Bytes of all the groups between the statistics half and the apply half (what has to stay in L2).
+static size_t g_window_bytes = (size_t)56 << 20;
+#ifdef CUNN_B200_DEV_HOOKS
+// sweeps only: CUNN_B200_BN_GROUP_MB / CUNN_B200_BN_WINDOW_MB override the budgets (group 0 disables the grouped kernels)
+static const bool g_group_bytes_from_env = [] {
+    if (const char *e = getenv("CUNN_B200_BN_GROUP_MB")) g_group_bytes = (size_t)atol(e) << 20;
+    if (const char *e = getenv("CUNN_B200_BN_WINDOW_MB")) g_window_bytes = (size_t)atol(e) << 20;
+    return true;
+}();
+#endif
+
+// 0: never use the grouped kernels; 1 (default): where measurements show they win — the training forward pass with
+// channel slabs of at least 6 MB (below that the per-group hand-offs cost more than the saved pass; the backward
+// kernel moves the algorithmic 3 passes but is instruction-bound and 10-20 % slower than the two-launch path);
+// 2: wherever they apply.
+static int g_grouped_mode = 1;
+static const size_t kGroupedMinSlab = (size_t)6 << 20;
+
+static int grouped_grid_cap() { return sm_count() * 2; }
+
+// Size of the partials region: the per-(channel, chunk) partials of the two-launch path, or the per-(channel, CTA)
+// partials of the grouped path (capped; shapes that would need more take the two-launch path).
+static size_t part_region_bytes(int N, int C)
+{
+    const size_t two_launch = ((size_t)C * pick_chunks(N, C) * sizeof(ChunkStat) + 255) & ~(size_t)255;
+    const size_t grouped = std::min((size_t)C * (grouped_grid_cap() + 2) * sizeof(ChunkStat), (size_t)8 << 20);
+    return std::max(two_launch, (grouped + 255) & ~(size_t)255);
+}
+
+// Fills gp and returns true when the grouped kernels apply: 16-byte rows, channel slabs (tensors_per_item tensors
+// of N planes) that fit the group budget, enough items for every CTA in every group, partials that fit.
+static bool plan_groups(int N, int C, int S, int tensors, const void *a, const void *b, const void *c, int grid, GroupPlan *gp)
+{
+    if (g_grouped_mode == 0) return false;
+    if (g_grouped_mode == 1 && (tensors != 1 || (size_t)N * S * sizeof(float) < kGroupedMinSlab)) return false;
+    if (S % 4 != 0 || ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) != 0) || C > kMaxCounterChannels || grid < 1) return false;
+    const size_t slab = (size_t)N * S * sizeof(float) * tensors;
+    if (slab * 2 > g_window_bytes) return false;                 // two groups of one channel must fit the window
+    const int gmax = (int)std::min<size_t>(std::max<size_t>(g_group_bytes / slab, 1), (size_t)C);
+    const int groups = ceil_div(C, gmax);
+    const int G = ceil_div(C, groups);
+    const int glast = C - (ceil_div(C, G) - 1) * G;
+    gp->N = N; gp->C = C; gp->S = S; gp->L = S / 4;
+    gp->G = G; gp->groups = ceil_div(C, G);
+    gp->NL = (long long)N * gp->L;
+    gp->pstride = grid / glast + 2;
+    gp->lookahead = (int)std::max<size_t>(2, g_window_bytes / ((size_t)G * slab));
+    if ((long long)glast * gp->NL < 8LL * grid) return false;                      // too little work per CTA and group
+    if ((size_t)C * gp->pstride * sizeof(ChunkStat) > part_region_bytes(N, C)) return false;
+    return true;
+}
+
+// CTAs of a grouped launch: as many as are co-resident (the kernels wait on one another), two per SM at most.
+static int grouped_grid(const void *kernel)
+{
+    const int smem = 2 * kStages * kStageBytes;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 0;
+    int occ = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, kGroupedThreads, smem) != cudaSuccess || occ < 1) return 0;
+    return sm_count() * std::min(occ, 2);
+}
+
+extern "C" CUNN_API size_t cunn_b200_batchnorm_counter_bytes(void) { return kCounterBytes; }
+extern "C" CUNN_API void cunn_b200_batchnorm_set_grouped(int mode) { g_grouped_mode = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
+extern "C" CUNN_API int cunn_b200_batchnorm_get_grouped(void) { return g_grouped_mode; }
+
+// Workspace layout: [counters, kCounterBytes] [partials, part_region_bytes] [gradient coefficients].
 extern "C" CUNN_API size_t cunn_b200_batchnorm_workspace(int N, int C)
 {
     if (N <= 0 || C <= 0) return 0;
-    const size_t chunks = (size_t)pick_chunks(N, C);
-    return kCounterBytes + (((size_t)C * chunks * sizeof(ChunkStat) + 255) & ~(size_t)255) + (size_t)C * sizeof(GradCoef) + 256;
+    return kCounterBytes + part_region_bytes(N, C) + (size_t)C * sizeof(GradCoef) + 256;
 }
 
 static int bn_forward_impl(const float *x, float *y, const float *weight, const float *bias, float *running_mean,
@@ -703,12 +1301,27 @@ static int bn_forward_impl(const float *x, float *y, const float *weight, const 
     if (train) {
         CUNN_CHECK_ARG(save_mean && save_std, "training-mode batch norm needs save_mean and save_std");
         const int chunks = pick_chunks(N, C);
-        const size_t need = kCounterBytes + (size_t)C * chunks * sizeof(ChunkStat);
+        const size_t need = kCounterBytes + part_region_bytes(N, C);
         CUNN_CHECK_ARG(workspace && workspace_bytes >= need && ((uintptr_t)workspace & 15) == 0,
                        "batch norm needs %zu bytes of 16-byte aligned workspace, got %zu", need,
                        workspace ? workspace_bytes : (size_t)0);
         unsigned int *counters = C <= kMaxCounterChannels ? (unsigned int *)workspace : nullptr;
         ChunkStat *part = (ChunkStat *)((char *)workspace + kCounterBytes);
+        {
+            GroupedArgs ga{};
+            const void *fn = relu ? (const void *)grouped_kernel<false, true> : (const void *)grouped_kernel<false, false>;
+            const int grid = grouped_grid(fn);
+            if (plan_groups(N, C, S, 1, x, y, y, grid, &ga.gp)) {
+                unsigned int *cw = (unsigned int *)workspace;
+                ga.x = x; ga.out = y; ga.weight = weight; ga.bias = bias; ga.part = part;
+                ga.cn = GroupCounters{cw, cw + 2 * kMaxCounterChannels, cw + 3 * kMaxCounterChannels};
+                ga.running_mean = running_mean; ga.running_var = running_var; ga.save_mean = save_mean; ga.save_std = save_std;
+                ga.momentum = momentum; ga.eps = eps; ga.train = 1; ga.status = device_status_ptr();
+                void *args[] = {(void *)&ga};
+                CUNN_CUDA(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kGroupedThreads), args, (size_t)2 * kStages * kStageBytes, stream));
+                return 0;
+            }
+        }
         stats_kernel<<<C * chunks, 256, 0, stream>>>(x, part, N, C, S, chunks, counters, running_mean, running_var, save_mean,
                                                      save_std, momentum, eps);
         CUNN_LAUNCH_CHECK("batch norm statistics");
@@ -761,7 +1374,7 @@ static int bn_backward_impl(const float *x, const float *gy, bool relu, const fl
     CUNN_CHECK_ARG(train ? (save_mean && save_std) : (running_mean && running_var),
                    "batch norm backward needs %s", train ? "save_mean and save_std" : "running_mean and running_var");
     const int chunks = pick_chunks(N, C);
-    const size_t part_bytes = ((size_t)C * chunks * sizeof(ChunkStat) + 255) & ~(size_t)255;
+    const size_t part_bytes = part_region_bytes(N, C);
     const size_t need = kCounterBytes + part_bytes + (size_t)C * sizeof(GradCoef);
     CUNN_CHECK_ARG(workspace && workspace_bytes >= need && ((uintptr_t)workspace & 15) == 0,
                    "batch norm backward needs %zu bytes of 16-byte aligned workspace, got %zu", need,
@@ -774,6 +1387,21 @@ static int bn_backward_impl(const float *x, const float *gy, bool relu, const fl
     const long long planes = (long long)N * C;
     // inference-mode input gradient needs no sums; they are still required for gradWeight / gradBias
     const bool need_sums = train || grad_weight || grad_bias;
+    if (gx && need_sums) {
+        GroupedArgs ga{};
+        const void *fn = relu ? (const void *)grouped_kernel<true, true> : (const void *)grouped_kernel<true, false>;
+        const int grid = grouped_grid(fn);
+        if (plan_groups(N, C, S, 2, x, gy, gx, grid, &ga.gp)) {
+            unsigned int *cw = (unsigned int *)workspace;
+            ga.x = x; ga.gy = gy; ga.out = gx; ga.weight = weight; ga.bias = bias; ga.part = part;
+            ga.cn = GroupCounters{cw + kMaxCounterChannels, cw + 4 * kMaxCounterChannels, cw + 5 * kMaxCounterChannels};
+            ga.mean_v = mean_v; ga.std_or_var = sv; ga.grad_weight = grad_weight; ga.grad_bias = grad_bias; ga.coef = coef;
+            ga.eps = eps; ga.scale = scale; ga.train = train; ga.status = device_status_ptr();
+            void *args[] = {(void *)&ga};
+            CUNN_CUDA(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kGroupedThreads), args, (size_t)2 * kStages * kStageBytes, stream));
+            return 0;
+        }
+    }
     if (need_sums) {
         if (relu) grad_stats_kernel<true><<<C * chunks, 256, 0, stream>>>(x, gy, part, mean_v, sv, weight, bias, train, (float)eps, N, C, S, chunks,
                                                                           counters, eps, scale, grad_weight, grad_bias, coef);

@@ -47,6 +47,7 @@ enum StatusCode : int {
     STATUS_OK = 0,
     STATUS_MBARRIER_TIMEOUT = 1,
     STATUS_TMEM_TIMEOUT = 2,
+    STATUS_FLAG_TIMEOUT = 3,      // a CTA gave up waiting for another CTA of its own grid
 };
 
 #ifdef __CUDACC__
@@ -109,6 +110,14 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uin
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
+// The same copy with an L2 eviction-priority policy (createpolicy) attached to the global read.
+__device__ __forceinline__ void bulk_g2s_hint(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar), "l"(policy)
         : "memory");
 }
 

@@ -10,72 +10,13 @@
 // Both directions are HBM-bound.  The 3x3 / stride 2 / pad 1 case (ResNet, MobileNet stems) has
 // dedicated kernels with 16-byte loads and stores; everything else runs shape-generic kernels.
 #include "common.cuh"
+#include "pool_generic.cuh"
 
 #include <float.h>
 #include <algorithm>
 
 namespace cunn {
 namespace pool {
-
-// ---------------------------------------------------------------------------
-// Shape-generic kernels
-// ---------------------------------------------------------------------------
-
-__global__ void __launch_bounds__(256)
-fwd_generic_kernel(const float *__restrict__ x, float *__restrict__ y, long long *__restrict__ ind, int H, int W,
-                   int oH, int oW, int kH, int kW, int dH, int dW, int padH, int padW, int dilH, int dilW,
-                   long long total)
-{
-    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
-         idx += (long long)gridDim.x * blockDim.x) {
-        const int pw = (int)(idx % oW);
-        const long long t = idx / oW;
-        const int ph = (int)(t % oH);
-        const long long plane = t / oH;
-        int hs = ph * dH - padH, ws = pw * dW - padW;
-        const int he = min(hs + (kH - 1) * dilH + 1, H);
-        const int we = min(ws + (kW - 1) * dilW + 1, W);
-        while (hs < 0) hs += dilH;
-        while (ws < 0) ws += dilW;
-        const float *xp = x + plane * (long long)H * W;
-        float best = -FLT_MAX;
-        int bi = -1;
-        for (int h = hs; h < he; h += dilH)
-            for (int w = ws; w < we; w += dilW) {
-                const float v = __ldg(xp + h * W + w);
-                if (v > best) { best = v; bi = h * W + w; }
-            }
-        y[idx] = best;
-        ind[idx] = (long long)bi + CUNN_B200_INDEX_BASE;
-    }
-}
-
-__global__ void __launch_bounds__(256)
-bwd_generic_kernel(const float *__restrict__ gy, const long long *__restrict__ ind, float *__restrict__ gx, int H,
-                   int W, int oH, int oW, int kH, int kW, int dH, int dW, int padH, int padW, int dilH, int dilW,
-                   long long total)
-{
-    const int eh = (kH - 1) * dilH + 1, ew = (kW - 1) * dilW + 1;
-    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
-         idx += (long long)gridDim.x * blockDim.x) {
-        const int w = (int)(idx % W);
-        const long long t = idx / W;
-        const int h = (int)(t % H);
-        const long long plane = t / H;
-        const int phs = (h + padH < eh) ? 0 : (h + padH - eh) / dH + 1;
-        const int phe = min((h + padH) / dH + 1, oH);
-        const int pws = (w + padW < ew) ? 0 : (w + padW - ew) / dW + 1;
-        const int pwe = min((w + padW) / dW + 1, oW);
-        const float *gp = gy + plane * (long long)oH * oW;
-        const long long *ip = ind + plane * (long long)oH * oW;
-        const long long me = (long long)h * W + w + CUNN_B200_INDEX_BASE;
-        float g = 0.f;
-        for (int ph = phs; ph < phe; ++ph)
-            for (int pw = pws; pw < pwe; ++pw)
-                if (__ldg(ip + ph * oW + pw) == me) g += __ldg(gp + ph * oW + pw);
-        gx[idx] = g;
-    }
-}
 
 // ---------------------------------------------------------------------------
 // 3x3, stride 2, pad 1, even W with W % 8 == 0 (so oW == W / 2 and oW % 4 == 0)
@@ -316,7 +257,7 @@ extern "C" CUNN_API int cunn_b200_maxpool_forward(const float *x, float *y, int6
         return 0;
     }
     const long long total = planes * oH * oW;
-    fwd_generic_kernel<<<grid_for(total), 256, 0, stream>>>(x, y, (long long *)indices, H, W, oH, oW, kH, kW, dH, dW,
+    forward_taps_kernel<float><<<grid_for(total), 256, 0, stream>>>(x, y, (long long *)indices, H, W, oH, oW, kH, kW, dH, dW,
                                                            padH, padW, dilH, dilW, total);
     CUNN_LAUNCH_CHECK("maxpool forward (generic)");
     return 0;
@@ -340,7 +281,7 @@ extern "C" CUNN_API int cunn_b200_maxpool_backward(const float *gy, const int64_
         return 0;
     }
     const long long total = planes * H * W;
-    bwd_generic_kernel<<<grid_for(total), 256, 0, stream>>>(gy, (const long long *)indices, gx, H, W, oH, oW, kH, kW, dH,
+    backward_taps_kernel<float><<<grid_for(total), 256, 0, stream>>>(gy, (const long long *)indices, gx, H, W, oH, oW, kH, kW, dH,
                                                            dW, padH, padW, dilH, dilW, total);
     CUNN_LAUNCH_CHECK("maxpool backward (generic)");
     return 0;

@@ -204,7 +204,7 @@ extern "C" CUNN_API int cunn_b200_mobilenet_step(const cunn_b200_mobilenet_confi
     // batch normalisation keeps its ticket counters in the first 32 KiB of its own workspace
     void *bnwork = base + a.bnwork;
     const size_t bnbytes = a.bnwork_bytes;
-    CUNN_CUDA(cudaMemsetAsync(bnwork, 0, 32 << 10, (cudaStream_t)stream));
+    CUNN_CUDA(cudaMemsetAsync(bnwork, 0, cunn_b200_batchnorm_counter_bytes(), (cudaStream_t)stream));
 
     // ---------------- forward ----------------
     const float *x = images;

@@ -27,10 +27,52 @@ extern "C" void thcunn_b200_not_implemented(THCState *state, const char *name)
     else fprintf(stderr, "THCUNN error: %s is not implemented in this build\n", name);
 }
 
+// ---- element types of the hot path ---------------------------------------------------------------------
+// The reference instantiates every entry point for float and double (THCGenerateFloatTypes.h); here the hot-path
+// wrappers below are templates over one of these two descriptions: element type, `accreal` of the binding
+// (THCUNN.lua:48,54), tensor struct, and the flat entry points that do the work.
+struct RealFloat {
+    typedef float real;
+    typedef float accreal;
+    typedef THCudaTensor tensor;
+    static constexpr auto dwconv_forward = &cunn_b200_dwconv_forward;
+    static constexpr auto dwconv_grad_input = &cunn_b200_dwconv_grad_input;
+    static constexpr auto dwconv_acc_grad_workspace = &cunn_b200_dwconv_acc_grad_workspace;
+    static constexpr auto dwconv_acc_grad = &cunn_b200_dwconv_acc_grad;
+    static constexpr auto convmm_forward = &cunn_b200_convmm_forward;
+    static constexpr auto convmm_grad_input = &cunn_b200_convmm_grad_input;
+    static constexpr auto convmm_acc_grad_workspace = &cunn_b200_convmm_acc_grad_workspace;
+    static constexpr auto convmm_acc_grad = &cunn_b200_convmm_acc_grad;
+    static constexpr auto batchnorm_workspace = &cunn_b200_batchnorm_workspace;
+    static constexpr auto batchnorm_forward = &cunn_b200_batchnorm_forward;
+    static constexpr auto batchnorm_backward = &cunn_b200_batchnorm_backward;
+    static constexpr auto maxpool_forward = &cunn_b200_maxpool_forward;
+    static constexpr auto maxpool_backward = &cunn_b200_maxpool_backward;
+};
+struct RealDouble {
+    typedef double real;
+    typedef double accreal;
+    typedef THCudaDoubleTensor tensor;
+    static constexpr auto dwconv_forward = &cunn_b200_double_dwconv_forward;
+    static constexpr auto dwconv_grad_input = &cunn_b200_double_dwconv_grad_input;
+    static constexpr auto dwconv_acc_grad_workspace = &cunn_b200_double_dwconv_acc_grad_workspace;
+    static constexpr auto dwconv_acc_grad = &cunn_b200_double_dwconv_acc_grad;
+    static constexpr auto convmm_forward = &cunn_b200_double_convmm_forward;
+    static constexpr auto convmm_grad_input = &cunn_b200_double_convmm_grad_input;
+    static constexpr auto convmm_acc_grad_workspace = &cunn_b200_double_convmm_acc_grad_workspace;
+    static constexpr auto convmm_acc_grad = &cunn_b200_double_convmm_acc_grad;
+    static constexpr auto batchnorm_workspace = &cunn_b200_double_batchnorm_workspace;
+    static constexpr auto batchnorm_forward = &cunn_b200_double_batchnorm_forward;
+    static constexpr auto batchnorm_backward = &cunn_b200_double_batchnorm_backward;
+    static constexpr auto maxpool_forward = &cunn_b200_double_maxpool_forward;
+    static constexpr auto maxpool_backward = &cunn_b200_double_maxpool_backward;
+};
+
 // ---- SpatialDepthWiseConvolution -------------------------------------------------------------------
 // Shape rules of lib/THCUNN/generic/SpatialDepthWiseConvolution.cu:5-56.  A 2-D weight [M, C*kH*kW] is
 // given its 4-D shape in place, as the reference does (:76-80).
-static bool dw_prepare(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *weight, THCudaTensor *bias,
+template <class Tensor>
+static bool dw_prepare(THCState *s, Tensor *input, Tensor *gradOutput, Tensor *weight, Tensor *bias,
                        int kH, int kW, int dH, int dW, int padH, int padW, long *N, long *C, long *M, long *H, long *W,
                        long *oH, long *oW)
 {
@@ -64,58 +106,61 @@ static bool dw_prepare(THCState *s, THCudaTensor *input, THCudaTensor *gradOutpu
     return true;
 }
 
-extern "C" CUNN_API void THNN_CudaSpatialDepthWiseConvolution_updateOutput(
-    THCState *s, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias, THCudaTensor *,
-    THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH)
+template <class R>
+static void hot_SpatialDepthWiseConvolution_updateOutput(
+    THCState *s, typename R::tensor *input, typename R::tensor *output, typename R::tensor *weight, typename R::tensor *bias, typename R::tensor *,
+    typename R::tensor *, int kW, int kH, int dW, int dH, int padW, int padH)
 {
     long N, C, M, H, W, oH, oW;
-    if (!dw_prepare(s, input, nullptr, weight, bias, kH, kW, dH, dW, padH, padW, &N, &C, &M, &H, &W, &oH, &oW)) return;
-    THCudaTensor *x = new_contiguous(s, input), *w = new_contiguous(s, weight), *b = bias ? new_contiguous(s, bias) : nullptr;
+    if (!dw_prepare<typename R::tensor>(s, input, nullptr, weight, bias, kH, kW, dH, dW, padH, padW, &N, &C, &M, &H, &W, &oH, &oW)) return;
+    typename R::tensor *x = new_contiguous(s, input, (int)sizeof(typename R::real)), *w = new_contiguous(s, weight, (int)sizeof(typename R::real)), *b = bias ? new_contiguous(s, bias, (int)sizeof(typename R::real)) : nullptr;
     if (x && w && (!bias || b)) {
         const long sz4[4] = {N, C * M, oH, oW};
-        if (tensor_resize(s, output, 4, sz4, 4)) {
-            TH_CALL(s, cunn_b200_dwconv_forward(tdata<float>(x), tdata<float>(w), tdata<float>(b), tdata<float>(output), (int)N,
+        if (tensor_resize(s, output, 4, sz4, (int)sizeof(typename R::real))) {
+            TH_CALL(s, R::dwconv_forward(tdata<typename R::real>(x), tdata<typename R::real>(w), tdata<typename R::real>(b), tdata<typename R::real>(output), (int)N,
                                                 (int)C, (int)H, (int)W, (int)M, kH, kW, dH, dW, padH, padW, state_stream(s)));
-            if (input->nDimension == 3) tensor_resize(s, output, 3, sz4 + 1, 4);
+            if (input->nDimension == 3) tensor_resize(s, output, 3, sz4 + 1, (int)sizeof(typename R::real));
         }
     }
 done:
     tensor_free(s, x); tensor_free(s, w); tensor_free(s, b);
 }
 
-extern "C" CUNN_API void THNN_CudaSpatialDepthWiseConvolution_updateGradInput(
-    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight,
-    THCudaTensor *, THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH)
+template <class R>
+static void hot_SpatialDepthWiseConvolution_updateGradInput(
+    THCState *s, typename R::tensor *input, typename R::tensor *gradOutput, typename R::tensor *gradInput, typename R::tensor *weight,
+    typename R::tensor *, typename R::tensor *, int kW, int kH, int dW, int dH, int padW, int padH)
 {
     long N, C, M, H, W, oH, oW;
-    if (!dw_prepare(s, input, gradOutput, weight, nullptr, kH, kW, dH, dW, padH, padW, &N, &C, &M, &H, &W, &oH, &oW)) return;
+    if (!dw_prepare<typename R::tensor>(s, input, gradOutput, weight, nullptr, kH, kW, dH, dW, padH, padW, &N, &C, &M, &H, &W, &oH, &oW)) return;
     // unlike the reference (which views a strided gradOutput as if it were contiguous), gy is made contiguous
-    THCudaTensor *gy = new_contiguous(s, gradOutput), *w = new_contiguous(s, weight);
+    typename R::tensor *gy = new_contiguous(s, gradOutput, (int)sizeof(typename R::real)), *w = new_contiguous(s, weight, (int)sizeof(typename R::real));
     if (gy && w) {
         const long sz4[4] = {N, C, H, W};
-        if (tensor_resize(s, gradInput, 4, sz4, 4)) {
-            TH_CALL(s, cunn_b200_dwconv_grad_input(tdata<float>(gy), tdata<float>(w), tdata<float>(gradInput), (int)N, (int)C,
+        if (tensor_resize(s, gradInput, 4, sz4, (int)sizeof(typename R::real))) {
+            TH_CALL(s, R::dwconv_grad_input(tdata<typename R::real>(gy), tdata<typename R::real>(w), tdata<typename R::real>(gradInput), (int)N, (int)C,
                                                    (int)H, (int)W, (int)M, kH, kW, dH, dW, padH, padW, state_stream(s)));
-            if (input->nDimension == 3) tensor_resize(s, gradInput, 3, sz4 + 1, 4);
+            if (input->nDimension == 3) tensor_resize(s, gradInput, 3, sz4 + 1, (int)sizeof(typename R::real));
         }
     }
 done:
     tensor_free(s, gy); tensor_free(s, w);
 }
 
-extern "C" CUNN_API void THNN_CudaSpatialDepthWiseConvolution_accGradParameters(
-    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias,
-    THCudaTensor *, THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH, float scale)
+template <class R>
+static void hot_SpatialDepthWiseConvolution_accGradParameters(
+    THCState *s, typename R::tensor *input, typename R::tensor *gradOutput, typename R::tensor *gradWeight, typename R::tensor *gradBias,
+    typename R::tensor *, typename R::tensor *, int kW, int kH, int dW, int dH, int padW, int padH, typename R::accreal scale)
 {
     long N, C, M, H, W, oH, oW;
-    if (!dw_prepare(s, input, gradOutput, gradWeight, gradBias, kH, kW, dH, dW, padH, padW, &N, &C, &M, &H, &W, &oH, &oW)) return;
+    if (!dw_prepare<typename R::tensor>(s, input, gradOutput, gradWeight, gradBias, kH, kW, dH, dW, padH, padW, &N, &C, &M, &H, &W, &oH, &oW)) return;
     TH_CHECK(s, is_contiguous(gradWeight) && (!gradBias || is_contiguous(gradBias)), "gradWeight and gradBias have to be contiguous");
-    THCudaTensor *x = new_contiguous(s, input), *gy = new_contiguous(s, gradOutput);
+    typename R::tensor *x = new_contiguous(s, input, (int)sizeof(typename R::real)), *gy = new_contiguous(s, gradOutput, (int)sizeof(typename R::real));
     if (x && gy) {
-        const size_t need = cunn_b200_dwconv_acc_grad_workspace((int)N, (int)C, (int)H, (int)W, (int)M, kH, kW, dH, dW, padH, padW);
+        const size_t need = R::dwconv_acc_grad_workspace((int)N, (int)C, (int)H, (int)W, (int)M, kH, kW, dH, dW, padH, padW);
         void *ws = need ? state_scratch(s, 1, need) : nullptr;
         if (!need || ws)
-            TH_CALL(s, cunn_b200_dwconv_acc_grad(tdata<float>(x), tdata<float>(gy), tdata<float>(gradWeight), tdata<float>(gradBias),
+            TH_CALL(s, R::dwconv_acc_grad(tdata<typename R::real>(x), tdata<typename R::real>(gy), tdata<typename R::real>(gradWeight), tdata<typename R::real>(gradBias),
                                                  (int)N, (int)C, (int)H, (int)W, (int)M, kH, kW, dH, dW, padH, padW, scale, ws,
                                                  state_scratch_bytes(s, 1), state_stream(s)));
     }
@@ -126,7 +171,8 @@ done:
 // ---- SpatialConvolutionMM ----------------------------------------------------------------------------
 // Shape rules of lib/THCUNN/generic/SpatialConvolutionMM.cu:5-56; the weight must be contiguous (:74) and
 // may be 2-D [K, C*kH*kW] or 4-D.
-static bool mm_prepare(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *weight, THCudaTensor *bias,
+template <class Tensor>
+static bool mm_prepare(THCState *s, Tensor *input, Tensor *gradOutput, Tensor *weight, Tensor *bias,
                        int kH, int kW, int dH, int dW, int padH, int padW, long *N, long *C, long *K, long *H, long *W,
                        long *oH, long *oW, int dilH = 1, int dilW = 1)
 {
@@ -154,56 +200,59 @@ static bool mm_prepare(THCState *s, THCudaTensor *input, THCudaTensor *gradOutpu
     return true;
 }
 
-extern "C" CUNN_API void THNN_CudaSpatialConvolutionMM_updateOutput(
-    THCState *s, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias, THCudaTensor *,
-    THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH)
+template <class R>
+static void hot_SpatialConvolutionMM_updateOutput(
+    THCState *s, typename R::tensor *input, typename R::tensor *output, typename R::tensor *weight, typename R::tensor *bias, typename R::tensor *,
+    typename R::tensor *, int kW, int kH, int dW, int dH, int padW, int padH)
 {
     long N, C, K, H, W, oH, oW;
-    if (!mm_prepare(s, input, nullptr, weight, bias, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW)) return;
-    THCudaTensor *x = new_contiguous(s, input);
+    if (!mm_prepare<typename R::tensor>(s, input, nullptr, weight, bias, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW)) return;
+    typename R::tensor *x = new_contiguous(s, input, (int)sizeof(typename R::real));
     if (x) {
         const long sz4[4] = {N, K, oH, oW};
-        if (tensor_resize(s, output, 4, sz4, 4)) {
-            TH_CALL(s, cunn_b200_convmm_forward(tdata<float>(x), tdata<float>(weight), bias ? tdata<float>(bias) : nullptr, tdata<float>(output),
+        if (tensor_resize(s, output, 4, sz4, (int)sizeof(typename R::real))) {
+            TH_CALL(s, R::convmm_forward(tdata<typename R::real>(x), tdata<typename R::real>(weight), bias ? tdata<typename R::real>(bias) : nullptr, tdata<typename R::real>(output),
                                                 (int)N, (int)C, (int)H, (int)W, (int)K, kH, kW, dH, dW, padH, padW, state_stream(s)));
-            if (input->nDimension == 3) tensor_resize(s, output, 3, sz4 + 1, 4);
+            if (input->nDimension == 3) tensor_resize(s, output, 3, sz4 + 1, (int)sizeof(typename R::real));
         }
     }
 done:
     tensor_free(s, x);
 }
 
-extern "C" CUNN_API void THNN_CudaSpatialConvolutionMM_updateGradInput(
-    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight,
-    THCudaTensor *, THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH)
+template <class R>
+static void hot_SpatialConvolutionMM_updateGradInput(
+    THCState *s, typename R::tensor *input, typename R::tensor *gradOutput, typename R::tensor *gradInput, typename R::tensor *weight,
+    typename R::tensor *, typename R::tensor *, int kW, int kH, int dW, int dH, int padW, int padH)
 {
     long N, C, K, H, W, oH, oW;
-    if (!mm_prepare(s, input, gradOutput, weight, nullptr, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW)) return;
-    THCudaTensor *gy = new_contiguous(s, gradOutput);
+    if (!mm_prepare<typename R::tensor>(s, input, gradOutput, weight, nullptr, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW)) return;
+    typename R::tensor *gy = new_contiguous(s, gradOutput, (int)sizeof(typename R::real));
     if (gy) {
         const long sz4[4] = {N, C, H, W};
-        if (tensor_resize(s, gradInput, 4, sz4, 4)) {
-            TH_CALL(s, cunn_b200_convmm_grad_input(tdata<float>(gy), tdata<float>(weight), tdata<float>(gradInput), (int)N, (int)C, (int)H,
+        if (tensor_resize(s, gradInput, 4, sz4, (int)sizeof(typename R::real))) {
+            TH_CALL(s, R::convmm_grad_input(tdata<typename R::real>(gy), tdata<typename R::real>(weight), tdata<typename R::real>(gradInput), (int)N, (int)C, (int)H,
                                                    (int)W, (int)K, kH, kW, dH, dW, padH, padW, state_stream(s)));
-            if (input->nDimension == 3) tensor_resize(s, gradInput, 3, sz4 + 1, 4);
+            if (input->nDimension == 3) tensor_resize(s, gradInput, 3, sz4 + 1, (int)sizeof(typename R::real));
         }
     }
 done:
     tensor_free(s, gy);
 }
 
-extern "C" CUNN_API void THNN_CudaSpatialConvolutionMM_accGradParameters(
-    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias,
-    THCudaTensor *, THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH, float scale)
+template <class R>
+static void hot_SpatialConvolutionMM_accGradParameters(
+    THCState *s, typename R::tensor *input, typename R::tensor *gradOutput, typename R::tensor *gradWeight, typename R::tensor *gradBias,
+    typename R::tensor *, typename R::tensor *, int kW, int kH, int dW, int dH, int padW, int padH, typename R::accreal scale)
 {
     long N, C, K, H, W, oH, oW;
-    if (!mm_prepare(s, input, gradOutput, gradWeight, gradBias, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW)) return;
-    THCudaTensor *x = new_contiguous(s, input), *gy = new_contiguous(s, gradOutput);
+    if (!mm_prepare<typename R::tensor>(s, input, gradOutput, gradWeight, gradBias, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW)) return;
+    typename R::tensor *x = new_contiguous(s, input, (int)sizeof(typename R::real)), *gy = new_contiguous(s, gradOutput, (int)sizeof(typename R::real));
     if (x && gy) {
-        const size_t need = cunn_b200_convmm_acc_grad_workspace((int)N, (int)C, (int)H, (int)W, (int)K, kH, kW, dH, dW, padH, padW);
-        void *ws = state_scratch(s, 0, need);
-        if (ws)
-            TH_CALL(s, cunn_b200_convmm_acc_grad(tdata<float>(x), tdata<float>(gy), tdata<float>(gradWeight), gradBias ? tdata<float>(gradBias) : nullptr,
+        const size_t need = R::convmm_acc_grad_workspace((int)N, (int)C, (int)H, (int)W, (int)K, kH, kW, dH, dW, padH, padW);
+        void *ws = need ? state_scratch(s, 0, need) : nullptr;
+        if (!need || ws)
+            TH_CALL(s, R::convmm_acc_grad(tdata<typename R::real>(x), tdata<typename R::real>(gy), tdata<typename R::real>(gradWeight), gradBias ? tdata<typename R::real>(gradBias) : nullptr,
                                                  (int)N, (int)C, (int)H, (int)W, (int)K, kH, kW, dH, dW, padH, padW, scale, ws,
                                                  state_scratch_bytes(s, 0), state_stream(s)));
     }
@@ -218,7 +267,7 @@ extern "C" CUNN_API void THNN_CudaSpatialDilatedConvolution_updateOutput(
     THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH, int dilationW, int dilationH)
 {
     long N, C, K, H, W, oH, oW;
-    if (!mm_prepare(s, input, nullptr, weight, bias, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW, dilationH, dilationW)) return;
+    if (!mm_prepare<THCudaTensor>(s, input, nullptr, weight, bias, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW, dilationH, dilationW)) return;
     THCudaTensor *x = new_contiguous(s, input);
     if (x) {
         const long sz4[4] = {N, K, oH, oW};
@@ -238,7 +287,7 @@ extern "C" CUNN_API void THNN_CudaSpatialDilatedConvolution_updateGradInput(
     THCudaTensor *, int kW, int kH, int dW, int dH, int padW, int padH, int dilationW, int dilationH)
 {
     long N, C, K, H, W, oH, oW;
-    if (!mm_prepare(s, input, gradOutput, weight, nullptr, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW, dilationH, dilationW)) return;
+    if (!mm_prepare<THCudaTensor>(s, input, gradOutput, weight, nullptr, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW, dilationH, dilationW)) return;
     THCudaTensor *gy = new_contiguous(s, gradOutput);
     if (gy) {
         const long sz4[4] = {N, C, H, W};
@@ -259,13 +308,13 @@ extern "C" CUNN_API void THNN_CudaSpatialDilatedConvolution_accGradParameters(
     float scale)
 {
     long N, C, K, H, W, oH, oW;
-    if (!mm_prepare(s, input, gradOutput, gradWeight, gradBias, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW, dilationH, dilationW)) return;
+    if (!mm_prepare<THCudaTensor>(s, input, gradOutput, gradWeight, gradBias, kH, kW, dH, dW, padH, padW, &N, &C, &K, &H, &W, &oH, &oW, dilationH, dilationW)) return;
     THCudaTensor *x = new_contiguous(s, input), *gy = new_contiguous(s, gradOutput);
     if (x && gy) {
         const size_t need = cunn_b200_dilated_conv_acc_grad_workspace((int)N, (int)C, (int)H, (int)W, (int)K, kH, kW, dH, dW, padH, padW,
                                                                        dilationH, dilationW);
-        void *ws = state_scratch(s, 0, need);
-        if (ws)
+        void *ws = need ? state_scratch(s, 0, need) : nullptr;
+        if (!need || ws)
             TH_CALL(s, cunn_b200_dilated_conv_acc_grad(tdata<float>(x), tdata<float>(gy), tdata<float>(gradWeight),
                                                        gradBias ? tdata<float>(gradBias) : nullptr, (int)N, (int)C, (int)H, (int)W, (int)K,
                                                        kH, kW, dH, dW, padH, padW, dilationH, dilationW, scale, ws, need, state_stream(s)));
@@ -363,8 +412,8 @@ extern "C" CUNN_API void THNN_CudaSpatialFullDilatedConvolution_accGradParameter
     if (x && gy) {
         const size_t need = cunn_b200_full_conv_acc_grad_workspace((int)N, (int)P, (int)H, (int)W, (int)Q, kH, kW, dH, dW, padH, padW,
                                                                     dilationH, dilationW, adjH, adjW);
-        void *ws = state_scratch(s, 0, need);
-        if (ws)
+        void *ws = need ? state_scratch(s, 0, need) : nullptr;
+        if (!need || ws)
             TH_CALL(s, cunn_b200_full_conv_acc_grad(tdata<float>(x), tdata<float>(gy), tdata<float>(gradWeight),
                                                     gradBias ? tdata<float>(gradBias) : nullptr, (int)N, (int)P, (int)H, (int)W, (int)Q,
                                                     kH, kW, dH, dW, padH, padW, dilationH, dilationW, adjH, adjW, scale, ws, need,
@@ -402,7 +451,8 @@ extern "C" CUNN_API void THNN_CudaSpatialFullConvolution_accGradParameters(
 
 // ---- BatchNormalization --------------------------------------------------------------------------------
 // Any [N, C, ...] input is viewed as [N, C, S] (lib/THCUNN/generic/BatchNormalization.cu:8-32).
-static bool bn_dims(THCState *s, const THCudaTensor *t, long *N, long *C, long *S)
+template <class Tensor>
+static bool bn_dims(THCState *s, const Tensor *t, long *N, long *C, long *S)
 {
     if (t->nDimension < 2) { raise(s, "batch normalisation expects at least 2 dimensions, got: %s", size_desc(t).c_str()); return false; }
     *N = t->size[0]; *C = t->size[1]; *S = 1;
@@ -410,22 +460,23 @@ static bool bn_dims(THCState *s, const THCudaTensor *t, long *N, long *C, long *
     return true;
 }
 
-extern "C" CUNN_API void THNN_CudaBatchNormalization_updateOutput(
-    THCState *s, THCudaTensor *input_, THCudaTensor *output_, THCudaTensor *weight_, THCudaTensor *bias_,
-    THCudaTensor *runningMean_, THCudaTensor *runningVar_, THCudaTensor *saveMean_, THCudaTensor *saveStd_, bool train,
+template <class R>
+static void hot_BatchNormalization_updateOutput(
+    THCState *s, typename R::tensor *input_, typename R::tensor *output_, typename R::tensor *weight_, typename R::tensor *bias_,
+    typename R::tensor *runningMean_, typename R::tensor *runningVar_, typename R::tensor *saveMean_, typename R::tensor *saveStd_, bool train,
     double momentum, double eps)
 {
     long N, C, S;
-    if (!bn_dims(s, input_, &N, &C, &S)) return;
-    THCudaTensor *x = new_contiguous(s, input_);
-    if (x && tensor_resize(s, output_, input_->nDimension, input_->size, 4)) {
+    if (!bn_dims<typename R::tensor>(s, input_, &N, &C, &S)) return;
+    typename R::tensor *x = new_contiguous(s, input_, (int)sizeof(typename R::real));
+    if (x && tensor_resize(s, output_, input_->nDimension, input_->size, (int)sizeof(typename R::real))) {
         const long c1[1] = {C};
-        if (!train || (tensor_resize(s, saveMean_, 1, c1, 4) && tensor_resize(s, saveStd_, 1, c1, 4))) {
-            void *ws = state_scratch(s, 2, cunn_b200_batchnorm_workspace((int)N, (int)C));
+        if (!train || (tensor_resize(s, saveMean_, 1, c1, (int)sizeof(typename R::real)) && tensor_resize(s, saveStd_, 1, c1, (int)sizeof(typename R::real)))) {
+            void *ws = state_scratch(s, 2, R::batchnorm_workspace((int)N, (int)C));
             if (ws)
-                TH_CALL(s, cunn_b200_batchnorm_forward(tdata<float>(x), tdata<float>(output_), weight_ ? tdata<float>(weight_) : nullptr,
-                                                       bias_ ? tdata<float>(bias_) : nullptr, tdata<float>(runningMean_), tdata<float>(runningVar_),
-                                                       tdata<float>(saveMean_), tdata<float>(saveStd_), (int)N, (int)C, (int)S, train ? 1 : 0,
+                TH_CALL(s, R::batchnorm_forward(tdata<typename R::real>(x), tdata<typename R::real>(output_), weight_ ? tdata<typename R::real>(weight_) : nullptr,
+                                                       bias_ ? tdata<typename R::real>(bias_) : nullptr, tdata<typename R::real>(runningMean_), tdata<typename R::real>(runningVar_),
+                                                       tdata<typename R::real>(saveMean_), tdata<typename R::real>(saveStd_), (int)N, (int)C, (int)S, train ? 1 : 0,
                                                        momentum, eps, ws, state_scratch_bytes(s, 2), state_stream(s)));
         }
     }
@@ -433,23 +484,24 @@ done:
     tensor_free(s, x);
 }
 
-extern "C" CUNN_API void THNN_CudaBatchNormalization_backward(
-    THCState *s, THCudaTensor *input_, THCudaTensor *gradOutput_, THCudaTensor *gradInput_, THCudaTensor *gradWeight_,
-    THCudaTensor *gradBias_, THCudaTensor *weight_, THCudaTensor *runningMean_, THCudaTensor *runningVar_,
-    THCudaTensor *saveMean_, THCudaTensor *saveStd_, bool train, double scale, double eps)
+template <class R>
+static void hot_BatchNormalization_backward(
+    THCState *s, typename R::tensor *input_, typename R::tensor *gradOutput_, typename R::tensor *gradInput_, typename R::tensor *gradWeight_,
+    typename R::tensor *gradBias_, typename R::tensor *weight_, typename R::tensor *runningMean_, typename R::tensor *runningVar_,
+    typename R::tensor *saveMean_, typename R::tensor *saveStd_, bool train, double scale, double eps)
 {
     long N, C, S;
-    if (!bn_dims(s, input_, &N, &C, &S)) return;
+    if (!bn_dims<typename R::tensor>(s, input_, &N, &C, &S)) return;
     TH_CHECK(s, nelem(gradOutput_) == nelem(input_), "input and gradOutput have different number of elements: input%s, gradOutput%s",
              size_desc(input_).c_str(), size_desc(gradOutput_).c_str());
-    THCudaTensor *x = new_contiguous(s, input_), *gy = new_contiguous(s, gradOutput_);
-    if (x && gy && (!gradInput_ || tensor_resize(s, gradInput_, input_->nDimension, input_->size, 4))) {
-        void *ws = state_scratch(s, 2, cunn_b200_batchnorm_workspace((int)N, (int)C));
+    typename R::tensor *x = new_contiguous(s, input_, (int)sizeof(typename R::real)), *gy = new_contiguous(s, gradOutput_, (int)sizeof(typename R::real));
+    if (x && gy && (!gradInput_ || tensor_resize(s, gradInput_, input_->nDimension, input_->size, (int)sizeof(typename R::real)))) {
+        void *ws = state_scratch(s, 2, R::batchnorm_workspace((int)N, (int)C));
         if (ws)
-            TH_CALL(s, cunn_b200_batchnorm_backward(tdata<float>(x), tdata<float>(gy), gradInput_ ? tdata<float>(gradInput_) : nullptr,
-                                                    gradWeight_ ? tdata<float>(gradWeight_) : nullptr, gradBias_ ? tdata<float>(gradBias_) : nullptr,
-                                                    weight_ ? tdata<float>(weight_) : nullptr, tdata<float>(runningMean_), tdata<float>(runningVar_),
-                                                    tdata<float>(saveMean_), tdata<float>(saveStd_), (int)N, (int)C, (int)S, train ? 1 : 0, scale, eps,
+            TH_CALL(s, R::batchnorm_backward(tdata<typename R::real>(x), tdata<typename R::real>(gy), gradInput_ ? tdata<typename R::real>(gradInput_) : nullptr,
+                                                    gradWeight_ ? tdata<typename R::real>(gradWeight_) : nullptr, gradBias_ ? tdata<typename R::real>(gradBias_) : nullptr,
+                                                    weight_ ? tdata<typename R::real>(weight_) : nullptr, tdata<typename R::real>(runningMean_), tdata<typename R::real>(runningVar_),
+                                                    tdata<typename R::real>(saveMean_), tdata<typename R::real>(saveStd_), (int)N, (int)C, (int)S, train ? 1 : 0, scale, eps,
                                                     ws, state_scratch_bytes(s, 2), state_stream(s)));
     }
 done:
@@ -457,7 +509,8 @@ done:
 }
 
 // ---- SpatialMaxPooling ------------------------------------------------------------------------------------
-extern "C" CUNN_API void THNN_CudaSpatialMaxPooling_updateOutput(THCState *s, THCudaTensor *input, THCudaTensor *output,
+template <class R>
+static void hot_SpatialMaxPooling_updateOutput(THCState *s, typename R::tensor *input, typename R::tensor *output,
                                                                  THCudaLongTensor *indices, int kW, int kH, int dW, int dH,
                                                                  int padW, int padH, bool ceil_mode)
 {
@@ -468,21 +521,22 @@ extern "C" CUNN_API void THNN_CudaSpatialMaxPooling_updateOutput(THCState *s, TH
     const int b = nd == 4;
     const long N = b ? input->size[0] : 1, C = input->size[b], H = input->size[b + 1], W = input->size[b + 2];
     const long oH = cunn_b200_maxpool_out_size((int)H, kH, dH, padH, 1, ceil_mode), oW = cunn_b200_maxpool_out_size((int)W, kW, dW, padW, 1, ceil_mode);
-    THCudaTensor *x = new_contiguous(s, input);
+    typename R::tensor *x = new_contiguous(s, input, (int)sizeof(typename R::real));
     if (x) {
         const long sz4[4] = {N, C, oH > 0 ? oH : 0, oW > 0 ? oW : 0};
-        if (oH < 1 || oW < 1 || (tensor_resize(s, output, 4, sz4, 4) && tensor_resize(s, indices, 4, sz4, 8))) {
-            TH_CALL(s, cunn_b200_maxpool_forward(tdata<float>(x), tdata<float>(output), tdata<int64_t>(indices), (int)N, (int)C, (int)H, (int)W, kH,
+        if (oH < 1 || oW < 1 || (tensor_resize(s, output, 4, sz4, (int)sizeof(typename R::real)) && tensor_resize(s, indices, 4, sz4, 8))) {
+            TH_CALL(s, R::maxpool_forward(tdata<typename R::real>(x), tdata<typename R::real>(output), tdata<int64_t>(indices), (int)N, (int)C, (int)H, (int)W, kH,
                                                  kW, dH, dW, padH, padW, 1, 1, ceil_mode, state_stream(s)));
-            if (nd == 3) tensor_resize(s, output, 3, sz4 + 1, 4);   // indices stay 4-D, as in the reference
+            if (nd == 3) tensor_resize(s, output, 3, sz4 + 1, (int)sizeof(typename R::real));   // indices stay 4-D, as in the reference
         }
     }
 done:
     tensor_free(s, x);
 }
 
-extern "C" CUNN_API void THNN_CudaSpatialMaxPooling_updateGradInput(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput,
-                                                                    THCudaTensor *gradInput, THCudaLongTensor *indices, int kW,
+template <class R>
+static void hot_SpatialMaxPooling_updateGradInput(THCState *s, typename R::tensor *input, typename R::tensor *gradOutput,
+                                                                    typename R::tensor *gradInput, THCudaLongTensor *indices, int kW,
                                                                     int kH, int dW, int dH, int padW, int padH, bool ceil_mode)
 {
     const int nd = input->nDimension;
@@ -494,12 +548,94 @@ extern "C" CUNN_API void THNN_CudaSpatialMaxPooling_updateGradInput(THCState *s,
              "Need gradOutput of dimension %d and shape [.. x %ld x %ld x %ld] but got gradOutput to be of shape: %s", nd, C, oH, oW,
              size_desc(gradOutput).c_str());
     TH_CHECK(s, nelem(indices) == nelem(gradOutput) && is_contiguous(indices), "indices and gradOutput shapes do not match");
-    THCudaTensor *gy = new_contiguous(s, gradOutput);
-    if (gy && tensor_resize(s, gradInput, nd, input->size, 4))
-        TH_CALL(s, cunn_b200_maxpool_backward(tdata<float>(gy), tdata<int64_t>(indices), tdata<float>(gradInput), (int)N, (int)C, (int)H, (int)W,
+    typename R::tensor *gy = new_contiguous(s, gradOutput, (int)sizeof(typename R::real));
+    if (gy && tensor_resize(s, gradInput, nd, input->size, (int)sizeof(typename R::real)))
+        TH_CALL(s, R::maxpool_backward(tdata<typename R::real>(gy), tdata<int64_t>(indices), tdata<typename R::real>(gradInput), (int)N, (int)C, (int)H, (int)W,
                                               kH, kW, dH, dW, padH, padW, 1, 1, ceil_mode, state_stream(s)));
 done:
     tensor_free(s, gy);
+}
+
+// ---- exported entry points of the hot path, float and double ----------------------------------------------------
+extern "C" CUNN_API void THNN_CudaSpatialDepthWiseConvolution_updateOutput(THCState *s, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias, THCudaTensor *unused5, THCudaTensor *unused6, int kW, int kH, int dW, int dH, int padW, int padH)
+{
+    hot_SpatialDepthWiseConvolution_updateOutput<RealFloat>(s, input, output, weight, bias, unused5, unused6, kW, kH, dW, dH, padW, padH);
+}
+extern "C" CUNN_API void THNN_CudaDoubleSpatialDepthWiseConvolution_updateOutput(THCState *s, THCudaDoubleTensor *input, THCudaDoubleTensor *output, THCudaDoubleTensor *weight, THCudaDoubleTensor *bias, THCudaDoubleTensor *unused5, THCudaDoubleTensor *unused6, int kW, int kH, int dW, int dH, int padW, int padH)
+{
+    hot_SpatialDepthWiseConvolution_updateOutput<RealDouble>(s, input, output, weight, bias, unused5, unused6, kW, kH, dW, dH, padW, padH);
+}
+extern "C" CUNN_API void THNN_CudaSpatialDepthWiseConvolution_updateGradInput(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight, THCudaTensor *unused5, THCudaTensor *unused6, int kW, int kH, int dW, int dH, int padW, int padH)
+{
+    hot_SpatialDepthWiseConvolution_updateGradInput<RealFloat>(s, input, gradOutput, gradInput, weight, unused5, unused6, kW, kH, dW, dH, padW, padH);
+}
+extern "C" CUNN_API void THNN_CudaDoubleSpatialDepthWiseConvolution_updateGradInput(THCState *s, THCudaDoubleTensor *input, THCudaDoubleTensor *gradOutput, THCudaDoubleTensor *gradInput, THCudaDoubleTensor *weight, THCudaDoubleTensor *unused5, THCudaDoubleTensor *unused6, int kW, int kH, int dW, int dH, int padW, int padH)
+{
+    hot_SpatialDepthWiseConvolution_updateGradInput<RealDouble>(s, input, gradOutput, gradInput, weight, unused5, unused6, kW, kH, dW, dH, padW, padH);
+}
+extern "C" CUNN_API void THNN_CudaSpatialDepthWiseConvolution_accGradParameters(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias, THCudaTensor *unused5, THCudaTensor *unused6, int kW, int kH, int dW, int dH, int padW, int padH, float scale)
+{
+    hot_SpatialDepthWiseConvolution_accGradParameters<RealFloat>(s, input, gradOutput, gradWeight, gradBias, unused5, unused6, kW, kH, dW, dH, padW, padH, scale);
+}
+extern "C" CUNN_API void THNN_CudaDoubleSpatialDepthWiseConvolution_accGradParameters(THCState *s, THCudaDoubleTensor *input, THCudaDoubleTensor *gradOutput, THCudaDoubleTensor *gradWeight, THCudaDoubleTensor *gradBias, THCudaDoubleTensor *unused5, THCudaDoubleTensor *unused6, int kW, int kH, int dW, int dH, int padW, int padH, double scale)
+{
+    hot_SpatialDepthWiseConvolution_accGradParameters<RealDouble>(s, input, gradOutput, gradWeight, gradBias, unused5, unused6, kW, kH, dW, dH, padW, padH, scale);
+}
+extern "C" CUNN_API void THNN_CudaSpatialConvolutionMM_updateOutput(THCState *s, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias, THCudaTensor *unused5, THCudaTensor *unused6, int kW, int kH, int dW, int dH, int padW, int padH)
+{
+    hot_SpatialConvolutionMM_updateOutput<RealFloat>(s, input, output, weight, bias, unused5, unused6, kW, kH, dW, dH, padW, padH);
+}
+extern "C" CUNN_API void THNN_CudaDoubleSpatialConvolutionMM_updateOutput(THCState *s, THCudaDoubleTensor *input, THCudaDoubleTensor *output, THCudaDoubleTensor *weight, THCudaDoubleTensor *bias, THCudaDoubleTensor *unused5, THCudaDoubleTensor *unused6, int kW, int kH, int dW, int dH, int padW, int padH)
+{
+    hot_SpatialConvolutionMM_updateOutput<RealDouble>(s, input, output, weight, bias, unused5, unused6, kW, kH, dW, dH, padW, padH);
+}
+extern "C" CUNN_API void THNN_CudaSpatialConvolutionMM_updateGradInput(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight, THCudaTensor *unused5, THCudaTensor *unused6, int kW, int kH, int dW, int dH, int padW, int padH)
+{
+    hot_SpatialConvolutionMM_updateGradInput<RealFloat>(s, input, gradOutput, gradInput, weight, unused5, unused6, kW, kH, dW, dH, padW, padH);
+}
+extern "C" CUNN_API void THNN_CudaDoubleSpatialConvolutionMM_updateGradInput(THCState *s, THCudaDoubleTensor *input, THCudaDoubleTensor *gradOutput, THCudaDoubleTensor *gradInput, THCudaDoubleTensor *weight, THCudaDoubleTensor *unused5, THCudaDoubleTensor *unused6, int kW, int kH, int dW, int dH, int padW, int padH)
+{
+    hot_SpatialConvolutionMM_updateGradInput<RealDouble>(s, input, gradOutput, gradInput, weight, unused5, unused6, kW, kH, dW, dH, padW, padH);
+}
+extern "C" CUNN_API void THNN_CudaSpatialConvolutionMM_accGradParameters(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias, THCudaTensor *unused5, THCudaTensor *unused6, int kW, int kH, int dW, int dH, int padW, int padH, float scale)
+{
+    hot_SpatialConvolutionMM_accGradParameters<RealFloat>(s, input, gradOutput, gradWeight, gradBias, unused5, unused6, kW, kH, dW, dH, padW, padH, scale);
+}
+extern "C" CUNN_API void THNN_CudaDoubleSpatialConvolutionMM_accGradParameters(THCState *s, THCudaDoubleTensor *input, THCudaDoubleTensor *gradOutput, THCudaDoubleTensor *gradWeight, THCudaDoubleTensor *gradBias, THCudaDoubleTensor *unused5, THCudaDoubleTensor *unused6, int kW, int kH, int dW, int dH, int padW, int padH, double scale)
+{
+    hot_SpatialConvolutionMM_accGradParameters<RealDouble>(s, input, gradOutput, gradWeight, gradBias, unused5, unused6, kW, kH, dW, dH, padW, padH, scale);
+}
+extern "C" CUNN_API void THNN_CudaBatchNormalization_updateOutput(THCState *s, THCudaTensor *input_, THCudaTensor *output_, THCudaTensor *weight_, THCudaTensor *bias_, THCudaTensor *runningMean_, THCudaTensor *runningVar_, THCudaTensor *saveMean_, THCudaTensor *saveStd_, bool train, double momentum, double eps)
+{
+    hot_BatchNormalization_updateOutput<RealFloat>(s, input_, output_, weight_, bias_, runningMean_, runningVar_, saveMean_, saveStd_, train, momentum, eps);
+}
+extern "C" CUNN_API void THNN_CudaDoubleBatchNormalization_updateOutput(THCState *s, THCudaDoubleTensor *input_, THCudaDoubleTensor *output_, THCudaDoubleTensor *weight_, THCudaDoubleTensor *bias_, THCudaDoubleTensor *runningMean_, THCudaDoubleTensor *runningVar_, THCudaDoubleTensor *saveMean_, THCudaDoubleTensor *saveStd_, bool train, double momentum, double eps)
+{
+    hot_BatchNormalization_updateOutput<RealDouble>(s, input_, output_, weight_, bias_, runningMean_, runningVar_, saveMean_, saveStd_, train, momentum, eps);
+}
+extern "C" CUNN_API void THNN_CudaBatchNormalization_backward(THCState *s, THCudaTensor *input_, THCudaTensor *gradOutput_, THCudaTensor *gradInput_, THCudaTensor *gradWeight_, THCudaTensor *gradBias_, THCudaTensor *weight_, THCudaTensor *runningMean_, THCudaTensor *runningVar_, THCudaTensor *saveMean_, THCudaTensor *saveStd_, bool train, double scale, double eps)
+{
+    hot_BatchNormalization_backward<RealFloat>(s, input_, gradOutput_, gradInput_, gradWeight_, gradBias_, weight_, runningMean_, runningVar_, saveMean_, saveStd_, train, scale, eps);
+}
+extern "C" CUNN_API void THNN_CudaDoubleBatchNormalization_backward(THCState *s, THCudaDoubleTensor *input_, THCudaDoubleTensor *gradOutput_, THCudaDoubleTensor *gradInput_, THCudaDoubleTensor *gradWeight_, THCudaDoubleTensor *gradBias_, THCudaDoubleTensor *weight_, THCudaDoubleTensor *runningMean_, THCudaDoubleTensor *runningVar_, THCudaDoubleTensor *saveMean_, THCudaDoubleTensor *saveStd_, bool train, double scale, double eps)
+{
+    hot_BatchNormalization_backward<RealDouble>(s, input_, gradOutput_, gradInput_, gradWeight_, gradBias_, weight_, runningMean_, runningVar_, saveMean_, saveStd_, train, scale, eps);
+}
+extern "C" CUNN_API void THNN_CudaSpatialMaxPooling_updateOutput(THCState *s, THCudaTensor *input, THCudaTensor *output, THCudaLongTensor *indices, int kW, int kH, int dW, int dH, int padW, int padH, bool ceil_mode)
+{
+    hot_SpatialMaxPooling_updateOutput<RealFloat>(s, input, output, indices, kW, kH, dW, dH, padW, padH, ceil_mode);
+}
+extern "C" CUNN_API void THNN_CudaDoubleSpatialMaxPooling_updateOutput(THCState *s, THCudaDoubleTensor *input, THCudaDoubleTensor *output, THCudaLongTensor *indices, int kW, int kH, int dW, int dH, int padW, int padH, bool ceil_mode)
+{
+    hot_SpatialMaxPooling_updateOutput<RealDouble>(s, input, output, indices, kW, kH, dW, dH, padW, padH, ceil_mode);
+}
+extern "C" CUNN_API void THNN_CudaSpatialMaxPooling_updateGradInput(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaLongTensor *indices, int kW, int kH, int dW, int dH, int padW, int padH, bool ceil_mode)
+{
+    hot_SpatialMaxPooling_updateGradInput<RealFloat>(s, input, gradOutput, gradInput, indices, kW, kH, dW, dH, padW, padH, ceil_mode);
+}
+extern "C" CUNN_API void THNN_CudaDoubleSpatialMaxPooling_updateGradInput(THCState *s, THCudaDoubleTensor *input, THCudaDoubleTensor *gradOutput, THCudaDoubleTensor *gradInput, THCudaLongTensor *indices, int kW, int kH, int dW, int dH, int padW, int padH, bool ceil_mode)
+{
+    hot_SpatialMaxPooling_updateGradInput<RealDouble>(s, input, gradOutput, gradInput, indices, kW, kH, dW, dH, padW, padH, ceil_mode);
 }
 
 // ---- support operators ---------------------------------------------------------------------------------------

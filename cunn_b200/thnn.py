@@ -81,13 +81,26 @@ for _name, _args in _SIGS.items():
     _f.restype = None
     _f.argtypes = [c_void_p] + _args
 
+# the hot path also exists for double tensors (THNN_CudaDouble*): accreal, i.e. `scale`, is a double there
+DOUBLE_ENTRY_POINTS = [n for n in _SIGS if n.split("_")[0] in ("SpatialDepthWiseConvolution", "SpatialConvolutionMM",
+                                                                "BatchNormalization", "SpatialMaxPooling")]
+for _name in DOUBLE_ENTRY_POINTS:
+    _f = getattr(lib, "THNN_CudaDouble" + _name)
+    _f.restype = None
+    _f.argtypes = [c_void_p] + [c_double if a is _F else a for a in _SIGS[_name]]
+
 
 class THNNError(CunnError):
     """An argument or launch error reported through the state's error hook (TH's THError)."""
 
 
 class THNN:
-    def __init__(self):
+    """Drives the THNN_Cuda* entry points (dtype=torch.float32) or the THNN_CudaDouble* ones (torch.float64)
+    the way the LuaJIT binding does: a state first, tensor structs, outputs resized by the callee."""
+
+    def __init__(self, dtype=torch.float32):
+        self.real = dtype
+        self.prefix = "THNN_CudaDouble" if dtype == torch.float64 else "THNN_Cuda"
         self.state = lib.THCState_b200_new()
         self.errors = []
         self._hook = _ERRFN(lambda msg, ctx: self.errors.append(msg.decode()))
@@ -115,8 +128,9 @@ class THNN:
         self._keep.append(t)
         return h
 
-    def out(self, capacity, dtype=torch.float32, device="cuda"):
+    def out(self, capacity, dtype=None, device="cuda"):
         """An output tensor with no shape yet over `capacity` elements of torch memory: the callee resizes it."""
+        dtype = dtype or self.real
         buf = torch.empty(max(int(capacity), 1), dtype=dtype, device=device)
         sizes = (c_long * 1)(0)
         h = lib.THCudaTensor_b200_wrap(self.state, buf.data_ptr(), buf.numel(), 0, sizes, None, buf.element_size(), 0)
@@ -137,7 +151,7 @@ class THNN:
     def call(self, name, *args):
         lib.THCState_b200_setStream(self.state, torch.cuda.current_stream().cuda_stream)
         n0 = len(self.errors)
-        getattr(lib, "THNN_Cuda" + name)(self.state, *args)
+        getattr(lib, self.prefix + name)(self.state, *args)
         if len(self.errors) > n0:
             raise THNNError(self.errors[-1])
 

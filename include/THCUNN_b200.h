@@ -52,6 +52,7 @@ typedef struct THCudaTensor {
 } THCudaTensor;
 
 typedef THCudaTensor THCudaLongTensor;   /* same layout, 8-byte elements */
+typedef THCudaTensor THCudaDoubleTensor; /* same layout, 8-byte elements */
 typedef struct THCState THCState;        /* opaque here: current stream, error hook, scratch */
 #endif
 
@@ -153,6 +154,40 @@ CUNN_API void THNN_CudaSpatialMaxPooling_updateGradInput(
     THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaLongTensor *indices,
     int kW, int kH, int dW, int dH, int padW, int padH, bool ceil_mode);
 
+/* ---- hot path (double): the same ten entry points for THCudaDoubleTensor, accreal = double (THCUNN.lua:54) ---- */
+CUNN_API void THNN_CudaDoubleSpatialDepthWiseConvolution_updateOutput(
+    THCState *state, THCudaDoubleTensor *input, THCudaDoubleTensor *output, THCudaDoubleTensor *weight, THCudaDoubleTensor *bias,
+    THCudaDoubleTensor *columns, THCudaDoubleTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH);
+CUNN_API void THNN_CudaDoubleSpatialDepthWiseConvolution_updateGradInput(
+    THCState *state, THCudaDoubleTensor *input, THCudaDoubleTensor *gradOutput, THCudaDoubleTensor *gradInput, THCudaDoubleTensor *weight,
+    THCudaDoubleTensor *gradColumns, THCudaDoubleTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH);
+CUNN_API void THNN_CudaDoubleSpatialDepthWiseConvolution_accGradParameters(
+    THCState *state, THCudaDoubleTensor *input, THCudaDoubleTensor *gradOutput, THCudaDoubleTensor *gradWeight, THCudaDoubleTensor *gradBias,
+    THCudaDoubleTensor *columns, THCudaDoubleTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH, double scale);
+CUNN_API void THNN_CudaDoubleSpatialConvolutionMM_updateOutput(
+    THCState *state, THCudaDoubleTensor *input, THCudaDoubleTensor *output, THCudaDoubleTensor *weight, THCudaDoubleTensor *bias,
+    THCudaDoubleTensor *columns, THCudaDoubleTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH);
+CUNN_API void THNN_CudaDoubleSpatialConvolutionMM_updateGradInput(
+    THCState *state, THCudaDoubleTensor *input, THCudaDoubleTensor *gradOutput, THCudaDoubleTensor *gradInput, THCudaDoubleTensor *weight,
+    THCudaDoubleTensor *gradColumns, THCudaDoubleTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH);
+CUNN_API void THNN_CudaDoubleSpatialConvolutionMM_accGradParameters(
+    THCState *state, THCudaDoubleTensor *input, THCudaDoubleTensor *gradOutput, THCudaDoubleTensor *gradWeight, THCudaDoubleTensor *gradBias,
+    THCudaDoubleTensor *columns, THCudaDoubleTensor *ones, int kW, int kH, int dW, int dH, int padW, int padH, double scale);
+CUNN_API void THNN_CudaDoubleBatchNormalization_updateOutput(
+    THCState *state, THCudaDoubleTensor *input_, THCudaDoubleTensor *output_, THCudaDoubleTensor *weight_, THCudaDoubleTensor *bias_,
+    THCudaDoubleTensor *runningMean_, THCudaDoubleTensor *runningVar_, THCudaDoubleTensor *saveMean_, THCudaDoubleTensor *saveStd_,
+    bool train, double momentum, double eps);
+CUNN_API void THNN_CudaDoubleBatchNormalization_backward(
+    THCState *state, THCudaDoubleTensor *input_, THCudaDoubleTensor *gradOutput_, THCudaDoubleTensor *gradInput_,
+    THCudaDoubleTensor *gradWeight_, THCudaDoubleTensor *gradBias_, THCudaDoubleTensor *weight_, THCudaDoubleTensor *runningMean_,
+    THCudaDoubleTensor *runningVar_, THCudaDoubleTensor *saveMean_, THCudaDoubleTensor *saveStd_, bool train, double scale, double eps);
+CUNN_API void THNN_CudaDoubleSpatialMaxPooling_updateOutput(
+    THCState *state, THCudaDoubleTensor *input, THCudaDoubleTensor *output, THCudaLongTensor *indices, int kW, int kH, int dW,
+    int dH, int padW, int padH, bool ceil_mode);
+CUNN_API void THNN_CudaDoubleSpatialMaxPooling_updateGradInput(
+    THCState *state, THCudaDoubleTensor *input, THCudaDoubleTensor *gradOutput, THCudaDoubleTensor *gradInput, THCudaLongTensor *indices,
+    int kW, int kH, int dW, int dH, int padW, int padH, bool ceil_mode);
+
 /* ---- support operators (float) --------------------------------------------------------------------- */
 CUNN_API void THNN_CudaThreshold_updateOutput(THCState *state, THCudaTensor *input, THCudaTensor *output,
                                               float threshold, float val, bool inplace);
@@ -176,7 +211,7 @@ CUNN_API void THNN_CudaClassNLLCriterion_updateGradInput(THCState *state, THCuda
                                                          THCudaTensor *weights, THCudaTensor *total_weight,
                                                          long ignore_index);
 
-/* Every other THNN_Cuda<Op>_<method> and every THNN_CudaDouble<Op>_<method> name of the reference header is
+/* Every other THNN_Cuda<Op>_<method> and THNN_CudaDouble<Op>_<method> name of the reference header is
  * exported too, so the binding's symbol lookup cannot fail, but only reports "not implemented in this
  * build" through the error hook of the state it is given. */
 

@@ -195,13 +195,22 @@ CUNN_API int cunn_b200_maxpool_backward(const float *gy, const int64_t *indices,
  * save_mean = mean, save_std = invstd = 1/sqrt(var + eps); running_mean/var updated with `momentum`,
  * running_var from the UNBIASED variance.  Inference: uses the running statistics and leaves them alone.
  * weight / bias may be NULL (gamma = 1, beta = 0).  `workspace`: caller-owned scratch of at least
- * cunn_b200_batchnorm_workspace(N, C) bytes, 16-byte aligned.  Its first 32 KiB hold per-channel ticket counters
- * (the CTA that hands in a channel's last partial sum finishes the channel, which saves a launch): they must be
- * zero when a call is enqueued and every call leaves them zero, so zero the buffer once and let no other
- * operator write there; the rest of the buffer needs no initialisation.
+ * cunn_b200_batchnorm_workspace(N, C) bytes, 16-byte aligned.  Its first cunn_b200_batchnorm_counter_bytes()
+ * bytes hold per-channel ticket counters and ready flags (the CTA that hands in a channel's last partial sum
+ * finishes the channel; large tensors are reduced and normalised group by group inside one launch so that the
+ * second read comes from L2): they must be zero when a call is enqueued and every call leaves them zero, so zero
+ * the buffer once and let no other operator write there; the rest of the buffer needs no initialisation.  If
+ * cunn_b200_device_status() ever reports a wait that ran out, zero the counters again before the next call.
  * Replaces THNN_(BatchNormalization_updateOutput) (lib/THCUNN/generic/BatchNormalization.cu:34-66,
  * kernels lib/THCUNN/BatchNormalization.cu:141-212). */
 CUNN_API size_t cunn_b200_batchnorm_workspace(int N, int C);
+CUNN_API size_t cunn_b200_batchnorm_counter_bytes(void);
+/* Which shapes take the one-launch, group-by-group kernels (statistics and normalisation of a group of channels
+ * back to back, so that the second read of the group comes from L2).  0: none; 1 (default): the training forward
+ * pass when a channel's N planes are at least 6 MB and two such slabs fit the L2 window; 2: every shape they
+ * apply to, forward and backward.  Results do not depend on the mode beyond rounding.  Process-wide. */
+CUNN_API void cunn_b200_batchnorm_set_grouped(int mode);
+CUNN_API int cunn_b200_batchnorm_get_grouped(void);
 CUNN_API int cunn_b200_batchnorm_forward(const float *x, float *y, const float *weight, const float *bias,
                                          float *running_mean, float *running_var, float *save_mean, float *save_std,
                                          int N, int C, int S, int train, double momentum, double eps,
@@ -295,6 +304,51 @@ CUNN_API int cunn_b200_mobilenet_step(const cunn_b200_mobilenet_config *cfg, con
                                       int batch, float inv_global_batch, const float *params, float *grads,
                                       float *bn_running, void *arena, size_t arena_bytes, float *loss,
                                       double momentum, double eps, cunn_stream_t stream);
+
+/* ---- fp64 twins of the hot path -----------------------------------------------------------------------
+ * The operators above for double tensors, behind THNN_CudaDouble* (the reference instantiates every entry point
+ * for float and double: lib/THCUNN/SpatialDepthWiseConvolution.cu:9, SpatialConvolutionMM.cu:9,
+ * BatchNormalization.cu:285-286, SpatialDilatedMaxPooling.cu:82-83 include THCGenerateFloatTypes.h; `accreal`
+ * is double, THCUNN.lua:54).  Same argument meaning, layouts, accumulate semantics and error behaviour; plain fp64
+ * CUDA-core kernels of any shape (the convolution is an implicit GEMM on the fp64 FMA pipes).  The
+ * parameter-gradient calls need no scratch (their workspace queries return 0 and the arguments are ignored);
+ * batch norm needs cunn_b200_double_batchnorm_workspace(N, C) bytes whose contents are irrelevant. */
+CUNN_API int cunn_b200_double_dwconv_forward(const double *x, const double *weight, const double *bias, double *y, int N, int C,
+                                             int H, int W, int M, int kH, int kW, int dH, int dW, int padH, int padW,
+                                             cunn_stream_t stream);
+CUNN_API int cunn_b200_double_dwconv_grad_input(const double *gy, const double *weight, double *gx, int N, int C, int H, int W,
+                                                int M, int kH, int kW, int dH, int dW, int padH, int padW, cunn_stream_t stream);
+CUNN_API size_t cunn_b200_double_dwconv_acc_grad_workspace(int N, int C, int H, int W, int M, int kH, int kW, int dH, int dW,
+                                                           int padH, int padW);
+CUNN_API int cunn_b200_double_dwconv_acc_grad(const double *x, const double *gy, double *grad_weight, double *grad_bias, int N,
+                                              int C, int H, int W, int M, int kH, int kW, int dH, int dW, int padH, int padW,
+                                              double scale, void *workspace, size_t workspace_bytes, cunn_stream_t stream);
+CUNN_API int cunn_b200_double_convmm_forward(const double *x, const double *weight, const double *bias, double *y, int N, int C,
+                                             int H, int W, int K, int kH, int kW, int dH, int dW, int padH, int padW,
+                                             cunn_stream_t stream);
+CUNN_API int cunn_b200_double_convmm_grad_input(const double *gy, const double *weight, double *gx, int N, int C, int H, int W,
+                                                int K, int kH, int kW, int dH, int dW, int padH, int padW, cunn_stream_t stream);
+CUNN_API size_t cunn_b200_double_convmm_acc_grad_workspace(int N, int C, int H, int W, int K, int kH, int kW, int dH, int dW,
+                                                           int padH, int padW);
+CUNN_API int cunn_b200_double_convmm_acc_grad(const double *x, const double *gy, double *grad_weight, double *grad_bias, int N,
+                                              int C, int H, int W, int K, int kH, int kW, int dH, int dW, int padH, int padW,
+                                              double scale, void *workspace, size_t workspace_bytes, cunn_stream_t stream);
+CUNN_API size_t cunn_b200_double_batchnorm_workspace(int N, int C);
+CUNN_API int cunn_b200_double_batchnorm_forward(const double *x, double *y, const double *weight, const double *bias,
+                                                double *running_mean, double *running_var, double *save_mean, double *save_std,
+                                                int N, int C, int S, int train, double momentum, double eps, void *workspace,
+                                                size_t workspace_bytes, cunn_stream_t stream);
+CUNN_API int cunn_b200_double_batchnorm_backward(const double *x, const double *gy, double *gx, double *grad_weight,
+                                                 double *grad_bias, const double *weight, const double *running_mean,
+                                                 const double *running_var, const double *save_mean, const double *save_std, int N,
+                                                 int C, int S, int train, double scale, double eps, void *workspace,
+                                                 size_t workspace_bytes, cunn_stream_t stream);
+CUNN_API int cunn_b200_double_maxpool_forward(const double *x, double *y, int64_t *indices, int N, int C, int H, int W, int kH,
+                                              int kW, int dH, int dW, int padH, int padW, int dilH, int dilW, int ceil_mode,
+                                              cunn_stream_t stream);
+CUNN_API int cunn_b200_double_maxpool_backward(const double *gy, const int64_t *indices, double *gx, int N, int C, int H, int W,
+                                               int kH, int kW, int dH, int dW, int padH, int padW, int dilH, int dilW, int ceil_mode,
+                                               cunn_stream_t stream);
 
 #ifdef __cplusplus
 }

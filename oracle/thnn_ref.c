@@ -8,9 +8,11 @@
  * benchmark have something to compare the CUDA kernels with.  Nothing in the
  * shipped library links, loads or calls it.
  *
- * The file is compiled twice (see the Makefile next to it):
+ * The file is compiled three times (see the Makefile next to it):
  *   -DREF_ACC=double -DREF_PREFIX=ref64_   the oracle proper: fp32 tensors,
  *                                          every sum carried in fp64;
+ *   -DREF_REAL=double -DREF_ACC=double -DREF_PREFIX=refd_   the oracle of the
+ *                                          CudaDouble entry points: fp64 tensors;
  *   -DREF_ACC=float  -DREF_PREFIX=ref32_   the timed CPU baseline: the same
  *                                          loops with fp32 accumulators, which
  *                                          is the arithmetic torch/nn's CPU
@@ -49,6 +51,16 @@
 
 typedef REF_ACC acc_t;
 
+/* Element type of every tensor: float for the Cuda (float) entry points, double for the CudaDouble ones. */
+#ifndef REF_REAL
+#define REF_REAL float
+#endif
+typedef REF_REAL real_t;
+#define REAL_IS_DOUBLE (sizeof(real_t) == 8)
+/* lowest finite value of the element type: the start value of the max-pooling scan
+ * (THCNumerics<AccType>::min(), lib/THCUNN/SpatialDilatedMaxPooling.cu:28) */
+#define REAL_LOWEST ((real_t)(REAL_IS_DOUBLE ? -DBL_MAX : -FLT_MAX))
+
 /* Index base of stored pooling indices and class targets.  libTH defines
  * TH_INDEX_BASE as 1 for the Lua build the reference's tests run under
  * (lib/THCUNN/SpatialDilatedMaxPooling.cu:40 adds it to every stored index). */
@@ -79,7 +91,7 @@ int FN(max_threads)(void) { return 1; }
  * plane plus a bias broadcast
  * (lib/THCUNN/generic/SpatialDepthWiseConvolution.cu:150-226; unfold with zero
  * padding: lib/THCUNN/im2col.h:18-37). */
-void FN(dwconv_forward)(const float *x, const float *w, const float *bias, float *y,
+void FN(dwconv_forward)(const real_t *x, const real_t *w, const real_t *bias, real_t *y,
                         int N, int C, int H, int W, int M, int kH, int kW,
                         int dH, int dW, int padH, int padW)
 {
@@ -88,10 +100,10 @@ void FN(dwconv_forward)(const float *x, const float *w, const float *bias, float
 #pragma omp parallel for collapse(2) schedule(static)
     for (int n = 0; n < N; ++n)
         for (int c = 0; c < C; ++c) {
-            const float *xp = x + ((size_t)n * C + c) * H * W;
+            const real_t *xp = x + ((size_t)n * C + c) * H * W;
             for (int j = 0; j < M; ++j) {
-                const float *wp = w + ((size_t)j * C + c) * kH * kW;
-                float *yp = y + (((size_t)n * C + c) * M + j) * oH * oW;
+                const real_t *wp = w + ((size_t)j * C + c) * kH * kW;
+                real_t *yp = y + (((size_t)n * C + c) * M + j) * oH * oW;
                 const acc_t b = bias ? (acc_t)bias[(size_t)j * C + c] : (acc_t)0;
                 for (int oh = 0; oh < oH; ++oh)
                     for (int ow = 0; ow < oW; ++ow) {
@@ -105,7 +117,7 @@ void FN(dwconv_forward)(const float *x, const float *w, const float *bias, float
                                 s += (acc_t)wp[kh * kW + kw] * (acc_t)xp[ih * W + iw];
                             }
                         }
-                        yp[oh * oW + ow] = (float)s;
+                        yp[oh * oW + ow] = (real_t)s;
                     }
             }
         }
@@ -114,7 +126,7 @@ void FN(dwconv_forward)(const float *x, const float *w, const float *bias, float
 /* Input gradient: W^T * gy per (image, channel), folded back with col2im
  * (lib/THCUNN/generic/SpatialDepthWiseConvolution.cu:346-400; fold:
  * lib/THCUNN/im2col.h:72-101).  gy is read as contiguous [N,C,M,oH,oW]. */
-void FN(dwconv_grad_input)(const float *gy, const float *w, float *gx,
+void FN(dwconv_grad_input)(const real_t *gy, const real_t *w, real_t *gx,
                            int N, int C, int H, int W, int M, int kH, int kW,
                            int dH, int dW, int padH, int padW)
 {
@@ -123,13 +135,13 @@ void FN(dwconv_grad_input)(const float *gy, const float *w, float *gx,
 #pragma omp parallel for collapse(2) schedule(static)
     for (int n = 0; n < N; ++n)
         for (int c = 0; c < C; ++c) {
-            float *gxp = gx + ((size_t)n * C + c) * H * W;
+            real_t *gxp = gx + ((size_t)n * C + c) * H * W;
             for (int h = 0; h < H; ++h)
                 for (int wi = 0; wi < W; ++wi) {
                     acc_t s = 0;
                     for (int j = 0; j < M; ++j) {
-                        const float *wp = w + ((size_t)j * C + c) * kH * kW;
-                        const float *gyp = gy + (((size_t)n * C + c) * M + j) * oH * oW;
+                        const real_t *wp = w + ((size_t)j * C + c) * kH * kW;
+                        const real_t *gyp = gy + (((size_t)n * C + c) * M + j) * oH * oW;
                         for (int kh = 0; kh < kH; ++kh) {
                             const int t = h + padH - kh;
                             if (t < 0 || t % dH) continue;
@@ -144,16 +156,16 @@ void FN(dwconv_grad_input)(const float *gy, const float *w, float *gx,
                             }
                         }
                     }
-                    gxp[h * W + wi] = (float)s;
+                    gxp[h * W + wi] = (real_t)s;
                 }
         }
 }
 
 /* Parameter gradients, ACCUMULATED into gw / gb (GEMM and GEMV with beta = 1:
  * lib/THCUNN/generic/SpatialDepthWiseConvolution.cu:546-613). gb may be NULL. */
-void FN(dwconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
+void FN(dwconv_acc_grad)(const real_t *x, const real_t *gy, real_t *gw, real_t *gb,
                          int N, int C, int H, int W, int M, int kH, int kW,
-                         int dH, int dW, int padH, int padW, float scale)
+                         int dH, int dW, int padH, int padW, real_t scale)
 {
     const int oH = (H + 2 * padH - kH) / dH + 1;
     const int oW = (W + 2 * padW - kW) / dW + 1;
@@ -165,8 +177,8 @@ void FN(dwconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
             const int kk = kH * kW;
             for (int i = 0; i < kk && i < 64; ++i) sw[i] = 0;
             for (int n = 0; n < N; ++n) {
-                const float *xp = x + ((size_t)n * C + c) * H * W;
-                const float *gyp = gy + (((size_t)n * C + c) * M + j) * oH * oW;
+                const real_t *xp = x + ((size_t)n * C + c) * H * W;
+                const real_t *gyp = gy + (((size_t)n * C + c) * M + j) * oH * oW;
                 for (int oh = 0; oh < oH; ++oh)
                     for (int ow = 0; ow < oW; ++ow) {
                         const acc_t g = gyp[oh * oW + ow];
@@ -182,9 +194,9 @@ void FN(dwconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
                         }
                     }
             }
-            float *gwp = gw + ((size_t)j * C + c) * kk;
-            for (int i = 0; i < kk; ++i) gwp[i] = (float)((acc_t)gwp[i] + (acc_t)scale * sw[i]);
-            if (gb) gb[(size_t)j * C + c] = (float)((acc_t)gb[(size_t)j * C + c] + (acc_t)scale * sb);
+            real_t *gwp = gw + ((size_t)j * C + c) * kk;
+            for (int i = 0; i < kk; ++i) gwp[i] = (real_t)((acc_t)gwp[i] + (acc_t)scale * sw[i]);
+            if (gb) gb[(size_t)j * C + c] = (real_t)((acc_t)gb[(size_t)j * C + c] + (acc_t)scale * sb);
         }
 }
 
@@ -199,7 +211,7 @@ void FN(dwconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
 
 /* Forward: y_n = bias*ones + W * im2col(x_n)
  * (lib/THCUNN/generic/SpatialConvolutionMM.cu:129-194, SpatialDilatedConvolution.cu:140-196). */
-void FN(dilconv_forward)(const float *x, const float *w, const float *bias, float *y,
+void FN(dilconv_forward)(const real_t *x, const real_t *w, const real_t *bias, real_t *y,
                          int N, int C, int H, int W, int K, int kH, int kW,
                          int dH, int dW, int padH, int padW, int dilH, int dilW)
 {
@@ -208,14 +220,14 @@ void FN(dilconv_forward)(const float *x, const float *w, const float *bias, floa
 #pragma omp parallel for collapse(2) schedule(static)
     for (int n = 0; n < N; ++n)
         for (int k = 0; k < K; ++k) {
-            float *yp = y + ((size_t)n * K + k) * oH * oW;
+            real_t *yp = y + ((size_t)n * K + k) * oH * oW;
             const acc_t b = bias ? (acc_t)bias[k] : (acc_t)0;
             for (int oh = 0; oh < oH; ++oh)
                 for (int ow = 0; ow < oW; ++ow) {
                     acc_t s = b;
                     for (int c = 0; c < C; ++c) {
-                        const float *xp = x + ((size_t)n * C + c) * H * W;
-                        const float *wp = w + ((size_t)k * C + c) * kH * kW;
+                        const real_t *xp = x + ((size_t)n * C + c) * H * W;
+                        const real_t *wp = w + ((size_t)k * C + c) * kH * kW;
                         for (int kh = 0; kh < kH; ++kh) {
                             const int ih = oh * dH - padH + kh * dilH;
                             if (ih < 0 || ih >= H) continue;
@@ -226,14 +238,14 @@ void FN(dilconv_forward)(const float *x, const float *w, const float *bias, floa
                             }
                         }
                     }
-                    yp[oh * oW + ow] = (float)s;
+                    yp[oh * oW + ow] = (real_t)s;
                 }
         }
 }
 
 /* Input gradient: gx_n = col2im(W^T * gy_n)
  * (lib/THCUNN/generic/SpatialConvolutionMM.cu:272-308, SpatialDilatedConvolution.cu:244-290). */
-void FN(dilconv_grad_input)(const float *gy, const float *w, float *gx,
+void FN(dilconv_grad_input)(const real_t *gy, const real_t *w, real_t *gx,
                             int N, int C, int H, int W, int K, int kH, int kW,
                             int dH, int dW, int padH, int padW, int dilH, int dilW)
 {
@@ -242,7 +254,7 @@ void FN(dilconv_grad_input)(const float *gy, const float *w, float *gx,
 #pragma omp parallel for collapse(2) schedule(static)
     for (int n = 0; n < N; ++n)
         for (int c = 0; c < C; ++c) {
-            float *gxp = gx + ((size_t)n * C + c) * H * W;
+            real_t *gxp = gx + ((size_t)n * C + c) * H * W;
             for (int h = 0; h < H; ++h)
                 for (int wi = 0; wi < W; ++wi) {
                     acc_t s = 0;
@@ -261,7 +273,7 @@ void FN(dilconv_grad_input)(const float *gy, const float *w, float *gx,
                                      (acc_t)gy[((size_t)n * K + k) * oH * oW + oh * oW + ow];
                         }
                     }
-                    gxp[h * W + wi] = (float)s;
+                    gxp[h * W + wi] = (real_t)s;
                 }
         }
 }
@@ -269,9 +281,9 @@ void FN(dilconv_grad_input)(const float *gy, const float *w, float *gx,
 /* Parameter gradients, accumulated: gW += scale * sum_n gy_n * im2col(x_n)^T,
  * gb += scale * sum gy  (lib/THCUNN/generic/SpatialConvolutionMM.cu:396-470,
  * SpatialDilatedConvolution.cu:350-440). */
-void FN(dilconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
+void FN(dilconv_acc_grad)(const real_t *x, const real_t *gy, real_t *gw, real_t *gb,
                           int N, int C, int H, int W, int K, int kH, int kW,
-                          int dH, int dW, int padH, int padW, int dilH, int dilW, float scale)
+                          int dH, int dW, int padH, int padW, int dilH, int dilW, real_t scale)
 {
     const int oH = (H + 2 * padH - (dilH * (kH - 1) + 1)) / dH + 1;
     const int oW = (W + 2 * padW - (dilW * (kW - 1) + 1)) / dW + 1;
@@ -282,8 +294,8 @@ void FN(dilconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
                 for (int kw = 0; kw < kW; ++kw) {
                     acc_t s = 0;
                     for (int n = 0; n < N; ++n) {
-                        const float *xp = x + ((size_t)n * C + c) * H * W;
-                        const float *gyp = gy + ((size_t)n * K + k) * oH * oW;
+                        const real_t *xp = x + ((size_t)n * C + c) * H * W;
+                        const real_t *gyp = gy + ((size_t)n * K + k) * oH * oW;
                         for (int oh = 0; oh < oH; ++oh) {
                             const int ih = oh * dH - padH + kh * dilH;
                             if (ih < 0 || ih >= H) continue;
@@ -294,7 +306,7 @@ void FN(dilconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
                             }
                         }
                     }
-                    float *p = gw + ((size_t)k * C + c) * kH * kW + kh * kW + kw;
+                    real_t *p = gw + ((size_t)k * C + c) * kH * kW + kh * kW + kw;
                     *p = (float)((acc_t)*p + (acc_t)scale * s);
                 }
         }
@@ -303,31 +315,31 @@ void FN(dilconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
         for (int k = 0; k < K; ++k) {
             acc_t s = 0;
             for (int n = 0; n < N; ++n) {
-                const float *gyp = gy + ((size_t)n * K + k) * oH * oW;
+                const real_t *gyp = gy + ((size_t)n * K + k) * oH * oW;
                 for (int i = 0; i < oH * oW; ++i) s += (acc_t)gyp[i];
             }
-            gb[k] = (float)((acc_t)gb[k] + (acc_t)scale * s);
+            gb[k] = (real_t)((acc_t)gb[k] + (acc_t)scale * s);
         }
     }
 }
 
-void FN(convmm_forward)(const float *x, const float *w, const float *bias, float *y,
+void FN(convmm_forward)(const real_t *x, const real_t *w, const real_t *bias, real_t *y,
                         int N, int C, int H, int W, int K, int kH, int kW,
                         int dH, int dW, int padH, int padW)
 {
     FN(dilconv_forward)(x, w, bias, y, N, C, H, W, K, kH, kW, dH, dW, padH, padW, 1, 1);
 }
 
-void FN(convmm_grad_input)(const float *gy, const float *w, float *gx,
+void FN(convmm_grad_input)(const real_t *gy, const real_t *w, real_t *gx,
                            int N, int C, int H, int W, int K, int kH, int kW,
                            int dH, int dW, int padH, int padW)
 {
     FN(dilconv_grad_input)(gy, w, gx, N, C, H, W, K, kH, kW, dH, dW, padH, padW, 1, 1);
 }
 
-void FN(convmm_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
+void FN(convmm_acc_grad)(const real_t *x, const real_t *gy, real_t *gw, real_t *gb,
                          int N, int C, int H, int W, int K, int kH, int kW,
-                         int dH, int dW, int padH, int padW, float scale)
+                         int dH, int dW, int padH, int padW, real_t scale)
 {
     FN(dilconv_acc_grad)(x, gy, gw, gb, N, C, H, W, K, kH, kW, dH, dW, padH, padW, 1, 1, scale);
 }
@@ -339,7 +351,7 @@ void FN(convmm_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
 
 /* Forward: y_n = col2im(W^T * x_n) + bias
  * (lib/THCUNN/generic/SpatialFullDilatedConvolution.cu:68-209; output size :51-52). */
-void FN(fullconv_forward)(const float *x, const float *w, const float *bias, float *y,
+void FN(fullconv_forward)(const real_t *x, const real_t *w, const real_t *bias, real_t *y,
                           int N, int P, int H, int W, int Q, int kH, int kW,
                           int dH, int dW, int padH, int padW, int dilH, int dilW, int adjH, int adjW)
 {
@@ -348,7 +360,7 @@ void FN(fullconv_forward)(const float *x, const float *w, const float *bias, flo
 #pragma omp parallel for collapse(2) schedule(static)
     for (int n = 0; n < N; ++n)
         for (int q = 0; q < Q; ++q) {
-            float *yp = y + ((size_t)n * Q + q) * OH * OW;
+            real_t *yp = y + ((size_t)n * Q + q) * OH * OW;
             for (int oh = 0; oh < OH; ++oh)
                 for (int ow = 0; ow < OW; ++ow) {
                     acc_t s = bias ? (acc_t)bias[q] : (acc_t)0;
@@ -363,14 +375,14 @@ void FN(fullconv_forward)(const float *x, const float *w, const float *bias, flo
                                      (acc_t)x[(((size_t)n * P + p) * H + t / dH) * W + u / dW];
                         }
                     }
-                    yp[oh * OW + ow] = (float)s;
+                    yp[oh * OW + ow] = (real_t)s;
                 }
         }
 }
 
 /* Input gradient: gx_n = W * im2col(gy_n)
  * (lib/THCUNN/generic/SpatialFullDilatedConvolution.cu:211-317). */
-void FN(fullconv_grad_input)(const float *gy, const float *w, float *gx,
+void FN(fullconv_grad_input)(const real_t *gy, const real_t *w, real_t *gx,
                              int N, int P, int H, int W, int Q, int kH, int kW,
                              int dH, int dW, int padH, int padW, int dilH, int dilW, int adjH, int adjW)
 {
@@ -383,8 +395,8 @@ void FN(fullconv_grad_input)(const float *gy, const float *w, float *gx,
                 for (int iw = 0; iw < W; ++iw) {
                     acc_t s = 0;
                     for (int q = 0; q < Q; ++q) {
-                        const float *gyp = gy + ((size_t)n * Q + q) * OH * OW;
-                        const float *wp = w + ((size_t)p * Q + q) * kH * kW;
+                        const real_t *gyp = gy + ((size_t)n * Q + q) * OH * OW;
+                        const real_t *wp = w + ((size_t)p * Q + q) * kH * kW;
                         for (int kh = 0; kh < kH; ++kh) {
                             const int oh = ih * dH - padH + kh * dilH;
                             if (oh < 0 || oh >= OH) continue;
@@ -395,15 +407,15 @@ void FN(fullconv_grad_input)(const float *gy, const float *w, float *gx,
                             }
                         }
                     }
-                    gx[(((size_t)n * P + p) * H + ih) * W + iw] = (float)s;
+                    gx[(((size_t)n * P + p) * H + ih) * W + iw] = (real_t)s;
                 }
 }
 
 /* Parameter gradients, accumulated: gW += scale * sum_n x_n * im2col(gy_n)^T, gb += scale * sum gy
  * (lib/THCUNN/generic/SpatialFullDilatedConvolution.cu:319-461). */
-void FN(fullconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb,
+void FN(fullconv_acc_grad)(const real_t *x, const real_t *gy, real_t *gw, real_t *gb,
                            int N, int P, int H, int W, int Q, int kH, int kW,
-                           int dH, int dW, int padH, int padW, int dilH, int dilW, int adjH, int adjW, float scale)
+                           int dH, int dW, int padH, int padW, int dilH, int dilW, int adjH, int adjW, real_t scale)
 {
     const int OH = (H - 1) * dH - 2 * padH + dilH * (kH - 1) + 1 + adjH;
     const int OW = (W - 1) * dW - 2 * padW + dilW * (kW - 1) + 1 + adjW;
@@ -414,8 +426,8 @@ void FN(fullconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb
                 for (int kw = 0; kw < kW; ++kw) {
                     acc_t s = 0;
                     for (int n = 0; n < N; ++n) {
-                        const float *xp = x + ((size_t)n * P + p) * H * W;
-                        const float *gyp = gy + ((size_t)n * Q + q) * OH * OW;
+                        const real_t *xp = x + ((size_t)n * P + p) * H * W;
+                        const real_t *gyp = gy + ((size_t)n * Q + q) * OH * OW;
                         for (int ih = 0; ih < H; ++ih) {
                             const int oh = ih * dH - padH + kh * dilH;
                             if (oh < 0 || oh >= OH) continue;
@@ -426,7 +438,7 @@ void FN(fullconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb
                             }
                         }
                     }
-                    float *g = gw + ((size_t)p * Q + q) * kH * kW + kh * kW + kw;
+                    real_t *g = gw + ((size_t)p * Q + q) * kH * kW + kh * kW + kw;
                     *g = (float)((acc_t)*g + (acc_t)scale * s);
                 }
     if (gb) {
@@ -434,10 +446,10 @@ void FN(fullconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb
         for (int q = 0; q < Q; ++q) {
             acc_t s = 0;
             for (int n = 0; n < N; ++n) {
-                const float *gyp = gy + ((size_t)n * Q + q) * OH * OW;
+                const real_t *gyp = gy + ((size_t)n * Q + q) * OH * OW;
                 for (int i = 0; i < OH * OW; ++i) s += (acc_t)gyp[i];
             }
-            gb[q] = (float)((acc_t)gb[q] + (acc_t)scale * s);
+            gb[q] = (real_t)((acc_t)gb[q] + (acc_t)scale * s);
         }
     }
 }
@@ -450,8 +462,8 @@ void FN(fullconv_acc_grad)(const float *x, const float *gy, float *gw, float *gb
  * (0 when var == 0 and eps == 0), running stats updated with the UNBIASED
  * variance (lib/THCUNN/BatchNormalization.cu:167-212).  Eval: running stats
  * (lib/THCUNN/BatchNormalization.cu:141-164).  weight/bias may be NULL. */
-void FN(bn_forward)(const float *x, float *y, const float *weight, const float *bias,
-                    float *running_mean, float *running_var, float *save_mean, float *save_std,
+void FN(bn_forward)(const real_t *x, real_t *y, const real_t *weight, const real_t *bias,
+                    real_t *running_mean, real_t *running_var, real_t *save_mean, real_t *save_std,
                     int N, int C, int S, int train, double momentum, double eps)
 {
 #pragma omp parallel for schedule(static)
@@ -461,13 +473,13 @@ void FN(bn_forward)(const float *x, float *y, const float *weight, const float *
             const acc_t cnt = (acc_t)N * S;
             acc_t s = 0;
             for (int n = 0; n < N; ++n) {
-                const float *xp = x + ((size_t)n * C + c) * S;
+                const real_t *xp = x + ((size_t)n * C + c) * S;
                 for (int i = 0; i < S; ++i) s += (acc_t)xp[i];
             }
             mean = s / cnt;
             acc_t v = 0;
             for (int n = 0; n < N; ++n) {
-                const float *xp = x + ((size_t)n * C + c) * S;
+                const real_t *xp = x + ((size_t)n * C + c) * S;
                 for (int i = 0; i < S; ++i) {
                     const acc_t d = (acc_t)xp[i] - mean;
                     v += d * d;
@@ -476,10 +488,10 @@ void FN(bn_forward)(const float *x, float *y, const float *weight, const float *
             invstd = 0;
             if (v != 0 || eps != 0) invstd = (acc_t)1 / (acc_t)sqrt((double)(v / cnt + (acc_t)eps));
             const acc_t unbiased = v / (cnt - 1);
-            save_mean[c] = (float)mean;
-            save_std[c] = (float)invstd;
-            running_mean[c] = (float)((1 - momentum) * running_mean[c] + momentum * mean);
-            running_var[c] = (float)((1 - momentum) * running_var[c] + momentum * unbiased);
+            save_mean[c] = (real_t)mean;
+            save_std[c] = (real_t)invstd;
+            running_mean[c] = (real_t)((1 - momentum) * running_mean[c] + momentum * mean);
+            running_var[c] = (real_t)((1 - momentum) * running_var[c] + momentum * unbiased);
         } else {
             mean = running_mean[c];
             invstd = (acc_t)1 / (acc_t)sqrt((double)((acc_t)running_var[c] + (acc_t)eps));
@@ -487,18 +499,18 @@ void FN(bn_forward)(const float *x, float *y, const float *weight, const float *
         const acc_t g = weight ? (acc_t)weight[c] : (acc_t)1;
         const acc_t b = bias ? (acc_t)bias[c] : (acc_t)0;
         for (int n = 0; n < N; ++n) {
-            const float *xp = x + ((size_t)n * C + c) * S;
-            float *yp = y + ((size_t)n * C + c) * S;
-            for (int i = 0; i < S; ++i) yp[i] = (float)(g * ((acc_t)xp[i] - mean) * invstd + b);
+            const real_t *xp = x + ((size_t)n * C + c) * S;
+            real_t *yp = y + ((size_t)n * C + c) * S;
+            for (int i = 0; i < S; ++i) yp[i] = (real_t)(g * ((acc_t)xp[i] - mean) * invstd + b);
         }
     }
 }
 
 /* Backward (lib/THCUNN/BatchNormalization.cu:215-283).  gx, gw, gb may each be
  * NULL; gw and gb are accumulated with `scale`. */
-void FN(bn_backward)(const float *x, const float *gy, float *gx, float *gw, float *gb,
-                     const float *weight, const float *running_mean, const float *running_var,
-                     const float *save_mean, const float *save_std,
+void FN(bn_backward)(const real_t *x, const real_t *gy, real_t *gx, real_t *gw, real_t *gb,
+                     const real_t *weight, const real_t *running_mean, const real_t *running_var,
+                     const real_t *save_mean, const real_t *save_std,
                      int N, int C, int S, int train, double scale, double eps)
 {
 #pragma omp parallel for schedule(static)
@@ -515,8 +527,8 @@ void FN(bn_backward)(const float *x, const float *gy, float *gx, float *gw, floa
         const acc_t norm = (acc_t)1 / ((acc_t)N * S);
         acc_t sum = 0, dot = 0;
         for (int n = 0; n < N; ++n) {
-            const float *xp = x + ((size_t)n * C + c) * S;
-            const float *gp = gy + ((size_t)n * C + c) * S;
+            const real_t *xp = x + ((size_t)n * C + c) * S;
+            const real_t *gp = gy + ((size_t)n * C + c) * S;
             for (int i = 0; i < S; ++i) {
                 sum += (acc_t)gp[i];
                 dot += (acc_t)gp[i] * ((acc_t)xp[i] - mean);
@@ -527,19 +539,19 @@ void FN(bn_backward)(const float *x, const float *gy, float *gx, float *gw, floa
         const acc_t grad_scale = stdv * wv;
         if (gx) {
             for (int n = 0; n < N; ++n) {
-                const float *xp = x + ((size_t)n * C + c) * S;
-                const float *gp = gy + ((size_t)n * C + c) * S;
-                float *op = gx + ((size_t)n * C + c) * S;
+                const real_t *xp = x + ((size_t)n * C + c) * S;
+                const real_t *gp = gy + ((size_t)n * C + c) * S;
+                real_t *op = gx + ((size_t)n * C + c) * S;
                 for (int i = 0; i < S; ++i) {
                     if (train)
-                        op[i] = (float)(((acc_t)gp[i] - ((acc_t)xp[i] - mean) * proj_scale - grad_mean) * grad_scale);
+                        op[i] = (real_t)(((acc_t)gp[i] - ((acc_t)xp[i] - mean) * proj_scale - grad_mean) * grad_scale);
                     else
-                        op[i] = (float)((acc_t)gp[i] * grad_scale);
+                        op[i] = (real_t)((acc_t)gp[i] * grad_scale);
                 }
             }
         }
-        if (gw) gw[c] = (float)((acc_t)gw[c] + (acc_t)scale * dot * stdv);
-        if (gb) gb[c] = (float)((acc_t)gb[c] + (acc_t)scale * sum);
+        if (gw) gw[c] = (real_t)((acc_t)gw[c] + (acc_t)scale * dot * stdv);
+        if (gb) gb[c] = (real_t)((acc_t)gb[c] + (acc_t)scale * sum);
     }
 }
 
@@ -563,14 +575,14 @@ int FN(pool_out_size)(int in, int k, int d, int pad, int dil, int ceil_mode)
 /* Forward: first strict maximum in row-major window order starting from
  * -FLT_MAX with index -1; stored index = per-plane flat h*W+w + index base
  * (lib/THCUNN/SpatialDilatedMaxPooling.cu:8-42).  NaN never wins. */
-void FN(maxpool_forward)(const float *x, float *y, int64_t *ind,
+void FN(maxpool_forward)(const real_t *x, real_t *y, int64_t *ind,
                          int N, int C, int H, int W, int oH, int oW,
                          int kH, int kW, int dH, int dW, int padH, int padW,
                          int dilH, int dilW)
 {
 #pragma omp parallel for schedule(static)
     for (long p = 0; p < (long)N * C; ++p) {
-        const float *xp = x + (size_t)p * H * W;
+        const real_t *xp = x + (size_t)p * H * W;
         for (int ph = 0; ph < oH; ++ph)
             for (int pw = 0; pw < oW; ++pw) {
                 int hs = ph * dH - padH, ws = pw * dW - padW;
@@ -578,7 +590,7 @@ void FN(maxpool_forward)(const float *x, float *y, int64_t *ind,
                 int we = ws + (kW - 1) * dilW + 1; if (we > W) we = W;
                 while (hs < 0) hs += dilH;
                 while (ws < 0) ws += dilW;
-                float best = -FLT_MAX;
+                real_t best = REAL_LOWEST;
                 int bi = -1;
                 for (int h = hs; h < he; h += dilH)
                     for (int w = ws; w < we; w += dilW)
@@ -591,14 +603,14 @@ void FN(maxpool_forward)(const float *x, float *y, int64_t *ind,
 
 /* Backward, gather form: every input pixel sums gy over the outputs whose
  * stored index names it (lib/THCUNN/SpatialDilatedMaxPooling.cu:46-80). */
-void FN(maxpool_backward)(const float *gy, const int64_t *ind, float *gx,
+void FN(maxpool_backward)(const real_t *gy, const int64_t *ind, real_t *gx,
                           int N, int C, int H, int W, int oH, int oW,
                           int kH, int kW, int dH, int dW, int padH, int padW,
                           int dilH, int dilW)
 {
 #pragma omp parallel for schedule(static)
     for (long p = 0; p < (long)N * C; ++p) {
-        const float *gp = gy + (size_t)p * oH * oW;
+        const real_t *gp = gy + (size_t)p * oH * oW;
         const int64_t *ip = ind + (size_t)p * oH * oW;
         for (int h = 0; h < H; ++h)
             for (int w = 0; w < W; ++w) {
@@ -611,7 +623,7 @@ void FN(maxpool_backward)(const float *gy, const int64_t *ind, float *gx,
                 for (int ph = phs; ph < phe; ++ph)
                     for (int pw = pws; pw < pwe; ++pw)
                         if (ip[ph * oW + pw] - REF_INDEX_BASE == h * W + w) g += (acc_t)gp[ph * oW + pw];
-                gx[(size_t)p * H * W + h * W + w] = (float)g;
+                gx[(size_t)p * H * W + h * W + w] = (real_t)g;
             }
     }
 }
@@ -621,14 +633,14 @@ void FN(maxpool_backward)(const float *gy, const int64_t *ind, float *gx,
 /* ------------------------------------------------------------------------ */
 
 /* Threshold forward: y = x > th ? x : val (lib/THCUNN/Threshold.cu:6-38). */
-void FN(threshold_forward)(const float *x, float *y, size_t n, float th, float val)
+void FN(threshold_forward)(const real_t *x, real_t *y, size_t n, real_t th, real_t val)
 {
 #pragma omp parallel for schedule(static)
     for (long i = 0; i < (long)n; ++i) y[i] = x[i] > th ? x[i] : val;
 }
 
 /* Threshold backward: gx = x > th ? gy : 0 (lib/THCUNN/Threshold.cu:40-72). */
-void FN(threshold_backward)(const float *x, const float *gy, float *gx, size_t n, float th)
+void FN(threshold_backward)(const real_t *x, const real_t *gy, real_t *gx, size_t n, real_t th)
 {
 #pragma omp parallel for schedule(static)
     for (long i = 0; i < (long)n; ++i) gx[i] = x[i] > th ? gy[i] : 0.0f;
@@ -637,7 +649,7 @@ void FN(threshold_backward)(const float *x, const float *gy, float *gx, size_t n
 /* Average pooling forward (lib/THCUNN/SpatialAveragePooling.cu:7-39): window
  * clipped to input + pad for the divisor when count_include_pad, else to the
  * input. */
-void FN(avgpool_forward)(const float *x, float *y, int N, int C, int H, int W, int oH, int oW,
+void FN(avgpool_forward)(const real_t *x, real_t *y, int N, int C, int H, int W, int oH, int oW,
                          int kH, int kW, int dH, int dW, int padH, int padW, int count_include_pad)
 {
 #pragma omp parallel for schedule(static)
@@ -656,12 +668,12 @@ void FN(avgpool_forward)(const float *x, float *y, int N, int C, int H, int W, i
                 for (int h = hs; h < he; ++h)
                     for (int w = ws; w < we; ++w) s += (acc_t)x[(size_t)p * H * W + h * W + w];
                 const int div = count_include_pad ? pool : (he - hs) * (we - ws);
-                y[(size_t)p * oH * oW + ph * oW + pw] = (float)(s / div);
+                y[(size_t)p * oH * oW + ph * oW + pw] = (real_t)(s / div);
             }
 }
 
 /* Average pooling backward (lib/THCUNN/SpatialAveragePooling.cu:42-82). */
-void FN(avgpool_backward)(const float *gy, float *gx, int N, int C, int H, int W, int oH, int oW,
+void FN(avgpool_backward)(const real_t *gy, real_t *gx, int N, int C, int H, int W, int oH, int oW,
                           int kH, int kW, int dH, int dW, int padH, int padW, int count_include_pad)
 {
 #pragma omp parallel for schedule(static)
@@ -687,44 +699,44 @@ void FN(avgpool_backward)(const float *gy, float *gx, int N, int C, int H, int W
                         const int div = count_include_pad ? pool : (he - hs) * (we - ws);
                         g += (acc_t)gy[(size_t)p * oH * oW + ph * oW + pw] / div;
                     }
-                gx[(size_t)p * H * W + h0 * W + w0] = (float)g;
+                gx[(size_t)p * H * W + h0 * W + w0] = (real_t)g;
             }
 }
 
 /* LogSoftMax over the last dimension of [B, D]
  * (lib/THCUNN/LogSoftMax.cu:246-296): x - max - log(sum exp(x - max)). */
-void FN(logsoftmax_forward)(const float *x, float *y, int B, int D)
+void FN(logsoftmax_forward)(const real_t *x, real_t *y, int B, int D)
 {
 #pragma omp parallel for schedule(static)
     for (int b = 0; b < B; ++b) {
-        const float *xp = x + (size_t)b * D;
-        float m = -FLT_MAX;
+        const real_t *xp = x + (size_t)b * D;
+        real_t m = REAL_LOWEST;
         for (int i = 0; i < D; ++i) if (xp[i] > m) m = xp[i];
         acc_t s = 0;
         for (int i = 0; i < D; ++i) s += (acc_t)exp((double)xp[i] - (double)m);
         const acc_t l = (acc_t)m + (acc_t)log((double)s);
-        for (int i = 0; i < D; ++i) y[(size_t)b * D + i] = (float)((acc_t)xp[i] - l);
+        for (int i = 0; i < D; ++i) y[(size_t)b * D + i] = (real_t)((acc_t)xp[i] - l);
     }
 }
 
 /* LogSoftMax backward (lib/THCUNN/LogSoftMax.cu:298-344):
  * gx = gy - exp(y) * sum(gy). */
-void FN(logsoftmax_backward)(const float *y, const float *gy, float *gx, int B, int D)
+void FN(logsoftmax_backward)(const real_t *y, const real_t *gy, real_t *gx, int B, int D)
 {
 #pragma omp parallel for schedule(static)
     for (int b = 0; b < B; ++b) {
         acc_t s = 0;
         for (int i = 0; i < D; ++i) s += (acc_t)gy[(size_t)b * D + i];
         for (int i = 0; i < D; ++i)
-            gx[(size_t)b * D + i] = (float)((acc_t)gy[(size_t)b * D + i] - (acc_t)exp((double)y[(size_t)b * D + i]) * s);
+            gx[(size_t)b * D + i] = (real_t)((acc_t)gy[(size_t)b * D + i] - (acc_t)exp((double)y[(size_t)b * D + i]) * s);
     }
 }
 
 /* ClassNLL forward over log-probabilities [B, D] with targets carrying the
  * index base (lib/THCUNN/ClassNLLCriterion.cu:38-84): loss = -sum w_t lp[t],
  * divided by sum w_t when size_average.  weights may be NULL. */
-void FN(classnll_forward)(const float *lp, const int64_t *target, const float *weights,
-                          float *loss, float *total_weight, int B, int D,
+void FN(classnll_forward)(const real_t *lp, const int64_t *target, const real_t *weights,
+                          real_t *loss, real_t *total_weight, int B, int D,
                           int size_average, int64_t ignore_index)
 {
     acc_t s = 0, tw = 0;
@@ -743,8 +755,8 @@ void FN(classnll_forward)(const float *lp, const int64_t *target, const float *w
 /* ClassNLL backward (lib/THCUNN/ClassNLLCriterion.cu:108-132): writes only the
  * target entries of gx; the caller zeroes gx first, as nn.ClassNLLCriterion
  * does. */
-void FN(classnll_backward)(const int64_t *target, const float *weights, float total_weight,
-                           float *gx, int B, int D, int size_average, int64_t ignore_index)
+void FN(classnll_backward)(const int64_t *target, const real_t *weights, real_t total_weight,
+                           real_t *gx, int B, int D, int size_average, int64_t ignore_index)
 {
     if (total_weight <= 0) return;
     const acc_t norm = size_average ? (acc_t)1 / (acc_t)total_weight : (acc_t)1;
@@ -752,7 +764,7 @@ void FN(classnll_backward)(const int64_t *target, const float *weights, float to
         const int64_t t = target[b] - REF_INDEX_BASE;
         if (t == ignore_index - REF_INDEX_BASE) continue;
         const acc_t w = weights ? (acc_t)weights[t] : (acc_t)1;
-        gx[(size_t)b * D + t] = (float)(-w * norm);
+        gx[(size_t)b * D + t] = (real_t)(-w * norm);
     }
 }
 

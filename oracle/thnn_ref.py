@@ -24,8 +24,11 @@ def build(force=False):
     return _SO
 
 
+_DTYPE = [np.float32]          # element type of the library prefix in use (set by Ref methods; the fp64 build is "refd_")
+
+
 def _f(a):
-    return np.ascontiguousarray(a, dtype=np.float32)
+    return np.ascontiguousarray(a, dtype=_DTYPE[0])
 
 
 def _p(a):
@@ -43,7 +46,17 @@ class Ref:
         build()
         self.lib = ctypes.CDLL(_SO)
         self.prefix = prefix
+        self.dtype = np.float64 if prefix == "refd_" else np.float32
+        self.creal = ctypes.c_double if prefix == "refd_" else ctypes.c_float
         self.index_base = self._fn("index_base", ctypes.c_int)()
+
+    def __getattribute__(self, name):
+        # looking up a routine selects this instance's element type for the array conversions of the call
+        if not name.startswith("_"):
+            d = object.__getattribute__(self, "__dict__").get("dtype")
+            if d is not None:
+                _DTYPE[0] = d
+        return object.__getattribute__(self, name)
 
     def set_threads(self, n):
         """Fixes the OpenMP thread count of this library (both prefixes share one runtime); returns the count in use."""
@@ -61,7 +74,7 @@ class Ref:
         b = None if b is None else _f(b)
         N, C, H, W = x.shape
         M, _, kH, kW = w.shape
-        y = np.empty((N, C * M, conv_out(H, kH, dH, padH), conv_out(W, kW, dW, padW)), np.float32)
+        y = np.empty((N, C * M, conv_out(H, kH, dH, padH), conv_out(W, kW, dW, padW)), self.dtype)
         self._fn("dwconv_forward")(_p(x), _p(w), _p(b), _p(y), N, C, H, W, M, kH, kW, dH, dW, padH, padW)
         return y
 
@@ -69,7 +82,7 @@ class Ref:
         gy, w = _f(gy), _f(w)
         M, C, kH, kW = w.shape
         N = gy.shape[0]
-        gx = np.empty((N, C, H, W), np.float32)
+        gx = np.empty((N, C, H, W), self.dtype)
         self._fn("dwconv_grad_input")(_p(gy), _p(w), _p(gx), N, C, H, W, M, kH, kW, dH, dW, padH, padW)
         return gx
 
@@ -81,7 +94,7 @@ class Ref:
         N, C, H, W = x.shape
         M, _, kH, kW = gw.shape
         self._fn("dwconv_acc_grad")(_p(x), _p(gy), _p(gw), _p(gb), N, C, H, W, M, kH, kW, dH, dW, padH, padW,
-                                    ctypes.c_float(scale))
+                                    self.creal(scale))
         return gw, gb
 
     # -- im2col + GEMM convolution ----------------------------------------------
@@ -90,7 +103,7 @@ class Ref:
         b = None if b is None else _f(b)
         N, C, H, W = x.shape
         K, _, kH, kW = w.shape
-        y = np.empty((N, K, conv_out(H, kH, dH, padH), conv_out(W, kW, dW, padW)), np.float32)
+        y = np.empty((N, K, conv_out(H, kH, dH, padH), conv_out(W, kW, dW, padW)), self.dtype)
         self._fn("convmm_forward")(_p(x), _p(w), _p(b), _p(y), N, C, H, W, K, kH, kW, dH, dW, padH, padW)
         return y
 
@@ -98,7 +111,7 @@ class Ref:
         gy, w = _f(gy), _f(w)
         K, C, kH, kW = w.shape
         N = gy.shape[0]
-        gx = np.empty((N, C, H, W), np.float32)
+        gx = np.empty((N, C, H, W), self.dtype)
         self._fn("convmm_grad_input")(_p(gy), _p(w), _p(gx), N, C, H, W, K, kH, kW, dH, dW, padH, padW)
         return gx
 
@@ -109,7 +122,7 @@ class Ref:
         N, C, H, W = x.shape
         K, _, kH, kW = gw.shape
         self._fn("convmm_acc_grad")(_p(x), _p(gy), _p(gw), _p(gb), N, C, H, W, K, kH, kW, dH, dW, padH, padW,
-                                    ctypes.c_float(scale))
+                                    self.creal(scale))
         return gw, gb
 
     # -- dilated convolution (SpatialDilatedConvolution; dilation 1 is SpatialConvolutionMM) -------
@@ -120,7 +133,7 @@ class Ref:
         K, _, kH, kW = w.shape
         oH = (H + 2 * padH - (dilH * (kH - 1) + 1)) // dH + 1
         oW = (W + 2 * padW - (dilW * (kW - 1) + 1)) // dW + 1
-        y = np.empty((N, K, oH, oW), np.float32)
+        y = np.empty((N, K, oH, oW), self.dtype)
         self._fn("dilconv_forward")(_p(x), _p(w), _p(b), _p(y), N, C, H, W, K, kH, kW, dH, dW, padH, padW, dilH, dilW)
         return y
 
@@ -128,7 +141,7 @@ class Ref:
         gy, w = _f(gy), _f(w)
         K, C, kH, kW = w.shape
         N = gy.shape[0]
-        gx = np.empty((N, C, H, W), np.float32)
+        gx = np.empty((N, C, H, W), self.dtype)
         self._fn("dilconv_grad_input")(_p(gy), _p(w), _p(gx), N, C, H, W, K, kH, kW, dH, dW, padH, padW, dilH, dilW)
         return gx
 
@@ -139,7 +152,7 @@ class Ref:
         N, C, H, W = x.shape
         K, _, kH, kW = gw.shape
         self._fn("dilconv_acc_grad")(_p(x), _p(gy), _p(gw), _p(gb), N, C, H, W, K, kH, kW, dH, dW, padH, padW,
-                                     dilH, dilW, ctypes.c_float(scale))
+                                     dilH, dilW, self.creal(scale))
         return gw, gb
 
     # -- transposed convolution (SpatialFullDilatedConvolution; weight [P, Q, kH, kW]) -------------
@@ -154,7 +167,7 @@ class Ref:
         N, P, H, W = x.shape
         _, Q, kH, kW = w.shape
         OH, OW = self.fullconv_out_size(H, W, kH, kW, dH, dW, padH, padW, dilH, dilW, adjH, adjW)
-        y = np.empty((N, Q, OH, OW), np.float32)
+        y = np.empty((N, Q, OH, OW), self.dtype)
         self._fn("fullconv_forward")(_p(x), _p(w), _p(b), _p(y), N, P, H, W, Q, kH, kW, dH, dW, padH, padW,
                                      dilH, dilW, adjH, adjW)
         return y
@@ -163,7 +176,7 @@ class Ref:
         gy, w = _f(gy), _f(w)
         P, Q, kH, kW = w.shape
         N = gy.shape[0]
-        gx = np.empty((N, P, H, W), np.float32)
+        gx = np.empty((N, P, H, W), self.dtype)
         self._fn("fullconv_grad_input")(_p(gy), _p(w), _p(gx), N, P, H, W, Q, kH, kW, dH, dW, padH, padW,
                                         dilH, dilW, adjH, adjW)
         return gx
@@ -175,7 +188,7 @@ class Ref:
         N, P, H, W = x.shape
         _, Q, kH, kW = gw.shape
         self._fn("fullconv_acc_grad")(_p(x), _p(gy), _p(gw), _p(gb), N, P, H, W, Q, kH, kW, dH, dW, padH, padW,
-                                      dilH, dilW, adjH, adjW, ctypes.c_float(scale))
+                                      dilH, dilW, adjH, adjW, self.creal(scale))
         return gw, gb
 
     # -- batch norm --------------------------------------------------------------
@@ -186,7 +199,7 @@ class Ref:
         S = int(np.prod(x.shape[2:])) if x.ndim > 2 else 1
         y = np.empty_like(x)
         rm, rv = _f(running_mean).copy(), _f(running_var).copy()
-        sm, ss = np.zeros(C, np.float32), np.zeros(C, np.float32)
+        sm, ss = np.zeros(C, self.dtype), np.zeros(C, self.dtype)
         weight = None if weight is None else _f(weight)
         bias = None if bias is None else _f(bias)
         self._fn("bn_forward")(_p(x), _p(y), _p(weight), _p(bias), _p(rm), _p(rv), _p(sm), _p(ss),
@@ -216,7 +229,7 @@ class Ref:
         N, C, H, W = x.shape
         oH = self.pool_out_size(H, kH, dH, padH, dilH, ceil_mode)
         oW = self.pool_out_size(W, kW, dW, padW, dilW, ceil_mode)
-        y = np.empty((N, C, oH, oW), np.float32)
+        y = np.empty((N, C, oH, oW), self.dtype)
         ind = np.empty((N, C, oH, oW), np.int64)
         self._fn("maxpool_forward")(_p(x), _p(y), _p(ind), N, C, H, W, oH, oW, kH, kW, dH, dW, padH, padW,
                                     dilH, dilW)
@@ -226,7 +239,7 @@ class Ref:
         gy = _f(gy)
         ind = np.ascontiguousarray(ind, dtype=np.int64)
         N, C, oH, oW = gy.shape
-        gx = np.empty((N, C, H, W), np.float32)
+        gx = np.empty((N, C, H, W), self.dtype)
         self._fn("maxpool_backward")(_p(gy), _p(ind), _p(gx), N, C, H, W, oH, oW, kH, kW, dH, dW, padH, padW,
                                      dilH, dilW)
         return gx
@@ -235,13 +248,13 @@ class Ref:
     def threshold_forward(self, x, th=0.0, val=0.0):
         x = _f(x)
         y = np.empty_like(x)
-        self._fn("threshold_forward")(_p(x), _p(y), ctypes.c_size_t(x.size), ctypes.c_float(th), ctypes.c_float(val))
+        self._fn("threshold_forward")(_p(x), _p(y), ctypes.c_size_t(x.size), self.creal(th), self.creal(val))
         return y
 
     def threshold_backward(self, x, gy, th=0.0):
         x, gy = _f(x), _f(gy)
         gx = np.empty_like(x)
-        self._fn("threshold_backward")(_p(x), _p(gy), _p(gx), ctypes.c_size_t(x.size), ctypes.c_float(th))
+        self._fn("threshold_backward")(_p(x), _p(gy), _p(gx), ctypes.c_size_t(x.size), self.creal(th))
         return gx
 
     def avgpool_forward(self, x, kH, kW, dH, dW, padH, padW, ceil_mode=False, count_include_pad=True):
@@ -249,7 +262,7 @@ class Ref:
         N, C, H, W = x.shape
         oH = self.pool_out_size(H, kH, dH, padH, 1, ceil_mode)
         oW = self.pool_out_size(W, kW, dW, padW, 1, ceil_mode)
-        y = np.empty((N, C, oH, oW), np.float32)
+        y = np.empty((N, C, oH, oW), self.dtype)
         self._fn("avgpool_forward")(_p(x), _p(y), N, C, H, W, oH, oW, kH, kW, dH, dW, padH, padW,
                                     int(count_include_pad))
         return y
@@ -257,7 +270,7 @@ class Ref:
     def avgpool_backward(self, gy, H, W, kH, kW, dH, dW, padH, padW, count_include_pad=True):
         gy = _f(gy)
         N, C, oH, oW = gy.shape
-        gx = np.empty((N, C, H, W), np.float32)
+        gx = np.empty((N, C, H, W), self.dtype)
         self._fn("avgpool_backward")(_p(gy), _p(gx), N, C, H, W, oH, oW, kH, kW, dH, dW, padH, padW,
                                      int(count_include_pad))
         return gx
@@ -278,7 +291,7 @@ class Ref:
         lp = _f(lp)
         target = np.ascontiguousarray(target, dtype=np.int64)
         weights = None if weights is None else _f(weights)
-        loss, tw = ctypes.c_float(), ctypes.c_float()
+        loss, tw = self.creal(), self.creal()
         self._fn("classnll_forward")(_p(lp), _p(target), _p(weights), ctypes.byref(loss), ctypes.byref(tw),
                                      lp.shape[0], lp.shape[1], int(size_average), ctypes.c_int64(ignore_index))
         return loss.value, tw.value
@@ -286,8 +299,8 @@ class Ref:
     def classnll_backward(self, target, total_weight, B, D, weights=None, size_average=True, ignore_index=-100):
         target = np.ascontiguousarray(target, dtype=np.int64)
         weights = None if weights is None else _f(weights)
-        gx = np.zeros((B, D), np.float32)
-        self._fn("classnll_backward")(_p(target), _p(weights), ctypes.c_float(total_weight), _p(gx), B, D,
+        gx = np.zeros((B, D), self.dtype)
+        self._fn("classnll_backward")(_p(target), _p(weights), self.creal(total_weight), _p(gx), B, D,
                                       int(size_average), ctypes.c_int64(ignore_index))
         return gx
 

@@ -26,6 +26,13 @@ def ref64():
 
 
 @pytest.fixture(scope="session")
+def refd():
+    """The oracle built for fp64 tensors (the CudaDouble entry points)."""
+    from oracle.thnn_ref import Ref
+    return Ref("refd_")
+
+
+@pytest.fixture(scope="session")
 def ref32():
     from oracle.thnn_ref import Ref
     return Ref("ref32_")

@@ -16,7 +16,7 @@ def declared(header):
 def test_library_exports_every_declared_symbol():
     from cunn_b200._lib import lib, SO_PATH
     assert os.path.exists(SO_PATH)
-    names = declared("cunn_b200.h") + declared("THCUNN_b200.h")
+    names = declared("cunn_b200.h") + declared("THCUNN_b200.h") + declared("cunn_b200_dpt.h")
     assert len(names) > 60
     for n in names:
         assert hasattr(lib, n), n
@@ -75,9 +75,11 @@ def test_cutorch_backend_of_the_entry_points_compiles(tmp_path):
     defined = {l.split()[-1] for l in syms if " T " in l}
     thc = {n for n in undefined if n.startswith(("THC", "_THError"))}
     assert thc == {"THCState_getCurrentStream", "THCudaMalloc", "THCudaFree", "THCudaTensor_new", "THCudaTensor_free",
-                   "THCudaTensor_newContiguous", "THCudaTensor_resizeNd", "THCudaLongTensor_resizeNd", "_THError"} - \
+                   "THCudaTensor_newContiguous", "THCudaTensor_resizeNd", "THCudaLongTensor_resizeNd", "_THError",
+                   "THCudaDoubleTensor_free", "THCudaDoubleTensor_newContiguous", "THCudaDoubleTensor_resizeNd"} - \
         ({"THCudaTensor_new"} - thc)
     for n in ("THNN_CudaSpatialDepthWiseConvolution_updateOutput", "THNN_CudaSpatialConvolutionMM_accGradParameters",
-              "THNN_CudaBatchNormalization_backward", "THNN_CudaSpatialMaxPooling_updateOutput"):
+              "THNN_CudaBatchNormalization_backward", "THNN_CudaSpatialMaxPooling_updateOutput",
+              "THNN_CudaDoubleSpatialDepthWiseConvolution_updateOutput", "THNN_CudaDoubleBatchNormalization_backward"):
         assert n in defined
     assert not any(n.startswith("THCState_b200") for n in defined)      # the harness layer is built-in only

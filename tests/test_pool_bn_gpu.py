@@ -28,6 +28,17 @@ def F():
     assert device_status() == 0
 
 
+@pytest.fixture(params=[1, 2], ids=["default-kernels", "grouped-kernels"])
+def grouped_mode(request):
+    """Batch norm has two kernel families: two launches (statistics, then normalise) and one launch that walks
+    groups of channels so that the second read comes from L2.  Mode 2 routes every shape the latter applies to
+    through it, forward and backward; mode 1 is the library's default choice."""
+    from cunn_b200._lib import lib
+    lib.cunn_b200_batchnorm_set_grouped(request.param)
+    yield request.param
+    lib.cunn_b200_batchnorm_set_grouped(1)
+
+
 # ---------------------------------------------------------------- max pooling
 @pytest.mark.parametrize("name", ["maxpool_3s2p1", "maxpool_ceil", "maxpool_ties", "maxpool_2s2"])
 def test_maxpool_golden(F, ref64, name):
@@ -183,8 +194,11 @@ def test_bn_golden(F, name):
     ((4, 8, 2, 3), True),          # 24 elements per channel
     ((16, 4100, 2, 2), True),      # more channels than ticket counters: the merge runs as a separate launch
     ((40, 2, 16, 16), True),       # 40 chunks per channel: more than one warp-lane round in the merge
+    ((64, 6, 28, 28), True),       # grouped kernels: several channels per CTA share
+    ((12, 37, 20, 20), False),     # grouped kernels: a channel count that does not divide into equal groups
+    ((48, 3, 112, 112), True),     # grouped kernels: planes longer than a stage
 ])
-def test_bn_shapes(F, ref64, shape, affine):
+def test_bn_shapes(F, ref64, shape, affine, grouped_mode):
     rng = np.random.default_rng(abs(hash(shape)) % 99991)
     C = shape[1]
     x = (0.5 + 2.0 * rng.standard_normal(shape)).astype(np.float32)
@@ -197,7 +211,7 @@ def test_bn_shapes(F, ref64, shape, affine):
              gw0=rng.standard_normal(C).astype(np.float32), gb0=rng.standard_normal(C).astype(np.float32))
 
 
-def test_bn_large_mean_small_std(F, ref64):
+def test_bn_large_mean_small_std(F, ref64, grouped_mode):
     # |mean| >> std: a plain sum-of-squares in fp32 would lose the variance; the shifted sums must not.
     rng = np.random.default_rng(11)
     x = (100.0 + 0.01 * rng.standard_normal((8, 4, 28, 28))).astype(np.float32)
@@ -219,8 +233,8 @@ def test_bn_single_element_and_zero_variance(F):
     assert torch.all(torch.isnan(rv))
 
 
-@pytest.mark.parametrize("shape", [(4, 8, 14, 14), (3, 5, 7, 9)])
-def test_bn_relu_fused_equals_separate_calls(F, shape):
+@pytest.mark.parametrize("shape", [(4, 8, 14, 14), (3, 5, 7, 9), (64, 6, 28, 28)])
+def test_bn_relu_fused_equals_separate_calls(F, shape, grouped_mode):
     # the fused BN+ReLU pair must equal BatchNormalization followed by Threshold(0, 0), forward and backward
     g = torch.Generator(device="cuda").manual_seed(9)
     C = shape[1]

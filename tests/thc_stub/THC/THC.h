@@ -18,6 +18,8 @@ typedef struct THCState THCState;
 
 typedef struct THCudaStorage { float *data; ptrdiff_t size; int refcount; char flag; void *allocator; void *allocatorContext; struct THCudaStorage *view; int device; } THCudaStorage;
 typedef struct THCudaLongStorage { long *data; ptrdiff_t size; int refcount; char flag; void *allocator; void *allocatorContext; struct THCudaLongStorage *view; int device; } THCudaLongStorage;
+typedef struct THCudaDoubleStorage { double *data; ptrdiff_t size; int refcount; char flag; void *allocator; void *allocatorContext; struct THCudaDoubleStorage *view; int device; } THCudaDoubleStorage;
+typedef struct THCudaDoubleTensor { long *size; long *stride; int nDimension; THCudaDoubleStorage *storage; ptrdiff_t storageOffset; int refcount; char flag; } THCudaDoubleTensor;
 typedef struct THCudaTensor { long *size; long *stride; int nDimension; THCudaStorage *storage; ptrdiff_t storageOffset; int refcount; char flag; } THCudaTensor;
 typedef struct THCudaLongTensor { long *size; long *stride; int nDimension; THCudaLongStorage *storage; ptrdiff_t storageOffset; int refcount; char flag; } THCudaLongTensor;
 
@@ -29,6 +31,9 @@ THCudaTensor *THCudaTensor_new(THCState *state);
 void THCudaTensor_free(THCState *state, THCudaTensor *self);
 THCudaTensor *THCudaTensor_newContiguous(THCState *state, THCudaTensor *tensor);
 void THCudaTensor_resizeNd(THCState *state, THCudaTensor *tensor, int nDimension, long *size, long *stride);
+void THCudaDoubleTensor_free(THCState *state, THCudaDoubleTensor *self);
+THCudaDoubleTensor *THCudaDoubleTensor_newContiguous(THCState *state, THCudaDoubleTensor *tensor);
+void THCudaDoubleTensor_resizeNd(THCState *state, THCudaDoubleTensor *tensor, int nDimension, long *size, long *stride);
 void THCudaLongTensor_resizeNd(THCState *state, THCudaLongTensor *tensor, int nDimension, long *size, long *stride);
 
 void _THError(const char *file, const int line, const char *fmt, ...);
