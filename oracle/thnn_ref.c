@@ -307,7 +307,7 @@ void FN(dilconv_acc_grad)(const real_t *x, const real_t *gy, real_t *gw, real_t 
                         }
                     }
                     real_t *p = gw + ((size_t)k * C + c) * kH * kW + kh * kW + kw;
-                    *p = (float)((acc_t)*p + (acc_t)scale * s);
+                    *p = (real_t)((acc_t)*p + (acc_t)scale * s);
                 }
         }
     if (gb) {
@@ -439,7 +439,7 @@ void FN(fullconv_acc_grad)(const real_t *x, const real_t *gy, real_t *gw, real_t
                         }
                     }
                     real_t *g = gw + ((size_t)p * Q + q) * kH * kW + kh * kW + kw;
-                    *g = (float)((acc_t)*g + (acc_t)scale * s);
+                    *g = (real_t)((acc_t)*g + (acc_t)scale * s);
                 }
     if (gb) {
 #pragma omp parallel for schedule(static)
@@ -748,8 +748,8 @@ void FN(classnll_forward)(const real_t *lp, const int64_t *target, const real_t 
         tw += w;
     }
     if (size_average && tw > 0) s /= tw;
-    *loss = (float)s;
-    *total_weight = (float)tw;
+    *loss = (real_t)s;
+    *total_weight = (real_t)tw;
 }
 
 /* ClassNLL backward (lib/THCUNN/ClassNLLCriterion.cu:108-132): writes only the

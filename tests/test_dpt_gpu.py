@@ -160,7 +160,6 @@ RANK_SCRIPT = textwrap.dedent("""
     torch.cuda.synchronize()
     assert torch.all(bufs[2] == world * (world + 1) / 2), bufs[2][:4]
     assert torch.all(bufs[0] == 0.0)
-    assert t.scatter(0, 5, 4, [0])[0] == (3 if rank == 0 else 2) or True
     t.close()
     print("rank", rank, "ok")
 """)
