@@ -243,7 +243,8 @@ def workload_config(n, world):
             "batch_per_gpu": n, "global_batch": n * world, "layers": len(LAYERS),
             "layout": "NCHW fp32", "l2": "inputs larger than L2: one step touches 2.5 GB of tensors per GPU and a "
                                          "tensor is re-read only after >= 1.2 GB of other traffic",
-            "parallelism": "dp%d (batch-sharded, NCCL all-reduce of depthwise weight gradients)" % world
+            "parallelism": "dp%d (batch-sharded; ncclAllReduce of the depthwise weight gradients issued by the library's "
+                           "DataParallelTable on a communication stream)" % world
                            if world > 1 else "single GPU",
             "launch": "39 kernels per step replayed from CUDA graphs, consecutive (independent) layers on alternating "
                       "streams; with N > 1 the weight-gradient all-reduce overlaps the input-gradient kernels",
@@ -344,7 +345,7 @@ def mobilenet_bench(args, dev, world, rank, dist):
     images = torch.randn((count, 3, 224, 224), device=dev)
     labels = torch.randint(1, 1001, (count,), device=dev, dtype=torch.int64)
     rep = mb.MobileNetV1(cfg, dev, mb.init_params(cfg, SEED), max_batch=max(count, 1))
-    step = mb.DataParallelStep(rep, dist, use_graph=not args.no_graph)   # forward + backward replayed from a CUDA graph
+    step = mb.DataParallelStep(rep, dist, use_graph=not args.no_graph, native=not args.torch_allreduce)   # forward + backward replayed from a CUDA graph
     warm, timed = 3, max(3, min(args.steps, 8))
     for _ in range(warm):
         step.train_step(images, labels, gb, 0.01)
@@ -424,6 +425,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--graph-streams", type=int, default=2,
                     help="streams the launches of the depthwise stack alternate between inside the CUDA graph")
+    ap.add_argument("--torch-allreduce", action="store_true",
+                    help="exchange gradients with torch.distributed.all_reduce instead of the library's DataParallelTable")
     ap.add_argument("--no-mobilenet", action="store_true")
     ap.add_argument("--no-others", action="store_true", help="skip the single-kernel timings of the GEMM convolution, batch norm and pooling")
     ap.add_argument("--mobilenet-batch", type=int, default=1024, help="global batch of the MobileNetV1 step")
@@ -520,7 +523,23 @@ def main():
             stream.wait_stream(s2)
 
     graphs = None
-    if world > 1:
+    table = None
+    if world > 1 and not args.torch_allreduce:
+        # The exchange runs in the library's DataParallelTable: ncclAllReduce of the local gradient buffer on a
+        # communication stream behind an event, then visible += sum, local = 0 (DataParallelTable.lua:247-265).
+        from cunn_b200 import dpt
+        uid = torch.zeros(128, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            uid.copy_(torch.frombuffer(bytearray(dpt.unique_id()), dtype=torch.uint8))
+        dist.broadcast(uid, src=0)
+        visible_grad = torch.zeros_like(flat_grad)
+        scratch_params = torch.zeros_like(flat_grad)
+        table = dpt.NativeDataParallelTable().add_rank(nparams, local_rank, rank, world, bytes(uid.cpu().numpy().tobytes()))
+        table.set_buffers(0, scratch_params.data_ptr(), flat_grad.data_ptr(), visible_grad.data_ptr())
+        table.set_stream(0, stream.cuda_stream)
+        table.reduce()                  # creates the NCCL channels up front
+        torch.cuda.synchronize()
+    elif world > 1:
         dist.all_reduce(flat_grad)      # creates the NCCL communicator up front
         torch.cuda.synchronize()
     if not args.no_graph:
@@ -543,12 +562,18 @@ def main():
             graphs[0].replay()
         else:
             part(("fwd", "wgrad"))
-        work = dist.all_reduce(flat_grad, async_op=True)
+        if table is not None:
+            table.bucketReady(0, 0)     # event on the compute stream; the all-reduce starts behind it on the comm stream
+        else:
+            work = dist.all_reduce(flat_grad, async_op=True)
         if graphs:
             graphs[1].replay()
         else:
             part(("dgrad",))
-        work.wait()                     # the compute stream waits for the collective; the host does not
+        if table is not None:
+            table.reduce()              # compute stream waits for the collective, folds the sum into the visible buffer
+        else:
+            work.wait()                 # the compute stream waits for the collective; the host does not
 
     for _ in range(warmup):
         step()
@@ -783,6 +808,8 @@ def main():
                 "gpu_launches": launches_per_step * steps * rounds, "parity": parity,
                 "roofline": roofline, "cpu_baseline": cpu, "mobilenet_v1": mbn, "other_configs": others, "device_status": status}
         print(json.dumps(line))
+    if table is not None:
+        table.close()
     if world > 1:
         dist.destroy_process_group()
 

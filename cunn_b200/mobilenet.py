@@ -128,11 +128,15 @@ class DataParallelStep:
     parameter gradients are SUMMED over replicas, BN statistics stay per shard, every replica applies the
     same update so parameters stay identical without a broadcast.  With dist=None it is a single replica."""
 
-    def __init__(self, replica, dist=None, use_graph=False):
+    def __init__(self, replica, dist=None, use_graph=False, native=True):
         """use_graph: replay zero_grad + forward + loss + backward from a CUDA graph (one per distinct pair of
         input buffers, batch and global batch; captured on the second use of the pair).  The ~300 launches of
         a step then cost one graph launch, which matters at small per-GPU batches.  The gradient all-reduce and
-        the update stay outside the graph."""
+        the update stay outside the graph.
+        native: with several ranks, the exchange and the update run in the library's DataParallelTable
+        (cunn_b200_dpt_*: ncclAllReduce on a communication stream, visible += sum, update on every replica);
+        torch.distributed then only carries the 128-byte NCCL id to the ranks.  native=False keeps
+        torch.distributed.all_reduce."""
         self.replica = replica
         self.dist = dist
         self.world = dist.get_world_size() if dist is not None else 1
@@ -140,6 +144,18 @@ class DataParallelStep:
         self.use_graph = use_graph
         self._graphs = {}
         self._seen = set()
+        self.table = None
+        if native and self.world > 1:
+            from . import dpt
+            dev = replica.params.device
+            uid = torch.zeros(128, dtype=torch.uint8, device=dev)
+            if self.rank == 0:
+                uid.copy_(torch.frombuffer(bytearray(dpt.unique_id()), dtype=torch.uint8))
+            dist.broadcast(uid, src=0)
+            self.visible = torch.zeros_like(replica.grads)
+            self.table = dpt.NativeDataParallelTable().add_rank(replica.nparams, dev.index, self.rank, self.world,
+                                                               bytes(uid.cpu().numpy().tobytes()))
+            self.table.set_buffers(0, replica.params.data_ptr(), replica.grads.data_ptr(), self.visible.data_ptr())
 
     def shard(self, global_batch):
         return slice_range(global_batch, self.world, self.rank)
@@ -166,6 +182,13 @@ class DataParallelStep:
                     self._graphs[key] = graph
                 else:
                     self._seen.add(key)
+        if self.table is not None:
+            # visible = sum over the ranks of the local gradients (local is cleared), then the same update everywhere
+            self.table.set_stream(0, torch.cuda.current_stream().cuda_stream)
+            self.visible.zero_()
+            self.table.reduce()
+            self.table.updateParameters(lr)
+            return loss
         if self.dist is not None and self.world > 1:
             self.dist.all_reduce(r.grads)
         r.sgd(lr)
