@@ -140,7 +140,7 @@ def make_host_inputs(n):
     return data
 
 
-def run_reference(args):
+def run_reference(args, emit):
     """--impl reference: the CPU arm.  torch/nn's CPU THNN (what the reference's tests compare with) is not
     part of the reference tree and the reference's own depthwise path is GPU code, so this times the fp32
     OpenMP port of the oracle on all host cores, on the full workload (64 images per layer), every step."""
@@ -157,7 +157,7 @@ def run_reference(args):
         "e2e": {"value": res["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 def cpu_baseline(steps=1, warmup=0, budget_seconds=30.0):
@@ -431,8 +431,18 @@ def main():
     ap.add_argument("--no-others", action="store_true", help="skip the single-kernel timings of the GEMM convolution, batch norm and pooling")
     ap.add_argument("--mobilenet-batch", type=int, default=1024, help="global batch of the MobileNetV1 step")
     args = ap.parse_args()
+    # Libraries (NCCL's version banner) may write to stdout; the one JSON line must be alone there.  File descriptor 1
+    # points at stderr while the benchmark runs and `emit` writes the line to the real stdout.
+    real_stdout = os.dup(1)
+    sys.stdout.flush()
+    os.dup2(2, 1)
+
+    def emit(obj):
+        sys.stdout.flush()
+        os.write(real_stdout, (json.dumps(obj) + "\n").encode())
+
     if args.impl == "reference":
-        run_reference(args)
+        run_reference(args, emit)
         return
 
     import torch
@@ -807,7 +817,7 @@ def main():
                 "clocks": clocks, "timed": timed, "single_stream": single_stream, "e2e": e2e,
                 "gpu_launches": launches_per_step * steps * rounds, "parity": parity,
                 "roofline": roofline, "cpu_baseline": cpu, "mobilenet_v1": mbn, "other_configs": others, "device_status": status}
-        print(json.dumps(line))
+        emit(line)
     if table is not None:
         table.close()
     if world > 1:
