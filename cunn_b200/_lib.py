@@ -49,6 +49,14 @@ _decl("cunn_b200_full_conv_forward", c_int, [c_void_p] * 4 + _FCONV + [c_void_p]
 _decl("cunn_b200_full_conv_grad_input", c_int, [c_void_p] * 3 + _FCONV + [c_void_p])
 _decl("cunn_b200_full_conv_acc_grad_workspace", c_size_t, _FCONV)
 _decl("cunn_b200_full_conv_acc_grad", c_int, [c_void_p] * 4 + _FCONV + [c_float, c_void_p, c_size_t, c_void_p])
+_LCONV = _CONV + [c_int, c_int]  # ... oH oW
+_decl("cunn_b200_local_conv_forward", c_int, [c_void_p] * 4 + _LCONV + [c_void_p])
+_decl("cunn_b200_local_conv_grad_input", c_int, [c_void_p] * 3 + _LCONV + [c_void_p])
+_decl("cunn_b200_local_conv_acc_grad", c_int, [c_void_p] * 4 + _LCONV + [c_float, c_void_p])
+_decl("cunn_b200_adaptive_maxpool_forward", c_int, [c_void_p] * 3 + [c_int] * 5 + [c_void_p])
+_decl("cunn_b200_adaptive_maxpool_backward", c_int, [c_void_p] * 3 + [c_int] * 5 + [c_void_p])
+_decl("cunn_b200_adaptive_avgpool_forward", c_int, [c_void_p] * 2 + [c_int] * 5 + [c_void_p])
+_decl("cunn_b200_adaptive_avgpool_backward", c_int, [c_void_p] * 2 + [c_int] * 5 + [c_void_p])
 _decl("cunn_b200_maxpool_out_size", c_int, [c_int] * 6)
 _decl("cunn_b200_maxpool_forward", c_int, [c_void_p] * 3 + [c_int] * 13 + [c_void_p])
 _decl("cunn_b200_maxpool_backward", c_int, [c_void_p] * 3 + [c_int] * 13 + [c_void_p])

@@ -638,6 +638,172 @@ extern "C" CUNN_API void THNN_CudaDoubleSpatialMaxPooling_updateGradInput(THCSta
     hot_SpatialMaxPooling_updateGradInput<RealDouble>(s, input, gradOutput, gradInput, indices, kW, kH, dW, dH, padW, padH, ceil_mode);
 }
 
+// ---- SpatialConvolutionLocal (generic/SpatialConvolutionLocal.cu; decl generic/THCUNN.h:587-628) --------------------
+// weight 3-D [oH*oW, K, C*kH*kW] or 6-D [oH, oW, K, C, kH, kW] (:58-77); bias [K, oH, oW]; finput / fgradInput are the
+// reference's unfolded copies and are not used.
+static bool local_prepare(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *weight, THCudaTensor *bias, int kH, int kW,
+                          int dH, int dW, long inputHeight, long inputWidth, long outputHeight, long outputWidth, long *N, long *C, long *K)
+{
+    if (!(kW > 0 && kH > 0)) { raise(s, "kernel size should be greater than zero, but got kH: %d kW: %d", kH, kW); return false; }
+    if (!(dW > 0 && dH > 0)) { raise(s, "stride should be greater than zero, but got dH: %d dW: %d", dH, dW); return false; }
+    const int nd = input->nDimension;
+    if (nd != 3 && nd != 4) { raise(s, "3D or 4D input tensor expected but got: %s", size_desc(input).c_str()); return false; }
+    if (weight->nDimension != 3 && weight->nDimension != 6) { raise(s, "weight tensor should be 3D or 6D - got %dD", weight->nDimension); return false; }
+    if (!is_contiguous(weight)) { raise(s, "weight tensor has to be contiguous"); return false; }
+    const bool six = weight->nDimension == 6;
+    *K = six ? weight->size[2] : weight->size[1];
+    const long R = six ? weight->size[3] * weight->size[4] * weight->size[5] : weight->size[2];
+    const long Pw = six ? weight->size[0] * weight->size[1] : weight->size[0];
+    *C = R / (kH * kW);
+    if (Pw != outputHeight * outputWidth) { raise(s, "weight holds %ld output positions, expected %ld x %ld", Pw, outputHeight, outputWidth); return false; }
+    if (bias && !(check_dim_size(s, bias, "bias", 3, 0, *K) && check_dim_size(s, bias, "bias", 3, 1, outputHeight) &&
+                  check_dim_size(s, bias, "bias", 3, 2, outputWidth))) return false;
+    const int b = nd == 4;
+    *N = b ? input->size[0] : 1;
+    if (!check_dim_size(s, input, "input", nd, b, *C)) return false;
+    if (input->size[b + 1] != inputHeight || input->size[b + 2] != inputWidth) {
+        raise(s, "input is %ld x %ld, the module was built for %ld x %ld", input->size[b + 1], input->size[b + 2], inputHeight, inputWidth);
+        return false;
+    }
+    if (gradOutput && !(check_dim_size(s, gradOutput, "gradOutput", nd, b, *K) && check_dim_size(s, gradOutput, "gradOutput", nd, b + 1, outputHeight) &&
+                        check_dim_size(s, gradOutput, "gradOutput", nd, b + 2, outputWidth))) return false;
+    return true;
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialConvolutionLocal_updateOutput(
+    THCState *s, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias, THCudaTensor *, THCudaTensor *, int kW,
+    int kH, int dW, int dH, int padW, int padH, long inputWidth, long inputHeight, long outputWidth, long outputHeight)
+{
+    long N, C, K;
+    if (!local_prepare(s, input, nullptr, weight, bias, kH, kW, dH, dW, inputHeight, inputWidth, outputHeight, outputWidth, &N, &C, &K)) return;
+    THCudaTensor *x = new_contiguous(s, input), *b = bias ? new_contiguous(s, bias) : nullptr;
+    if (x && (!bias || b)) {
+        const long sz4[4] = {N, K, outputHeight, outputWidth};
+        if (tensor_resize(s, output, 4, sz4, 4)) {
+            TH_CALL(s, cunn_b200_local_conv_forward(tdata<float>(x), tdata<float>(weight), tdata<float>(b), tdata<float>(output), (int)N, (int)C,
+                                                    (int)inputHeight, (int)inputWidth, (int)K, kH, kW, dH, dW, padH, padW, (int)outputHeight,
+                                                    (int)outputWidth, state_stream(s)));
+            if (input->nDimension == 3) tensor_resize(s, output, 3, sz4 + 1, 4);
+        }
+    }
+done:
+    tensor_free(s, x); tensor_free(s, b);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialConvolutionLocal_updateGradInput(
+    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight, THCudaTensor *, THCudaTensor *,
+    int kW, int kH, int dW, int dH, int padW, int padH, long inputWidth, long inputHeight, long outputWidth, long outputHeight)
+{
+    long N, C, K;
+    if (!local_prepare(s, input, gradOutput, weight, nullptr, kH, kW, dH, dW, inputHeight, inputWidth, outputHeight, outputWidth, &N, &C, &K)) return;
+    THCudaTensor *gy = new_contiguous(s, gradOutput);
+    if (gy && tensor_resize(s, gradInput, input->nDimension, input->size, 4))
+        TH_CALL(s, cunn_b200_local_conv_grad_input(tdata<float>(gy), tdata<float>(weight), tdata<float>(gradInput), (int)N, (int)C, (int)inputHeight,
+                                                   (int)inputWidth, (int)K, kH, kW, dH, dW, padH, padW, (int)outputHeight, (int)outputWidth,
+                                                   state_stream(s)));
+done:
+    tensor_free(s, gy);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialConvolutionLocal_accGradParameters(
+    THCState *s, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias, THCudaTensor *, THCudaTensor *,
+    int kW, int kH, int dW, int dH, int padW, int padH, long inputWidth, long inputHeight, long outputWidth, long outputHeight, float scale)
+{
+    long N, C, K;
+    if (!local_prepare(s, input, gradOutput, gradWeight, gradBias, kH, kW, dH, dW, inputHeight, inputWidth, outputHeight, outputWidth, &N, &C, &K)) return;
+    TH_CHECK(s, !gradBias || is_contiguous(gradBias), "gradBias has to be contiguous");
+    THCudaTensor *x = new_contiguous(s, input), *gy = new_contiguous(s, gradOutput);
+    if (x && gy)
+        TH_CALL(s, cunn_b200_local_conv_acc_grad(tdata<float>(x), tdata<float>(gy), tdata<float>(gradWeight), gradBias ? tdata<float>(gradBias) : nullptr,
+                                                 (int)N, (int)C, (int)inputHeight, (int)inputWidth, (int)K, kH, kW, dH, dW, padH, padW,
+                                                 (int)outputHeight, (int)outputWidth, scale, state_stream(s)));
+done:
+    tensor_free(s, x); tensor_free(s, gy);
+}
+
+// ---- SpatialAdaptiveMaxPooling / SpatialAdaptiveAveragePooling (decl generic/THCUNN.h:520-546) ---------------------
+static bool adaptive_dims(THCState *s, const THCudaTensor *input, long *planes, long *H, long *W)
+{
+    const int nd = input->nDimension;
+    if (nd != 3 && nd != 4) { raise(s, "3D or 4D (batch mode) tensor expected for input, but got: %s", size_desc(input).c_str()); return false; }
+    const int b = nd == 4;
+    *planes = (b ? input->size[0] : 1) * input->size[b];
+    *H = input->size[b + 1];
+    *W = input->size[b + 2];
+    return true;
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialAdaptiveMaxPooling_updateOutput(THCState *s, THCudaTensor *input, THCudaTensor *output,
+                                                                         THCudaLongTensor *indices, int nOutputCols, int nOutputRows)
+{
+    long planes, H, W;
+    if (!adaptive_dims(s, input, &planes, &H, &W)) return;
+    const int b = input->nDimension == 4;
+    THCudaTensor *x = new_contiguous(s, input);
+    if (x) {
+        const long osz[4] = {b ? input->size[0] : 0, input->size[b], nOutputRows, nOutputCols};
+        const long isz[5] = {2, b ? input->size[0] : 0, input->size[b], nOutputRows, nOutputCols};
+        const long isz3[4] = {2, input->size[b], nOutputRows, nOutputCols};
+        // indices: [2, (N,) C, oH, oW] as the reference resizes them (generic/SpatialAdaptiveMaxPooling.cu:35,64)
+        const bool ok = b ? (tensor_resize(s, output, 4, osz, 4) && tensor_resize(s, indices, 5, isz, 8))
+                          : (tensor_resize(s, output, 3, osz + 1, 4) && tensor_resize(s, indices, 4, isz3, 8));
+        if (ok)
+            TH_CALL(s, cunn_b200_adaptive_maxpool_forward(tdata<float>(x), tdata<float>(output), tdata<int64_t>(indices), (int)planes, (int)H, (int)W,
+                                                          nOutputRows, nOutputCols, state_stream(s)));
+    }
+done:
+    tensor_free(s, x);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialAdaptiveMaxPooling_updateGradInput(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput,
+                                                                            THCudaTensor *gradInput, THCudaLongTensor *indices)
+{
+    long planes, H, W;
+    if (!adaptive_dims(s, input, &planes, &H, &W)) return;
+    const int b = input->nDimension == 4;
+    TH_CHECK(s, gradOutput->nDimension == input->nDimension, "gradOutput must have input's number of dimensions");
+    const long oH = gradOutput->size[b + 1], oW = gradOutput->size[b + 2];
+    TH_CHECK(s, nelem(indices) == 2 * nelem(gradOutput) && is_contiguous(indices), "indices and gradOutput shapes do not match");
+    THCudaTensor *gy = new_contiguous(s, gradOutput);
+    if (gy && tensor_resize(s, gradInput, input->nDimension, input->size, 4))
+        TH_CALL(s, cunn_b200_adaptive_maxpool_backward(tdata<float>(gy), tdata<int64_t>(indices), tdata<float>(gradInput), (int)planes, (int)H, (int)W,
+                                                       (int)oH, (int)oW, state_stream(s)));
+done:
+    tensor_free(s, gy);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialAdaptiveAveragePooling_updateOutput(THCState *s, THCudaTensor *input, THCudaTensor *output,
+                                                                             int nOutputCols, int nOutputRows)
+{
+    long planes, H, W;
+    if (!adaptive_dims(s, input, &planes, &H, &W)) return;
+    const int b = input->nDimension == 4;
+    THCudaTensor *x = new_contiguous(s, input);
+    if (x) {
+        const long osz[4] = {b ? input->size[0] : 0, input->size[b], nOutputRows, nOutputCols};
+        if (tensor_resize(s, output, b ? 4 : 3, b ? osz : osz + 1, 4))
+            TH_CALL(s, cunn_b200_adaptive_avgpool_forward(tdata<float>(x), tdata<float>(output), (int)planes, (int)H, (int)W, nOutputRows,
+                                                          nOutputCols, state_stream(s)));
+    }
+done:
+    tensor_free(s, x);
+}
+
+extern "C" CUNN_API void THNN_CudaSpatialAdaptiveAveragePooling_updateGradInput(THCState *s, THCudaTensor *input, THCudaTensor *gradOutput,
+                                                                                THCudaTensor *gradInput)
+{
+    long planes, H, W;
+    if (!adaptive_dims(s, input, &planes, &H, &W)) return;
+    const int b = input->nDimension == 4;
+    TH_CHECK(s, gradOutput->nDimension == input->nDimension, "gradOutput must have input's number of dimensions");
+    THCudaTensor *gy = new_contiguous(s, gradOutput);
+    if (gy && tensor_resize(s, gradInput, input->nDimension, input->size, 4))
+        TH_CALL(s, cunn_b200_adaptive_avgpool_backward(tdata<float>(gy), tdata<float>(gradInput), (int)planes, (int)H, (int)W,
+                                                       (int)gradOutput->size[b + 1], (int)gradOutput->size[b + 2], state_stream(s)));
+done:
+    tensor_free(s, gy);
+}
+
 // ---- support operators ---------------------------------------------------------------------------------------
 extern "C" CUNN_API void THNN_CudaThreshold_updateOutput(THCState *s, THCudaTensor *input, THCudaTensor *output, float threshold,
                                                          float val, bool inplace)

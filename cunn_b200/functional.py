@@ -370,3 +370,70 @@ def batchnorm_relu_backward(x, gy, weight, bias, running_mean, running_var, save
                                                 _ptr(save_std), N, C, S, int(train), scale, eps, _ptr(ws), ws.numel(),
                                                 _stream()))
     return out
+
+
+def local_conv_forward(x, weight, bias, kH, kW, dH, dW, padH, padW, out=None):
+    """SpatialConvolutionLocal forward; weight [oH*oW, K, C*kH*kW], bias [K, oH, oW] or None."""
+    _chk(x, weight, bias)
+    N, C, H, W = x.shape
+    K = weight.shape[1]
+    oH, oW = conv_out(H, kH, dH, padH), conv_out(W, kW, dW, padW)
+    if out is None:
+        out = torch.empty((N, K, oH, oW), dtype=torch.float32, device=x.device)
+    check(lib.cunn_b200_local_conv_forward(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), N, C, H, W, K, kH, kW, dH, dW, padH, padW,
+                                           oH, oW, _stream()))
+    return out
+
+
+def local_conv_grad_input(gy, weight, C, H, W, kH, kW, dH, dW, padH, padW, out=None):
+    _chk(gy, weight)
+    N, K, oH, oW = gy.shape
+    if out is None:
+        out = torch.empty((N, C, H, W), dtype=torch.float32, device=gy.device)
+    check(lib.cunn_b200_local_conv_grad_input(_ptr(gy), _ptr(weight), _ptr(out), N, C, H, W, K, kH, kW, dH, dW, padH, padW, oH, oW,
+                                              _stream()))
+    return out
+
+
+def local_conv_acc_grad(x, gy, grad_weight, grad_bias, kH, kW, dH, dW, padH, padW, scale=1.0):
+    """Accumulates into grad_weight [oH*oW, K, C*kH*kW] and grad_bias [K, oH, oW] (may be None) in place."""
+    _chk(x, gy, grad_weight, grad_bias)
+    N, C, H, W = x.shape
+    _, K, oH, oW = gy.shape
+    check(lib.cunn_b200_local_conv_acc_grad(_ptr(x), _ptr(gy), _ptr(grad_weight), _ptr(grad_bias), N, C, H, W, K, kH, kW, dH, dW, padH,
+                                            padW, oH, oW, scale, _stream()))
+    return grad_weight, grad_bias
+
+
+def adaptive_maxpool_forward(x, oH, oW):
+    """Returns y [N, C, oH, oW] and int64 indices [2, N, C, oH, oW]: row and column of the maximum inside its window."""
+    _chk(x)
+    N, C, H, W = x.shape
+    y = torch.empty((N, C, oH, oW), dtype=torch.float32, device=x.device)
+    ind = torch.empty((2, N, C, oH, oW), dtype=torch.int64, device=x.device)
+    check(lib.cunn_b200_adaptive_maxpool_forward(_ptr(x), _ptr(y), _ptr(ind), N * C, H, W, oH, oW, _stream()))
+    return y, ind
+
+
+def adaptive_maxpool_backward(gy, indices, H, W):
+    _chk(gy, indices)
+    N, C, oH, oW = gy.shape
+    gx = torch.empty((N, C, H, W), dtype=torch.float32, device=gy.device)
+    check(lib.cunn_b200_adaptive_maxpool_backward(_ptr(gy), _ptr(indices), _ptr(gx), N * C, H, W, oH, oW, _stream()))
+    return gx
+
+
+def adaptive_avgpool_forward(x, oH, oW):
+    _chk(x)
+    N, C, H, W = x.shape
+    y = torch.empty((N, C, oH, oW), dtype=torch.float32, device=x.device)
+    check(lib.cunn_b200_adaptive_avgpool_forward(_ptr(x), _ptr(y), N * C, H, W, oH, oW, _stream()))
+    return y
+
+
+def adaptive_avgpool_backward(gy, H, W):
+    _chk(gy)
+    N, C, oH, oW = gy.shape
+    gx = torch.empty((N, C, H, W), dtype=torch.float32, device=gy.device)
+    check(lib.cunn_b200_adaptive_avgpool_backward(_ptr(gy), _ptr(gx), N * C, H, W, oH, oW, _stream()))
+    return gx

@@ -67,6 +67,13 @@ _SIGS = {
     "BatchNormalization_backward": [_T] * 10 + [_B, _D, _D],
     "SpatialMaxPooling_updateOutput": [_T] * 3 + _CONV + [_B],
     "SpatialMaxPooling_updateGradInput": [_T] * 4 + _CONV + [_B],
+    "SpatialConvolutionLocal_updateOutput": [_T] * 6 + _CONV + [_L] * 4,
+    "SpatialConvolutionLocal_updateGradInput": [_T] * 6 + _CONV + [_L] * 4,
+    "SpatialConvolutionLocal_accGradParameters": [_T] * 6 + _CONV + [_L] * 4 + [_F],
+    "SpatialAdaptiveMaxPooling_updateOutput": [_T, _T, _T, _I, _I],
+    "SpatialAdaptiveMaxPooling_updateGradInput": [_T] * 4,
+    "SpatialAdaptiveAveragePooling_updateOutput": [_T, _T, _I, _I],
+    "SpatialAdaptiveAveragePooling_updateGradInput": [_T] * 3,
     "Threshold_updateOutput": [_T, _T, _F, _F, _B],
     "Threshold_updateGradInput": [_T, _T, _T, _F, _F, _B],
     "SpatialAveragePooling_updateOutput": [_T, _T] + _CONV + [_B, _B],
@@ -299,6 +306,73 @@ class THNN:
             return self.view(ho, buf)
         finally:
             self.free(hx, hw, hb, ho)
+
+    def SpatialConvolutionLocal_updateOutput(self, x, weight, bias, kW, kH, dW, dH, padW, padH, iW, iH, oW, oH):
+        b = x.dim() == 4
+        K = weight.shape[2] if weight.dim() == 6 else weight.shape[1]
+        hx, hw, hb = self.wrap(x), self.wrap(weight), self.wrap(bias)
+        ho, buf = self.out((x.shape[0] if b else 1) * K * oH * oW)
+        try:
+            self.call("SpatialConvolutionLocal_updateOutput", hx, ho, hw, hb, None, None, kW, kH, dW, dH, padW, padH, iW, iH, oW, oH)
+            return self.view(ho, buf)
+        finally:
+            self.free(hx, hw, hb, ho)
+
+    def SpatialConvolutionLocal_updateGradInput(self, x, gy, weight, kW, kH, dW, dH, padW, padH, iW, iH, oW, oH):
+        hx, hg, hw = self.wrap(x), self.wrap(gy), self.wrap(weight)
+        ho, buf = self.out(x.numel())
+        try:
+            self.call("SpatialConvolutionLocal_updateGradInput", hx, hg, ho, hw, None, None, kW, kH, dW, dH, padW, padH, iW, iH, oW, oH)
+            return self.view(ho, buf)
+        finally:
+            self.free(hx, hg, hw, ho)
+
+    def SpatialConvolutionLocal_accGradParameters(self, x, gy, gw, gb, kW, kH, dW, dH, padW, padH, iW, iH, oW, oH, scale):
+        hx, hg, hw, hb = self.wrap(x), self.wrap(gy), self.wrap(gw), self.wrap(gb)
+        try:
+            self.call("SpatialConvolutionLocal_accGradParameters", hx, hg, hw, hb, None, None, kW, kH, dW, dH, padW, padH, iW, iH,
+                      oW, oH, scale)
+        finally:
+            self.free(hx, hg, hw, hb)
+
+    def SpatialAdaptiveMaxPooling_updateOutput(self, x, nOutputCols, nOutputRows):
+        planes = x.numel() // (x.shape[-1] * x.shape[-2])
+        hx = self.wrap(x)
+        ho, buf = self.out(planes * nOutputCols * nOutputRows)
+        hi, ibuf = self.out(2 * planes * nOutputCols * nOutputRows, torch.int64)
+        try:
+            self.call("SpatialAdaptiveMaxPooling_updateOutput", hx, ho, hi, nOutputCols, nOutputRows)
+            return self.view(ho, buf), self.view(hi, ibuf)
+        finally:
+            self.free(hx, ho, hi)
+
+    def SpatialAdaptiveMaxPooling_updateGradInput(self, x, gy, indices):
+        hx, hg, hi = self.wrap(x), self.wrap(gy), self.wrap(indices)
+        ho, buf = self.out(x.numel())
+        try:
+            self.call("SpatialAdaptiveMaxPooling_updateGradInput", hx, hg, ho, hi)
+            return self.view(ho, buf)
+        finally:
+            self.free(hx, hg, hi, ho)
+
+    def SpatialAdaptiveAveragePooling_updateOutput(self, x, nOutputCols, nOutputRows):
+        planes = x.numel() // (x.shape[-1] * x.shape[-2])
+        hx = self.wrap(x)
+        ho, buf = self.out(planes * nOutputCols * nOutputRows)
+        try:
+            self.call("SpatialAdaptiveAveragePooling_updateOutput", hx, ho, nOutputCols, nOutputRows)
+            return self.view(ho, buf)
+        finally:
+            self.free(hx, ho)
+
+    def SpatialAdaptiveAveragePooling_updateGradInput(self, x, gy):
+        hx, hg = self.wrap(x), self.wrap(gy)
+        ho, buf = self.out(x.numel())
+        try:
+            self.call("SpatialAdaptiveAveragePooling_updateGradInput", hx, hg, ho)
+            return self.view(ho, buf)
+        finally:
+            self.free(hx, hg, ho)
 
     def BatchNormalization_updateOutput(self, x, weight, bias, running_mean, running_var, train, momentum, eps):
         C = x.shape[1]

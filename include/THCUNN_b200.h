@@ -154,6 +154,28 @@ CUNN_API void THNN_CudaSpatialMaxPooling_updateGradInput(
     THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaLongTensor *indices,
     int kW, int kH, int dW, int dH, int padW, int padH, bool ceil_mode);
 
+/* lib/THCUNN/generic/THCUNN.h:587-628 (SpatialConvolutionLocal), :520-546 (adaptive pooling) */
+CUNN_API void THNN_CudaSpatialConvolutionLocal_updateOutput(
+    THCState *state, THCudaTensor *input, THCudaTensor *output, THCudaTensor *weight, THCudaTensor *bias, THCudaTensor *finput,
+    THCudaTensor *fgradInput, int kW, int kH, int dW, int dH, int padW, int padH, long inputWidth, long inputHeight,
+    long outputWidth, long outputHeight);
+CUNN_API void THNN_CudaSpatialConvolutionLocal_updateGradInput(
+    THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradInput, THCudaTensor *weight,
+    THCudaTensor *finput, THCudaTensor *fgradInput, int kW, int kH, int dW, int dH, int padW, int padH, long inputWidth,
+    long inputHeight, long outputWidth, long outputHeight);
+CUNN_API void THNN_CudaSpatialConvolutionLocal_accGradParameters(
+    THCState *state, THCudaTensor *input, THCudaTensor *gradOutput, THCudaTensor *gradWeight, THCudaTensor *gradBias,
+    THCudaTensor *finput, THCudaTensor *fgradInput, int kW, int kH, int dW, int dH, int padW, int padH, long inputWidth,
+    long inputHeight, long outputWidth, long outputHeight, float scale);
+CUNN_API void THNN_CudaSpatialAdaptiveMaxPooling_updateOutput(THCState *state, THCudaTensor *input, THCudaTensor *output,
+                                                              THCudaLongTensor *indices, int nOutputCols, int nOutputRows);
+CUNN_API void THNN_CudaSpatialAdaptiveMaxPooling_updateGradInput(THCState *state, THCudaTensor *input, THCudaTensor *gradOutput,
+                                                                 THCudaTensor *gradInput, THCudaLongTensor *indices);
+CUNN_API void THNN_CudaSpatialAdaptiveAveragePooling_updateOutput(THCState *state, THCudaTensor *input, THCudaTensor *output,
+                                                                  int nOutputCols, int nOutputRows);
+CUNN_API void THNN_CudaSpatialAdaptiveAveragePooling_updateGradInput(THCState *state, THCudaTensor *input, THCudaTensor *gradOutput,
+                                                                     THCudaTensor *gradInput);
+
 /* ---- hot path (double): the same ten entry points for THCudaDoubleTensor, accreal = double (THCUNN.lua:54) ---- */
 CUNN_API void THNN_CudaDoubleSpatialDepthWiseConvolution_updateOutput(
     THCState *state, THCudaDoubleTensor *input, THCudaDoubleTensor *output, THCudaDoubleTensor *weight, THCudaDoubleTensor *bias,

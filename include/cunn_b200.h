@@ -305,6 +305,35 @@ CUNN_API int cunn_b200_mobilenet_step(const cunn_b200_mobilenet_config *cfg, con
                                       float *bn_running, void *arena, size_t arena_bytes, float *loss,
                                       double momentum, double eps, cunn_stream_t stream);
 
+/* ---- SpatialConvolutionLocal: convolution with weights that are not shared between output positions ----------
+ * weight [oH*oW, K, C*kH*kW] (the reference's 3-D view of its 6-D [oH, oW, K, C, kH, kW] weight,
+ * lib/THCUNN/generic/SpatialConvolutionLocal.cu:58-77), bias [K, oH, oW] or NULL, x [N, C, H, W], y [N, K, oH, oW];
+ * oH, oW must be the sizes that follow from H, W, kernel, stride and padding.  acc_grad accumulates with `scale`.
+ * Replace THNN_(SpatialConvolutionLocal_updateOutput / _updateGradInput / _accGradParameters) (:79-407). */
+CUNN_API int cunn_b200_local_conv_forward(const float *x, const float *weight, const float *bias, float *y, int N, int C, int H, int W,
+                                          int K, int kH, int kW, int dH, int dW, int padH, int padW, int oH, int oW,
+                                          cunn_stream_t stream);
+CUNN_API int cunn_b200_local_conv_grad_input(const float *gy, const float *weight, float *gx, int N, int C, int H, int W, int K, int kH,
+                                             int kW, int dH, int dW, int padH, int padW, int oH, int oW, cunn_stream_t stream);
+CUNN_API int cunn_b200_local_conv_acc_grad(const float *x, const float *gy, float *grad_weight, float *grad_bias, int N, int C, int H,
+                                           int W, int K, int kH, int kW, int dH, int dW, int padH, int padW, int oH, int oW,
+                                           float scale, cunn_stream_t stream);
+
+/* ---- SpatialAdaptiveMaxPooling / SpatialAdaptiveAveragePooling over `planes` = N*C planes of H x W --------------
+ * Output size oH x oW is given; the window of output row i is [floor(i/oH*H), ceil((i+1)/oH*H)) in the float
+ * arithmetic of the reference kernels.  Max pooling stores TWO index planes, indices [2, planes, oH, oW]: first the
+ * row, then the column of the maximum RELATIVE to the window start, plus CUNN_B200_INDEX_BASE (first maximum wins,
+ * strict compare from -FLT_MAX).  The backward passes are gathers (deterministic; the reference adds atomically).
+ * Replace THNN_(SpatialAdaptiveMaxPooling_*) (lib/THCUNN/SpatialAdaptiveMaxPooling.cu:15-176, generic/...:7-190) and
+ * THNN_(SpatialAdaptiveAveragePooling_*) (lib/THCUNN/SpatialAdaptiveAveragePooling.cu:6-190, generic/...:7-170). */
+CUNN_API int cunn_b200_adaptive_maxpool_forward(const float *x, float *y, int64_t *indices, int planes, int H, int W, int oH, int oW,
+                                                cunn_stream_t stream);
+CUNN_API int cunn_b200_adaptive_maxpool_backward(const float *gy, const int64_t *indices, float *gx, int planes, int H, int W, int oH,
+                                                 int oW, cunn_stream_t stream);
+CUNN_API int cunn_b200_adaptive_avgpool_forward(const float *x, float *y, int planes, int H, int W, int oH, int oW, cunn_stream_t stream);
+CUNN_API int cunn_b200_adaptive_avgpool_backward(const float *gy, float *gx, int planes, int H, int W, int oH, int oW,
+                                                 cunn_stream_t stream);
+
 /* ---- fp64 twins of the hot path -----------------------------------------------------------------------
  * The operators above for double tensors, behind THNN_CudaDouble* (the reference instantiates every entry point
  * for float and double: lib/THCUNN/SpatialDepthWiseConvolution.cu:9, SpatialConvolutionMM.cu:9,

@@ -86,6 +86,37 @@ class RefKernelsCPU:
         return gx
 
 
+    def adaptive_maxpool_forward(self, x, oH, oW):
+        x = _f(x)
+        N, C, H, W = x.shape
+        y = np.empty((N, C, oH, oW), np.float32)
+        ind = np.empty((2, N, C, oH, oW), np.int64)
+        self.lib.refk_cpu_adaptive_maxpool_forward(_p(x), _p(y), _p(ind), N * C, H, W, oH, oW)
+        return y, ind
+
+    def adaptive_maxpool_backward(self, gy, ind, H, W):
+        gy = _f(gy)
+        ind = np.ascontiguousarray(ind, dtype=np.int64)
+        N, C, oH, oW = gy.shape
+        gx = np.zeros((N, C, H, W), np.float32)                       # the reference's wrapper zeroes gradInput first
+        self.lib.refk_cpu_adaptive_maxpool_backward(_p(gx), _p(gy), _p(ind), N * C, H, W, oH, oW)
+        return gx
+
+    def adaptive_avgpool_forward(self, x, oH, oW):
+        x = _f(x)
+        N, C, H, W = x.shape
+        y = np.empty((N, C, oH, oW), np.float32)
+        self.lib.refk_cpu_adaptive_avgpool_forward(_p(x), _p(y), N * C, H, W, oH, oW)
+        return y
+
+    def adaptive_avgpool_backward(self, gy, H, W):
+        gy = _f(gy)
+        N, C, oH, oW = gy.shape
+        gx = np.zeros((N, C, H, W), np.float32)
+        self.lib.refk_cpu_adaptive_avgpool_backward(_p(gx), _p(gy), N * C, H, W, oH, oW)
+        return gx
+
+
 def _out(size, k, d, pad, dil=1):
     return (size + 2 * pad - (dil * (k - 1) + 1)) // d + 1
 

@@ -1,6 +1,7 @@
 /* Test infrastructure: launches the reference's OWN pooling kernels, compiled from where they lie
  * in the reference tree (lib/THCUNN/SpatialDilatedMaxPooling.cu:8-80 MaxPoolForward / MaxPoolBackward,
- * lib/THCUNN/SpatialAveragePooling.cu:7-82 AvePoolForward / AvePoolBackward) behind the stand-in
+ * lib/THCUNN/SpatialAveragePooling.cu:7-82 AvePoolForward / AvePoolBackward,
+ * lib/THCUNN/SpatialAdaptiveMaxPooling.cu:15-176 and SpatialAdaptiveAveragePooling.cu:16-190) behind the stand-in
  * headers of ref_shim/.  No reference source is copied here; this file only holds launchers.
  *
  * Launch shapes follow the reference's host wrappers: one thread per output element for the
@@ -14,6 +15,8 @@
  */
 #include "SpatialDilatedMaxPooling.cu"
 #include "SpatialAveragePooling.cu"
+#include "SpatialAdaptiveMaxPooling.cu"
+#include "SpatialAdaptiveAveragePooling.cu"
 
 #ifdef REFK_CPU
 #define REFK_NAME(n) refk_cpu_##n
@@ -63,6 +66,33 @@ REFK_EXPORT void REFK_NAME(avgpool_backward)(const float *gy, float *gx, int N, 
     REFK_LAUNCH((AvePoolBackward<float, float, true>), count, count, gy, N, C, H, W, oH, oW, kH, kW, dH, dW, padH, padW, gx);
   else
     REFK_LAUNCH((AvePoolBackward<float, float, false>), count, count, gy, N, C, H, W, oH, oW, kH, kW, dH, dW, padH, padW, gx);
+}
+
+/* Adaptive pooling: one block per plane (generic/SpatialAdaptiveMaxPooling.cu:39-50, :121-141; the wrappers always
+ * take the atomic backward kernels).  indices: [2, planes, oH, oW], row offsets first (the wrapper passes the second
+ * half as indices_x).  gx must be zero on entry, as the wrappers zero gradInput before the launch. */
+#ifdef REFK_CPU
+#define REFK_LAUNCH_PLANES(kernel, planes, ...) REFK_LAUNCH(kernel, planes, __VA_ARGS__)
+#else
+#define REFK_LAUNCH_PLANES(kernel, planes, ...) \
+  do { int yb = 16 / (planes); if (yb < 1) yb = 1; kernel<<<dim3(planes, yb), dim3(32, 8)>>>(__VA_ARGS__); THCudaCheck(cudaGetLastError()); } while (0)
+#endif
+
+REFK_EXPORT void REFK_NAME(adaptive_maxpool_forward)(float *x, float *y, long *ind, int planes, int H, int W, int oH, int oW) {
+  if (planes == 0) return;
+  REFK_LAUNCH_PLANES((adaptivemaxpool<float>), planes, x, y, ind + (long)planes * oH * oW, ind, planes, H, W, oH, oW, W, 1, H * W);
+}
+REFK_EXPORT void REFK_NAME(adaptive_maxpool_backward)(float *gx, float *gy, long *ind, int planes, int H, int W, int oH, int oW) {
+  if (planes == 0) return;
+  REFK_LAUNCH_PLANES((atomicadaptivemaxgradinput<float>), planes, gx, gy, ind + (long)planes * oH * oW, ind, planes, H, W, oH, oW);
+}
+REFK_EXPORT void REFK_NAME(adaptive_avgpool_forward)(float *x, float *y, int planes, int H, int W, int oH, int oW) {
+  if (planes == 0) return;
+  REFK_LAUNCH_PLANES((adaptiveaveragepool<float>), planes, x, y, planes, H, W, oH, oW, W, 1, H * W);
+}
+REFK_EXPORT void REFK_NAME(adaptive_avgpool_backward)(float *gx, float *gy, int planes, int H, int W, int oH, int oW) {
+  if (planes == 0) return;
+  REFK_LAUNCH_PLANES((atomicadaptiveaveragegradinput<float>), planes, gx, gy, planes, H, W, oH, oW);
 }
 
 REFK_EXPORT int REFK_NAME(index_base)(void) { return TH_INDEX_BASE; }

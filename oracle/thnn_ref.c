@@ -38,6 +38,7 @@
 #include <stdint.h>
 #include <float.h>
 #include <string.h>
+#include <stdlib.h>
 
 #ifndef REF_ACC
 #define REF_ACC double
@@ -771,6 +772,180 @@ void FN(classnll_backward)(const int64_t *target, const real_t *weights, real_t 
 /* ------------------------------------------------------------------------ */
 /* DataParallelTable shard rule.                                             */
 /* ------------------------------------------------------------------------ */
+
+/* ------------------------------------------------------------------------ */
+/* SpatialConvolutionLocal: a convolution whose weights are NOT shared       */
+/* between output positions (lib/THCUNN/generic/SpatialConvolutionLocal.cu). */
+/* weight [oH*oW, K, C*kH*kW] (:58-77), bias [K, oH, oW] (:37-41).           */
+/*   y[n,k,p]  = bias[k,p] + sum_r W[p,k,r] col[n,r,p]          (:132-156)   */
+/*   gx        = fold over p of W[p]^T gy[n,:,p]                (:232-262)   */
+/*   gW[p,k,r] += scale sum_n gy[n,k,p] col[n,r,p]; gb += scale sum_n gy (:366-379) */
+/* ------------------------------------------------------------------------ */
+void FN(localconv_forward)(const real_t *x, const real_t *w, const real_t *bias, real_t *y,
+                           int N, int C, int H, int W, int K, int kH, int kW,
+                           int dH, int dW, int padH, int padW, int oH, int oW)
+{
+    const int P = oH * oW, R = C * kH * kW;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int n = 0; n < N; ++n)
+        for (int k = 0; k < K; ++k)
+            for (int p = 0; p < P; ++p) {
+                const int oh = p / oW, ow = p % oW;
+                acc_t s = bias ? (acc_t)bias[(size_t)k * P + p] : 0;
+                const real_t *wp = w + ((size_t)p * K + k) * R;
+                for (int c = 0; c < C; ++c)
+                    for (int kh = 0; kh < kH; ++kh) {
+                        const int ih = oh * dH - padH + kh;
+                        if (ih < 0 || ih >= H) continue;
+                        for (int kw_ = 0; kw_ < kW; ++kw_) {
+                            const int iw = ow * dW - padW + kw_;
+                            if (iw < 0 || iw >= W) continue;
+                            s += (acc_t)wp[(c * kH + kh) * kW + kw_] * (acc_t)x[(((size_t)n * C + c) * H + ih) * W + iw];
+                        }
+                    }
+                y[((size_t)n * K + k) * P + p] = (real_t)s;
+            }
+}
+
+void FN(localconv_grad_input)(const real_t *gy, const real_t *w, real_t *gx,
+                              int N, int C, int H, int W, int K, int kH, int kW,
+                              int dH, int dW, int padH, int padW, int oH, int oW)
+{
+    const int P = oH * oW, R = C * kH * kW;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int n = 0; n < N; ++n)
+        for (int c = 0; c < C; ++c)
+            for (int h = 0; h < H; ++h)
+                for (int wi = 0; wi < W; ++wi) {
+                    acc_t s = 0;
+                    for (int kh = 0; kh < kH; ++kh) {
+                        const int a = h + padH - kh;
+                        if (a < 0 || a % dH || a / dH >= oH) continue;
+                        for (int kw_ = 0; kw_ < kW; ++kw_) {
+                            const int b = wi + padW - kw_;
+                            if (b < 0 || b % dW || b / dW >= oW) continue;
+                            const int p = (a / dH) * oW + b / dW;
+                            for (int k = 0; k < K; ++k)
+                                s += (acc_t)w[((size_t)p * K + k) * R + (c * kH + kh) * kW + kw_] * (acc_t)gy[((size_t)n * K + k) * P + p];
+                        }
+                    }
+                    gx[(((size_t)n * C + c) * H + h) * W + wi] = (real_t)s;
+                }
+}
+
+void FN(localconv_acc_grad)(const real_t *x, const real_t *gy, real_t *gw, real_t *gb,
+                            int N, int C, int H, int W, int K, int kH, int kW,
+                            int dH, int dW, int padH, int padW, int oH, int oW, real_t scale)
+{
+    const int P = oH * oW, R = C * kH * kW;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int p = 0; p < P; ++p)
+        for (int k = 0; k < K; ++k) {
+            const int oh = p / oW, ow = p % oW;
+            for (int c = 0; c < C; ++c)
+                for (int kh = 0; kh < kH; ++kh)
+                    for (int kw_ = 0; kw_ < kW; ++kw_) {
+                        const int ih = oh * dH - padH + kh, iw = ow * dW - padW + kw_;
+                        acc_t s = 0;
+                        if (ih >= 0 && ih < H && iw >= 0 && iw < W)
+                            for (int n = 0; n < N; ++n)
+                                s += (acc_t)gy[((size_t)n * K + k) * P + p] * (acc_t)x[(((size_t)n * C + c) * H + ih) * W + iw];
+                        real_t *g = gw + ((size_t)p * K + k) * R + (c * kH + kh) * kW + kw_;
+                        *g = (real_t)((acc_t)*g + (acc_t)scale * s);
+                    }
+            if (gb) {
+                acc_t s = 0;
+                for (int n = 0; n < N; ++n) s += (acc_t)gy[((size_t)n * K + k) * P + p];
+                gb[(size_t)k * P + p] = (real_t)((acc_t)gb[(size_t)k * P + p] + (acc_t)scale * s);
+            }
+        }
+}
+
+/* ------------------------------------------------------------------------ */
+/* Adaptive pooling to a given output size.  Window of output row i:         */
+/*   max:     [floor(float(i) / oH * H), ceil(float(i + 1) / oH * H))   (lib/THCUNN/SpatialAdaptiveMaxPooling.cu:44-52)     */
+/*   average: [floor((float)(i * H) / oH), ceil((float)((i + 1) * H) / oH))  (lib/THCUNN/SpatialAdaptiveAveragePooling.cu:6-7) */
+/* both in float arithmetic, as the kernels compute them.                    */
+/* Max: strict > from the lowest finite value, first maximum wins; indices are stored as two planes,               */
+/* ind[0] = row and ind[1] = column of the maximum RELATIVE to the window start, plus the index base              */
+/* (:62-78, launch generic/SpatialAdaptiveMaxPooling.cu:48-50: indices_x is the second half).                      */
+/* ------------------------------------------------------------------------ */
+static int amax_start(int i, int o, int n) { return (int)floorf((float)i / (float)o * (float)n); }
+static int amax_end(int i, int o, int n) { return (int)ceilf((float)(i + 1) / (float)o * (float)n); }
+static int aavg_start(int i, int o, int n) { return (int)floorf((float)(i * n) / (float)o); }
+static int aavg_end(int i, int o, int n) { return (int)ceilf((float)((i + 1) * n) / (float)o); }
+
+void FN(adaptive_maxpool_forward)(const real_t *x, real_t *y, int64_t *ind, int planes, int H, int W, int oH, int oW)
+{
+    const size_t half = (size_t)planes * oH * oW;
+#pragma omp parallel for schedule(static)
+    for (int p = 0; p < planes; ++p)
+        for (int yy = 0; yy < oH; ++yy)
+            for (int xx = 0; xx < oW; ++xx) {
+                const int y0 = amax_start(yy, oH, H), y1 = amax_end(yy, oH, H), x0 = amax_start(xx, oW, W), x1 = amax_end(xx, oW, W);
+                real_t best = REAL_LOWEST;
+                int by = -1, bx = -1;
+                for (int h = y0; h < y1; ++h)
+                    for (int w = x0; w < x1; ++w) {
+                        const real_t v = x[((size_t)p * H + h) * W + w];
+                        if (v > best) { best = v; by = h - y0; bx = w - x0; }
+                    }
+                const size_t o = ((size_t)p * oH + yy) * oW + xx;
+                y[o] = best;
+                ind[o] = by + REF_INDEX_BASE;
+                ind[half + o] = bx + REF_INDEX_BASE;
+            }
+}
+
+/* gx[window start + stored offset] += gy, summed over the outputs (atomicadaptivemaxgradinput, :133-176). */
+void FN(adaptive_maxpool_backward)(const real_t *gy, const int64_t *ind, real_t *gx, int planes, int H, int W, int oH, int oW)
+{
+    const size_t half = (size_t)planes * oH * oW;
+#pragma omp parallel for schedule(static)
+    for (int p = 0; p < planes; ++p) {
+        acc_t *tmp = (acc_t *)calloc((size_t)H * W, sizeof(acc_t));
+        for (int yy = 0; yy < oH; ++yy)
+            for (int xx = 0; xx < oW; ++xx) {
+                const size_t o = ((size_t)p * oH + yy) * oW + xx;
+                const int h = amax_start(yy, oH, H) + (int)(ind[o] - REF_INDEX_BASE), w = amax_start(xx, oW, W) + (int)(ind[half + o] - REF_INDEX_BASE);
+                tmp[(size_t)h * W + w] += (acc_t)gy[o];
+            }
+        for (int i = 0; i < H * W; ++i) gx[(size_t)p * H * W + i] = (real_t)tmp[i];
+        free(tmp);
+    }
+}
+
+void FN(adaptive_avgpool_forward)(const real_t *x, real_t *y, int planes, int H, int W, int oH, int oW)
+{
+#pragma omp parallel for schedule(static)
+    for (int p = 0; p < planes; ++p)
+        for (int yy = 0; yy < oH; ++yy)
+            for (int xx = 0; xx < oW; ++xx) {
+                const int y0 = aavg_start(yy, oH, H), y1 = aavg_end(yy, oH, H), x0 = aavg_start(xx, oW, W), x1 = aavg_end(xx, oW, W);
+                acc_t s = 0;
+                for (int h = y0; h < y1; ++h)
+                    for (int w = x0; w < x1; ++w) s += (acc_t)x[((size_t)p * H + h) * W + w];
+                y[((size_t)p * oH + yy) * oW + xx] = (real_t)(s / (y1 - y0) / (x1 - x0));
+            }
+}
+
+/* every input of a window receives gy / kW / kH (atomicadaptiveaveragegradinput, lib/THCUNN/SpatialAdaptiveAveragePooling.cu:143-190). */
+void FN(adaptive_avgpool_backward)(const real_t *gy, real_t *gx, int planes, int H, int W, int oH, int oW)
+{
+#pragma omp parallel for schedule(static)
+    for (int p = 0; p < planes; ++p) {
+        acc_t *tmp = (acc_t *)calloc((size_t)H * W, sizeof(acc_t));
+        for (int yy = 0; yy < oH; ++yy)
+            for (int xx = 0; xx < oW; ++xx) {
+                const int y0 = aavg_start(yy, oH, H), y1 = aavg_end(yy, oH, H), x0 = aavg_start(xx, oW, W), x1 = aavg_end(xx, oW, W);
+                const acc_t z = (acc_t)gy[((size_t)p * oH + yy) * oW + xx] / (x1 - x0) / (y1 - y0);
+                for (int h = y0; h < y1; ++h)
+                    for (int w = x0; w < x1; ++w) tmp[(size_t)h * W + w] += z;
+            }
+        for (int i = 0; i < H * W; ++i) gx[(size_t)p * H * W + i] = (real_t)tmp[i];
+        free(tmp);
+    }
+}
 
 /* Rows [start, start+count) of a batch of `n` rows that replica `i` (0-based)
  * of `g` receives: the first n mod g replicas get one extra row

@@ -304,6 +304,66 @@ class Ref:
                                       int(size_average), ctypes.c_int64(ignore_index))
         return gx
 
+    # -- SpatialConvolutionLocal (weight [oH*oW, K, C*kH*kW], bias [K, oH, oW]) -----------------
+    def localconv_forward(self, x, w, b, kH, kW, dH, dW, padH, padW):
+        x, w = _f(x), _f(w)
+        b = None if b is None else _f(b)
+        N, C, H, W = x.shape
+        K = w.shape[1]
+        oH, oW = conv_out(H, kH, dH, padH), conv_out(W, kW, dW, padW)
+        y = np.empty((N, K, oH, oW), self.dtype)
+        self._fn("localconv_forward")(_p(x), _p(w), _p(b), _p(y), N, C, H, W, K, kH, kW, dH, dW, padH, padW, oH, oW)
+        return y
+
+    def localconv_grad_input(self, gy, w, C, H, W, kH, kW, dH, dW, padH, padW):
+        gy, w = _f(gy), _f(w)
+        N, K, oH, oW = gy.shape
+        gx = np.empty((N, C, H, W), self.dtype)
+        self._fn("localconv_grad_input")(_p(gy), _p(w), _p(gx), N, C, H, W, K, kH, kW, dH, dW, padH, padW, oH, oW)
+        return gx
+
+    def localconv_acc_grad(self, x, gy, gw, gb, kH, kW, dH, dW, padH, padW, scale):
+        x, gy = _f(x), _f(gy)
+        gw = _f(gw).copy()
+        gb = None if gb is None else _f(gb).copy()
+        N, C, H, W = x.shape
+        _, K, oH, oW = gy.shape
+        self._fn("localconv_acc_grad")(_p(x), _p(gy), _p(gw), _p(gb), N, C, H, W, K, kH, kW, dH, dW, padH, padW, oH, oW,
+                                       self.creal(scale))
+        return gw, gb
+
+    # -- adaptive pooling ------------------------------------------------------------------------
+    def adaptive_maxpool_forward(self, x, oH, oW):
+        """Returns y [N, C, oH, oW] and indices [2, N, C, oH, oW] (row, column offsets inside the window + base)."""
+        x = _f(x)
+        N, C, H, W = x.shape
+        y = np.empty((N, C, oH, oW), self.dtype)
+        ind = np.empty((2, N, C, oH, oW), np.int64)
+        self._fn("adaptive_maxpool_forward")(_p(x), _p(y), _p(ind), N * C, H, W, oH, oW)
+        return y, ind
+
+    def adaptive_maxpool_backward(self, gy, ind, H, W):
+        gy = _f(gy)
+        ind = np.ascontiguousarray(ind, dtype=np.int64)
+        N, C, oH, oW = gy.shape
+        gx = np.empty((N, C, H, W), self.dtype)
+        self._fn("adaptive_maxpool_backward")(_p(gy), _p(ind), _p(gx), N * C, H, W, oH, oW)
+        return gx
+
+    def adaptive_avgpool_forward(self, x, oH, oW):
+        x = _f(x)
+        N, C, H, W = x.shape
+        y = np.empty((N, C, oH, oW), self.dtype)
+        self._fn("adaptive_avgpool_forward")(_p(x), _p(y), N * C, H, W, oH, oW)
+        return y
+
+    def adaptive_avgpool_backward(self, gy, H, W):
+        gy = _f(gy)
+        N, C, oH, oW = gy.shape
+        gx = np.empty((N, C, H, W), self.dtype)
+        self._fn("adaptive_avgpool_backward")(_p(gy), _p(gx), N * C, H, W, oH, oW)
+        return gx
+
     def slice_range(self, n, g, i):
         s, c = ctypes.c_long(), ctypes.c_long()
         self._fn("slice_range")(ctypes.c_long(n), g, i, ctypes.byref(s), ctypes.byref(c))

@@ -94,3 +94,21 @@ def test_avgpool_oracle_equals_reference_kernels(ref64, refk, case, include_pad)
     gx = ref64.avgpool_backward(gy, H, W, kH, kW, dH, dW, padH, padW, include_pad)
     gx_r = refk.avgpool_backward(gy, H, W, kH, kW, dH, dW, padH, padW, include_pad)
     _close(gx, gx_r)
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 7, 7, 3, 3), (1, 4, 10, 13, 4, 5), (2, 2, 8, 8, 8, 8), (1, 3, 5, 9, 7, 2), (3, 2, 14, 14, 1, 1),
+                                   (1, 2, 6, 6, 4, 4)])
+def test_adaptive_pooling_oracle_equals_reference_kernels(ref64, refk, shape):
+    # SpatialAdaptiveMaxPooling / SpatialAdaptiveAveragePooling: the reference's kernels (window bounds in float
+    # arithmetic, two index planes relative to the window start) run on the host, one emulated thread per block.
+    N, C, H, W, oH, oW = shape
+    rng = np.random.default_rng(abs(hash(shape)) % (2 ** 32))
+    x = rng.integers(-4, 5, (N, C, H, W)).astype(np.float32) * 0.25           # ties inside windows
+    y, ind = ref64.adaptive_maxpool_forward(x, oH, oW)
+    y_r, ind_r = refk.adaptive_maxpool_forward(x, oH, oW)
+    assert np.array_equal(y, y_r) and np.array_equal(ind, ind_r)
+    gy = rng.standard_normal(y.shape).astype(np.float32)
+    _close(ref64.adaptive_maxpool_backward(gy, ind, H, W), refk.adaptive_maxpool_backward(gy, ind_r, H, W))
+    x = rng.standard_normal((N, C, H, W)).astype(np.float32)
+    _close(ref64.adaptive_avgpool_forward(x, oH, oW), refk.adaptive_avgpool_forward(x, oH, oW))
+    _close(ref64.adaptive_avgpool_backward(gy, H, W), refk.adaptive_avgpool_backward(gy, H, W))
