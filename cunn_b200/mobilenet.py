@@ -145,7 +145,7 @@ class DataParallelStep:
         self._graphs = {}
         self._seen = set()
         self.table = None
-        if native and self.world > 1:
+        if native and self.world > 1 and replica.params.is_cuda:      # CPU stand-ins (gloo tests) keep the torch exchange
             from . import dpt
             dev = replica.params.device
             uid = torch.zeros(128, dtype=torch.uint8, device=dev)
