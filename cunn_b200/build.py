@@ -30,6 +30,16 @@ if os.environ.get("CUNN_B200_DEV_HOOKS"):      # sweep builds only: tuning switc
     FLAGS.append("-DCUNN_B200_DEV_HOOKS=1")
 
 
+# Build inside a cutorch tree: CUNN_B200_USE_REAL_THC=<directory holding THC/THC.h>[:<directory holding libTHC.so>]
+# makes the THNN layer use cutorch's own THCState / THCudaTensor and resolve its tensor calls in libTHC.
+LINK_EXTRA = []
+_thc = os.environ.get("CUNN_B200_USE_REAL_THC")
+if _thc:
+    inc, _, libdir = _thc.partition(":")
+    FLAGS += ["-DCUNN_B200_USE_REAL_THC=1", "-I", inc]
+    LINK_EXTRA = (["-L", libdir] if libdir else []) + ["-lTHC"]
+
+
 def _sources():
     return sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cpp")))
 
@@ -68,7 +78,7 @@ def build(force=False, verbose=False):
     with open(stamp, "w") as f:
         f.write(flags)
     if jobs or not os.path.exists(SO):
-        cmd = [NVCC, "-shared", "-ccbin", "/usr/bin/g++", "-o", SO] + objs + ["--cudart", "static", "-Xlinker", "--no-undefined"]
+        cmd = [NVCC, "-shared", "-ccbin", "/usr/bin/g++", "-o", SO] + objs + ["--cudart", "static", "-Xlinker", "--no-undefined"] + LINK_EXTRA
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode:
             sys.stderr.write(r.stdout + r.stderr)
