@@ -56,26 +56,52 @@ threshold_bwd_kernel(const float *x, const float *gy, float *gx, long long n, fl
     }
 }
 
-// Average pooling (lib/THCUNN/SpatialAveragePooling.cu:7-82): the divisor is the window clipped to
-// input + padding (count_include_pad) or to the input.
+// Average pooling.  The divisor rule is the reference's and has to be (lib/THCUNN/SpatialAveragePooling.cu:7-82): a
+// window is first clipped to input + padding, which gives the count_include_pad divisor, then to the input, which gives
+// the summed range and the other divisor.  Both kernels treat the two axes separately through Span1D, so the 2-D divisor
+// is a product of two per-axis extents; the backward pass is in gather form (one thread per input pixel, no atomics).
+struct Span1D {
+    int lo, hi;      // taps inside the input: [lo, hi)
+    int padded;      // taps inside input + padding
+};
+
+__device__ __forceinline__ Span1D window_span(int o, int k, int d, int pad, int size)
+{
+    const int start = o * d - pad;
+    const int stop = min(start + k, size + pad);
+    Span1D s;
+    s.padded = stop - start;
+    s.lo = max(start, 0);
+    s.hi = min(stop, size);
+    return s;
+}
+
+__device__ __forceinline__ float window_divisor(const Span1D &r, const Span1D &c, int include_pad)
+{
+    return (float)(include_pad ? r.padded * c.padded : (r.hi - r.lo) * (c.hi - c.lo));
+}
+
+// outputs whose window covers input coordinate i (already shifted by the padding): [first, last)
+__device__ __forceinline__ void covering_outputs(int i_padded, int k, int d, int osize, int &first, int &last)
+{
+    first = i_padded < k ? 0 : (i_padded - k) / d + 1;
+    last = min(i_padded / d + 1, osize);
+}
+
 __global__ void __launch_bounds__(256)
 avgpool_fwd_kernel(const float *__restrict__ x, float *__restrict__ y, int H, int W, int oH, int oW, int kH, int kW, int dH,
                    int dW, int padH, int padW, int include_pad, long long total)
 {
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
-        const int pw = (int)(idx % oW);
+        const int ow = (int)(idx % oW);
         const long long t = idx / oW;
-        const int ph = (int)(t % oH);
-        const long long plane = t / oH;
-        int hs = ph * dH - padH, ws = pw * dW - padW;
-        int he = min(hs + kH, H + padH), we = min(ws + kW, W + padW);
-        const int pool = (he - hs) * (we - ws);
-        hs = max(hs, 0); ws = max(ws, 0); he = min(he, H); we = min(we, W);
-        const float *xp = x + plane * (long long)H * W;
+        const int oh = (int)(t % oH);
+        const Span1D r = window_span(oh, kH, dH, padH, H), c = window_span(ow, kW, dW, padW, W);
+        const float *xp = x + (t / oH) * (long long)H * W;
         float s = 0.f;
-        for (int h = hs; h < he; ++h)
-            for (int w = ws; w < we; ++w) s += __ldg(xp + h * W + w);
-        y[idx] = s / (float)(include_pad ? pool : (he - hs) * (we - ws));
+        for (int h = r.lo; h < r.hi; ++h)
+            for (int w = c.lo; w < c.hi; ++w) s += __ldg(xp + h * W + w);
+        y[idx] = s / window_divisor(r, c, include_pad);
     }
 }
 
@@ -84,22 +110,17 @@ avgpool_bwd_kernel(const float *__restrict__ gy, float *__restrict__ gx, int H, 
                    int dH, int dW, int padH, int padW, int include_pad, long long total)
 {
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
-        const int w = (int)(idx % W) + padW;
         const long long t = idx / W;
-        const int h = (int)(t % H) + padH;
-        const long long plane = t / H;
-        const int phs = (h < kH) ? 0 : (h - kH) / dH + 1, phe = min(h / dH + 1, oH);
-        const int pws = (w < kW) ? 0 : (w - kW) / dW + 1, pwe = min(w / dW + 1, oW);
-        const float *gp = gy + plane * (long long)oH * oW;
+        int oh0, oh1, ow0, ow1;
+        covering_outputs((int)(t % H) + padH, kH, dH, oH, oh0, oh1);
+        covering_outputs((int)(idx % W) + padW, kW, dW, oW, ow0, ow1);
+        const float *gp = gy + (t / H) * (long long)oH * oW;
         float g = 0.f;
-        for (int ph = phs; ph < phe; ++ph)
-            for (int pw = pws; pw < pwe; ++pw) {
-                int hs = ph * dH - padH, ws = pw * dW - padW;
-                int he = min(hs + kH, H + padH), we = min(ws + kW, W + padW);
-                const int pool = (he - hs) * (we - ws);
-                hs = max(hs, 0); ws = max(ws, 0); he = min(he, H); we = min(we, W);
-                g += __ldg(gp + ph * oW + pw) / (float)(include_pad ? pool : (he - hs) * (we - ws));
-            }
+        for (int oh = oh0; oh < oh1; ++oh) {
+            const Span1D r = window_span(oh, kH, dH, padH, H);
+            for (int ow = ow0; ow < ow1; ++ow)
+                g += __ldg(gp + oh * oW + ow) / window_divisor(r, window_span(ow, kW, dW, padW, W), include_pad);
+        }
         gx[idx] = g;
     }
 }
