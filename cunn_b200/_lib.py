@@ -62,6 +62,8 @@ _decl("cunn_b200_maxpool_forward", c_int, [c_void_p] * 3 + [c_int] * 13 + [c_voi
 _decl("cunn_b200_maxpool_backward", c_int, [c_void_p] * 3 + [c_int] * 13 + [c_void_p])
 _decl("cunn_b200_batchnorm_workspace", c_size_t, [c_int, c_int])
 _decl("cunn_b200_batchnorm_counter_bytes", c_size_t, [])
+_decl("cunn_b200_convmm_set_tma", None, [c_int])
+_decl("cunn_b200_convmm_get_tma", c_int, [])
 _decl("cunn_b200_batchnorm_set_grouped", None, [c_int])
 _decl("cunn_b200_batchnorm_get_grouped", c_int, [])
 _decl("cunn_b200_batchnorm_forward", c_int, [c_void_p] * 8 + [c_int] * 4 + [c_double, c_double, c_void_p, c_size_t, c_void_p])

@@ -623,6 +623,7 @@ struct Params {
     int dilH, dilW;    // distance between kernel taps (SpatialDilatedConvolution; 1 for SpatialConvolutionMM)
     int nacc, sets;    // accumulators per tile (nacc - 1 for the hi*hi products, k-blocks round-robin, + 1 for the cross terms), accumulator sets in TMEM (1 or 2)
     int bulk_out;      // FWD/DGRAD: planes of >= 1024 pixels (a multiple of 4), 16-byte aligned output: the columns of a tile leave as bulk stores
+    int gpi;           // tensor-map kernels: groups of 32 pixels per image, ceil(HW / 32)
 };
 
 // 3xTF32 split of a raw fp32 tile in place.  The tensor core reads only the upper 19 bits of a tf32 operand,
@@ -1265,6 +1266,8 @@ pw_gemm_kernel(const Params p)
 
 }  // namespace pw
 
+#include "pw_tma.cuh"
+
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
@@ -1415,6 +1418,60 @@ static int pw_launch(PwKernel kern, pw::Params &p, cudaStream_t stream)
     return 0;
 }
 
+// ---- tensor-map kernels (pw_tma.cuh) -----------------------------------------------------------------------------
+static int g_use_tma = 1;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// The driver's encoder, looked up through the runtime so that the library does not link libcuda.
+static EncodeTiledFn encode_tiled()
+{
+    static EncodeTiledFn fn = [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            ptr = nullptr;
+        return (EncodeTiledFn)ptr;
+    }();
+    return fn;
+}
+// fp32 tensor [d2][d1][d0] (d0 contiguous; d2 = 0: two dimensions), boxes of box0 x box1 (x 1), zero fill outside.
+static int make_map(CUtensorMap *m, const float *base, long long d0, long long d1, long long d2, int box0, int box1, CUtensorMapSwizzle swz)
+{
+    const cuuint32_t rank = d2 ? 3 : 2;
+    cuuint64_t dims[3] = {(cuuint64_t)d0, (cuuint64_t)d1, (cuuint64_t)(d2 ? d2 : 1)};
+    cuuint64_t strides[2] = {(cuuint64_t)d0 * 4, (cuuint64_t)d0 * (cuuint64_t)d1 * 4};
+    cuuint32_t box[3] = {(cuuint32_t)box0, (cuuint32_t)box1, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = encode_tiled()(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, rank, (void *)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                      swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+static bool tma_applies(const void *a, const void *b, const void *c, int HW, int C)
+{
+    return g_use_tma && HW % 4 == 0 && C % 4 == 0 && aligned16(a) && aligned16(b) && aligned16(c) && encode_tiled() != nullptr;
+}
+typedef void (*PwTmaKernel)(const pw::Params, const CUtensorMap, const CUtensorMap);
+template <int OP>
+static PwTmaKernel pw_tma_pick(int bn)
+{
+    switch (bn) {
+        case 32: return pwt::pw_tma_kernel<OP, 32>;
+        case 64: return pwt::pw_tma_kernel<OP, 64>;
+        default: return pwt::pw_tma_kernel<OP, 128>;
+    }
+}
+static int pw_tma_launch(PwTmaKernel kern, pw::Params &p, CUtensorMap &ma, CUtensorMap &mb, cudaStream_t stream)
+{
+    const int grid = std::min(p.total_tiles, sm_count());
+    CUNN_CUDA(cudaFuncSetAttribute((const void *)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pw::SMEM));
+    void *args[] = {(void *)&p, (void *)&ma, (void *)&mb};
+    CUNN_CUDA(cudaLaunchKernel((const void *)kern, dim3(grid), dim3(pwt::TTHREADS), args, pw::SMEM, stream));
+    return 0;
+}
+
 // Splits of the image range for the weight gradient on the persistent kernel: every tile takes `imgs_per_split`
 // images.  Candidates are scored by (waves of the persistent grid) x (images per tile) — the time of the slowest
 // CTA — and tiles longer than ~128 k-blocks are avoided when a shorter choice exists (accumulation chains).
@@ -1464,6 +1521,15 @@ static int conv_forward(const float *x, const float *weight, const float *bias, 
         const int bn = pw_bn_for(K);
         q.n_tiles = ceil_div(K, bn); q.tiles_per_split = 0; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
         q.n_img = N; q.imgs_per_split = N; q.splits = 1;
+        if (tma_applies(x, weight, y, q.HW, C)) {
+            alignas(64) CUtensorMap ma, mb;
+            q.gpi = ceil_div(q.HW, 32); q.M_total = N * q.gpi * 32; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
+            q.bulk_out = (q.HW % 32 == 0) && q.HW >= 8 * BM;
+            pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
+            if (make_map(&ma, x, q.HW, C, N, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return 1;
+            if (make_map(&mb, weight, C, K, 0, 32, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return 1;
+            return pw_tma_launch(pw_tma_pick<OP_FWD>(bn), q, ma, mb, stream);
+        }
         q.vec_a = (q.HW % 4 == 0) && aligned16(x); q.vec_b = (C % 4 == 0) && aligned16(weight);
         q.bulk_out = (q.HW % 4 == 0) && q.HW >= 8 * BM && aligned16(y);
         pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
@@ -1510,6 +1576,15 @@ static int conv_grad_input(const float *gy, const float *weight, float *gx, int 
         const int bn = pw_bn_for(C);
         q.n_tiles = ceil_div(C, bn); q.tiles_per_split = 0; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
         q.n_img = N; q.imgs_per_split = N; q.splits = 1;
+        if (tma_applies(gy, weight, gx, q.HW, C)) {
+            alignas(64) CUtensorMap ma, mb;
+            q.gpi = ceil_div(q.HW, 32); q.M_total = N * q.gpi * 32; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
+            q.bulk_out = (q.HW % 32 == 0) && q.HW >= 8 * BM;
+            pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
+            if (make_map(&ma, gy, q.HW, K, N, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return 1;
+            if (make_map(&mb, weight, C, K, 0, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return 1;
+            return pw_tma_launch(pw_tma_pick<OP_DGRAD>(bn), q, ma, mb, stream);
+        }
         q.vec_a = (q.HW % 4 == 0) && aligned16(gy); q.vec_b = (C % 4 == 0) && aligned16(weight);
         q.bulk_out = (q.HW % 4 == 0) && q.HW >= 8 * BM && aligned16(gx);
         pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
@@ -1606,8 +1681,17 @@ static int conv_acc_grad(const float *x, const float *gy, float *grad_weight, fl
         q.n_tiles = ceil_div(C, bn); q.tiles_per_split = ceil_div(K, BM) * q.n_tiles; q.total_tiles = q.tiles_per_split * splits;
         q.n_img = N; q.imgs_per_split = ips; q.splits = splits;
         q.vec_a = (q.HW % 4 == 0) && aligned16(gy); q.vec_b = (q.HW % 4 == 0) && aligned16(x);
+        if (tma_applies(gy, x, workspace, q.HW, 4)) {
+            alignas(64) CUtensorMap ma, mb;
+            q.gpi = ceil_div(q.HW, 32); q.kblocks = ips * q.gpi;
+            pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets, true);
+            if (make_map(&ma, gy, q.HW, K, N, 32, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return 1;
+            if (make_map(&mb, x, q.HW, C, N, 32, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return 1;
+            if (pw_tma_launch(pw_tma_pick<OP_WGRAD>(bn), q, ma, mb, stream)) return 1;
+        } else {
         pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets, true);
         if (pw_launch(pw_pick<OP_WGRAD>(bn), q, stream)) return 1;
+        }
         const int rblocks = (int)std::max(1LL, std::min(ceil_div_ll(n + K, 256), (long long)sm_count() * 8));
         wgrad_bias_reduce_kernel<<<rblocks, 256, 0, stream>>>((const float *)workspace, grad_weight, n, splits, scale, q.bias_part, grad_bias, K);
         CUNN_LAUNCH_CHECK("convmm acc grad reduce");
@@ -1656,6 +1740,9 @@ static int conv_acc_grad(const float *x, const float *gy, float *grad_weight, fl
     }
     return 0;
 }
+
+extern "C" CUNN_API void cunn_b200_convmm_set_tma(int on) { cunn::mm::g_use_tma = on ? 1 : 0; }
+extern "C" CUNN_API int cunn_b200_convmm_get_tma(void) { return cunn::mm::g_use_tma; }
 
 extern "C" CUNN_API int cunn_b200_convmm_forward(const float *x, const float *weight, const float *bias, float *y, int N,
                                                  int C, int H, int W, int K, int kH, int kW, int dH, int dW, int padH,

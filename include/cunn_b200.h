@@ -123,6 +123,13 @@ CUNN_API int cunn_b200_convmm_acc_grad(const float *x, const float *gy, float *g
                                        int dH, int dW, int padH, int padW, float scale,
                                        void *workspace, size_t workspace_bytes, cunn_stream_t stream);
 
+/* 1x1 stride-1 convolutions on 16-byte aligned tensors with H*W and C multiples of 4 fetch their operand tiles with
+ * tensor-map (TMA) copies; everything else, and every shape after cunn_b200_convmm_set_tma(0), uses the element-copy
+ * loader.  Results are identical; the switch exists so that both loaders can be tested and timed.  No reference
+ * counterpart. */
+CUNN_API void cunn_b200_convmm_set_tma(int on);
+CUNN_API int cunn_b200_convmm_get_tma(void);
+
 /* ---- SpatialDilatedConvolution -------------------------------------------------
  * The same three passes with the kernel taps dilH x dilW apart: output size
  * (in + 2 pad - (dil (k - 1) + 1)) / stride + 1 (lib/THCUNN/generic/SpatialDilatedConvolution.cu:49-50).

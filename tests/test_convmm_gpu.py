@@ -105,6 +105,34 @@ def test_convmm_shapes(F, ref64, shape):
     check_against_oracle(ref64, F, *case, d, pad, 0.75)
 
 
+@pytest.fixture(params=[1, 0], ids=["tma", "element-copy"])
+def pointwise_loader(request):
+    """1x1 convolutions have two operand loaders: tensor-map copies (aligned tensors) and element copies."""
+    from cunn_b200._lib import lib
+    lib.cunn_b200_convmm_set_tma(request.param)
+    yield request.param
+    lib.cunn_b200_convmm_set_tma(1)
+
+
+@pytest.mark.parametrize("shape", [
+    # N, C, H, W, K, bias
+    (3, 64, 14, 14, 256, True),      # 196-pixel planes: 7 groups of 32, the last one 4 pixels wide; two column tiles
+    (5, 96, 14, 14, 40, False),      # row tiles that end inside an image and past the last image; K < 64
+    (2, 32, 28, 28, 64, True),       # 784 pixels: 24.5 groups
+    (3, 32, 56, 56, 64, True),       # 3136 = 98 x 32 pixels: bulk-store epilogue, one k-block
+    (2, 256, 32, 32, 200, True),     # 1024-pixel planes, 8 k-blocks, ragged column tile
+    (16, 128, 28, 28, 128, True),    # four k-blocks, two accumulator sets, several tiles per CTA
+    (4, 1024, 14, 14, 256, False),   # long reduction: four accumulators, one set
+    (6, 100, 6, 6, 20, True),        # 36-pixel planes (2 groups per image), C not a multiple of 32
+    (2, 36, 2, 2, 24, True),         # 4-pixel planes
+    (130, 64, 2, 4, 32, True),       # many tiny images: more groups than one wave of row tiles
+])
+def test_convmm_pointwise_both_loaders(F, ref64, shape, pointwise_loader):
+    N, C, H, W, K, bias = shape
+    case = make_case(abs(hash(shape)) % 99991, N, C, H, W, K, 1, 1, 0, bias)
+    check_against_oracle(ref64, F, *case, 1, 0, 0.75)
+
+
 def test_convmm_depthwise_equivalence(F):
     # The reference's own depthwise test (test.lua:6602-6661): depthwise forward == per-channel
     # SpatialConvolution(1, m, 3,3,1,1,1,1) on weight[:, c] / bias[:, c]; n=3, m=4, 28x28, batch 3, within 1e-5.
