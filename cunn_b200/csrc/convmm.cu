@@ -1453,22 +1453,47 @@ static bool tma_applies(const void *a, const void *b, const void *c, int HW, int
 {
     return g_use_tma && HW % 4 == 0 && C % 4 == 0 && aligned16(a) && aligned16(b) && aligned16(c) && encode_tiled() != nullptr;
 }
-typedef void (*PwTmaKernel)(const pw::Params, const CUtensorMap, const CUtensorMap);
-template <int OP>
-static PwTmaKernel pw_tma_pick(int bn)
+// Accumulator plan of the tensor-map kernels: tiles of one or two k-blocks put all products into one accumulator and
+// use up to four accumulator sets, so that the MMA warp runs several tiles ahead of the epilogue warps; longer tiles
+// follow pw_accumulators.
+static void tma_accumulators(int bn, int kblocks, int *nacc, int *sets, bool wgrad = false)
 {
+    const int cols = std::max(bn, 32);
+    if (kblocks <= 2) {
+        *nacc = 1;
+        *sets = std::min((int)pwt::MAX_SETS, 512 / cols);
+        return;
+    }
+    pw_accumulators(bn, kblocks, nacc, sets, wgrad);
+}
+typedef void (*PwTmaKernel)(const pw::Params, const CUtensorMap, const CUtensorMap, const CUtensorMap);
+// Tiles of up to four k-blocks: 4 splitter + 8 epilogue warps; longer tiles: 8 + 4.
+template <int OP>
+static PwTmaKernel pw_tma_pick(int bn, int kblocks)
+{
+    if (kblocks <= 4) {
+        switch (bn) {
+            case 32: return pwt::pw_tma_kernel<OP, 32, 4>;
+            case 64: return pwt::pw_tma_kernel<OP, 64, 4>;
+            default: return pwt::pw_tma_kernel<OP, 128, 4>;
+        }
+    }
     switch (bn) {
-        case 32: return pwt::pw_tma_kernel<OP, 32>;
-        case 64: return pwt::pw_tma_kernel<OP, 64>;
-        default: return pwt::pw_tma_kernel<OP, 128>;
+        case 32: return pwt::pw_tma_kernel<OP, 32, 8>;
+        case 64: return pwt::pw_tma_kernel<OP, 64, 8>;
+        default: return pwt::pw_tma_kernel<OP, 128, 8>;
     }
 }
-static int pw_tma_launch(PwTmaKernel kern, pw::Params &p, CUtensorMap &ma, CUtensorMap &mb, cudaStream_t stream)
+// `mo` is the map of the output tensor for the bulk-store epilogue (forward / input gradient); kernels that do not use
+// it get a copy of `ma`.
+static int pw_tma_launch(PwTmaKernel kern, pw::Params &p, CUtensorMap &ma, CUtensorMap &mb, CUtensorMap &mo, cudaStream_t stream)
 {
     const int grid = std::min(p.total_tiles, sm_count());
-    CUNN_CUDA(cudaFuncSetAttribute((const void *)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pw::SMEM));
-    void *args[] = {(void *)&p, (void *)&ma, (void *)&mb};
-    CUNN_CUDA(cudaLaunchKernel((const void *)kern, dim3(grid), dim3(pwt::TTHREADS), args, pw::SMEM, stream));
+    const size_t smem_bytes = pw::SMEM;
+    const int threads = pwt::TTHREADS;
+    CUNN_CUDA(cudaFuncSetAttribute((const void *)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    void *args[] = {(void *)&p, (void *)&ma, (void *)&mb, (void *)&mo};
+    CUNN_CUDA(cudaLaunchKernel((const void *)kern, dim3(grid), dim3(threads), args, smem_bytes, stream));
     return 0;
 }
 
@@ -1522,13 +1547,15 @@ static int conv_forward(const float *x, const float *weight, const float *bias, 
         q.n_tiles = ceil_div(K, bn); q.tiles_per_split = 0; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
         q.n_img = N; q.imgs_per_split = N; q.splits = 1;
         if (tma_applies(x, weight, y, q.HW, C)) {
-            alignas(64) CUtensorMap ma, mb;
+            alignas(64) CUtensorMap ma, mb, mo;
             q.gpi = ceil_div(q.HW, 32); q.M_total = N * q.gpi * 32; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
             q.bulk_out = (q.HW % 32 == 0) && q.HW >= 8 * BM;
-            pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
+            tma_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
             if (make_map(&ma, x, q.HW, C, N, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return 1;
             if (make_map(&mb, weight, C, K, 0, 32, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return 1;
-            return pw_tma_launch(pw_tma_pick<OP_FWD>(bn), q, ma, mb, stream);
+            if (q.bulk_out) { if (make_map(&mo, y, q.HW, K, N, BM, pwt::HALF_STAGE_COLS, CU_TENSOR_MAP_SWIZZLE_NONE)) return 1; }
+            else mo = ma;
+            return pw_tma_launch(pw_tma_pick<OP_FWD>(bn, q.kblocks), q, ma, mb, mo, stream);
         }
         q.vec_a = (q.HW % 4 == 0) && aligned16(x); q.vec_b = (C % 4 == 0) && aligned16(weight);
         q.bulk_out = (q.HW % 4 == 0) && q.HW >= 8 * BM && aligned16(y);
@@ -1577,13 +1604,15 @@ static int conv_grad_input(const float *gy, const float *weight, float *gx, int 
         q.n_tiles = ceil_div(C, bn); q.tiles_per_split = 0; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
         q.n_img = N; q.imgs_per_split = N; q.splits = 1;
         if (tma_applies(gy, weight, gx, q.HW, C)) {
-            alignas(64) CUtensorMap ma, mb;
+            alignas(64) CUtensorMap ma, mb, mo;
             q.gpi = ceil_div(q.HW, 32); q.M_total = N * q.gpi * 32; q.total_tiles = ceil_div(q.M_total, BM) * q.n_tiles;
             q.bulk_out = (q.HW % 32 == 0) && q.HW >= 8 * BM;
-            pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
+            tma_accumulators(bn, q.kblocks, &q.nacc, &q.sets);
             if (make_map(&ma, gy, q.HW, K, N, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return 1;
             if (make_map(&mb, weight, C, K, 0, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return 1;
-            return pw_tma_launch(pw_tma_pick<OP_DGRAD>(bn), q, ma, mb, stream);
+            if (q.bulk_out) { if (make_map(&mo, gx, q.HW, C, N, BM, pwt::HALF_STAGE_COLS, CU_TENSOR_MAP_SWIZZLE_NONE)) return 1; }
+            else mo = ma;
+            return pw_tma_launch(pw_tma_pick<OP_DGRAD>(bn, q.kblocks), q, ma, mb, mo, stream);
         }
         q.vec_a = (q.HW % 4 == 0) && aligned16(gy); q.vec_b = (C % 4 == 0) && aligned16(weight);
         q.bulk_out = (q.HW % 4 == 0) && q.HW >= 8 * BM && aligned16(gx);
@@ -1684,10 +1713,10 @@ static int conv_acc_grad(const float *x, const float *gy, float *grad_weight, fl
         if (tma_applies(gy, x, workspace, q.HW, 4)) {
             alignas(64) CUtensorMap ma, mb;
             q.gpi = ceil_div(q.HW, 32); q.kblocks = ips * q.gpi;
-            pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets, true);
+            tma_accumulators(bn, q.kblocks, &q.nacc, &q.sets, true);
             if (make_map(&ma, gy, q.HW, K, N, 32, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return 1;
             if (make_map(&mb, x, q.HW, C, N, 32, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return 1;
-            if (pw_tma_launch(pw_tma_pick<OP_WGRAD>(bn), q, ma, mb, stream)) return 1;
+            if (pw_tma_launch(pw_tma_pick<OP_WGRAD>(bn, q.kblocks), q, ma, mb, ma, stream)) return 1;
         } else {
         pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets, true);
         if (pw_launch(pw_pick<OP_WGRAD>(bn), q, stream)) return 1;

@@ -1,9 +1,10 @@
 // Pointwise (1x1, stride 1, no padding) convolution GEMMs whose operand tiles are fetched by the TMA unit.
 //
-// Same roles, tiles, 3xTF32 scheme, accumulator plan and epilogue as pw::pw_gemm_kernel (convmm.cu); what differs is
-// how the raw fp32 tiles reach shared memory.  There 16 producer warps issue element copies; here ONE thread issues
+// Same roles, tiles and 3xTF32 scheme as pw::pw_gemm_kernel (convmm.cu); what differs is how the raw fp32 tiles reach
+// shared memory and how the warps are divided.  There 16 producer warps issue element copies; here ONE thread issues
 // tensor-map copies (cp.async.bulk.tensor, no multicast) that land the tiles directly in the layouts the tensor core
-// reads, and the 16 warps only derive the lo tiles (an element-wise map over the 16 KB tile: lo = v - tf32(v)).
+// reads, 4 or 8 warps derive the lo tiles (an element-wise map over the 16 KB tile: lo = v - tf32(v)), one warp issues the
+// MMAs and 8 or 4 warps drain accumulators, up to four accumulator sets ahead for tiles of one or two k-blocks.
 //
 //   K-major operand (weights of the forward pass; both operands of the weight gradient, whose reduction runs over
 //   pixels): one box of 32 k values x rows, 128-byte rows, hardware 128-byte swizzle = piece_offset().
@@ -27,13 +28,19 @@ namespace pwt {
 
 using namespace pw;
 
-constexpr int SPLITTERS = 512;                                   // threads that derive the lo tiles (16 warps)
-constexpr int MMA_WARP = SPLITTERS / 32;                         // one warp that only issues MMAs
-constexpr int EPI_WARP0 = MMA_WARP + 1;                          // four epilogue warps
-constexpr int TMA_WARP = EPI_WARP0 + EPILOGUE_WARPS;             // one warp whose lane 0 issues the tensor-map copies
-constexpr int TTHREADS = (TMA_WARP + 1) * 32;                    // 704
+// The 12 worker warps are divided between splitting and draining per launch (template arguments SW + EW = 12, both
+// multiples of 4): tiles of few k-blocks spend their time in the epilogue (SW = 4, EW = 8: two epilogue warps per TMEM
+// lane quarter, each half of the columns), long tiles in the split (SW = 8, EW = 4).  Warps: [0, SW) splitters,
+// [SW, 12) epilogue, 12 MMA issue, 13 copy issue.
+constexpr int WORKER_WARPS = 12;
+constexpr int MMA_WARP = WORKER_WARPS;                           // one warp that only issues MMAs
+constexpr int TMA_WARP = MMA_WARP + 1;                           // one warp whose lane 0 issues the tensor-map copies
+constexpr int TTHREADS = (TMA_WARP + 1) * 32;                    // 448: 14 warps, register file shared as 16
+constexpr int MAX_SETS = 4;                                      // accumulator sets in TMEM the MMA warp may run ahead by
+constexpr int HALF_STAGE_COLS = 32;                              // bulk-store epilogue: columns one half of the warps stages at a time
 constexpr int GROUP_BYTES = 32 * 128;                            // one M/N-major group: 32 positions x 32 k values
 constexpr int MN_KSTEP = 512;                                    // M/N-major: bytes from 4 k values to the next 4 inside a group
+static_assert(2 * HALF_STAGE_COLS * BM * 4 == (int)OUT_STAGE, "the two halves share the output staging area");
 
 __device__ __forceinline__ uint64_t desc_mn_grouped(uint32_t addr) { return desc_of(addr, GROUP_BYTES, MN_KSTEP) | (1ull << 61); }
 
@@ -47,11 +54,161 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                  ::"r"(dst), "l"((uint64_t)map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * EPILOGUE_WARPS) : "memory"); }
+// Tensor-map store shared -> global of one box (dense rows in shared memory); joins the thread's bulk group.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int x, int y, int z)
+{
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"((uint64_t)map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+}
+// Barrier among the four epilogue warps of one column half (hardware barriers 1 and 2).
+__device__ __forceinline__ void half_sync(int half)
+{
+    if (half == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+    else asm volatile("bar.sync 2, 128;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-template <int OP, int BN>
+// Sum over the tile's accumulators of 16 columns starting at TMEM address `t0` (+ a * acc_cols), on top of `acc`.
+// Accumulators are read two at a time so that two loads are in flight per wait.
+__device__ __forceinline__ void gather_acc16(float (&acc)[16], uint32_t t0, int nhi_used, int nacc, int acc_cols)
+{
+    const int n = nhi_used + 1;                                   // the hi accumulators that were used, then the lo one
+    for (int a2 = 0; a2 < n; a2 += 2) {
+        const int a = a2 < nhi_used ? a2 : nacc - 1;
+        uint32_t r0[16], r1[16];
+        tmem_ld16_issue(t0 + (uint32_t)(a * acc_cols), r0);
+        const bool two = a2 + 1 < n;
+        if (two) {
+            const int b = a2 + 1 < nhi_used ? a2 + 1 : nacc - 1;
+            tmem_ld16_issue(t0 + (uint32_t)(b * acc_cols), r1);
+        }
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j] += __uint_as_float(r0[j]);
+        if (two) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] += __uint_as_float(r1[j]);
+        }
+    }
+}
+
+// Epilogue of one tile for one epilogue warp: sums the tile's accumulators (TMEM address `tset`: first column of the
+// accumulator set), adds the bias and writes the warp's 32 rows (TMEM lane quarter `quarter`) x its half of the columns.
+// `el` is the thread's index inside its half (0 .. 127), `stage_base` the 32 KB output staging area in shared memory.
+template <int OP, int BN, int HALVES>
+__device__ __forceinline__ void drain_tile(const Params &p, const CUtensorMap &map_out, float *stage_base, uint32_t tset, int t, int nhi_used,
+                                           int quarter, int half, int lane, int el)
+{
+    constexpr int ACC_COLS = BN < 32 ? 32 : BN;
+    constexpr int HALF_COLS = BN / HALVES;
+    const int row = quarter * 32 + lane;
+    const int col_lo = half * HALF_COLS, col_hi = col_lo + HALF_COLS;
+    const uint32_t tsrc = tset + ((uint32_t)(quarter * 32) << 16);
+    int n_tile0;
+    size_t dst_off = 0;
+    bool row_ok, done = false;
+    if (OP != OP_WGRAD) {
+        const int m_tile = t / p.n_tiles, n_tile = t - m_tile * p.n_tiles;
+        n_tile0 = n_tile * BN;
+        const int g = m_tile * 4 + quarter, im = g / p.gpi, pix = (g - im * p.gpi) * 32 + lane;
+        row_ok = im < p.n_img && pix < p.HW;
+        dst_off = ((size_t)im * p.N_total + n_tile0) * p.HW + pix;
+        if (p.bulk_out && (m_tile + 1) * BM <= p.n_img * p.HW) {
+            // planes of a multiple of 32 (and >= 1024) pixels: rows are flat pixel indices; each half stages 32 columns x
+            // 128 pixels at a time and the TMA unit writes every column's 512-byte run (two runs across an image boundary)
+            float *stage = stage_base + half * HALF_STAGE_COLS * BM;
+            const int m_tile0 = m_tile * BM;
+            const int im0 = m_tile0 / p.HW, pix0 = m_tile0 - im0 * p.HW;
+            const int len0 = min(BM, p.HW - pix0);
+#pragma unroll 1
+            for (int cbase = col_lo; cbase < col_hi; cbase += HALF_STAGE_COLS) {
+                bulk_wait_read_all();                        // this thread's earlier bulk stores have left the buffer
+                half_sync(half);
+#pragma unroll 1
+                for (int c0 = cbase; c0 < cbase + HALF_STAGE_COLS && c0 < col_hi; c0 += 16) {
+                    float acc[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[j] = (OP == OP_FWD && p.bias && n_tile0 + c0 + j < p.N_total) ? __ldg(p.bias + n_tile0 + c0 + j) : 0.f;
+                    gather_acc16(acc, tsrc + (uint32_t)c0, nhi_used, p.nacc, ACC_COLS);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) stage[(c0 - cbase + j) * BM + row] = acc[j];
+                }
+                fence_async_smem();
+                half_sync(half);
+                if (len0 == BM && HALF_COLS >= HALF_STAGE_COLS) {
+                    // the tile lies inside one image: one tensor-map store writes the 128 pixels x 32 columns staged
+                    // by this half (columns past the last output channel are clipped by the map's bounds)
+                    if (el == 0) {
+                        tma_store_3d(&map_out, smem_u32(stage), pix0, n_tile0 + cbase, im0);
+                        bulk_commit();
+                    }
+                    continue;
+                }
+                const int col = cbase + el, n = n_tile0 + col;
+                if (el < HALF_STAGE_COLS && col < col_hi && n < p.N_total) {
+                    const uint32_t src = smem_u32(stage + el * BM);
+                    float *dst = p.out + ((size_t)im0 * p.N_total + n) * p.HW + pix0;
+                    bulk_s2g_nocommit(dst, src, (uint32_t)len0 * 4u);
+                    if (len0 < BM) bulk_s2g_nocommit(p.out + ((size_t)(im0 + 1) * p.N_total + n) * p.HW, src + (uint32_t)len0 * 4u, (uint32_t)(BM - len0) * 4u);
+                    bulk_commit();
+                }
+            }
+            done = true;
+        }
+    } else {
+        const int split = t / p.tiles_per_split, r2 = t - split * p.tiles_per_split;
+        const int m_tile = r2 / p.n_tiles, n_tile = r2 - m_tile * p.n_tiles;
+        const int m = m_tile * BM + row;
+        n_tile0 = n_tile * BN;
+        row_ok = m < p.M_total;
+        dst_off = ((size_t)split * p.M_total + m) * p.N_total + n_tile0;
+    }
+    if (!done) {
+#pragma unroll 1
+        for (int c0 = col_lo; c0 < col_hi; c0 += 16) {
+            float acc[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                acc[j] = (OP == OP_FWD && p.bias && n_tile0 + c0 + j < p.N_total) ? __ldg(p.bias + n_tile0 + c0 + j) : 0.f;
+            gather_acc16(acc, tsrc + (uint32_t)c0, nhi_used, p.nacc, ACC_COLS);
+            if (row_ok) {
+                const int n0 = n_tile0 + c0;
+                if (OP != OP_WGRAD) {
+                    float *dst = p.out + dst_off + (size_t)c0 * p.HW;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (n0 + j < p.N_total) dst[(size_t)j * p.HW] = acc[j];
+                } else {
+                    float *dst = p.out + dst_off + c0;
+                    if ((p.N_total & 3) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4)
+                            if (n0 + j < p.N_total) *reinterpret_cast<float4 *>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (n0 + j < p.N_total) dst[j] = acc[j];
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <int OP, int BN, int SW>
 __global__ void __launch_bounds__(TTHREADS, 1)
-pw_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b)
+pw_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+              const __grid_constant__ CUtensorMap map_out)
 {
     constexpr bool A_MN = OP != OP_WGRAD;
     constexpr bool B_MN = OP == OP_DGRAD;
@@ -60,19 +217,29 @@ pw_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_a, const _
     constexpr uint32_t idesc = idesc_of(BN, A_MN, B_MN);
     constexpr uint32_t A_BYTES = TILE;                           // 128 rows (or 4 groups) x 32 k values
     constexpr uint32_t B_BYTES = (uint32_t)BN * 128u;
+    constexpr int EW = WORKER_WARPS - SW;                        // epilogue warps: 4 (each all columns) or 8 (two column halves)
+    constexpr int SPLITTERS = SW * 32;
+    constexpr int SPLIT_PIECES = TILE / 16 / SPLITTERS;          // 16-byte pieces of a tile per splitter thread
+    static_assert((SW == 4 || SW == 8) && SPLIT_PIECES % 4 == 0, "splitter warps");
 
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ uint64_t bars[RAW_STAGES + 2];   // MMAs of this stage done; then accumulators of set 0 / 1 ready
+    __shared__ uint64_t mmadone[RAW_STAGES];    // the MMAs that read this raw stage have finished: the TMA unit may refill it
+    __shared__ uint64_t lodone[LO_BUFS];         // the MMAs that read this lo buffer have finished: the splitters may rewrite it
+    __shared__ uint64_t accready[MAX_SETS];     // all MMAs of a tile have finished: its accumulator set can be read
+    __shared__ uint64_t accfree[MAX_SETS];      // accumulator set drained: one arrival per epilogue warp
     __shared__ uint64_t rawfull[RAW_STAGES];    // the stage's raw tiles have landed (transaction bytes)
     __shared__ uint64_t full[RAW_STAGES];       // lo tiles written and visible to the tensor core: one arrival per splitter warp
-    __shared__ uint64_t accfree[2];
     __shared__ uint32_t tmem_base_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int s = 0; s < RAW_STAGES + 2; ++s) mbar_init(smem_u32(bars + s), 1);
-        for (int s = 0; s < RAW_STAGES; ++s) { mbar_init(smem_u32(rawfull + s), 1); mbar_init(smem_u32(full + s), SPLITTERS / 32); }
-        for (int s = 0; s < 2; ++s) mbar_init(smem_u32(accfree + s), EPILOGUE_WARPS);
+        for (int s = 0; s < RAW_STAGES; ++s) {
+            mbar_init(smem_u32(mmadone + s), 1);
+            mbar_init(smem_u32(rawfull + s), 1);
+            mbar_init(smem_u32(full + s), SW);
+        }
+        for (int s = 0; s < LO_BUFS; ++s) mbar_init(smem_u32(lodone + s), 1);
+        for (int s = 0; s < MAX_SETS; ++s) { mbar_init(smem_u32(accready + s), 1); mbar_init(smem_u32(accfree + s), EW); }
         mbar_fence_init();
     }
     if (warp == 0) tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
@@ -82,20 +249,24 @@ pw_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_a, const _
     const uint32_t tmem_base = tmem_base_s;
 
     const int KB = p.kblocks;
+    constexpr int NS = RAW_STAGES, NL = LO_BUFS;                 // 4 raw stages + 2 lo buffers of 32 KB + the output staging area
     const int my_tiles = ((int)blockIdx.x < p.total_tiles) ? (p.total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
     const int total_it = my_tiles * KB;
-    const int nhi_used = KB < p.nacc - 1 ? KB : p.nacc - 1;
+    // nacc == 1: all three products of every k-block go to one accumulator (tiles of one or two k-blocks, whose chains are
+    // short anyway); otherwise the hi*hi products are dealt round-robin to nacc - 1 accumulators and the cross terms share the last
+    const int nhi = p.nacc - 1;
+    const int nhi_used = KB < nhi ? KB : nhi;
     const uint32_t set_cols = (uint32_t)(p.nacc * ACC_COLS);
-    unsigned char *const lo_base = smem + (size_t)RAW_STAGES * 2 * TILE;
+    unsigned char *const lo_base = smem + (size_t)NS * 2 * TILE;
     bool ok = true;
 
     if (warp == TMA_WARP) {
-        // ---- copy issue: k-block i goes to raw stage i % RAW_STAGES as soon as the MMAs that read it last are done ----
+        // ---- copy issue: k-block i goes to raw stage i % NS as soon as the MMAs that read it last are done ----
         if (lane == 0) {
             int t = (int)blockIdx.x, kb = 0;
             for (int i = 0; i < total_it; ++i) {
-                const int rs = i % RAW_STAGES;
-                if (i >= RAW_STAGES && !mbar_wait(smem_u32(bars + rs), (uint32_t)((i / RAW_STAGES - 1) & 1), p.status)) break;
+                const int rs = i % NS;
+                if (i >= NS && !mbar_wait(smem_u32(mmadone + rs), (uint32_t)((i / NS - 1) & 1), p.status)) break;
                 const uint32_t bar = smem_u32(rawfull + rs);
                 const uint32_t sa = smem_u32(smem + (size_t)rs * 2 * TILE), sb = sa + TILE;
                 mbar_arrive_expect_tx(bar, A_BYTES + B_BYTES);
@@ -125,189 +296,104 @@ pw_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_a, const _
     } else if (warp == MMA_WARP) {
         int kb = 0, count = 0;
         for (int i = 0; i < total_it; ++i) {
-            const int rs = i % RAW_STAGES, lb = i % LO_BUFS;
-            if (!mbar_wait(smem_u32(full + rs), (uint32_t)((i / RAW_STAGES) & 1), p.status)) { ok = false; break; }
-            if (kb == 0 && count >= p.sets) {
-                const int set = (p.sets == 2) ? (count & 1) : 0;
-                const int use = (p.sets == 2) ? (count >> 1) : count;
+            const int rs = i % NS, lb = i % NL;
+            const int set = count % p.sets, use = count / p.sets;
+            if (!mbar_wait(smem_u32(full + rs), (uint32_t)((i / NS) & 1), p.status)) { ok = false; break; }
+            if (kb == 0 && use > 0) {
+                // the epilogue warps must have drained the tile that used this accumulator set before
                 if (!mbar_wait(smem_u32(accfree + set), (uint32_t)((use - 1) & 1), p.status)) { ok = false; break; }
             }
             if (lane == 0) {
                 tc_fence_after();
-                const int set = (p.sets == 2) ? (count & 1) : 0;
                 const uint32_t acc0 = tmem_base + (uint32_t)set * set_cols;
-                const int nhi = p.nacc - 1;
-                const uint32_t d_hi = acc0 + (uint32_t)((kb % nhi) * ACC_COLS), d_lo = acc0 + (uint32_t)(nhi * ACC_COLS);
-                const bool first_hi = kb < nhi, first_lo = kb == 0;
+                const uint32_t d_hi = acc0 + (uint32_t)((nhi ? kb % nhi : 0) * ACC_COLS), d_lo = acc0 + (uint32_t)(nhi * ACC_COLS);
+                const bool first_hi = nhi && kb < nhi, first_lo = kb == 0;
                 const uint32_t sa_hi = smem_u32(smem + (size_t)rs * 2 * TILE), sb_hi = sa_hi + TILE;
                 const uint32_t sa_lo = smem_u32(lo_base + (size_t)lb * 2 * TILE), sb_lo = sa_lo + TILE;
 #pragma unroll
                 for (int j = 0; j < BK / 8; ++j) {
-                    const uint32_t ao = A_MN ? (uint32_t)(j * 2 * MN_KSTEP) : (uint32_t)(j * 32);
                     const uint32_t bo = B_MN ? (uint32_t)(j * 2 * MN_KSTEP) : (uint32_t)(j * 32);
-                    const uint64_t ah = A_MN ? desc_mn_grouped(sa_hi + ao) : smem_desc(sa_hi + ao);
-                    const uint64_t al = A_MN ? desc_mn_grouped(sa_lo + ao) : smem_desc(sa_lo + ao);
                     const uint64_t bh = B_MN ? desc_mn_grouped(sb_hi + bo) : smem_desc(sb_hi + bo);
                     const uint64_t bl = B_MN ? desc_mn_grouped(sb_lo + bo) : smem_desc(sb_lo + bo);
-                    umma_tf32(d_lo, al, bh, idesc, (first_lo && j == 0) ? 0u : 1u);
-                    umma_tf32(d_lo, ah, bl, idesc, 1u);
-                    umma_tf32(d_hi, ah, bh, idesc, (first_hi && j == 0) ? 0u : 1u);
+                        const uint32_t ao = A_MN ? (uint32_t)(j * 2 * MN_KSTEP) : (uint32_t)(j * 32);
+                        const uint64_t ah = A_MN ? desc_mn_grouped(sa_hi + ao) : smem_desc(sa_hi + ao);
+                        const uint64_t al = A_MN ? desc_mn_grouped(sa_lo + ao) : smem_desc(sa_lo + ao);
+                        umma_tf32(d_lo, al, bh, idesc, (first_lo && j == 0) ? 0u : 1u);
+                        umma_tf32(d_lo, ah, bl, idesc, 1u);
+                        umma_tf32(d_hi, ah, bh, idesc, (first_hi && j == 0) ? 0u : 1u);
                 }
-                umma_commit(smem_u32(bars + rs));
-                if (kb == KB - 1) umma_commit(smem_u32(bars + RAW_STAGES + set));
+                umma_commit(smem_u32(mmadone + rs));
+                umma_commit(smem_u32(lodone + lb));
+                if (kb == KB - 1) umma_commit(smem_u32(accready + set));
             }
             __syncwarp();
             if (++kb == KB) { kb = 0; ++count; }
         }
-    } else if (warp >= EPI_WARP0) {
-        // ---- epilogue warps: TMEM -> registers -> global memory, one pass over this CTA's tiles ----
-        const int quarter = warp & 3;                                 // the TMEM lanes this warp may read
-        const int row = quarter * 32 + lane;
-        for (int count = 0; count < my_tiles && ok; ++count) {
+    } else if (warp >= SW && warp < MMA_WARP) {
+        // ---- epilogue warps: TMEM -> registers -> global memory, one pass over this CTA's tiles.  Warp e reads the TMEM
+        // lanes of quarter e % 4 (the hardware's rule) and the columns of half e / 4. ----
+        const int e = warp - SW, quarter = e & 3, half = e >> 2;
+        for (int count = 0; count < my_tiles; ++count) {
             const int t = (int)blockIdx.x + count * (int)gridDim.x;
-            const int set = (p.sets == 2) ? (count & 1) : 0;
-            const uint32_t parity = (uint32_t)(((p.sets == 2) ? (count >> 1) : count) & 1);
-            if (!mbar_wait(smem_u32(bars + RAW_STAGES + set), parity, p.status)) { ok = false; break; }
+            const int set = count % p.sets;
+            if (!mbar_wait(smem_u32(accready + set), (uint32_t)((count / p.sets) & 1), p.status)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)set * set_cols;
-            int n_tile0;
-            size_t dst_off = 0;
-            bool row_ok;
-            if (OP != OP_WGRAD) {
-                const int m_tile = t / p.n_tiles, n_tile = t - m_tile * p.n_tiles;
-                n_tile0 = n_tile * BN;
-                const int g = m_tile * 4 + quarter, im = g / p.gpi, pix = (g - im * p.gpi) * 32 + lane;
-                row_ok = im < p.n_img && pix < p.HW;
-                dst_off = ((size_t)im * p.N_total + n_tile0) * p.HW + pix;
-                if (p.bulk_out && (m_tile + 1) * BM <= p.n_img * p.HW) {
-                    // planes of a multiple of 32 (and >= 1024) pixels: rows are flat pixel indices; stage 64 columns x 128
-                    // pixels and let the TMA unit write each column's 512-byte run (two runs across an image boundary)
-                    float *stage = reinterpret_cast<float *>(smem + (size_t)(RAW_STAGES + LO_BUFS) * 2 * TILE);
-                    const int e = tid - EPI_WARP0 * 32;              // 0 .. 127
-                    const int m_tile0 = m_tile * BM;
-                    const int im0 = m_tile0 / p.HW, pix0 = m_tile0 - im0 * p.HW;
-                    const int len0 = min(BM, p.HW - pix0);
-#pragma unroll 1
-                    for (int cbase = 0; cbase < BN; cbase += STAGE_COLS) {
-                        bulk_wait_read_all();
-                        epi_sync();
-#pragma unroll 1
-                        for (int c0 = cbase; c0 < cbase + STAGE_COLS && c0 < BN; c0 += 16) {
-                            float acc[16];
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) acc[j] = (OP == OP_FWD && p.bias && n_tile0 + c0 + j < p.N_total) ? __ldg(p.bias + n_tile0 + c0 + j) : 0.f;
-                            for (int a2 = 0; a2 <= nhi_used; ++a2) {
-                                const int a = a2 < nhi_used ? a2 : p.nacc - 1;
-                                uint32_t r[16];
-                                tmem_ld16(tsrc + (uint32_t)(a * ACC_COLS + c0), r);
-#pragma unroll
-                                for (int j = 0; j < 16; ++j) acc[j] += __uint_as_float(r[j]);
-                            }
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) stage[(c0 - cbase + j) * BM + row] = acc[j];
-                        }
-                        fence_async_smem();
-                        epi_sync();
-                        const int col = cbase + e, n = n_tile0 + col;
-                        if (e < STAGE_COLS && col < BN && n < p.N_total) {
-                            const uint32_t src = smem_u32(stage + e * BM);
-                            float *dst = p.out + ((size_t)im0 * p.N_total + n) * p.HW + pix0;
-                            bulk_s2g_nocommit(dst, src, (uint32_t)len0 * 4u);
-                            if (len0 < BM) bulk_s2g_nocommit(p.out + ((size_t)(im0 + 1) * p.N_total + n) * p.HW, src + (uint32_t)len0 * 4u, (uint32_t)(BM - len0) * 4u);
-                            bulk_commit();
-                        }
-                    }
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(accfree + set));
-                    continue;
-                }
-            } else {
-                const int split = t / p.tiles_per_split, r2 = t - split * p.tiles_per_split;
-                const int m_tile = r2 / p.n_tiles, n_tile = r2 - m_tile * p.n_tiles;
-                const int m = m_tile * BM + row;
-                n_tile0 = n_tile * BN;
-                row_ok = m < p.M_total;
-                dst_off = ((size_t)split * p.M_total + m) * p.N_total + n_tile0;
-            }
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                float acc[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    acc[j] = (OP == OP_FWD && p.bias && n_tile0 + c0 + j < p.N_total) ? __ldg(p.bias + n_tile0 + c0 + j) : 0.f;
-                for (int a2 = 0; a2 <= nhi_used; ++a2) {
-                    const int a = a2 < nhi_used ? a2 : p.nacc - 1;
-                    uint32_t r[16];
-                    tmem_ld16(tsrc + (uint32_t)(a * ACC_COLS + c0), r);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) acc[j] += __uint_as_float(r[j]);
-                }
-                if (row_ok) {
-                    const int n0 = n_tile0 + c0;
-                    if (OP != OP_WGRAD) {
-                        float *dst = p.out + dst_off + (size_t)c0 * p.HW;
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (n0 + j < p.N_total) dst[(size_t)j * p.HW] = acc[j];
-                    } else {
-                        float *dst = p.out + dst_off + c0;
-                        if ((p.N_total & 3) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 16; j += 4)
-                                if (n0 + j < p.N_total) *reinterpret_cast<float4 *>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (n0 + j < p.N_total) dst[j] = acc[j];
-                        }
-                    }
-                }
-            }
-            tc_fence_before();
+            drain_tile<OP, BN, EW / 4>(p, map_out, reinterpret_cast<float *>(smem + (size_t)(NS + NL) * 2 * TILE), tmem_base + (uint32_t)set * set_cols, t,
+                               nhi_used, quarter, half, lane, tid - (SW + 4 * half) * 32);
+            tc_fence_before();                                       // the TMEM reads above are ordered before the arrival
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(accfree + set));
         }
-        bulk_wait_read_all();
-    } else {
-        // ---- splitter warps: lo = v - tf32(v), element-wise over the raw tiles; thread t owns the 16-byte pieces at
-        // byte offsets 16 t and 16 t + 8192 of both tiles (row t / 8 + 64 i of a K-major tile) ----
-        float bsum[2] = {0.f, 0.f};                                  // WGRAD: running row sums of gy (bias gradient)
+        bulk_wait_read_all();                                        // shared memory must outlive the last bulk stores' reads
+    } else if (warp < SW) {
+        // ---- splitter warps: lo = v - tf32(v), element-wise over the raw tiles; thread t owns the 16-byte pieces at byte
+        // offsets 16 t + SPLITTERS * 16 h of both tiles, i.e. row t / 8 + SPLITTERS / 8 * h of a K-major tile ----
+        constexpr uint32_t PSTEP = SPLITTERS * 16;
+        float bsum[SPLIT_PIECES];                                    // WGRAD: running row sums of gy (bias gradient)
+#pragma unroll
+        for (int h = 0; h < SPLIT_PIECES; ++h) bsum[h] = 0.f;
         int c_tile = (int)blockIdx.x, c_kb = 0;
         for (int i = 0; i < total_it; ++i) {
-            const int rs = i % RAW_STAGES, lb = i % LO_BUFS;
-            if (!mbar_wait(smem_u32(rawfull + rs), (uint32_t)((i / RAW_STAGES) & 1), p.status)) { ok = false; break; }
-            if (i >= LO_BUFS) {
-                const int j = i - LO_BUFS;                           // the MMAs of k-block i - 2 read this lo buffer
-                if (!mbar_wait(smem_u32(bars + j % RAW_STAGES), (uint32_t)((j / RAW_STAGES) & 1), p.status)) { ok = false; break; }
+            const int rs = i % NS, lb = i % NL;
+            if (!mbar_wait(smem_u32(rawfull + rs), (uint32_t)((i / NS) & 1), p.status)) { ok = false; break; }
+            if (i >= NL) {
+                // the MMAs of k-block i - NL read this lo buffer
+                if (!mbar_wait(smem_u32(lodone + lb), (uint32_t)((i / NL - 1) & 1), p.status)) { ok = false; break; }
             }
             const unsigned char *a_hi = smem + (size_t)rs * 2 * TILE, *b_hi = a_hi + TILE;
             unsigned char *a_lo = lo_base + (size_t)lb * 2 * TILE, *b_lo = a_lo + TILE;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const uint32_t off = (uint32_t)(tid * 16 + h * 8192);
-                const float4 va = *reinterpret_cast<const float4 *>(a_hi + off);
-                store_lo_at(a_lo, off, va);
-                if (OP == OP_WGRAD) bsum[h] += (va.x + va.y) + (va.z + va.w);
-                if (off < B_BYTES) {
-                    const float4 vb = *reinterpret_cast<const float4 *>(b_hi + off);
-                    store_lo_at(b_lo, off, vb);
+            for (int h0 = 0; h0 < SPLIT_PIECES; h0 += 4) {
+                float4 va[4], vb[4];
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    const uint32_t off = (uint32_t)tid * 16u + (uint32_t)(h0 + h) * PSTEP;
+                    va[h] = *reinterpret_cast<const float4 *>(a_hi + off);
+                    if (off < B_BYTES) vb[h] = *reinterpret_cast<const float4 *>(b_hi + off);
+                }
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    const uint32_t off = (uint32_t)tid * 16u + (uint32_t)(h0 + h) * PSTEP;
+                    store_lo_at(a_lo, off, va[h]);
+                    if (OP == OP_WGRAD) bsum[h0 + h] += (va[h].x + va[h].y) + (va[h].z + va[h].w);
+                    if (off < B_BYTES) store_lo_at(b_lo, off, vb[h]);
                 }
             }
-            fence_async_smem();
+            fence_async_smem();                                      // generic-proxy stores -> visible to the tensor core's async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(full + rs));
             if (c_kb == KB - 1) {
                 if (OP == OP_WGRAD) {
+                    // bias gradient: the eight lanes that share a row hold its partial sums
 #pragma unroll
-                    for (int r = 0; r < 2; ++r) {
+                    for (int r = 0; r < SPLIT_PIECES; ++r) {
                         float sum = bsum[r];
                         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
                         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
                         sum += __shfl_xor_sync(0xffffffffu, sum, 4);
                         const int split = c_tile / p.tiles_per_split, r2 = c_tile - split * p.tiles_per_split;
                         const int m_tile = r2 / p.n_tiles, n_tile = r2 - m_tile * p.n_tiles;
-                        const int m = m_tile * BM + (tid >> 3) + 64 * r;
+                        const int m = m_tile * BM + (tid >> 3) + (SPLITTERS / 8) * r;
                         if (p.bias_part && n_tile == 0 && (tid & 7) == 0 && m < p.M_total) p.bias_part[(size_t)m * p.splits + split] = sum;
                         bsum[r] = 0.f;
                     }

@@ -123,6 +123,8 @@ def pointwise_loader(request):
     (2, 256, 32, 32, 200, True),     # 1024-pixel planes, 8 k-blocks, ragged column tile
     (16, 128, 28, 28, 128, True),    # four k-blocks, two accumulator sets, several tiles per CTA
     (4, 1024, 14, 14, 256, False),   # long reduction: four accumulators, one set
+    (3, 40, 64, 64, 24, True),       # 4096-pixel planes, narrow column tile (32): per-column bulk stores
+    (2, 64, 40, 40, 128, False),     # 1600-pixel planes: tiles that cross an image boundary in the bulk-store epilogue
     (6, 100, 6, 6, 20, True),        # 36-pixel planes (2 groups per image), C not a multiple of 32
     (2, 36, 2, 2, 24, True),         # 4-pixel planes
     (130, 64, 2, 4, 32, True),       # many tiny images: more groups than one wave of row tiles
