@@ -1467,21 +1467,15 @@ static void tma_accumulators(int bn, int kblocks, int *nacc, int *sets, bool wgr
     pw_accumulators(bn, kblocks, nacc, sets, wgrad);
 }
 typedef void (*PwTmaKernel)(const pw::Params, const CUtensorMap, const CUtensorMap, const CUtensorMap);
-// Tiles of up to four k-blocks: 4 splitter + 8 epilogue warps; longer tiles: 8 + 4.
+// 4 splitter + 8 epilogue warps for every tile length: measured against 8 + 4 and 16 + 4 on tiles of 8, 16 and 32 k-blocks,
+// 4 + 8 was never slower (16 + 4 runs at 80 registers and was 4-14 % slower).
 template <int OP>
-static PwTmaKernel pw_tma_pick(int bn, int kblocks)
+static PwTmaKernel pw_tma_pick(int bn)
 {
-    if (kblocks <= 4) {
-        switch (bn) {
-            case 32: return pwt::pw_tma_kernel<OP, 32, 4>;
-            case 64: return pwt::pw_tma_kernel<OP, 64, 4>;
-            default: return pwt::pw_tma_kernel<OP, 128, 4>;
-        }
-    }
     switch (bn) {
-        case 32: return pwt::pw_tma_kernel<OP, 32, 8>;
-        case 64: return pwt::pw_tma_kernel<OP, 64, 8>;
-        default: return pwt::pw_tma_kernel<OP, 128, 8>;
+        case 32: return pwt::pw_tma_kernel<OP, 32, 4, 8>;
+        case 64: return pwt::pw_tma_kernel<OP, 64, 4, 8>;
+        default: return pwt::pw_tma_kernel<OP, 128, 4, 8>;
     }
 }
 // `mo` is the map of the output tensor for the bulk-store epilogue (forward / input gradient); kernels that do not use
@@ -1490,7 +1484,7 @@ static int pw_tma_launch(PwTmaKernel kern, pw::Params &p, CUtensorMap &ma, CUten
 {
     const int grid = std::min(p.total_tiles, sm_count());
     const size_t smem_bytes = pw::SMEM;
-    const int threads = pwt::TTHREADS;
+    const int threads = pwt::tma_threads(4, 8);
     CUNN_CUDA(cudaFuncSetAttribute((const void *)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     void *args[] = {(void *)&p, (void *)&ma, (void *)&mb, (void *)&mo};
     CUNN_CUDA(cudaLaunchKernel((const void *)kern, dim3(grid), dim3(threads), args, smem_bytes, stream));
@@ -1555,7 +1549,7 @@ static int conv_forward(const float *x, const float *weight, const float *bias, 
             if (make_map(&mb, weight, C, K, 0, 32, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return 1;
             if (q.bulk_out) { if (make_map(&mo, y, q.HW, K, N, BM, pwt::HALF_STAGE_COLS, CU_TENSOR_MAP_SWIZZLE_NONE)) return 1; }
             else mo = ma;
-            return pw_tma_launch(pw_tma_pick<OP_FWD>(bn, q.kblocks), q, ma, mb, mo, stream);
+            return pw_tma_launch(pw_tma_pick<OP_FWD>(bn), q, ma, mb, mo, stream);
         }
         q.vec_a = (q.HW % 4 == 0) && aligned16(x); q.vec_b = (C % 4 == 0) && aligned16(weight);
         q.bulk_out = (q.HW % 4 == 0) && q.HW >= 8 * BM && aligned16(y);
@@ -1612,7 +1606,7 @@ static int conv_grad_input(const float *gy, const float *weight, float *gx, int 
             if (make_map(&mb, weight, C, K, 0, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return 1;
             if (q.bulk_out) { if (make_map(&mo, gx, q.HW, C, N, BM, pwt::HALF_STAGE_COLS, CU_TENSOR_MAP_SWIZZLE_NONE)) return 1; }
             else mo = ma;
-            return pw_tma_launch(pw_tma_pick<OP_DGRAD>(bn, q.kblocks), q, ma, mb, mo, stream);
+            return pw_tma_launch(pw_tma_pick<OP_DGRAD>(bn), q, ma, mb, mo, stream);
         }
         q.vec_a = (q.HW % 4 == 0) && aligned16(gy); q.vec_b = (C % 4 == 0) && aligned16(weight);
         q.bulk_out = (q.HW % 4 == 0) && q.HW >= 8 * BM && aligned16(gx);
@@ -1716,7 +1710,7 @@ static int conv_acc_grad(const float *x, const float *gy, float *grad_weight, fl
             tma_accumulators(bn, q.kblocks, &q.nacc, &q.sets, true);
             if (make_map(&ma, gy, q.HW, K, N, 32, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return 1;
             if (make_map(&mb, x, q.HW, C, N, 32, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return 1;
-            if (pw_tma_launch(pw_tma_pick<OP_WGRAD>(bn, q.kblocks), q, ma, mb, ma, stream)) return 1;
+            if (pw_tma_launch(pw_tma_pick<OP_WGRAD>(bn), q, ma, mb, ma, stream)) return 1;
         } else {
         pw_accumulators(bn, q.kblocks, &q.nacc, &q.sets, true);
         if (pw_launch(pw_pick<OP_WGRAD>(bn), q, stream)) return 1;

@@ -28,14 +28,11 @@ namespace pwt {
 
 using namespace pw;
 
-// The 12 worker warps are divided between splitting and draining per launch (template arguments SW + EW = 12, both
-// multiples of 4): tiles of few k-blocks spend their time in the epilogue (SW = 4, EW = 8: two epilogue warps per TMEM
-// lane quarter, each half of the columns), long tiles in the split (SW = 8, EW = 4).  Warps: [0, SW) splitters,
-// [SW, 12) epilogue, 12 MMA issue, 13 copy issue.
-constexpr int WORKER_WARPS = 12;
-constexpr int MMA_WARP = WORKER_WARPS;                           // one warp that only issues MMAs
-constexpr int TMA_WARP = MMA_WARP + 1;                           // one warp whose lane 0 issues the tensor-map copies
-constexpr int TTHREADS = (TMA_WARP + 1) * 32;                    // 448: 14 warps, register file shared as 16
+// Warps: [0, SW) splitters, [SW, SW + EW) epilogue, then one warp that issues the MMAs and one whose lane 0 issues the
+// copies.  The library runs SW = 4, EW = 8 (two epilogue warps per TMEM lane quarter, each half of the columns; 448 threads,
+// up to 128 registers each): tiles of few k-blocks spend their time in the epilogue, and on long tiles it measured equal
+// to 8 + 4 and 4-14 % faster than 16 + 4 (704 threads, 80 registers).
+__host__ __device__ constexpr int tma_threads(int sw, int ew) { return (sw + ew + 2) * 32; }
 constexpr int MAX_SETS = 4;                                      // accumulator sets in TMEM the MMA warp may run ahead by
 constexpr int HALF_STAGE_COLS = 32;                              // bulk-store epilogue: columns one half of the warps stages at a time
 constexpr int GROUP_BYTES = 32 * 128;                            // one M/N-major group: 32 positions x 32 k values
@@ -79,15 +76,16 @@ __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Sum over the tile's accumulators of 16 columns starting at TMEM address `t0` (+ a * acc_cols), on top of `acc`.
-// Accumulators are read two at a time so that two loads are in flight per wait.
+// PAIRS: accumulators are read two at a time, so that two loads are in flight per wait (16 more registers).
+template <bool PAIRS>
 __device__ __forceinline__ void gather_acc16(float (&acc)[16], uint32_t t0, int nhi_used, int nacc, int acc_cols)
 {
     const int n = nhi_used + 1;                                   // the hi accumulators that were used, then the lo one
-    for (int a2 = 0; a2 < n; a2 += 2) {
+    for (int a2 = 0; a2 < n; a2 += PAIRS ? 2 : 1) {
         const int a = a2 < nhi_used ? a2 : nacc - 1;
         uint32_t r0[16], r1[16];
         tmem_ld16_issue(t0 + (uint32_t)(a * acc_cols), r0);
-        const bool two = a2 + 1 < n;
+        const bool two = PAIRS && a2 + 1 < n;
         if (two) {
             const int b = a2 + 1 < nhi_used ? a2 + 1 : nacc - 1;
             tmem_ld16_issue(t0 + (uint32_t)(b * acc_cols), r1);
@@ -139,7 +137,7 @@ __device__ __forceinline__ void drain_tile(const Params &p, const CUtensorMap &m
                     float acc[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) acc[j] = (OP == OP_FWD && p.bias && n_tile0 + c0 + j < p.N_total) ? __ldg(p.bias + n_tile0 + c0 + j) : 0.f;
-                    gather_acc16(acc, tsrc + (uint32_t)c0, nhi_used, p.nacc, ACC_COLS);
+                    gather_acc16<HALVES == 2>(acc, tsrc + (uint32_t)c0, nhi_used, p.nacc, ACC_COLS);
 #pragma unroll
                     for (int j = 0; j < 16; ++j) stage[(c0 - cbase + j) * BM + row] = acc[j];
                 }
@@ -180,7 +178,7 @@ __device__ __forceinline__ void drain_tile(const Params &p, const CUtensorMap &m
 #pragma unroll
             for (int j = 0; j < 16; ++j)
                 acc[j] = (OP == OP_FWD && p.bias && n_tile0 + c0 + j < p.N_total) ? __ldg(p.bias + n_tile0 + c0 + j) : 0.f;
-            gather_acc16(acc, tsrc + (uint32_t)c0, nhi_used, p.nacc, ACC_COLS);
+            gather_acc16<HALVES == 2>(acc, tsrc + (uint32_t)c0, nhi_used, p.nacc, ACC_COLS);
             if (row_ok) {
                 const int n0 = n_tile0 + c0;
                 if (OP != OP_WGRAD) {
@@ -205,8 +203,8 @@ __device__ __forceinline__ void drain_tile(const Params &p, const CUtensorMap &m
     }
 }
 
-template <int OP, int BN, int SW>
-__global__ void __launch_bounds__(TTHREADS, 1)
+template <int OP, int BN, int SW, int EW>
+__global__ void __launch_bounds__(tma_threads(SW, EW), 1)
 pw_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
               const __grid_constant__ CUtensorMap map_out)
 {
@@ -217,14 +215,13 @@ pw_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_a, const _
     constexpr uint32_t idesc = idesc_of(BN, A_MN, B_MN);
     constexpr uint32_t A_BYTES = TILE;                           // 128 rows (or 4 groups) x 32 k values
     constexpr uint32_t B_BYTES = (uint32_t)BN * 128u;
-    constexpr int EW = WORKER_WARPS - SW;                        // epilogue warps: 4 (each all columns) or 8 (two column halves)
+    constexpr int MMA_WARP = SW + EW, TMA_WARP = MMA_WARP + 1;
     constexpr int SPLITTERS = SW * 32;
     constexpr int SPLIT_PIECES = TILE / 16 / SPLITTERS;          // 16-byte pieces of a tile per splitter thread
-    static_assert((SW == 4 || SW == 8) && SPLIT_PIECES % 4 == 0, "splitter warps");
+    static_assert(SW % 4 == 0 && (EW == 4 || EW == 8) && (SPLIT_PIECES % 4 == 0 || SPLIT_PIECES == 2), "warp roles");
 
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ uint64_t mmadone[RAW_STAGES];    // the MMAs that read this raw stage have finished: the TMA unit may refill it
-    __shared__ uint64_t lodone[LO_BUFS];         // the MMAs that read this lo buffer have finished: the splitters may rewrite it
+    __shared__ uint64_t mmadone[RAW_STAGES];    // the MMAs that read this raw stage (and the lo buffer of the same k-block) have finished
     __shared__ uint64_t accready[MAX_SETS];     // all MMAs of a tile have finished: its accumulator set can be read
     __shared__ uint64_t accfree[MAX_SETS];      // accumulator set drained: one arrival per epilogue warp
     __shared__ uint64_t rawfull[RAW_STAGES];    // the stage's raw tiles have landed (transaction bytes)
@@ -238,7 +235,6 @@ pw_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_a, const _
             mbar_init(smem_u32(rawfull + s), 1);
             mbar_init(smem_u32(full + s), SW);
         }
-        for (int s = 0; s < LO_BUFS; ++s) mbar_init(smem_u32(lodone + s), 1);
         for (int s = 0; s < MAX_SETS; ++s) { mbar_init(smem_u32(accready + s), 1); mbar_init(smem_u32(accfree + s), EW); }
         mbar_fence_init();
     }
@@ -250,6 +246,7 @@ pw_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_a, const _
 
     const int KB = p.kblocks;
     constexpr int NS = RAW_STAGES, NL = LO_BUFS;                 // 4 raw stages + 2 lo buffers of 32 KB + the output staging area
+    static_assert(NS >= NL, "one completion barrier per raw stage also guards the lo buffers");
     const int my_tiles = ((int)blockIdx.x < p.total_tiles) ? (p.total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
     const int total_it = my_tiles * KB;
     // nacc == 1: all three products of every k-block go to one accumulator (tiles of one or two k-blocks, whose chains are
@@ -323,7 +320,6 @@ pw_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_a, const _
                         umma_tf32(d_hi, ah, bh, idesc, (first_hi && j == 0) ? 0u : 1u);
                 }
                 umma_commit(smem_u32(mmadone + rs));
-                umma_commit(smem_u32(lodone + lb));
                 if (kb == KB - 1) umma_commit(smem_u32(accready + set));
             }
             __syncwarp();
@@ -357,22 +353,26 @@ pw_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_a, const _
             const int rs = i % NS, lb = i % NL;
             if (!mbar_wait(smem_u32(rawfull + rs), (uint32_t)((i / NS) & 1), p.status)) { ok = false; break; }
             if (i >= NL) {
-                // the MMAs of k-block i - NL read this lo buffer
-                if (!mbar_wait(smem_u32(lodone + lb), (uint32_t)((i / NL - 1) & 1), p.status)) { ok = false; break; }
+                // the MMAs of k-block i - NL read this lo buffer.  One commit per k-block serves both rings: the barrier of
+                // raw stage (i - NL) % NS cannot advance a second time before this wait, because the next k-block that uses
+                // that stage is i - NL + NS >= i, whose MMAs need this very split (NS >= NL)
+                const int j = i - NL;
+                if (!mbar_wait(smem_u32(mmadone + j % NS), (uint32_t)((j / NS) & 1), p.status)) { ok = false; break; }
             }
             const unsigned char *a_hi = smem + (size_t)rs * 2 * TILE, *b_hi = a_hi + TILE;
             unsigned char *a_lo = lo_base + (size_t)lb * 2 * TILE, *b_lo = a_lo + TILE;
+            constexpr int PG = SPLIT_PIECES < 4 ? SPLIT_PIECES : 4;      // pieces loaded before their lo values are stored
 #pragma unroll
-            for (int h0 = 0; h0 < SPLIT_PIECES; h0 += 4) {
-                float4 va[4], vb[4];
+            for (int h0 = 0; h0 < SPLIT_PIECES; h0 += PG) {
+                float4 va[PG], vb[PG];
 #pragma unroll
-                for (int h = 0; h < 4; ++h) {
+                for (int h = 0; h < PG; ++h) {
                     const uint32_t off = (uint32_t)tid * 16u + (uint32_t)(h0 + h) * PSTEP;
                     va[h] = *reinterpret_cast<const float4 *>(a_hi + off);
                     if (off < B_BYTES) vb[h] = *reinterpret_cast<const float4 *>(b_hi + off);
                 }
 #pragma unroll
-                for (int h = 0; h < 4; ++h) {
+                for (int h = 0; h < PG; ++h) {
                     const uint32_t off = (uint32_t)tid * 16u + (uint32_t)(h0 + h) * PSTEP;
                     store_lo_at(a_lo, off, va[h]);
                     if (OP == OP_WGRAD) bsum[h0 + h] += (va[h].x + va[h].y) + (va[h].z + va[h].w);
