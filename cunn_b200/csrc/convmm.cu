@@ -83,6 +83,11 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint6
         "}\n" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// The same with accumulation always on: no predicate to set up.
+__device__ __forceinline__ void umma_tf32_acc(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc)
+{
+    asm volatile("tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, 1;" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+}
 // Arrives on the mbarrier once every MMA issued so far by this thread has finished reading shared memory
 // and writing TMEM.
 __device__ __forceinline__ void umma_commit(uint32_t bar)
@@ -1032,22 +1037,6 @@ pw_gemm_kernel(const Params p)
     // hi*hi products go to accumulator d_hi, the two small cross terms to d_lo: the tensor core truncates when it
     // accumulates, and the error of a chain scales with the magnitude it carries, so the large terms get the short
     // chains (k-blocks round-robin over nacc - 1 accumulators) and all cross terms share one.
-    auto issue_mmas = [&](int rs, int lb, uint32_t d_hi, bool first_hi, uint32_t d_lo, bool first_lo) {
-        const uint32_t sa_hi = smem_u32(smem + (size_t)rs * 2 * TILE), sb_hi = sa_hi + TILE;
-        const uint32_t sa_lo = smem_u32(lo_base + (size_t)lb * 2 * TILE), sb_lo = sa_lo + TILE;
-#pragma unroll
-        for (int j = 0; j < BK / 8; ++j) {
-            const uint32_t ao = A_MN ? (uint32_t)(j * 2 * MN_KATOM) : (uint32_t)(j * 32);
-            const uint32_t bo = B_MN ? (uint32_t)(j * 2 * MN_KATOM) : (uint32_t)(j * 32);
-            const uint64_t ah = A_MN ? desc_mn(sa_hi + ao) : smem_desc(sa_hi + ao);
-            const uint64_t al = A_MN ? desc_mn(sa_lo + ao) : smem_desc(sa_lo + ao);
-            const uint64_t bh = B_MN ? desc_mn(sb_hi + bo) : smem_desc(sb_hi + bo);
-            const uint64_t bl = B_MN ? desc_mn(sb_lo + bo) : smem_desc(sb_lo + bo);
-            umma_tf32(d_lo, al, bh, idesc, (first_lo && j == 0) ? 0u : 1u);
-            umma_tf32(d_lo, ah, bl, idesc, 1u);
-            umma_tf32(d_hi, ah, bh, idesc, (first_hi && j == 0) ? 0u : 1u);
-        }
-    };
     // Epilogue warps: reads the accumulators of tile `t` (the `count`-th tile of this CTA), writes the warp's 32
     // rows of the output and hands the accumulator set back to the MMA warp.
     auto epilogue = [&](int t, int count) -> bool {
@@ -1163,28 +1152,65 @@ pw_gemm_kernel(const Params p)
 
     bool ok = true;
     if (warp == PRODUCERS / 32) {
-        // ---- MMA warp: waits for a split stage, issues its twelve MMAs, commits them to the stage's barrier ----
-        int kb = 0, count = 0;
-        for (int i = 0; i < total_it; ++i) {
-            const int rs = i % RAW_STAGES, lb = i % LO_BUFS;
-            if (!mbar_wait(smem_u32(full + rs), (uint32_t)((i / RAW_STAGES) & 1), p.status)) { ok = false; break; }
-            if (kb == 0 && count >= p.sets) {
-                // the epilogue warps must have drained the tile that used this accumulator set before
-                const int set = (p.sets == 2) ? (count & 1) : 0;
-                const int use = (p.sets == 2) ? (count >> 1) : count;
-                if (!mbar_wait(smem_u32(accfree + set), (uint32_t)((use - 1) & 1), p.status)) { ok = false; break; }
-            }
-            if (lane == 0) {
+        // ---- MMA warp: waits for a split stage, issues its twelve MMAs, commits them to the stage's barrier.  The tensor
+        // pipe takes one of these MMAs every 64 clocks only if the issuing thread keeps up: every instruction between two
+        // tcgen05.mma of this one thread is time the pipe idles.  So one lane runs the whole loop, descriptors are a
+        // constant upper word + a lower word that advances by additions, ring positions and barrier parities are carried
+        // incrementally, and the steady state uses the form without a predicate. ----
+        if (lane == 0) {
+            constexpr uint32_t A_LOW = A_MN ? ((uint32_t)(MN_ATOM >> 4) << 16) : (1u << 16);
+            constexpr uint32_t B_LOW = B_MN ? ((uint32_t)(MN_ATOM >> 4) << 16) : (1u << 16);
+            constexpr uint32_t A_HIGH = (A_MN ? (uint32_t)(MN_KATOM >> 4) : (uint32_t)(SBO >> 4)) | (1u << 14) | ((A_MN ? 1u : 2u) << 29);
+            constexpr uint32_t B_HIGH = (B_MN ? (uint32_t)(MN_KATOM >> 4) : (uint32_t)(SBO >> 4)) | (1u << 14) | ((B_MN ? 1u : 2u) << 29);
+            constexpr uint32_t A_STEP = A_MN ? (uint32_t)(2 * MN_KATOM >> 4) : 2u;     // 8 k values further, in 16-byte units
+            constexpr uint32_t B_STEP = B_MN ? (uint32_t)(2 * MN_KATOM >> 4) : 2u;
+            constexpr uint32_t STAGE_STEP = (uint32_t)(2 * TILE >> 4);
+            const uint32_t raw0 = (smem_u32(smem) >> 4) & 0x3fffu, lo0 = (smem_u32(lo_base) >> 4) & 0x3fffu;
+            auto desc = [](uint32_t low, uint32_t high) { return ((uint64_t)high << 32) | low; };
+            const int nhi = p.nacc - 1;
+            int rs = 0, lb = 0, kb = 0, set = 0, hi_slot = 0;
+            uint32_t full_parity = 0, free_parity = 0;             // accfree is first awaited on the second use of a set (its phase 0)
+            bool first_round = true;
+            uint32_t acc0 = tmem_base;
+            for (int i = 0; i < total_it; ++i) {
+                if (!mbar_wait(smem_u32(full + rs), full_parity, p.status)) break;
+                if (kb == 0 && !first_round) {
+                    // the epilogue warps must have drained the tile that used this accumulator set before
+                    if (!mbar_wait(smem_u32(accfree + set), free_parity, p.status)) break;
+                }
                 tc_fence_after();
-                const int set = (p.sets == 2) ? (count & 1) : 0;
-                const uint32_t acc0 = tmem_base + (uint32_t)set * set_cols;
-                const int nhi = p.nacc - 1;
-                issue_mmas(rs, lb, acc0 + (uint32_t)((kb % nhi) * ACC_COLS), kb < nhi, acc0 + (uint32_t)(nhi * ACC_COLS), kb == 0);
+                const uint32_t d_hi = acc0 + (uint32_t)(hi_slot * ACC_COLS), d_lo = acc0 + (uint32_t)(nhi * ACC_COLS);
+                const uint32_t ah = (raw0 + (uint32_t)rs * STAGE_STEP) | A_LOW, bh = (raw0 + (uint32_t)rs * STAGE_STEP + (uint32_t)(TILE >> 4)) | B_LOW;
+                const uint32_t al = (lo0 + (uint32_t)lb * STAGE_STEP) | A_LOW, bl = (lo0 + (uint32_t)lb * STAGE_STEP + (uint32_t)(TILE >> 4)) | B_LOW;
+                if (kb < nhi || kb == 0) {
+                    // first k-blocks of a tile: the first MMA into an accumulator overwrites it
+                    const uint32_t keep_lo = kb == 0 ? 0u : 1u, keep_hi = kb < nhi ? 0u : 1u;
+#pragma unroll
+                    for (int j = 0; j < BK / 8; ++j) {
+                        umma_tf32(d_lo, desc(al + j * A_STEP, A_HIGH), desc(bh + j * B_STEP, B_HIGH), idesc, j == 0 ? keep_lo : 1u);
+                        umma_tf32(d_lo, desc(ah + j * A_STEP, A_HIGH), desc(bl + j * B_STEP, B_HIGH), idesc, 1u);
+                        umma_tf32(d_hi, desc(ah + j * A_STEP, A_HIGH), desc(bh + j * B_STEP, B_HIGH), idesc, j == 0 ? keep_hi : 1u);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < BK / 8; ++j) {
+                        umma_tf32_acc(d_lo, desc(al + j * A_STEP, A_HIGH), desc(bh + j * B_STEP, B_HIGH), idesc);
+                        umma_tf32_acc(d_lo, desc(ah + j * A_STEP, A_HIGH), desc(bl + j * B_STEP, B_HIGH), idesc);
+                        umma_tf32_acc(d_hi, desc(ah + j * A_STEP, A_HIGH), desc(bh + j * B_STEP, B_HIGH), idesc);
+                    }
+                }
                 umma_commit(smem_u32(bars + rs));
-                if (kb == KB - 1) umma_commit(smem_u32(bars + RAW_STAGES + set));
+                if (++rs == RAW_STAGES) { rs = 0; full_parity ^= 1u; }
+                if (++lb == LO_BUFS) lb = 0;
+                if (++hi_slot == nhi) hi_slot = 0;
+                if (++kb == KB) {
+                    umma_commit(smem_u32(bars + RAW_STAGES + set));
+                    kb = 0;
+                    hi_slot = 0;
+                    acc0 += set_cols;
+                    if (++set == p.sets) { set = 0; acc0 = tmem_base; if (!first_round) free_parity ^= 1u; first_round = false; }
+                }
             }
-            __syncwarp();
-            if (++kb == KB) { kb = 0; ++count; }
         }
     } else if (warp > PRODUCERS / 32) {
         // ---- epilogue warps: one pass over this CTA's tiles ----
@@ -1473,9 +1499,9 @@ template <int OP>
 static PwTmaKernel pw_tma_pick(int bn)
 {
     switch (bn) {
-        case 32: return pwt::pw_tma_kernel<OP, 32, 4, 8>;
-        case 64: return pwt::pw_tma_kernel<OP, 64, 4, 8>;
-        default: return pwt::pw_tma_kernel<OP, 128, 4, 8>;
+        case 32: return pwt::pw_tma_kernel<OP, 32, 4, 8, 4, 2>;
+        case 64: return pwt::pw_tma_kernel<OP, 64, 4, 8, 4, 2>;
+        default: return pwt::pw_tma_kernel<OP, 128, 4, 8, 4, 2>;
     }
 }
 // `mo` is the map of the output tensor for the bulk-store epilogue (forward / input gradient); kernels that do not use
@@ -1484,7 +1510,7 @@ static int pw_tma_launch(PwTmaKernel kern, pw::Params &p, CUtensorMap &ma, CUten
 {
     const int grid = std::min(p.total_tiles, sm_count());
     const size_t smem_bytes = pw::SMEM;
-    const int threads = pwt::tma_threads(4, 8);
+    const int threads = pwt::tma_threads(4, 8);          // every configuration has 14 warps
     CUNN_CUDA(cudaFuncSetAttribute((const void *)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     void *args[] = {(void *)&p, (void *)&ma, (void *)&mb, (void *)&mo};
     CUNN_CUDA(cudaLaunchKernel((const void *)kern, dim3(grid), dim3(threads), args, smem_bytes, stream));

@@ -33,6 +33,7 @@ using namespace pw;
 // up to 128 registers each): tiles of few k-blocks spend their time in the epilogue, and on long tiles it measured equal
 // to 8 + 4 and 4-14 % faster than 16 + 4 (704 threads, 80 registers).
 __host__ __device__ constexpr int tma_threads(int sw, int ew) { return (sw + ew + 2) * 32; }
+constexpr int MAX_STAGES = 5;                                    // barriers are laid out for up to five raw stages
 constexpr int MAX_SETS = 4;                                      // accumulator sets in TMEM the MMA warp may run ahead by
 constexpr int HALF_STAGE_COLS = 32;                              // bulk-store epilogue: columns one half of the warps stages at a time
 constexpr int GROUP_BYTES = 32 * 128;                            // one M/N-major group: 32 positions x 32 k values
@@ -203,7 +204,7 @@ __device__ __forceinline__ void drain_tile(const Params &p, const CUtensorMap &m
     }
 }
 
-template <int OP, int BN, int SW, int EW>
+template <int OP, int BN, int SW, int EW, int NS, int NL>
 __global__ void __launch_bounds__(tma_threads(SW, EW), 1)
 pw_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
               const __grid_constant__ CUtensorMap map_out)
@@ -221,16 +222,16 @@ pw_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_a, const _
     static_assert(SW % 4 == 0 && (EW == 4 || EW == 8) && (SPLIT_PIECES % 4 == 0 || SPLIT_PIECES == 2), "warp roles");
 
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ uint64_t mmadone[RAW_STAGES];    // the MMAs that read this raw stage (and the lo buffer of the same k-block) have finished
+    __shared__ uint64_t mmadone[MAX_STAGES];    // the MMAs that read this raw stage (and the lo buffer of the same k-block) have finished
     __shared__ uint64_t accready[MAX_SETS];     // all MMAs of a tile have finished: its accumulator set can be read
     __shared__ uint64_t accfree[MAX_SETS];      // accumulator set drained: one arrival per epilogue warp
-    __shared__ uint64_t rawfull[RAW_STAGES];    // the stage's raw tiles have landed (transaction bytes)
-    __shared__ uint64_t full[RAW_STAGES];       // lo tiles written and visible to the tensor core: one arrival per splitter warp
+    __shared__ uint64_t rawfull[MAX_STAGES];    // the stage's raw tiles have landed (transaction bytes)
+    __shared__ uint64_t full[MAX_STAGES];       // lo tiles written and visible to the tensor core: one arrival per splitter warp
     __shared__ uint32_t tmem_base_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int s = 0; s < RAW_STAGES; ++s) {
+        for (int s = 0; s < MAX_STAGES; ++s) {
             mbar_init(smem_u32(mmadone + s), 1);
             mbar_init(smem_u32(rawfull + s), 1);
             mbar_init(smem_u32(full + s), SW);
@@ -245,8 +246,9 @@ pw_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_a, const _
     const uint32_t tmem_base = tmem_base_s;
 
     const int KB = p.kblocks;
-    constexpr int NS = RAW_STAGES, NL = LO_BUFS;                 // 4 raw stages + 2 lo buffers of 32 KB + the output staging area
-    static_assert(NS >= NL, "one completion barrier per raw stage also guards the lo buffers");
+    // NS raw stages and NL lo buffers of 32 KB (the library runs 4 + 2, which leaves room for the 32 KB output staging area;
+    // 4 + 3 and 5 + 2 without the staging area measured within 3 % of it)
+    static_assert(NS >= NL && NS <= MAX_STAGES && (size_t)(NS + NL) * 2 * TILE + 1024 <= SMEM, "one completion barrier per raw stage also guards the lo buffers");
     const int my_tiles = ((int)blockIdx.x < p.total_tiles) ? (p.total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
     const int total_it = my_tiles * KB;
     // nacc == 1: all three products of every k-block go to one accumulator (tiles of one or two k-blocks, whose chains are
@@ -291,39 +293,67 @@ pw_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_a, const _
             }
         }
     } else if (warp == MMA_WARP) {
-        int kb = 0, count = 0;
-        for (int i = 0; i < total_it; ++i) {
-            const int rs = i % NS, lb = i % NL;
-            const int set = count % p.sets, use = count / p.sets;
-            if (!mbar_wait(smem_u32(full + rs), (uint32_t)((i / NS) & 1), p.status)) { ok = false; break; }
-            if (kb == 0 && use > 0) {
-                // the epilogue warps must have drained the tile that used this accumulator set before
-                if (!mbar_wait(smem_u32(accfree + set), (uint32_t)((use - 1) & 1), p.status)) { ok = false; break; }
-            }
-            if (lane == 0) {
+        // ---- MMA issue.  The tensor pipe takes a 128 x 128 x 8 tf32 MMA every 64 clocks only if the issuing thread keeps up:
+        // every instruction between two tcgen05.mma of this single thread is time the pipe idles (measured: 64 clocks per MMA
+        // from a bare loop, 102-130 with descriptors rebuilt and counters divided per MMA; running the loop on all 32 lanes with
+        // only the instruction predicated was slower).  So: one lane runs the whole loop,
+        // descriptors are a constant upper word + a lower word that advances by additions, ring positions and barrier
+        // parities are carried incrementally, and the accumulate flags of the steady state are constants. ----
+        if (lane == 0) {
+            // lower descriptor word = (address >> 4) | 1 << 16 (K-major: leading offset 16 bytes) or | GROUP_BYTES >> 4 << 16
+            constexpr uint32_t A_LOW = A_MN ? ((uint32_t)(GROUP_BYTES >> 4) << 16) : (1u << 16);
+            constexpr uint32_t B_LOW = B_MN ? ((uint32_t)(GROUP_BYTES >> 4) << 16) : (1u << 16);
+            // upper word: stride offset, descriptor version 1, swizzle (128B-base-32B = 1, 128B = 2)
+            constexpr uint32_t A_HIGH = (A_MN ? (uint32_t)(MN_KSTEP >> 4) : (uint32_t)(SBO >> 4)) | (1u << 14) | ((A_MN ? 1u : 2u) << 29);
+            constexpr uint32_t B_HIGH = (B_MN ? (uint32_t)(MN_KSTEP >> 4) : (uint32_t)(SBO >> 4)) | (1u << 14) | ((B_MN ? 1u : 2u) << 29);
+            constexpr uint32_t A_STEP = A_MN ? (uint32_t)(2 * MN_KSTEP >> 4) : 2u;     // 8 k values further, in 16-byte units
+            constexpr uint32_t B_STEP = B_MN ? (uint32_t)(2 * MN_KSTEP >> 4) : 2u;
+            constexpr uint32_t STAGE_STEP = (uint32_t)(2 * TILE >> 4);
+            const uint32_t raw0 = (smem_u32(smem) >> 4) & 0x3fffu, lo0 = (smem_u32(lo_base) >> 4) & 0x3fffu;
+            auto desc = [](uint32_t low, uint32_t high) { return ((uint64_t)high << 32) | low; };
+            int rs = 0, lb = 0, kb = 0, set = 0, hi_slot = 0;
+            uint32_t full_parity = 0, free_parity = 0;             // accfree is first awaited on the second use of a set (its phase 0)
+            bool first_round = true;
+            uint32_t acc0 = tmem_base;
+            for (int i = 0; i < total_it; ++i) {
+                if (!mbar_wait(smem_u32(full + rs), full_parity, p.status)) break;
+                if (kb == 0 && !first_round) {
+                    // the epilogue warps must have drained the tile that used this accumulator set before
+                    if (!mbar_wait(smem_u32(accfree + set), free_parity, p.status)) break;
+                }
                 tc_fence_after();
-                const uint32_t acc0 = tmem_base + (uint32_t)set * set_cols;
-                const uint32_t d_hi = acc0 + (uint32_t)((nhi ? kb % nhi : 0) * ACC_COLS), d_lo = acc0 + (uint32_t)(nhi * ACC_COLS);
-                const bool first_hi = nhi && kb < nhi, first_lo = kb == 0;
-                const uint32_t sa_hi = smem_u32(smem + (size_t)rs * 2 * TILE), sb_hi = sa_hi + TILE;
-                const uint32_t sa_lo = smem_u32(lo_base + (size_t)lb * 2 * TILE), sb_lo = sa_lo + TILE;
+                const uint32_t d_hi = acc0 + (uint32_t)(hi_slot * ACC_COLS), d_lo = acc0 + (uint32_t)(nhi * ACC_COLS);
+                const uint32_t ah = (raw0 + (uint32_t)rs * STAGE_STEP) | A_LOW, bh = (raw0 + (uint32_t)rs * STAGE_STEP + (uint32_t)(TILE >> 4)) | B_LOW;
+                const uint32_t al = (lo0 + (uint32_t)lb * STAGE_STEP) | A_LOW, bl = (lo0 + (uint32_t)lb * STAGE_STEP + (uint32_t)(TILE >> 4)) | B_LOW;
+                if (kb == 0 || (nhi && kb < nhi)) {
+                    // first k-block(s) of a tile: the first MMA into an accumulator overwrites it
+                    const uint32_t keep_lo = kb == 0 ? 0u : 1u, keep_hi = (nhi && kb < nhi) ? 0u : 1u;
 #pragma unroll
-                for (int j = 0; j < BK / 8; ++j) {
-                    const uint32_t bo = B_MN ? (uint32_t)(j * 2 * MN_KSTEP) : (uint32_t)(j * 32);
-                    const uint64_t bh = B_MN ? desc_mn_grouped(sb_hi + bo) : smem_desc(sb_hi + bo);
-                    const uint64_t bl = B_MN ? desc_mn_grouped(sb_lo + bo) : smem_desc(sb_lo + bo);
-                        const uint32_t ao = A_MN ? (uint32_t)(j * 2 * MN_KSTEP) : (uint32_t)(j * 32);
-                        const uint64_t ah = A_MN ? desc_mn_grouped(sa_hi + ao) : smem_desc(sa_hi + ao);
-                        const uint64_t al = A_MN ? desc_mn_grouped(sa_lo + ao) : smem_desc(sa_lo + ao);
-                        umma_tf32(d_lo, al, bh, idesc, (first_lo && j == 0) ? 0u : 1u);
-                        umma_tf32(d_lo, ah, bl, idesc, 1u);
-                        umma_tf32(d_hi, ah, bh, idesc, (first_hi && j == 0) ? 0u : 1u);
+                    for (int j = 0; j < BK / 8; ++j) {
+                        umma_tf32(d_lo, desc(al + j * A_STEP, A_HIGH), desc(bh + j * B_STEP, B_HIGH), idesc, j == 0 ? keep_lo : 1u);
+                        umma_tf32(d_lo, desc(ah + j * A_STEP, A_HIGH), desc(bl + j * B_STEP, B_HIGH), idesc, 1u);
+                        umma_tf32(d_hi, desc(ah + j * A_STEP, A_HIGH), desc(bh + j * B_STEP, B_HIGH), idesc, j == 0 ? keep_hi : 1u);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < BK / 8; ++j) {
+                        umma_tf32_acc(d_lo, desc(al + j * A_STEP, A_HIGH), desc(bh + j * B_STEP, B_HIGH), idesc);
+                        umma_tf32_acc(d_lo, desc(ah + j * A_STEP, A_HIGH), desc(bl + j * B_STEP, B_HIGH), idesc);
+                        umma_tf32_acc(d_hi, desc(ah + j * A_STEP, A_HIGH), desc(bh + j * B_STEP, B_HIGH), idesc);
+                    }
                 }
                 umma_commit(smem_u32(mmadone + rs));
-                if (kb == KB - 1) umma_commit(smem_u32(accready + set));
+                if (++rs == NS) { rs = 0; full_parity ^= 1u; }
+                if (++lb == NL) lb = 0;
+                if (nhi && ++hi_slot == nhi) hi_slot = 0;
+                if (++kb == KB) {
+                    umma_commit(smem_u32(accready + set));
+                    kb = 0;
+                    hi_slot = 0;
+                    acc0 += set_cols;
+                    if (++set == p.sets) { set = 0; acc0 = tmem_base; if (!first_round) free_parity ^= 1u; first_round = false; }
+                }
             }
-            __syncwarp();
-            if (++kb == KB) { kb = 0; ++count; }
         }
     } else if (warp >= SW && warp < MMA_WARP) {
         // ---- epilogue warps: TMEM -> registers -> global memory, one pass over this CTA's tiles.  Warp e reads the TMEM
