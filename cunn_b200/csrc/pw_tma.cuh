@@ -2,7 +2,7 @@
 //
 // Same roles, tiles and 3xTF32 scheme as pw::pw_gemm_kernel (convmm.cu); what differs is how the raw fp32 tiles reach
 // shared memory and how the warps are divided.  There 16 producer warps issue element copies; here ONE thread issues
-// tensor-map copies (cp.async.bulk.tensor, no multicast) that land the tiles directly in the layouts the tensor core
+// tensor-map copies (cp.async.bulk.tensor, one destination CTA each) that land the tiles directly in the layouts the tensor core
 // reads, 4 or 8 warps derive the lo tiles (an element-wise map over the 16 KB tile: lo = v - tf32(v)), one warp issues the
 // MMAs and 8 or 4 warps drain accumulators, up to four accumulator sets ahead for tiles of one or two k-blocks.
 //
