@@ -191,6 +191,7 @@ def test_bn_golden(F, name):
     ((3, 16, 32, 32), False),      # H*W = 1024, the reference's extra case; no affine
     ((300, 3, 2, 2), True),        # more images than chunks
     ((2, 1024, 7, 7), True),
+    ((6, 24, 14, 14), True),       # 196-element planes: a multiple of 16 bytes, yet on the flat elementwise kernels
     ((4, 8, 2, 3), True),          # 24 elements per channel
     ((16, 4100, 2, 2), True),      # more channels than ticket counters: the merge runs as a separate launch
     ((40, 2, 16, 16), True),       # 40 chunks per channel: more than one warp-lane round in the merge
