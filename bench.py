@@ -153,7 +153,7 @@ def run_reference(args, emit):
         "steps": res["steps"], "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(res["sample_images"], 1),
-        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample", "pytorch_cpu") if k in res},
         "e2e": {"value": res["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -190,10 +190,47 @@ def cpu_baseline(steps=1, warmup=0, budget_seconds=30.0):
     for _ in range(steps):
         one_step(data)
     dt = (time.perf_counter() - t0) / steps
-    return {"value": step_bytes(n) / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": "13-layer depthwise stack fwd+dgrad+wgrad on all %d images per layer, fp32 OpenMP port of the "
-                      "oracle on %d threads, %d step(s)" % (n, threads, steps),
-            "ms_per_step": dt * 1e3, "sample_images": n, "steps": steps}
+    out = {"value": step_bytes(n) / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+           "sample": "13-layer depthwise stack fwd+dgrad+wgrad on all %d images per layer, fp32 OpenMP port of the "
+                     "oracle on %d threads, %d step(s)" % (n, threads, steps),
+           "ms_per_step": dt * 1e3, "sample_images": n, "steps": steps}
+    try:
+        out["pytorch_cpu"] = pytorch_cpu_baseline(data, cores)
+    except Exception as exc:                         # a secondary figure: never fails the run
+        out["pytorch_cpu"] = {"unavailable": str(exc)[:200]}
+    return out
+
+
+def pytorch_cpu_baseline(data, threads):
+    """A second CPU figure for the same stack: PyTorch's CPU operators (grouped conv2d and its two gradient functions, the
+    living descendants of torch/nn's THNN CPU code), same tensors, same thread count, one warm-up and one timed step."""
+    import torch
+    import torch.nn.functional as Fn
+    from torch.nn import grad as G
+    old = torch.get_num_threads()
+    torch.set_num_threads(threads)
+    try:
+        T = [dict(x=torch.from_numpy(d["x"]), gy=torch.from_numpy(d["gy"]), w=torch.from_numpy(d["w"]).permute(1, 0, 2, 3).contiguous(),
+                  b=torch.from_numpy(d["b"]).reshape(-1)) for d in data]
+
+        def one_step():
+            with torch.no_grad():
+                for (C, HW, s), t in zip(LAYERS, T):
+                    Fn.conv2d(t["x"], t["w"], t["b"], stride=s, padding=1, groups=C)
+                for (C, HW, s), t in zip(LAYERS, T):
+                    G.conv2d_input(t["x"].shape, t["w"], t["gy"], stride=s, padding=1, groups=C)
+                for (C, HW, s), t in zip(LAYERS, T):
+                    G.conv2d_weight(t["x"], t["w"].shape, t["gy"], stride=s, padding=1, groups=C)
+                    t["gy"].sum(dim=(0, 2, 3))
+        one_step()
+        t0 = time.perf_counter()
+        one_step()
+        dt = time.perf_counter() - t0
+        n = data[0]["x"].shape[0]
+        return {"value": step_bytes(n) / dt / 1e9, "unit": "GB/s", "threads": threads, "ms_per_step": dt * 1e3,
+                "what": "torch %s CPU: F.conv2d(groups=C), torch.nn.grad.conv2d_input / conv2d_weight, bias gradient by sum" % torch.__version__}
+    finally:
+        torch.set_num_threads(old)
 
 
 def parity_check(T, fwd, dgrad, wgrad, layers=(7, 12, 13)):
@@ -835,6 +872,9 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu:
         c = cpu_baseline(steps=3, warmup=1, budget_seconds=30.0)
         cpu = {k: (round(c[k], 3) if isinstance(c[k], float) else c[k]) for k in ("value", "unit", "cores", "kind", "sample")}
+        pc = c.get("pytorch_cpu")
+        if pc:
+            cpu["pytorch_cpu"] = {k: (round(v, 3) if isinstance(v, float) else v) for k, v in pc.items()}
 
     if rank == 0:
         line = {"metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": steps,
